@@ -1,0 +1,357 @@
+#!/usr/bin/env python
+"""Benchmark of the per-batch embedding-training path: train edges/sec.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference] [--precision fp32|tf32]
+
+A step is one batch (unique-map -> fused decoder forward/loss/backward -> sparse Adagrad scatter -> dense Adagrad
+on the relation tables) of the single-GPU configuration: synthetic knowledge graph with 1,000,000 entities,
+1,000 relations, 20,000,000 triples (Zipf 1.1 degrees, Zipf 1.2 relations), ComplEx d=100 fp32, batch 10,000,
+1,000 negatives per chunk of 10 (half degree-proportional, half uniform), softmax loss, Adagrad lr 0.1.
+With N > 1 every rank trains its own partition-disjoint share of the edges at the same per-GPU batch (weak scaling)
+and the relation gradients are all-reduced over NCCL each step.  Prints ONE JSON line on rank 0.
+"""
+from __future__ import annotations
+
+import argparse
+import importlib
+import json
+import os
+import subprocess
+import sys
+import threading
+import time
+from pathlib import Path
+
+ROOT = Path(__file__).resolve().parent
+for _p in (ROOT, ROOT / "tests", ROOT / "oracle", ROOT / "oracle" / "_ref"):
+    if str(_p) not in sys.path:
+        sys.path.insert(0, str(_p))
+
+import numpy as np  # noqa: E402
+import torch  # noqa: E402
+
+CFG = dict(name="kg-1M-entities/1k-relations/20M-triples ComplEx d=100 B=10000 neg=10x1000 (50% degree)", nodes=1_000_000, relations=1000,
+           triples=20_000_000, decoder="COMPLEX", D=100, B=10_000, C=10, N=1000, degree_fraction=0.5, lr=0.1, alpha_nodes=1.1, alpha_rel=1.2)
+
+
+def peaks():
+    f = ROOT / "MEASURED_PEAKS.json"
+    if f.exists():
+        j = json.loads(f.read_text())
+        return dict(hbm=float(j["hbm_gbs"]), tf=float(j["bf16_tflops"]), tf_sustained=float(j.get("bf16_tflops_sustained", j["bf16_tflops"])), src="measured")
+    return dict(hbm=6650.0, tf=1590.0, tf_sustained=1400.0, src="fallback")
+
+
+def zipf_sample_torch(n, domain, alpha, gen, device):
+    """ids in [0, domain) with P(rank k) ~ k^-alpha through an inverse-CDF lookup, ranks scattered by a random relabel
+    (the preprocessor of the reference project assigns random ids, torch_converter.py:258-261)."""
+    w = torch.arange(1, domain + 1, dtype=torch.float64, device=device).pow_(-alpha)
+    cdf = torch.cumsum(w, 0)
+    cdf /= cdf[-1].clone()
+    u = torch.rand(n, dtype=torch.float64, device=device, generator=gen)
+    ranks = torch.searchsorted(cdf, u).clamp_(max=domain - 1)
+    perm = torch.randperm(domain, device=device, generator=gen)
+    return perm[ranks]
+
+
+def make_graph(cfg, n_edges, seed, device):
+    gen = torch.Generator(device=device)
+    gen.manual_seed(seed)
+    src = zipf_sample_torch(n_edges, cfg["nodes"], cfg["alpha_nodes"], gen, device)
+    dst = zipf_sample_torch(n_edges, cfg["nodes"], cfg["alpha_nodes"], gen, device)
+    rel = zipf_sample_torch(n_edges, cfg["relations"], cfg["alpha_rel"], gen, device)
+    return torch.stack([src, rel, dst], dim=1).contiguous()
+
+
+class ClockSampler:
+    """Samples SM clocks and throttle reasons with nvidia-smi while the timed region runs (read-only queries)."""
+    Q = "index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap"
+
+    def __init__(self, gpu_index):
+        self.idx = gpu_index
+        self.proc = None
+        self.lines = []
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(["nvidia-smi", f"--query-gpu={self.Q}", "--format=csv,noheader,nounits", "-lms", "100", "-i", str(self.idx)],
+                                         stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+            self.t = threading.Thread(target=self._read, daemon=True)
+            self.t.start()
+        except Exception:
+            self.proc = None
+
+    def _read(self):
+        for ln in self.proc.stdout:
+            self.lines.append(ln.strip())
+
+    def stop(self):
+        if self.proc is None:
+            return dict(sm_mhz=None, sm_max_mhz=None, reasons=["nvidia-smi unavailable"])
+        self.proc.terminate()
+        try:
+            self.proc.wait(timeout=2)
+        except Exception:
+            self.proc.kill()
+        sm, mx, reasons = [], [], set()
+        for ln in self.lines:
+            p = [x.strip() for x in ln.split(",")]
+            if len(p) < 9:
+                continue
+            try:
+                sm.append(float(p[1]))
+                mx.append(float(p[2]))
+            except ValueError:
+                continue
+            for name, v in zip(("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"), p[5:9]):
+                if v.lower().startswith("active"):
+                    reasons.add(name)
+        if not sm:
+            return dict(sm_mhz=None, sm_max_mhz=None, reasons=["no samples"])
+        return dict(sm_mhz=float(np.median(sm)), sm_max_mhz=float(max(mx)), reasons=sorted(reasons), samples=len(sm))
+
+
+# ----------------------------------------------------------------------------------------------------------------
+# CPU reference arm: the reference project's own CPU code for the path (oracle/_ref), else the numpy restatement
+# ----------------------------------------------------------------------------------------------------------------
+class CpuReference:
+    def __init__(self, cfg, seed):
+        self.cfg = cfg
+        self.cores = os.cpu_count() or 1
+        torch.set_num_threads(self.cores)
+        try:
+            import gege_ref  # the reference's CPU sources compiled by oracle/Makefile
+
+            self.ref = gege_ref
+            self.kind = "reference"
+        except Exception:
+            self.ref = None
+            self.kind = "port"
+        g = torch.Generator().manual_seed(seed)
+        n, D, R = cfg["nodes"], cfg["D"], cfg["relations"]
+        self.table = (torch.rand((n, D), generator=g) - 0.5) * 0.2
+        self.state = torch.zeros((n, D))
+        self.edges = make_graph(cfg, 64 * cfg["B"], seed, torch.device("cpu"))
+        if self.ref is not None:
+            self.model = self.ref.RefModel(cfg["decoder"], R, D, True, cfg["lr"], cfg["lr"])
+        else:
+            import ge2_oracle as O
+
+            self.O = O
+            self.rel = np.zeros((R, D), np.float32)
+            self.rel[:, : D // 2] = 1
+            self.inv = self.rel.copy()
+            self.rs, self.iss = np.zeros_like(self.rel), np.zeros_like(self.rel)
+        self.gen = g
+
+    def step(self, i):
+        """One batch of SynchronousTrainer's loop on CPU: sample, map_tensors, indexRead, train_batch, indexAdd."""
+        cfg = self.cfg
+        B, C, N, n = cfg["B"], cfg["C"], cfg["N"], cfg["nodes"]
+        nd = int(N * cfg["degree_fraction"])
+        e = self.edges[(i % 64) * B:(i % 64 + 1) * B]
+        uni = torch.randint(n, (C, N - nd), generator=self.gen)
+        rows = torch.randint(0, B, (C, nd), generator=self.gen)
+        dst_negs = torch.cat([e[:, 2][rows], uni], 1)
+        src_negs = torch.cat([e[:, 0][rows], uni], 1)
+        if self.ref is not None:
+            filt = self.ref.deg_negative_local_filter(rows, e)
+            # map_tensors: the reference's CPU unique (util.cpp:100-111) passes (return_inverse=false, return_counts=true) to
+            # unique_consecutive and throws with this torch; torch.unique(sorted, return_inverse) is what it evidently means
+            ids = torch.cat([e[:, 0], e[:, 2], src_negs.reshape(-1), dst_negs.reshape(-1)])
+            uniq, inv = torch.unique(ids, sorted=True, return_inverse=True)
+            local = torch.stack([inv[:B], e[:, 1], inv[B:2 * B]], 1)
+            sl = inv[2 * B:2 * B + C * N].reshape(C, N)
+            dl = inv[2 * B + C * N:].reshape(C, N)
+            emb, st = self.table.index_select(0, uniq), self.state.index_select(0, uniq)
+            out = self.model.train_batch(local, emb, st, dl, sl, filt, filt, True, False)
+            self.table.index_add_(0, uniq, out["node_update"])
+            self.state.index_add_(0, uniq, out["node_state_update"])
+            return float(out["loss"])
+        filt = self.O.deg_negative_local_filter(rows.numpy(), B)
+        loss, _ = self.O.train_step(cfg["decoder"], self.table.numpy(), self.state.numpy(), self.rel, self.rs, self.inv, self.iss, e.numpy(),
+                                    dst_negs.numpy(), src_negs.numpy(), filt, filt, cfg["lr"], n)
+        return loss
+
+    def timed(self, budget_s, min_steps=2, max_steps=40, warm=1):
+        for w in range(warm):
+            self.step(w)
+        t0 = time.perf_counter()
+        k = 0
+        while k < max_steps and (k < min_steps or time.perf_counter() - t0 < budget_s):
+            self.step(warm + k)
+            k += 1
+        dt = time.perf_counter() - t0
+        return k * self.cfg["B"] / dt, k, dt
+
+
+def reference_arm(args):
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return
+    cfg = CFG
+    cpu = CpuReference(cfg, 20262)
+    for w in range(min(args.warmup, 2)):
+        cpu.step(w)
+    t0 = time.perf_counter()
+    cpu.step(100)
+    t1 = time.perf_counter() - t0
+    steps_run = max(1, min(args.steps, int(200.0 / max(t1, 1e-3))))
+    t0 = time.perf_counter()
+    for k in range(steps_run):
+        cpu.step(200 + k)
+    dt = time.perf_counter() - t0
+    value = steps_run * cfg["B"] / dt
+    sample = f"{steps_run} batches of {cfg['B']} edges of the same workload on CPU ({cpu.kind}: " + (
+        "reference C++/libtorch decoder+loss+autograd+accumulateGradients, torch.unique for its broken CPU map_tensors" if cpu.kind == "reference" else "numpy restatement") + ")"
+    line = dict(metric="train edges/sec/box", value=value, unit="edges/s", n_gpus=args.gpus, steps=args.steps, warmup=args.warmup,
+                ms_per_step=1e3 * dt / steps_run, higher_is_better=True, scaling="weak", vs_baseline=None, dtype="f32", data="synthetic",
+                impl="reference", config=dict(workload=cfg["name"], steps_run=steps_run),
+                cpu_baseline=dict(value=value, unit="edges/s", cores=cpu.cores, kind=cpu.kind, sample=sample),
+                e2e=dict(value=value, unit="edges/s", h2d_bytes_per_step=0, d2h_bytes_per_step=0))
+    print(json.dumps(line), flush=True)
+
+
+# ----------------------------------------------------------------------------------------------------------------
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=100)
+    ap.add_argument("--warmup", type=int, default=5)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--precision", default=os.environ.get("GE2_PRECISION", "fp32"), choices=["fp32", "tf32"])
+    ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--cpu-budget", type=float, default=15.0)
+    args = ap.parse_args()
+    args.warmup = max(args.warmup, 3)
+
+    if args.impl == "reference":
+        reference_arm(args)
+        return
+
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py needs a CUDA device: the hot path has no CPU fallback")
+    torch.cuda.set_device(local_rank)
+    device = torch.device("cuda", local_rank)
+    dist = None
+    if world > 1:
+        import torch.distributed as dist_mod
+
+        dist = dist_mod
+        dist.init_process_group("nccl", device_id=device)
+
+    pkg = importlib.import_module("ge-2_b200")
+    pkg.load_library()
+    pipeline = importlib.import_module("ge-2_b200.pipeline")
+    cfg = CFG
+    B, C, N, D, R, nodes = cfg["B"], cfg["C"], cfg["N"], cfg["D"], cfg["relations"], cfg["nodes"]
+    K, W = args.steps, args.warmup
+
+    # ---- synthetic data, resident in HBM before the timed region -------------------------------------------
+    n_edges = cfg["triples"] if (K + W) * B <= cfg["triples"] else (K + W) * B
+    edges = make_graph(cfg, n_edges, 20262 + rank, device)  # each rank: its own edge share (weak scaling)
+    edges = edges[torch.randperm(n_edges, device=device)]    # epoch shuffle (dataloader.cpp:613-616 of the reference project)
+    gen = torch.Generator(device=device).manual_seed(7 + rank)
+    table = (torch.rand((nodes, D), device=device, generator=gen) - 0.5) * 0.2
+    state = torch.zeros((nodes, D), device=device)
+    rel = torch.zeros((R, D), device=device)
+    rel[:, : D // 2] = 1  # ComplEx relation init (complex.cpp:18-20 of the reference project)
+    inv_rel = rel.clone()
+    pcfg = pipeline.PipelineConfig(cfg["decoder"], B, C, N, cfg["degree_fraction"], D, R, nodes, lr=cfg["lr"], precision=args.precision)
+    pipe = pipeline.BatchPipeline(pcfg, table, state, rel, torch.zeros_like(rel), inv_rel, torch.zeros_like(inv_rel))
+    rel_hook = None
+    if world > 1:
+        pipe.grad_scale = 1.0 / world
+
+        def rel_hook(p):  # Model::all_reduce of the reference (model.cpp:174-204): sum of the replicas' relation gradients
+            dist.all_reduce(p.rel_grad)
+            dist.all_reduce(p.inv_rel_grad)
+
+    def barrier():
+        if dist is not None:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    def batch(i):
+        return edges[i * B:(i + 1) * B]
+
+    # ---- device-resident timing (`value`) --------------------------------------------------------------------
+    for i in range(W):
+        pipe.step(batch(i), i, rel_hook=rel_hook)
+    pipe.check_status()
+    ev_pairs = [(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)) for _ in range(K)]
+    start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    clocks = ClockSampler(local_rank)
+    barrier()
+    clocks.start()
+    start.record()
+    for i in range(K):
+        pipe.step(batch(W + i), W + i, scores_events=ev_pairs[i], rel_hook=rel_hook)
+    end.record()
+    barrier()
+    ms = start.elapsed_time(end)
+    scores_ms = float(np.mean([a.elapsed_time(b) for a, b in ev_pairs]))
+    pipe.check_status()
+
+    # ---- end-to-end timing (`e2e`): host edges in, loss out, through the same public step call -----------------
+    host_edges = torch.empty((K, B, 3), dtype=torch.int64).pin_memory()
+    host_edges.copy_(edges[W * B:(W + K) * B].reshape(K, B, 3).cpu())
+    host_loss = torch.zeros(K, dtype=torch.float32).pin_memory()
+    stage = torch.empty((B, 3), dtype=torch.int64, device=device)
+    for i in range(min(W, K)):
+        stage.copy_(host_edges[i], non_blocking=True)
+        pipe.step(stage, 10_000 + i, rel_hook=rel_hook)
+        host_loss[i:i + 1].copy_(pipe.loss, non_blocking=True)
+    s2, e2 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    barrier()
+    s2.record()
+    for i in range(K):
+        stage.copy_(host_edges[i], non_blocking=True)
+        pipe.step(stage, 20_000 + i, rel_hook=rel_hook)
+        host_loss[i:i + 1].copy_(pipe.loss, non_blocking=True)
+    e2.record()
+    barrier()
+    ms_e2e = s2.elapsed_time(e2)
+    clock_info = clocks.stop()
+    pipe.check_status()
+    assert bool(torch.isfinite(host_loss).all()) and float(host_loss[-1]) > 0
+
+    if dist is not None:
+        t = torch.tensor([ms, ms_e2e, scores_ms], device=device, dtype=torch.float64)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        ms, ms_e2e, scores_ms = (float(x) for x in t.cpu())
+
+    if rank == 0:
+        pk = peaks()
+        S = pcfg.sides
+        flops = 6.0 * S * B * N * D  # forward contraction + the two backward contractions, per side
+        achieved = flops / (scores_ms * 1e-3) / 1e12
+        line = dict(
+            metric="train edges/sec/box", value=world * K * B / (ms * 1e-3), unit="edges/s", n_gpus=world, steps=K, warmup=W,
+            ms_per_step=ms / K, higher_is_better=True, scaling="weak", vs_baseline=None,
+            dtype="f32" if args.precision == "fp32" else "tf32 tiles, f32 accumulate", data="synthetic",
+            config=dict(workload=cfg["name"], per_gpu_batch=B, global_batch=B * world, precision=args.precision,
+                        l2="tables (0.8 GB) and edge list larger than L2; rows touched per step are random", parallelism=f"dp{world}" if world > 1 else "single"),
+            e2e=dict(value=world * K * B / (ms_e2e * 1e-3), unit="edges/s", h2d_bytes_per_step=B * 3 * 8, d2h_bytes_per_step=4,
+                     note="pinned host edges -> H2D, step, loss -> pinned host, all stream-ordered; one synchronize at the end"),
+            gpu_launches=K * pipe.launches_per_step(),
+            clocks=clock_info,
+            roofline=dict(bound="tensor", kernel="lp_scores_%s" % args.precision, achieved=achieved, peak=pk["tf"], unit="TFLOP/s",
+                          frac=achieved / pk["tf"], traffic=None, peak_source=pk["src"] + " bf16 dense",
+                          ms_per_launch=scores_ms, flops_per_launch=flops),
+        )
+        if world == 1 and not args.no_cpu_baseline:
+            cpu = CpuReference(cfg, 20262)
+            v, k, dt = cpu.timed(args.cpu_budget)
+            line["cpu_baseline"] = dict(value=v, unit="edges/s", cores=cpu.cores, kind=cpu.kind,
+                                        sample=f"{k} batches of {B} edges of the same workload in {dt:.1f} s on the host cores")
+        print(json.dumps(line), flush=True)
+    if dist is not None:
+        dist.destroy_process_group()
+
+
+if __name__ == "__main__":
+    main()

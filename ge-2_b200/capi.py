@@ -1,0 +1,242 @@
+"""ctypes binding of the C ABI declared in include/ge2_b200.h.
+
+Thin by design: tensors are torch CUDA tensors used as device memory, every wrapper passes raw pointers and the
+current CUDA stream, checks the int status and raises Ge2Error.  No arithmetic happens on this side.
+"""
+from __future__ import annotations
+
+import ctypes as C
+import os
+from pathlib import Path
+from typing import Optional
+
+PKG = Path(__file__).resolve().parent
+
+GE2_OK = 0
+DECODER = {"DISTMULT": 0, "DOT": 0, "COMPLEX": 1}
+PRECISION = {"fp32": 0, "tf32": 1}
+STATUS_BITS = {1: "id out of range", 2: "scan timeout", 4: "filter collision", 8: "bad index", 16: "pipeline timeout"}
+
+EXPORTS = [
+    "ge2_version", "ge2_last_cuda_error", "ge2_status_string", "ge2_check_device", "ge2_unique_workspace_bytes",
+    "ge2_unique_bitmap", "ge2_pack_ids", "ge2_lp_workspace_bytes", "ge2_lp_step", "ge2_sparse_adagrad", "ge2_index_read",
+    "ge2_index_add", "ge2_adagrad_scatter", "ge2_dense_adagrad", "ge2_sample_negatives", "ge2_remap_edges_to_slots",
+    "ge2_copy_slabs",
+]
+
+
+class Ge2Error(RuntimeError):
+    pass
+
+
+class LpDesc(C.Structure):
+    _fields_ = [
+        ("decoder", C.c_int32), ("has_relations", C.c_int32), ("use_inverse", C.c_int32), ("precision", C.c_int32),
+        ("B", C.c_int32), ("C", C.c_int32), ("N", C.c_int32), ("D", C.c_int32), ("R", C.c_int32), ("phases", C.c_int32),
+        ("U", C.c_int64),
+        ("node_emb", C.c_void_p), ("row_index", C.c_void_p), ("emb_stride", C.c_int64),
+        ("src_ids", C.c_void_p), ("rel_ids", C.c_void_p), ("dst_ids", C.c_void_p), ("edge_stride", C.c_int64), ("rel_stride", C.c_int64),
+        ("dst_negs", C.c_void_p), ("src_negs", C.c_void_p),
+        ("dst_filter", C.c_void_p), ("dst_filter_n", C.c_int64), ("src_filter", C.c_void_p), ("src_filter_n", C.c_int64),
+        ("deg_sample_rows", C.c_void_p), ("n_deg", C.c_int32), ("reserved1", C.c_int32),
+        ("rel", C.c_void_p), ("inv_rel", C.c_void_p),
+        ("node_grad", C.c_void_p), ("rel_grad", C.c_void_p), ("inv_rel_grad", C.c_void_p), ("loss", C.c_void_p),
+        ("pos_scores", C.c_void_p), ("neg_scores", C.c_void_p), ("inv_pos_scores", C.c_void_p), ("inv_neg_scores", C.c_void_p),
+        ("status", C.c_void_p), ("workspace", C.c_void_p), ("workspace_bytes", C.c_size_t),
+    ]
+
+
+_lib = None
+
+
+def lib_path() -> Path:
+    return Path(os.environ.get("GE2_B200_LIB", PKG / "libge2_b200.so"))
+
+
+def load_library():
+    """Loads libge2_b200.so (once).  Raises Ge2Error when it has not been built: there is no fallback path."""
+    global _lib
+    if _lib is not None:
+        return _lib
+    path = lib_path()
+    if not path.exists():
+        raise Ge2Error(f"{path} is missing: build it with `python ge-2_b200/build.py` (needs nvcc); no CPU fallback exists")
+    lib = C.CDLL(str(path))
+    lib.ge2_version.restype = C.c_char_p
+    lib.ge2_status_string.restype = C.c_char_p
+    lib.ge2_status_string.argtypes = [C.c_int]
+    lib.ge2_unique_workspace_bytes.restype = C.c_size_t
+    lib.ge2_unique_workspace_bytes.argtypes = [C.c_int64]
+    lib.ge2_unique_bitmap.argtypes = [C.c_void_p, C.c_int64, C.c_int64, C.c_void_p, C.c_size_t, C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p]
+    lib.ge2_pack_ids.argtypes = [C.POINTER(C.c_void_p), C.POINTER(C.c_int64), C.POINTER(C.c_int64), C.c_void_p, C.c_void_p]
+    lib.ge2_lp_workspace_bytes.argtypes = [C.POINTER(LpDesc), C.POINTER(C.c_size_t)]
+    lib.ge2_lp_step.argtypes = [C.POINTER(LpDesc), C.c_void_p]
+    lib.ge2_sparse_adagrad.argtypes = [C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_int64, C.c_void_p, C.c_int32, C.c_float, C.c_void_p]
+    lib.ge2_index_read.argtypes = [C.c_void_p, C.c_int64, C.c_void_p, C.c_int64, C.c_void_p, C.c_int32, C.c_void_p, C.c_void_p, C.c_void_p]
+    lib.ge2_index_add.argtypes = [C.c_void_p, C.c_int64, C.c_void_p, C.c_int64, C.c_void_p, C.c_int32, C.c_void_p, C.c_void_p, C.c_void_p]
+    lib.ge2_adagrad_scatter.argtypes = [C.c_void_p, C.c_void_p, C.c_int64, C.c_void_p, C.c_int64, C.c_void_p, C.c_void_p, C.c_int32, C.c_float,
+                                        C.c_int32, C.c_void_p, C.c_void_p]
+    lib.ge2_dense_adagrad.argtypes = [C.c_void_p, C.c_void_p, C.c_void_p, C.c_int64, C.c_float, C.c_float, C.c_float, C.c_int32, C.c_void_p]
+    lib.ge2_sample_negatives.argtypes = [C.c_void_p, C.c_void_p, C.c_int64, C.c_int32, C.c_int32, C.c_int32, C.c_int32, C.c_int64, C.c_int32,
+                                         C.c_uint64, C.c_uint64, C.c_void_p, C.c_void_p, C.c_void_p]
+    lib.ge2_remap_edges_to_slots.argtypes = [C.c_void_p, C.c_int64, C.c_int32, C.c_void_p, C.c_int32, C.c_int64, C.c_void_p, C.c_void_p, C.c_void_p]
+    lib.ge2_copy_slabs.argtypes = [C.c_void_p, C.c_void_p, C.POINTER(C.c_int32), C.c_int32, C.c_int64, C.c_void_p]
+    lib.ge2_check_device.argtypes = [C.c_int]
+    _lib = lib
+    return lib
+
+
+def check(rc: int, what: str):
+    if rc != GE2_OK:
+        lib = load_library()
+        msg = lib.ge2_status_string(rc).decode()
+        extra = f" (cudaError {lib.ge2_last_cuda_error()})" if rc == 2 else ""
+        raise Ge2Error(f"{what}: {msg}{extra}")
+
+
+def ptr(t) -> Optional[int]:
+    return None if t is None else t.data_ptr()
+
+
+def cur_stream() -> int:
+    import torch
+
+    return torch.cuda.current_stream().cuda_stream
+
+
+def decode_status(word: int) -> str:
+    return ", ".join(name for bit, name in STATUS_BITS.items() if word & bit) or "clean"
+
+
+# ------------------------------------------------------------------------------------------------------------
+# wrappers (device tensors in, device tensors out; nothing is synchronised)
+# ------------------------------------------------------------------------------------------------------------
+def unique_workspace(domain: int, device):
+    import torch
+
+    return torch.empty(load_library().ge2_unique_workspace_bytes(domain), dtype=torch.uint8, device=device)
+
+
+def unique_bitmap(ids, domain: int, workspace=None, out_unique=None, out_inverse=None, out_count=None):
+    """ids: int64 CUDA [n].  Returns (unique[capacity], inverse[n], count[2] int32) -- count[0] distinct ids (device)."""
+    import torch
+
+    lib = load_library()
+    n = ids.numel()
+    dev = ids.device
+    if workspace is None:
+        workspace = unique_workspace(domain, dev)
+    if out_unique is None:
+        out_unique = torch.empty(max(1, min(n, domain)), dtype=torch.int64, device=dev)
+    if out_inverse is None:
+        out_inverse = torch.empty(max(1, n), dtype=torch.int64, device=dev)
+    if out_count is None:
+        out_count = torch.empty(2, dtype=torch.int32, device=dev)
+    check(lib.ge2_unique_bitmap(ptr(ids), n, domain, ptr(workspace), workspace.numel(), ptr(out_unique), ptr(out_inverse), ptr(out_count),
+                                cur_stream()), "ge2_unique_bitmap")
+    return out_unique, out_inverse[:n], out_count
+
+
+def make_lp_desc(*, decoder, precision, B, Cn, N, D, R, U, node_emb, row_index=None, emb_stride=None, src_ids, dst_ids, rel_ids=None,
+                 edge_stride=1, rel_stride=1, dst_negs, src_negs=None, dst_filter=None, src_filter=None, deg_sample_rows=None, n_deg=0,
+                 rel=None, inv_rel=None, node_grad, rel_grad=None, inv_rel_grad=None, loss, pos_scores=None, neg_scores=None,
+                 inv_pos_scores=None, inv_neg_scores=None, status=None, workspace=None) -> LpDesc:
+    d = LpDesc()
+    d.decoder = DECODER[decoder] if isinstance(decoder, str) else decoder
+    d.precision = PRECISION[precision] if isinstance(precision, str) else precision
+    d.has_relations = 1 if rel_ids is not None else 0
+    d.use_inverse = 1 if (src_negs is not None and inv_rel is not None) else 0
+    d.B, d.C, d.N, d.D, d.R, d.U = B, Cn, N, D, R, U
+    d.node_emb, d.row_index = ptr(node_emb), ptr(row_index)
+    d.emb_stride = emb_stride if emb_stride is not None else D
+    d.src_ids, d.rel_ids, d.dst_ids = ptr(src_ids), ptr(rel_ids), ptr(dst_ids)
+    d.edge_stride, d.rel_stride = edge_stride, rel_stride
+    d.dst_negs, d.src_negs = ptr(dst_negs), ptr(src_negs)
+    d.dst_filter, d.dst_filter_n = ptr(dst_filter), (0 if dst_filter is None else dst_filter.shape[0])
+    d.src_filter, d.src_filter_n = ptr(src_filter), (0 if src_filter is None else src_filter.shape[0])
+    if d.dst_filter_n == 0:
+        d.dst_filter = None
+    if d.src_filter_n == 0:
+        d.src_filter = None
+    d.deg_sample_rows, d.n_deg = ptr(deg_sample_rows), n_deg
+    d.rel, d.inv_rel = ptr(rel), ptr(inv_rel)
+    d.node_grad, d.rel_grad, d.inv_rel_grad, d.loss = ptr(node_grad), ptr(rel_grad), ptr(inv_rel_grad), ptr(loss)
+    d.pos_scores, d.neg_scores = ptr(pos_scores), ptr(neg_scores)
+    d.inv_pos_scores, d.inv_neg_scores = ptr(inv_pos_scores), ptr(inv_neg_scores)
+    d.status = ptr(status)
+    if workspace is not None:
+        d.workspace, d.workspace_bytes = ptr(workspace), workspace.numel()
+    return d
+
+
+def lp_workspace_bytes(desc: LpDesc) -> int:
+    out = C.c_size_t(0)
+    check(load_library().ge2_lp_workspace_bytes(C.byref(desc), C.byref(out)), "ge2_lp_workspace_bytes")
+    return out.value
+
+
+def lp_step(desc: LpDesc):
+    check(load_library().ge2_lp_step(C.byref(desc), cur_stream()), "ge2_lp_step")
+
+
+def sparse_adagrad(grad, state_local, lr: float, out_delta=None, out_state_update=None, rows_dev=None):
+    import torch
+
+    rows, D = grad.shape
+    if out_delta is None:
+        out_delta = torch.empty_like(grad)
+    if out_state_update is None:
+        out_state_update = torch.empty_like(grad)
+    check(load_library().ge2_sparse_adagrad(ptr(grad), ptr(state_local), ptr(out_delta), ptr(out_state_update), rows, ptr(rows_dev), D, lr,
+                                            cur_stream()), "ge2_sparse_adagrad")
+    return out_delta, out_state_update
+
+
+def index_read(table, ids, n_dev=None, out=None, status=None):
+    import torch
+
+    n, D = ids.numel(), table.shape[1]
+    if out is None:
+        out = torch.empty((n, D), dtype=table.dtype, device=table.device)
+    check(load_library().ge2_index_read(ptr(table), table.shape[0], ptr(ids), n, ptr(n_dev), D, ptr(out), ptr(status), cur_stream()),
+          "ge2_index_read")
+    return out
+
+
+def index_add(table, ids, values, n_dev=None, status=None):
+    n, D = ids.numel(), table.shape[1]
+    check(load_library().ge2_index_add(ptr(table), table.shape[0], ptr(ids), n, ptr(n_dev), D, ptr(values), ptr(status), cur_stream()),
+          "ge2_index_add")
+
+
+def adagrad_scatter(table, state, unique_ids, node_grad, lr: float, U=None, U_dev=None, clear_grad=False, status=None):
+    D = table.shape[1]
+    U = unique_ids.numel() if U is None else U
+    check(load_library().ge2_adagrad_scatter(ptr(table), ptr(state), table.shape[0], ptr(unique_ids), U, ptr(U_dev), ptr(node_grad), D, lr,
+                                             1 if clear_grad else 0, ptr(status), cur_stream()), "ge2_adagrad_scatter")
+
+
+def dense_adagrad(param, sum_state, grad, lr: float, eps: float = 1e-10, grad_scale: float = 1.0, clear_grad=False):
+    check(load_library().ge2_dense_adagrad(ptr(param), ptr(sum_state), ptr(grad), param.numel(), lr, eps, grad_scale, 1 if clear_grad else 0,
+                                           cur_stream()), "ge2_dense_adagrad")
+
+
+def sample_negatives(src_ids, dst_ids, edge_stride, B, Cn, N, n_deg, domain, want_src, seed, batch_index, out_packed, out_deg_rows):
+    check(load_library().ge2_sample_negatives(ptr(src_ids), ptr(dst_ids), edge_stride, B, Cn, N, n_deg, domain, 1 if want_src else 0, seed,
+                                              batch_index, ptr(out_packed), ptr(out_deg_rows), cur_stream()), "ge2_sample_negatives")
+
+
+def remap_edges_to_slots(edges, partition_to_slot, partition_size, out=None, status=None):
+    import torch
+
+    n, cols = edges.shape
+    if out is None:
+        out = torch.empty_like(edges)
+    check(load_library().ge2_remap_edges_to_slots(ptr(edges), n, cols, ptr(partition_to_slot), partition_to_slot.numel(), partition_size,
+                                                  ptr(out), ptr(status), cur_stream()), "ge2_remap_edges_to_slots")
+    return out
+
+
+def copy_slabs(src, dst, moves, slab_floats):
+    arr = (C.c_int32 * (2 * len(moves)))(*[v for m in moves for v in m])
+    check(load_library().ge2_copy_slabs(ptr(src), ptr(dst), arr, len(moves), slab_floats, cur_stream()), "ge2_copy_slabs")

@@ -1,0 +1,61 @@
+// Shared helpers for the sm_100a kernels behind the C ABI in include/ge2_b200.h.
+#pragma once
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+#include "../../include/ge2_b200.h"
+
+namespace ge2 {
+
+constexpr int kNumSMs = 148;  // B200: 2 dies x 74 SMs; grids of streaming kernels are sized in multiples of this
+
+extern thread_local int g_last_cuda_error;
+
+inline int cuda_fail(cudaError_t e) {
+    g_last_cuda_error = (int)e;
+    return GE2_ERR_CUDA;
+}
+
+#define GE2_CUDA_TRY(expr)                                  \
+    do {                                                    \
+        cudaError_t _e = (expr);                            \
+        if (_e != cudaSuccess) return ::ge2::cuda_fail(_e); \
+    } while (0)
+
+#define GE2_LAUNCH_CHECK()                                  \
+    do {                                                    \
+        cudaError_t _e = cudaGetLastError();                \
+        if (_e != cudaSuccess) return ::ge2::cuda_fail(_e); \
+    } while (0)
+
+inline cudaStream_t as_stream(ge2_stream_t s) { return reinterpret_cast<cudaStream_t>(s); }
+
+template <typename T>
+__host__ __device__ constexpr T ceil_div(T a, T b) {
+    return (a + b - 1) / b;
+}
+template <typename T>
+__host__ __device__ constexpr T round_up(T a, T b) {
+    return ceil_div(a, b) * b;
+}
+
+// number of CTAs for a grid-stride kernel over `work` items, `per_cta` items per CTA per sweep
+inline int stream_grid(int64_t work, int per_cta, int ctas_per_sm = 8) {
+    int64_t need = ceil_div<int64_t>(work, per_cta);
+    int64_t cap = (int64_t)kNumSMs * ctas_per_sm;
+    if (need < 1) need = 1;
+    return (int)(need < cap ? need : cap);
+}
+
+__device__ __forceinline__ void or_status(int32_t* status, int32_t bit) {
+    if (status != nullptr) atomicOr(status, bit);
+}
+
+// ceil(B / C) the way the reference computes it (float division, decoder_methods.cpp:772 of the reference project)
+inline int rows_per_chunk(int B, int C) {
+    float q = (float)B / (float)C;
+    int r = (int)q;
+    return ((float)r < q) ? r + 1 : r;
+}
+
+}  // namespace ge2

@@ -1,0 +1,79 @@
+// Internal layout shared by the kernels of the link-prediction training step (ge2_lp_step).
+//
+// Data flow of one step (S = corruption sides, Bp = C * ceil(B/C) padded batch rows, ld = padded row length):
+//   prep     : gather src/dst/relation rows, apply the relation operator        -> Q[S][Bp][ld], pos[S][Bp]
+//              gather negative rows                                              -> K[S][C*N][ld]
+//   scores   : per (side, chunk, row block): S = Q K^T, mask, row logsumexp with the positive score,
+//              P = exp(S - lse), dQ = P K, dK += P^T Q  (score tiles never leave the SM)  -> lse, dQ, dK
+//   finish   : relation-operator backward, d pos terms, duplicate-reducing scatter into node_grad / rel_grad, loss
+#pragma once
+#include "common.cuh"
+
+namespace ge2 {
+
+struct LpLayout {
+    int S;        // sides
+    int npc;      // rows per chunk = ceil(B / C)
+    int Bp;       // C * npc
+    int ld;       // padded row length of Q / K / dQ / dK (floats)
+    int64_t CN;   // C * N
+    // workspace sections
+    float* Q;         // [S][Bp][ld]
+    float* K;         // [S][CN][ld]
+    float* dQ;        // [S][Bp][ld]
+    float* dK;        // [S][CN][ld]   zeroed every step, reduced with atomics
+    float* pos;       // [S][Bp]
+    float* lse;       // [S][Bp]
+    int32_t* mask;    // [S][CN]  batch row whose score in this (chunk, column) is masked, or -1
+    size_t bytes;
+    size_t zero_begin, zero_bytes;  // dK range
+};
+
+struct LpKernelArgs {
+    ge2_lp_desc d;
+    LpLayout L;
+};
+
+inline size_t lp_align(size_t x) { return (x + 255) & ~(size_t)255; }
+
+inline int lp_row_ld(int D) { return D <= 64 ? 64 : 128; }
+
+inline LpLayout lp_make_layout(const ge2_lp_desc& d, void* base) {
+    LpLayout L;
+    L.S = (d.has_relations && d.use_inverse) ? 2 : 1;
+    L.npc = rows_per_chunk(d.B, d.C);
+    L.Bp = d.C * L.npc;
+    L.ld = lp_row_ld(d.D);
+    L.CN = (int64_t)d.C * d.N;
+    char* p = (char*)base;
+    size_t off = 0;
+    auto take = [&](size_t bytes) {
+        size_t o = off;
+        off += lp_align(bytes);
+        return o;
+    };
+    size_t oQ = take((size_t)L.S * L.Bp * L.ld * 4);
+    size_t oK = take((size_t)L.S * L.CN * L.ld * 4);
+    size_t odQ = take((size_t)L.S * L.Bp * L.ld * 4);
+    size_t odK = take((size_t)L.S * L.CN * L.ld * 4);
+    size_t opos = take((size_t)L.S * L.Bp * 4);
+    size_t olse = take((size_t)L.S * L.Bp * 4);
+    size_t omask = take((size_t)L.S * L.CN * 4);
+    L.Q = (float*)(p + oQ);
+    L.K = (float*)(p + oK);
+    L.dQ = (float*)(p + odQ);
+    L.dK = (float*)(p + odK);
+    L.pos = (float*)(p + opos);
+    L.lse = (float*)(p + olse);
+    L.mask = (int32_t*)(p + omask);
+    L.zero_begin = odK;
+    L.zero_bytes = (size_t)L.S * L.CN * L.ld * 4;
+    L.bytes = off;
+    return L;
+}
+
+// scores kernels (one per precision); both fill lse, dQ, dK (+ optional score dumps) from Q, K, pos, mask
+int lp_scores_fp32(const LpKernelArgs& a, cudaStream_t stream);
+int lp_scores_tf32(const LpKernelArgs& a, cudaStream_t stream);
+
+}  // namespace ge2

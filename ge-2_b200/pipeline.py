@@ -1,0 +1,153 @@
+"""Per-batch training pipeline on one GPU: the sequence SynchronousTrainer::train runs for every batch
+(cpp/src/engine/trainer.cpp:170-211 of the reference project), issued as a fixed list of launches on the current
+CUDA stream with no host synchronisation in between:
+
+    sample negatives + pack ids  ->  unique-map  ->  fused decoder forward/loss/backward  ->  sparse Adagrad scatter
+    ->  dense Adagrad on the relation tables
+
+Torch tensors are used as device memory only; every arithmetic step is a kernel of libge2_b200.so.
+"""
+from __future__ import annotations
+
+from dataclasses import dataclass
+from typing import Optional
+
+import torch
+
+from . import capi
+
+
+@dataclass
+class PipelineConfig:
+    decoder: str            # "DISTMULT" | "COMPLEX" ("DOT" = DISTMULT on 2-column edges)
+    B: int                  # batch size
+    C: int                  # num_chunks
+    N: int                  # negatives_per_positive (per chunk)
+    degree_fraction: float  # share of degree-based negatives
+    D: int
+    R: int                  # number of relations (0/1 => relation-free, 2-column edges)
+    domain: int             # nodes resident on the device (rows of the table)
+    lr: float = 0.1
+    dense_lr: Optional[float] = None
+    precision: str = "fp32"
+    seed: int = 20260
+    inverse: bool = True
+
+    @property
+    def has_relations(self):
+        return self.R > 1
+
+    @property
+    def sides(self):
+        return 2 if (self.has_relations and self.inverse) else 1
+
+    @property
+    def n_deg(self):
+        return int(self.N * self.degree_fraction)  # negative.cpp:945 of the reference project
+
+    @property
+    def n_ids(self):
+        return 2 * self.B + self.sides * self.C * self.N
+
+
+class BatchPipeline:
+    """Owns the per-batch scratch (ids, unique map, gradients, workspaces); tables are owned by the caller."""
+
+    def __init__(self, cfg: PipelineConfig, table, state, rel=None, rel_state=None, inv_rel=None, inv_rel_state=None):
+        capi.load_library()
+        self.cfg = cfg
+        dev = table.device
+        self.device = dev
+        self.table, self.state = table, state
+        self.rel, self.rel_state, self.inv_rel, self.inv_rel_state = rel, rel_state, inv_rel, inv_rel_state
+        assert table.is_cuda and table.dtype == torch.float32 and table.shape[1] == cfg.D and table.is_contiguous()
+        n_ids, CN = cfg.n_ids, cfg.C * cfg.N
+        self.cap = min(n_ids, cfg.domain)
+        i64 = dict(dtype=torch.int64, device=dev)
+        self.packed = torch.empty(n_ids, **i64)
+        self.deg_rows = torch.empty((cfg.C, max(cfg.n_deg, 1)), **i64)
+        self.unique = torch.empty(self.cap, **i64)
+        self.inverse = torch.empty(n_ids, **i64)
+        self.count = torch.zeros(2, dtype=torch.int32, device=dev)
+        self.status = torch.zeros(1, dtype=torch.int32, device=dev)
+        self.node_grad = torch.zeros((self.cap, cfg.D), dtype=torch.float32, device=dev)
+        self.loss = torch.zeros(1, dtype=torch.float32, device=dev)
+        self.uws = capi.unique_workspace(cfg.domain, dev)
+        if cfg.has_relations:
+            self.rel_grad = torch.zeros_like(rel)
+            self.inv_rel_grad = torch.zeros_like(inv_rel) if cfg.sides == 2 else None
+        else:
+            self.rel_grad = self.inv_rel_grad = None
+        B = cfg.B
+        self.src_local = self.inverse[0:B]
+        self.dst_local = self.inverse[B:2 * B]
+        off = 2 * B
+        self.src_negs_local = None
+        if cfg.sides == 2:
+            self.src_negs_local = self.inverse[off:off + CN]
+            off += CN
+        self.dst_negs_local = self.inverse[off:off + CN]
+        self._desc = None
+        self._ws = None
+        self.grad_scale = 1.0  # 1 / #GPUs when relation gradients are all-reduced (model.cpp:188-192 of the reference project)
+
+    def _make_desc(self, edges):
+        cfg = self.cfg
+        cols = edges.shape[1]
+        d = capi.make_lp_desc(
+            decoder=cfg.decoder, precision=cfg.precision, B=cfg.B, Cn=cfg.C, N=cfg.N, D=cfg.D, R=cfg.R if cfg.has_relations else 0,
+            U=self.cap, node_emb=self.table, row_index=self.unique, emb_stride=cfg.D, src_ids=self.src_local, dst_ids=self.dst_local,
+            rel_ids=edges[:, 1] if cfg.has_relations else None, edge_stride=1, rel_stride=cols, dst_negs=self.dst_negs_local,
+            src_negs=self.src_negs_local, deg_sample_rows=self.deg_rows if cfg.n_deg > 0 else None, n_deg=cfg.n_deg,
+            rel=self.rel, inv_rel=self.inv_rel if cfg.sides == 2 else None, node_grad=self.node_grad, rel_grad=self.rel_grad,
+            inv_rel_grad=self.inv_rel_grad, loss=self.loss, status=self.status)
+        if self._ws is None:
+            self._ws = torch.empty(capi.lp_workspace_bytes(d), dtype=torch.uint8, device=self.device)
+        d.workspace, d.workspace_bytes = self._ws.data_ptr(), self._ws.numel()
+        return d
+
+    def step(self, edges, batch_index: int, scores_events=None, rel_hook=None):
+        """edges: [B, 2|3] int64 device tensor with resident-table row ids (global ids, or buffer-local ids with a
+        partition buffer).  Enqueues one training step; returns nothing (loss stays in self.loss).
+        scores_events: optional (start, end) torch.cuda.Event pair recorded around the scores kernel alone.
+        rel_hook: optional callable run after the backward pass and before the dense optimizer step (the multi-GPU
+        trainer all-reduces the relation gradients there, Model::all_reduce of the reference)."""
+        cfg = self.cfg
+        cols = edges.shape[1]
+        assert edges.shape[0] == cfg.B and edges.dtype == torch.int64 and edges.is_contiguous()
+        capi.sample_negatives(edges, edges[:, cols - 1], cols, cfg.B, cfg.C, cfg.N, cfg.n_deg, cfg.domain, cfg.sides == 2, cfg.seed,
+                              batch_index, self.packed, self.deg_rows if cfg.n_deg > 0 else None)
+        capi.unique_bitmap(self.packed, cfg.domain, workspace=self.uws, out_unique=self.unique, out_inverse=self.inverse, out_count=self.count)
+        desc = self._make_desc(edges)
+        if scores_events is None:
+            capi.lp_step(desc)
+        else:  # same kernels, issued phase by phase so the scores kernel can be bracketed by events
+            desc.phases = 1
+            capi.lp_step(desc)
+            desc.phases = 2
+            scores_events[0].record()
+            capi.lp_step(desc)
+            scores_events[1].record()
+            desc.phases = 4
+            capi.lp_step(desc)
+        if rel_hook is not None:
+            rel_hook(self)
+        capi.adagrad_scatter(self.table, self.state, self.unique, self.node_grad, cfg.lr, U=self.cap, U_dev=self.count, status=self.status)
+        if cfg.has_relations:
+            dl = cfg.lr if cfg.dense_lr is None else cfg.dense_lr
+            capi.dense_adagrad(self.rel, self.rel_state, self.rel_grad, dl, grad_scale=self.grad_scale, clear_grad=True)
+            if cfg.sides == 2:
+                capi.dense_adagrad(self.inv_rel, self.inv_rel_state, self.inv_rel_grad, dl, grad_scale=self.grad_scale, clear_grad=True)
+
+    # kernels of libge2_b200.so launched per step (memsets not counted): sample, mark, scan, inverse, [mask], prep, scores,
+    # finish, loss, adagrad_scatter, dense adagrad per relation table
+    def launches_per_step(self) -> int:
+        cfg = self.cfg
+        return 4 + (1 if cfg.n_deg > 0 else 0) + 4 + 1 + (cfg.sides if cfg.has_relations else 0)
+
+    def check_status(self):
+        """Synchronises and raises if any kernel flagged bad data (call between epochs, not per batch)."""
+        torch.cuda.synchronize(self.device)
+        word = int(self.status.item()) | int(self.count[1].item())
+        if word:
+            raise capi.Ge2Error("device status: " + capi.decode_status(word))

@@ -1,0 +1,218 @@
+/*
+ * ge2_b200 -- C ABI of the B200 (sm_100a) per-batch embedding-training path.
+ *
+ * Every entry point takes plain device pointers, sizes and a CUDA stream (passed as void*, a cudaStream_t)
+ * and returns an int status (GE2_OK == 0).  Nothing here allocates, synchronises the stream or touches the
+ * host except where a function says so; scratch memory is passed in by the caller and sized by the matching
+ * *_workspace_bytes function.  Counts that only exist on the device (the number of unique ids of a batch)
+ * stay on the device: consumers take a pointer to them.
+ *
+ * Each declaration names the interface of the reference project (paths relative to gege/src/) that it
+ * stands in for.
+ */
+#ifndef GE2_B200_H_
+#define GE2_B200_H_
+
+#include <stddef.h>
+#include <stdint.h>
+
+#if defined(__GNUC__)
+#define GE2_API __attribute__((visibility("default")))
+#else
+#define GE2_API
+#endif
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+/* ---- status codes ------------------------------------------------------------------------------- */
+#define GE2_OK 0
+#define GE2_ERR_INVALID_ARGUMENT 1 /* null pointer, negative size, unsupported shape               */
+#define GE2_ERR_CUDA 2             /* a CUDA runtime call failed; ge2_last_cuda_error() has the code */
+#define GE2_ERR_WORKSPACE 3        /* workspace pointer null / too small / misaligned               */
+#define GE2_ERR_UNSUPPORTED 4      /* valid request outside what the kernels cover (e.g. D > 128)   */
+#define GE2_ERR_NO_DEVICE 5        /* no CUDA device, or not compute capability 10.x               */
+
+/* Bits of the device-side status word (int32) kernels OR into when the data itself is bad. */
+#define GE2_STATUS_ID_OUT_OF_RANGE 1  /* unique-map: id < 0 or >= domain (reference: fallback to sort backend) */
+#define GE2_STATUS_SCAN_TIMEOUT 2     /* unique-map: a scan tile gave up waiting for its predecessor        */
+#define GE2_STATUS_FILTER_COLLISION 4 /* lp step: two filter pairs name the same (chunk, column)            */
+#define GE2_STATUS_BAD_INDEX 8        /* lp step / scatter: a local id or relation id out of bounds         */
+#define GE2_STATUS_PIPE_TIMEOUT 16    /* lp step (tensor path): a bounded mbarrier wait ran out             */
+
+typedef void *ge2_stream_t; /* cudaStream_t */
+
+GE2_API const char *ge2_version(void);
+GE2_API int ge2_last_cuda_error(void);            /* cudaError_t of the last failing runtime call on this thread */
+GE2_API const char *ge2_status_string(int status);
+/* GE2_OK when device `device` exists and is compute capability 10.x; selects nothing. */
+GE2_API int ge2_check_device(int device);
+
+/* =====================================================================================================
+ * (1) unique-map -- replaces map_tensors_unique_inverse_cuda, bitmap backend
+ *     (cuda/src/common/unique_map_cuda.cu:771-882; declared cpp/include/common/unique_map_cuda.h:22-24),
+ *     the kernel behind map_tensors (cpp/include/common/util.h:100-101, cpp/src/common/util.cpp:311-387).
+ *
+ * ids[n] int64 in [0, domain).  out_unique receives the distinct ids in ASCENDING order (capacity
+ * min(n, domain) entries), out_inverse[n] the rank of ids[i] inside out_unique, out_count[0] the number of
+ * distinct ids and out_count[1] a GE2_STATUS_* word (0 when clean).  Bit-exact with the reference's output.
+ * No host synchronisation: the count is left on the device (the reference reads it back twice per call).
+ * ===================================================================================================== */
+GE2_API size_t ge2_unique_workspace_bytes(int64_t domain);
+GE2_API int ge2_unique_bitmap(const int64_t *ids, int64_t n, int64_t domain, void *workspace, size_t workspace_bytes,
+                      int64_t *out_unique, int64_t *out_inverse, int32_t *out_count, ge2_stream_t stream);
+
+/* Packs up to four id vectors into one contiguous buffer, the job of pack_ids_into_cached_buffer
+ * (cpp/src/common/util.cpp:113-159).  Any part may be NULL with length 0. */
+GE2_API int ge2_pack_ids(const int64_t *const parts[4], const int64_t lens[4], const int64_t strides[4], int64_t *out,
+                 ge2_stream_t stream);
+
+/* =====================================================================================================
+ * (2) link-prediction training step: forward scores, softmax cross-entropy, backward
+ *     replaces, for CORRUPT_NODE + RNS + SOFTMAX_CE(SUM):
+ *       Model::forward_lp / Model::train_batch up to loss.backward()   cpp/src/nn/model.cpp:318-397
+ *       mod_node_corrupt_forward                                        cpp/src/nn/decoders/edge/decoder_methods.cpp:724-806,933-946,1089-1097
+ *       DotCompare::operator() + pad_and_reshape                        cpp/src/nn/decoders/edge/comparators.cpp:62-75,128-138
+ *       HadamardOperator / ComplexHadamardOperator                      cpp/src/nn/decoders/edge/relation_operators.cpp:3-31
+ *       apply_score_filter                                              cpp/src/data/samplers/negative.cpp:570-575
+ *       SoftmaxCrossEntropy::operator()                                 cpp/src/nn/loss.cpp:46-63
+ * ===================================================================================================== */
+#define GE2_DECODER_DISTMULT 0 /* Hadamard relation operator; with has_relations == 0 this is the "Dot" decoder */
+#define GE2_DECODER_COMPLEX 1  /* complex Hadamard: first D/2 columns real, remaining D - D/2 imaginary         */
+
+#define GE2_PRECISION_FP32 0 /* CUDA-core FFMA contraction, fp32 throughout (1e-4 relative parity)      */
+#define GE2_PRECISION_TF32 1 /* tcgen05 kind::tf32 tiles, fp32 accumulate in TMEM (1e-2 relative parity) */
+
+typedef struct ge2_lp_desc {
+    int32_t decoder;       /* GE2_DECODER_*                                                       */
+    int32_t has_relations; /* 1: edges carry a relation id; 0: relation-free graph                */
+    int32_t use_inverse;   /* 1: also corrupt sources with inverse_relation_embeddings (needs has_relations) */
+    int32_t precision;     /* GE2_PRECISION_*                                                     */
+    int32_t B;             /* edges in the batch                                                  */
+    int32_t C;             /* num_chunks                                                          */
+    int32_t N;             /* negatives per chunk                                                 */
+    int32_t D;             /* embedding dimension (<= 128)                                        */
+    int32_t R;             /* rows of the relation tables                                         */
+    int32_t phases;        /* 0 = whole step; else bit mask 1 = gather/prepare, 2 = scores, 4 = scatter/loss: lets a
+                              benchmark time one phase on the workspace a full step left behind             */
+    int64_t U;             /* rows of node_grad (and of node_emb when row_index == NULL)          */
+
+    /* node embeddings: batch-local [U, D] when row_index == NULL (Batch::node_embeddings_), else a resident
+     * table of which row row_index[l] is local node l (skips the indexRead copy). Row stride emb_stride floats. */
+    const float *node_emb;
+    const int64_t *row_index;
+    int64_t emb_stride;
+
+    /* batch edges in local ids; element i of the endpoint columns is at ptr[i * edge_stride], of the relation column
+     * at rel_ids[i * rel_stride] (3/3 for the reference's interleaved [B,3] edges_, 2 for [B,2], 1 for separate
+     * columns such as slices of the unique-map's inverse). rel_ids may be NULL when !has_relations. */
+    const int64_t *src_ids;
+    const int64_t *rel_ids;
+    const int64_t *dst_ids;
+    int64_t edge_stride;
+    int64_t rel_stride;
+
+    const int64_t *dst_negs; /* [C, N] local ids (Batch::dst_neg_indices_mapping_)                 */
+    const int64_t *src_negs; /* [C, N] local ids, needed when use_inverse                           */
+
+    /* score filter, either form (both may be NULL):
+     *  - filter pairs [F, 2] (row, column), Batch::dst_neg_filter_ / src_neg_filter_; at most one row per
+     *    (chunk, column), which is what deg_negative_local_filter produces;
+     *  - or the degree-sample plan itself: deg_sample_rows[C, n_deg] = batch row each of the first n_deg negatives
+     *    of a chunk was drawn from (the filter is derived on the device, no nonzero()/host count). */
+    const int64_t *dst_filter;
+    int64_t dst_filter_n;
+    const int64_t *src_filter;
+    int64_t src_filter_n;
+    const int64_t *deg_sample_rows;
+    int32_t n_deg;
+    int32_t reserved1;
+
+    const float *rel;     /* [R, D] relation_embeddings                                           */
+    const float *inv_rel; /* [R, D] inverse_relation_embeddings                                   */
+
+    /* outputs */
+    float *node_grad;    /* [U, D]  d loss / d node_emb, overwritten                               */
+    float *rel_grad;     /* [R, D]  accumulated into (+=), like autograd's .grad                   */
+    float *inv_rel_grad; /* [R, D]  accumulated into (+=)                                          */
+    float *loss;         /* [1]     overwritten                                                    */
+    /* optional outputs for inspection (NULL to skip): the four score tensors forward_lp returns.
+     * pos: [C*ceil(B/C)], neg: [C*ceil(B/C), N] (padded rows included, masked entries = -1e9).
+     * Writing neg scores costs a [B,N] round trip the training path otherwise never makes. */
+    float *pos_scores;
+    float *neg_scores;
+    float *inv_pos_scores;
+    float *inv_neg_scores;
+
+    int32_t *status;      /* device int32, GE2_STATUS_* bits are OR-ed in; may be NULL             */
+    void *workspace;      /* ge2_lp_workspace_bytes() bytes, 256-byte aligned                      */
+    size_t workspace_bytes;
+} ge2_lp_desc;
+
+GE2_API int ge2_lp_workspace_bytes(const ge2_lp_desc *desc, size_t *bytes);
+GE2_API int ge2_lp_step(const ge2_lp_desc *desc, ge2_stream_t stream);
+
+/* =====================================================================================================
+ * (3) optimizer updates
+ * ===================================================================================================== */
+/* Batch::accumulateGradients (cpp/src/data/batch.cpp:229-286, math :264-266) on batch-local tensors:
+ * upd = g*g; state += upd (in place); delta = -lr * g / (sqrt(state) + 1e-10).  rows may come from the device
+ * (rows_dev != NULL: min(*rows_dev, rows) rows are processed).  delta may alias grad. */
+GE2_API int ge2_sparse_adagrad(const float *grad, float *state_local, float *out_delta, float *out_state_update, int64_t rows,
+                       const int32_t *rows_dev, int32_t D, float lr, ge2_stream_t stream);
+
+/* Storage::indexRead / indexAdd for device tables (cpp/include/storage/storage.h:49-51;
+ * InMemory: cpp/src/storage/storage.cpp:1173-1259; MemPartitionBuffer: cpp/src/storage/buffer.cpp:973-1045,1221-1228).
+ * ids must be distinct for index_add (the reference relies on that too, buffer.cpp:619). */
+GE2_API int ge2_index_read(const float *table, int64_t table_rows, const int64_t *ids, int64_t n, const int32_t *n_dev, int32_t D,
+                   float *out, int32_t *status, ge2_stream_t stream);
+GE2_API int ge2_index_add(float *table, int64_t table_rows, const int64_t *ids, int64_t n, const int32_t *n_dev, int32_t D,
+                  const float *values, int32_t *status, ge2_stream_t stream);
+
+/* The fused form of accumulateGradients + updateEmbeddings (cpp/src/data/dataloader.cpp:1381-1395,
+ * cpp/src/storage/graph_storage.cpp:539-546,603-614): for every unique node l < U,
+ *   row = unique_ids[l]; state[row] += g*g; table[row] += -lr * g / (sqrt(state[row]) + 1e-10)
+ * with g = node_grad[l].  One read-modify-write pass over the touched rows, no temporaries.
+ * clear_grad != 0 also zeroes node_grad rows after use (saves the next batch's memset). */
+GE2_API int ge2_adagrad_scatter(float *table, float *state, int64_t table_rows, const int64_t *unique_ids, int64_t U,
+                        const int32_t *U_dev, float *node_grad, int32_t D, float lr, int32_t clear_grad, int32_t *status,
+                        ge2_stream_t stream);
+
+/* AdagradOptimizer::step on a dense table (cpp/src/nn/optim.cpp:109-143; weight_decay = lr_decay = 0):
+ * sum += g*g; param += -lr * g / (sqrt(sum) + eps).  grad_scale multiplies g first (1/num_gpus in
+ * Model::all_reduce, cpp/src/nn/model.cpp:188-192); clear_grad != 0 zeroes grad afterwards (clear_grad_all). */
+GE2_API int ge2_dense_adagrad(float *param, float *sum_state, float *grad, int64_t numel, float lr, float eps, float grad_scale,
+                      int32_t clear_grad, ge2_stream_t stream);
+
+/* =====================================================================================================
+ * producer side kept on the device so a training step needs no host round trip
+ * ===================================================================================================== */
+/* Shared chunked negatives of NegativeSamplingBase::getNodeCorruptNegatives (cpp/src/data/samplers/negative.cpp:938-1119;
+ * plan :104-134, materialise :136-169): per chunk n_deg rows drawn uniformly from the batch (their dst / src ids are
+ * the degree-proportional negatives) followed by N - n_deg ids uniform over [0, domain).  The same picks serve both
+ * corruption sides.  Counter-based generator keyed by (seed, batch_index): reproducible, not the reference's Philox stream.
+ * Also packs ids = [src(B), dst(B), src_negs(C*N) if wanted, dst_negs(C*N)] for the unique-map
+ * (order of cpp/src/data/dataloader.cpp:1128-1137).  out_deg_rows[C, n_deg] feeds ge2_lp_desc.deg_sample_rows. */
+GE2_API int ge2_sample_negatives(const int64_t *src_ids, const int64_t *dst_ids, int64_t edge_stride, int32_t B, int32_t C, int32_t N,
+                         int32_t n_deg, int64_t domain, int32_t want_src_negs, uint64_t seed, uint64_t batch_index,
+                         int64_t *out_packed_ids, int64_t *out_deg_rows, ge2_stream_t stream);
+
+/* GraphModelStorage::mapEdgesWithPartitionSlots_ (cpp/src/storage/graph_storage.cpp:270-303):
+ * id -> slot[id / partition_size] * partition_size + id % partition_size on the first and last column of
+ * edges[n, cols] (int64, in place or out of place).  A non-resident partition sets GE2_STATUS_BAD_INDEX. */
+GE2_API int ge2_remap_edges_to_slots(const int64_t *edges, int64_t n, int32_t cols, const int64_t *partition_to_slot,
+                             int32_t num_partitions, int64_t partition_size, int64_t *out, int32_t *status,
+                             ge2_stream_t stream);
+
+/* Slab copies of MemPartitionBufferStorage::performNextSwap's relay branch that stay on one device
+ * (cpp/src/storage/storage.cpp:626-652, src_dev == device_idx): moves[k] = {src_slot, dst_slot}; copies whole
+ * partition slabs src[src_slot] -> dst[dst_slot] in one launch.  Slabs that cross devices travel by NCCL send/recv
+ * issued by the host layer. */
+GE2_API int ge2_copy_slabs(const float *src, float *dst, const int32_t *moves_host, int32_t num_moves, int64_t slab_floats,
+                   ge2_stream_t stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* GE2_B200_H_ */

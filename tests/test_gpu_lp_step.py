@@ -1,0 +1,147 @@
+"""GPU parity of the fused link-prediction step (through the C ABI) against the reference fixtures and the oracle."""
+from pathlib import Path
+
+import numpy as np
+import pytest
+
+import ge2_oracle as O
+import workloads
+from gpu_helpers import rel_err, run_lp_step
+
+pytestmark = pytest.mark.gpu
+GOLDEN = Path(__file__).resolve().parent / "golden"
+
+# north-star tolerances: 1e-4 relative for the fp32 path, 1e-2 for TF32 tensor tiles
+TOL = {"fp32": 1e-4, "tf32": 1e-2}
+
+
+def check_against(res, ref, tol, S):
+    assert res["status"] == 0
+    assert abs(res["loss"] - ref["loss"]) <= tol * abs(ref["loss"])
+    assert rel_err(res["node_grad"], ref["node_grad"]) < tol
+    if "rel_grad" in ref and ref["rel_grad"] is not None:
+        assert rel_err(res["rel_grad"], ref["rel_grad"]) < tol
+    if S == 2:
+        assert rel_err(res["inv_rel_grad"], ref["inv_rel_grad"]) < tol
+    if "neg_scores" in res:
+        masked = ref["neg_scores"] == O.MASK_VALUE
+        assert np.array_equal(res["neg_scores"] == O.MASK_VALUE, masked)
+        scale = np.abs(ref["neg_scores"][~masked]).max()
+        assert np.abs(res["neg_scores"][~masked] - ref["neg_scores"][~masked]).max() < tol * scale
+        assert rel_err(res["pos_scores"], ref["pos_scores"]) < tol
+        if S == 2:
+            assert np.abs(res["inv_neg_scores"][~masked] - ref["inv_neg_scores"][~masked]).max() < tol * np.abs(ref["inv_neg_scores"][~masked]).max()
+            assert rel_err(res["inv_pos_scores"], ref["inv_pos_scores"]) < tol
+
+
+def golden_ref(name):
+    g = np.load(GOLDEN / f"{name}.npz")
+    ref = {k[4:]: g[k] for k in g.files if k.startswith("ref_")}
+    ref["loss"] = float(ref["loss"])
+    return ref
+
+
+@pytest.mark.parametrize("precision", ["fp32", "tf32"])
+@pytest.mark.parametrize("name", sorted(workloads.GOLDEN_CASES))
+def test_golden_fixtures(capi, cuda_device, name, precision):
+    case = workloads.golden_case(name)
+    ref = golden_ref(name)
+    S = 2 if case.src_negs is not None else 1
+    res = run_lp_step(capi, case, cuda_device, precision=precision, filter_mode="pairs")
+    check_against(res, ref, TOL[precision], S)
+
+
+@pytest.mark.parametrize("name", ["complex_d100_deg_padded", "dot_d100_deg"])
+def test_filter_from_degree_rows_and_row_index(capi, cuda_device, name):
+    """The on-device filter derivation and the table-with-row-index addressing give the same result as the reference's forms."""
+    case = workloads.golden_case(name)
+    ref = golden_ref(name)
+    S = 2 if case.src_negs is not None else 1
+    res = run_lp_step(capi, case, cuda_device, filter_mode="deg_rows", indirect=True)
+    check_against(res, ref, TOL["fp32"], S)
+
+
+@pytest.mark.parametrize("precision", ["fp32", "tf32"])
+@pytest.mark.parametrize("kind,B,C,N,D,R,U,n_deg,relations,inverse", [
+    ("DISTMULT", 1000, 10, 1000, 50, 1345, 14951, 0, True, True),     # configuration 1 shape
+    ("COMPLEX", 2000, 2, 1000, 100, 1000, 30000, 500, True, True),    # configuration 2 shape, fewer chunks
+    ("DISTMULT", 1001, 7, 130, 128, 50, 900, 30, True, True),          # ragged: B % C != 0, N % 64 != 0
+    ("DISTMULT", 3000, 3, 1000, 100, 0, 20000, 500, False, False),     # Dot decoder, configuration 3 shape
+    ("COMPLEX", 64, 1, 5, 6, 3, 40, 2, True, True),                    # tiny everything
+])
+def test_against_oracle(capi, cuda_device, precision, kind, B, C, N, D, R, U, n_deg, relations, inverse):
+    case = workloads.make_case(kind, B, C, N, D, max(R, 1), U, n_deg, seed=B + N + D, relations=relations, inverse=inverse, alpha=1.1)
+    S = 2 if case.src_negs is not None else 1
+    o = O.lp_train_forward_backward(case.kind, case.edges, case.emb, case.rel, case.inv_rel, case.dst_negs, case.src_negs, case.filt,
+                                    case.filt if S == 2 else None)
+    ref = dict(loss=o.loss, node_grad=o.node_grad, rel_grad=o.rel_grad, inv_rel_grad=o.inv_rel_grad, neg_scores=o.neg_scores,
+               pos_scores=o.pos_scores, inv_neg_scores=o.inv_neg_scores, inv_pos_scores=o.inv_pos_scores)
+    res = run_lp_step(capi, case, cuda_device, precision=precision, filter_mode="deg_rows" if n_deg else "none")
+    check_against(res, ref, TOL[precision], S)
+    # without the score dump the training outputs are unchanged
+    res2 = run_lp_step(capi, case, cuda_device, precision=precision, filter_mode="pairs", dump_scores=False)
+    assert abs(res2["loss"] - res["loss"]) <= 1e-6 * abs(res["loss"]) + 1e-6
+    assert rel_err(res2["node_grad"], res["node_grad"]) < 1e-5
+
+
+def test_relation_grads_accumulate(capi, cuda_device):
+    """rel_grad is accumulated into, like autograd's .grad across train_batch(call_step=false) calls."""
+    import torch
+
+    from gpu_helpers import dev
+
+    case = workloads.golden_case("distmult_d50_uniform")
+    ref = golden_ref("distmult_d50_uniform")
+    B, C, N, D, R, U = case.dims
+    edges = dev(case.edges, cuda_device)
+    node_grad = torch.empty((U, D), device=cuda_device)
+    loss = torch.empty(1, device=cuda_device)
+    rg = torch.ones((R, D), device=cuda_device)
+    irg = torch.zeros((R, D), device=cuda_device)
+    d = capi.make_lp_desc(decoder=case.kind, precision="fp32", B=B, Cn=C, N=N, D=D, R=R, U=U, node_emb=dev(case.emb, cuda_device),
+                          src_ids=edges, dst_ids=edges[:, 2], rel_ids=edges[:, 1], edge_stride=3, rel_stride=3,
+                          dst_negs=dev(case.dst_negs, cuda_device), src_negs=dev(case.src_negs, cuda_device), rel=dev(case.rel, cuda_device),
+                          inv_rel=dev(case.inv_rel, cuda_device), node_grad=node_grad, rel_grad=rg, inv_rel_grad=irg, loss=loss)
+    ws = torch.empty(capi.lp_workspace_bytes(d), dtype=torch.uint8, device=cuda_device)
+    d.workspace, d.workspace_bytes = ws.data_ptr(), ws.numel()
+    capi.lp_step(d)
+    capi.lp_step(d)
+    torch.cuda.synchronize()
+    assert rel_err(rg.cpu().numpy(), 1.0 + 2.0 * ref["rel_grad"]) < 1e-4
+    assert rel_err(irg.cpu().numpy(), 2.0 * ref["inv_rel_grad"]) < 1e-4
+    assert rel_err(node_grad.cpu().numpy(), ref["node_grad"]) < 1e-4  # node_grad is overwritten, not accumulated
+
+
+def test_bad_inputs_set_status_without_faulting(capi, cuda_device):
+    case = workloads.golden_case("dot_d100_deg")
+    B, C, N, D, R, U = case.dims
+    bad = workloads.golden_case("dot_d100_deg")
+    bad.edges = bad.edges.copy()
+    bad.edges[3, 0] = U + 5      # out-of-range local id
+    bad.dst_negs = bad.dst_negs.copy()
+    bad.dst_negs[1, 2] = -4
+    res = run_lp_step(capi, bad, cuda_device, filter_mode="none")
+    assert res["status"] & 8
+    dup = workloads.golden_case("dot_d100_deg")
+    dup.filt = np.array([[0, 1], [5, 1]], np.int64)  # two rows of chunk 0 masked in the same column
+    res = run_lp_step(capi, dup, cuda_device, filter_mode="pairs")
+    assert res["status"] & 4
+
+
+def test_argument_validation(capi, cuda_device):
+    import torch
+
+    t = torch.zeros(16, device=cuda_device)
+    i = torch.zeros(16, dtype=torch.int64, device=cuda_device)
+    with pytest.raises(capi.Ge2Error):  # D > 128
+        d = capi.make_lp_desc(decoder="DISTMULT", precision="fp32", B=2, Cn=1, N=2, D=200, R=0, U=2, node_emb=t, src_ids=i, dst_ids=i,
+                              dst_negs=i, node_grad=t, loss=t)
+        capi.lp_workspace_bytes(d)
+    with pytest.raises(capi.Ge2Error):  # odd D with the complex operator
+        d = capi.make_lp_desc(decoder="COMPLEX", precision="fp32", B=2, Cn=1, N=2, D=5, R=1, U=2, node_emb=t, src_ids=i, dst_ids=i,
+                              rel_ids=i, dst_negs=i, rel=t, node_grad=t, rel_grad=t, loss=t)
+        capi.lp_workspace_bytes(d)
+    d = capi.make_lp_desc(decoder="DISTMULT", precision="fp32", B=2, Cn=1, N=2, D=4, R=0, U=2, node_emb=t, src_ids=i, dst_ids=i,
+                          dst_negs=i, node_grad=t, loss=t)
+    with pytest.raises(capi.Ge2Error):  # no workspace
+        capi.lp_step(d)
