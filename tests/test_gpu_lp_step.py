@@ -98,10 +98,11 @@ def test_relation_grads_accumulate(capi, cuda_device):
     loss = torch.empty(1, device=cuda_device)
     rg = torch.ones((R, D), device=cuda_device)
     irg = torch.zeros((R, D), device=cuda_device)
-    d = capi.make_lp_desc(decoder=case.kind, precision="fp32", B=B, Cn=C, N=N, D=D, R=R, U=U, node_emb=dev(case.emb, cuda_device),
+    # the descriptor holds raw pointers only: keep every tensor alive until the step has run
+    emb, dn, sn, rel, inv = (dev(a, cuda_device) for a in (case.emb, case.dst_negs, case.src_negs, case.rel, case.inv_rel))
+    d = capi.make_lp_desc(decoder=case.kind, precision="fp32", B=B, Cn=C, N=N, D=D, R=R, U=U, node_emb=emb,
                           src_ids=edges, dst_ids=edges[:, 2], rel_ids=edges[:, 1], edge_stride=3, rel_stride=3,
-                          dst_negs=dev(case.dst_negs, cuda_device), src_negs=dev(case.src_negs, cuda_device), rel=dev(case.rel, cuda_device),
-                          inv_rel=dev(case.inv_rel, cuda_device), node_grad=node_grad, rel_grad=rg, inv_rel_grad=irg, loss=loss)
+                          dst_negs=dn, src_negs=sn, rel=rel, inv_rel=inv, node_grad=node_grad, rel_grad=rg, inv_rel_grad=irg, loss=loss)
     ws = torch.empty(capi.lp_workspace_bytes(d), dtype=torch.uint8, device=cuda_device)
     d.workspace, d.workspace_bytes = ws.data_ptr(), ws.numel()
     capi.lp_step(d)
