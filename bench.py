@@ -1,7 +1,7 @@
 #!/usr/bin/env python
 """Benchmark of the per-batch embedding-training path: train edges/sec.
 
-    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference] [--precision fp32|tf32]
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference] [--precision fp32|f16]
 
 A step is one batch (unique-map -> fused decoder forward/loss/backward -> sparse Adagrad scatter -> dense Adagrad
 on the relation tables) of the single-GPU configuration: synthetic knowledge graph with 1,000,000 entities,
@@ -219,7 +219,7 @@ def main():
     ap.add_argument("--steps", type=int, default=100)
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
-    ap.add_argument("--precision", default=os.environ.get("GE2_PRECISION", "fp32"), choices=["fp32", "tf32"])
+    ap.add_argument("--precision", default=os.environ.get("GE2_PRECISION", "fp32"), choices=["fp32", "f16"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--cpu-budget", type=float, default=15.0)
     args = ap.parse_args()
@@ -332,7 +332,7 @@ def main():
         line = dict(
             metric="train edges/sec/box", value=world * K * B / (ms * 1e-3), unit="edges/s", n_gpus=world, steps=K, warmup=W,
             ms_per_step=ms / K, higher_is_better=True, scaling="weak", vs_baseline=None,
-            dtype="f32" if args.precision == "fp32" else "tf32 tiles, f32 accumulate", data="synthetic",
+            dtype="f32" if args.precision == "fp32" else "f16 tensor tiles, f32 accumulate and storage", data="synthetic",
             config=dict(workload=cfg["name"], per_gpu_batch=B, global_batch=B * world, precision=args.precision,
                         l2="tables (0.8 GB) and edge list larger than L2; rows touched per step are random", parallelism=f"dp{world}" if world > 1 else "single"),
             e2e=dict(value=world * K * B / (ms_e2e * 1e-3), unit="edges/s", h2d_bytes_per_step=B * 3 * 8, d2h_bytes_per_step=4,

@@ -14,7 +14,7 @@ PKG = Path(__file__).resolve().parent
 
 GE2_OK = 0
 DECODER = {"DISTMULT": 0, "DOT": 0, "COMPLEX": 1}
-PRECISION = {"fp32": 0, "tf32": 1}
+PRECISION = {"fp32": 0, "f16": 1}
 STATUS_BITS = {1: "id out of range", 2: "scan timeout", 4: "filter collision", 8: "bad index", 16: "pipeline timeout"}
 
 EXPORTS = [

@@ -7,6 +7,8 @@
 //              P = exp(S - lse), dQ = P K, dK += P^T Q  (score tiles never leave the SM)  -> lse, dQ, dK
 //   finish   : relation-operator backward, d pos terms, duplicate-reducing scatter into node_grad / rel_grad, loss
 #pragma once
+#include <cuda_fp16.h>
+
 #include "common.cuh"
 
 namespace ge2 {
@@ -25,6 +27,8 @@ struct LpLayout {
     float* pos;       // [S][Bp]
     float* lse;       // [S][Bp]
     int32_t* mask;    // [S][CN]  batch row whose score in this (chunk, column) is masked, or -1
+    __half* Qh;       // [S][Bp][ld]  fp16 copy of Q, operand of the tensor-core path (null on the fp32 path)
+    __half* Kh;       // [S][CN][ld]  fp16 copy of K
     size_t bytes;
     size_t zero_begin, zero_bytes;  // dK range
 };
@@ -59,6 +63,9 @@ inline LpLayout lp_make_layout(const ge2_lp_desc& d, void* base) {
     size_t opos = take((size_t)L.S * L.Bp * 4);
     size_t olse = take((size_t)L.S * L.Bp * 4);
     size_t omask = take((size_t)L.S * L.CN * 4);
+    const bool half_copies = d.precision == GE2_PRECISION_F16;
+    size_t oQh = half_copies ? take((size_t)L.S * L.Bp * L.ld * 2) : 0;
+    size_t oKh = half_copies ? take((size_t)L.S * L.CN * L.ld * 2) : 0;
     L.Q = (float*)(p + oQ);
     L.K = (float*)(p + oK);
     L.dQ = (float*)(p + odQ);
@@ -66,6 +73,8 @@ inline LpLayout lp_make_layout(const ge2_lp_desc& d, void* base) {
     L.pos = (float*)(p + opos);
     L.lse = (float*)(p + olse);
     L.mask = (int32_t*)(p + omask);
+    L.Qh = half_copies ? (__half*)(p + oQh) : nullptr;
+    L.Kh = half_copies ? (__half*)(p + oKh) : nullptr;
     L.zero_begin = odK;
     L.zero_bytes = (size_t)L.S * L.CN * L.ld * 4;
     L.bytes = off;
@@ -74,6 +83,6 @@ inline LpLayout lp_make_layout(const ge2_lp_desc& d, void* base) {
 
 // scores kernels (one per precision); both fill lse, dQ, dK (+ optional score dumps) from Q, K, pos, mask
 int lp_scores_fp32(const LpKernelArgs& a, cudaStream_t stream);
-int lp_scores_tf32(const LpKernelArgs& a, cudaStream_t stream);
+int lp_scores_f16(const LpKernelArgs& a, cudaStream_t stream);
 
 }  // namespace ge2

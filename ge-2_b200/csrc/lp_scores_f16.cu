@@ -1,13 +1,16 @@
-// Tensor-core scores kernel of the link-prediction step: tcgen05.mma kind::tf32 with fp32 accumulators in tensor
-// memory, operands staged in shared memory by TMA (plain tiled loads, no multicast).  The 1e-2-parity path.
+// Tensor-core scores kernel of the link-prediction step: tcgen05.mma kind::f16 (fp16 operands, the 11-bit significand
+// of TF32) with fp32 accumulators in tensor memory, operands staged in shared memory by TMA (plain tiled loads, no
+// multicast).  The 1e-2-parity path; everything outside the three contractions stays fp32.
 //
 // One CTA = (side, chunk, 128-row block).  Shared memory holds the query block Q [128 x DP], one tile of negatives
-// K [128 x DP] and one tile of probabilities P [128 x 128], all in the 128-byte-swizzled layout TMA writes
-// (32-float column blocks of 128 rows at a 128-byte pitch).  That one layout serves every contraction, because a
+// K [128 x DP] and one tile of probabilities P [128 x 128] as fp16, all in the 128-byte-swizzled layout TMA writes
+// (64-element column blocks of 128 rows at a 128-byte pitch).  That one layout serves every contraction, because a
 // block read along its rows is a K-major operand and read along its columns an MN-major operand:
 //   S  [row, n] = Q  K^T   A = Q  (K-major, k = d)    B = K (K-major, k = d)      -> TMEM columns [0, 128)
 //   dQ [row, d] += P  K    A = P  (K-major, k = n)    B = K (MN-major, k = n)     -> TMEM columns [128, 128 + DP)
 //   dK [n, d]   = P^T Q    A = P  (MN-major, k = row) B = Q (MN-major, k = row)   -> TMEM columns [256, 256 + DP)
+// (32-bit tf32 operands cannot do this: the hardware transposes them only from a different, 32-byte-atom swizzle, so
+// every tile would be needed twice and the set no longer fits in shared memory.)
 // Sweep 1 runs the first contraction alone to get each row's logsumexp; sweep 2 recomputes S, turns it into
 // P = exp(S - lse) in registers, writes P to shared memory and issues the two gradient contractions.
 // The [rows x N] score matrix never leaves the SM.  Replaces the reference's bmm + logsumexp + cross_entropy +
@@ -24,44 +27,52 @@ namespace {
 
 using namespace tc;
 
-constexpr int BM = 128;               // query rows per CTA  (MMA M)
-constexpr int BN = 128;               // negatives per tile  (MMA N of the score contraction)
-constexpr int kThreads = 160;         // 4 row warps + 1 control warp
-constexpr int kCtl = 128;             // the thread that issues TMA and MMA
-constexpr int kBlockBytes = 128 * 128;  // one 32-float column block of 128 rows
+constexpr int BM = 128;                 // query rows per CTA  (MMA M)
+constexpr int BN = 128;                 // negatives per tile  (MMA N of the score contraction)
+constexpr int kThreads = 160;           // 4 row warps + 1 control warp
+constexpr int kCtl = 128;               // the thread that issues TMA and MMA
+constexpr int kBlockBytes = 128 * 128;  // one 64-half column block of 128 rows
+constexpr int kMmaK = 16;               // k extent of one kind::f16 MMA (32 bytes)
 constexpr uint32_t kTmemCols = 512;
 constexpr float kMasked = -1e9f;
 
 template <int DP>
 struct Layout {
-    static constexpr int NB = DP / 32;               // column blocks of Q / K
+    static constexpr int NB = DP / 64;               // column blocks of Q / K
     static constexpr int kQ = 0;
     static constexpr int kK = kQ + NB * kBlockBytes;
     static constexpr int kP = kK + NB * kBlockBytes;
-    static constexpr int kBars = kP + (BN / 32) * kBlockBytes;  // two mbarriers
+    static constexpr int kBars = kP + (BN / 64) * kBlockBytes;  // two mbarriers
     static constexpr int kTmem = kBars + 16;                      // tensor memory base address
     static constexpr int kAbort = kTmem + 4;
     static constexpr int kMask = kAbort + 12;                     // BN int32
     static constexpr int kEnd = kMask + BN * 4;
-    static constexpr int kDynamic = kEnd + 1024;                  // slack to align the base to 1024 bytes
+    // 1024 bytes of slack to align the base; at least 120 KB so that one CTA owns the SM and its tensor memory
+    static constexpr int kDynamic = (kEnd + 1024) > 120 * 1024 ? (kEnd + 1024) : 120 * 1024;
 };
 
-// K-major operand: k-step `ks` (8 tf32 = 32 bytes) sits in column block ks/4 at byte (ks%4)*32; 8-row groups are 1024 bytes apart
+// K-major operand: k-step `ks` (16 halves = 32 bytes) sits in column block ks/4 at byte (ks%4)*32; 8-row groups are 1024 bytes apart
 __device__ __forceinline__ uint64_t desc_kmajor(uint32_t tile, int ks) {
     return smem_desc_sw128(tile + (ks >> 2) * kBlockBytes + (ks & 3) * 32, 16, 1024);
 }
-// MN-major operand: k-step `ks` is the 8-row group ks (1024 bytes); the 32-element MN blocks are kBlockBytes apart
-__device__ __forceinline__ uint64_t desc_mnmajor(uint32_t tile, int ks) { return smem_desc_sw128(tile + ks * 1024, kBlockBytes, 1024); }
+// MN-major operand: k-step `ks` is rows [16 ks, 16 ks + 16) = two 8-row groups of 1024 bytes; the 64-element MN blocks are
+// kBlockBytes apart
+__device__ __forceinline__ uint64_t desc_mnmajor(uint32_t tile, int ks) { return smem_desc_sw128(tile + ks * 2048, kBlockBytes, 1024); }
 
-// byte offset of element (row, col) of a [128 x 32*nb] tile in the swizzled block layout
-__device__ __forceinline__ uint32_t swz_offset(int row, int col) {
-    const int chunk = (col & 31) >> 2;  // 16-byte chunk inside the 128-byte row
-    return (uint32_t)((col >> 5) * kBlockBytes + row * 128 + ((chunk ^ (row & 7)) << 4) + (col & 3) * 4);
+// byte offset of the 16-byte chunk holding halves [col, col + 8) of row `row` in the swizzled block layout (col % 8 == 0)
+__device__ __forceinline__ uint32_t swz_chunk_offset(int row, int col) {
+    const int chunk = (col & 63) >> 3;
+    return (uint32_t)((col >> 6) * kBlockBytes + row * 128 + ((chunk ^ (row & 7)) << 4));
+}
+
+__device__ __forceinline__ uint32_t pack_half2(float a, float b) {
+    __half2 h = __floats2half2_rn(a, b);
+    return *reinterpret_cast<uint32_t*>(&h);
 }
 
 template <int DP>
 __global__ void __launch_bounds__(kThreads, 1)
-    lp_scores_tf32_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK, LpKernelArgs a) {
+    lp_scores_f16_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK, LpKernelArgs a) {
     using LY = Layout<DP>;
     extern __shared__ unsigned char smem_raw[];
     unsigned char* smem = (unsigned char*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
@@ -106,16 +117,14 @@ __global__ void __launch_bounds__(kThreads, 1)
     const uint32_t tS = tmem, tdQ = tmem + 128, tdK = tmem + 256;
     const uint32_t lane_sel = (uint32_t)((warp & 3) * 32) << 16;  // this warp's quarter of the 128 TMEM lanes
     const uint32_t aQ = smem_u32(sQ), aK = smem_u32(sK), aP = smem_u32(sP);
-    constexpr uint32_t kIdescS = idesc_tf32(BM, BN, 0, 0);
-    constexpr uint32_t kIdescDQ = idesc_tf32(BM, DP, 0, 1);
-    constexpr uint32_t kIdescDK = idesc_tf32(BN, DP, 1, 1);
+    constexpr uint32_t kIdescS = idesc_f16(BM, BN, 0, 0);
+    constexpr uint32_t kIdescDQ = idesc_f16(BM, DP, 0, 1);
+    constexpr uint32_t kIdescDK = idesc_f16(BN, DP, 1, 1);
     uint32_t ph_tma = 0, ph_mma = 0;
-    bool ok = true;
 
     // wait on a barrier phase; on timeout flag the CTA for an orderly exit (everybody still reaches the next __syncthreads)
     auto wait_phase = [&](uint64_t* bar, uint32_t& phase) {
         if (!mbar_wait(bar, phase)) {
-            ok = false;
             *s_abort = 1;
             or_status(d.status, GE2_STATUS_PIPE_TIMEOUT);
         }
@@ -124,12 +133,12 @@ __global__ void __launch_bounds__(kThreads, 1)
     auto load_k_tile = [&](int n0) {  // control thread only
         mbar_expect_tx(bar_tma, kTileBytes);
 #pragma unroll
-        for (int b = 0; b < NB; b++) tma_load_3d(sK + b * kBlockBytes, &tmK, b * 32, n0, zc, bar_tma);
+        for (int b = 0; b < NB; b++) tma_load_3d(sK + b * kBlockBytes, &tmK, b * 64, n0, zc, bar_tma);
     };
     auto issue_scores = [&]() {  // control thread only: S = Q K^T
         tc_fence_after();
 #pragma unroll
-        for (int ks = 0; ks < DP / 8; ks++) mma_tf32_ss(tS, desc_kmajor(aQ, ks), desc_kmajor(aK, ks), kIdescS, ks > 0);
+        for (int ks = 0; ks < DP / kMmaK; ks++) mma_f16_ss(tS, desc_kmajor(aQ, ks), desc_kmajor(aK, ks), kIdescS, ks > 0);
         mma_commit(bar_mma);
     };
 
@@ -139,12 +148,12 @@ __global__ void __launch_bounds__(kThreads, 1)
         prefetch_tensormap(&tmK);
         mbar_expect_tx(bar_tma, kTileBytes);
 #pragma unroll
-        for (int b = 0; b < NB; b++) tma_load_3d(sQ + b * kBlockBytes, &tmQ, b * 32, row0, zc, bar_tma);
+        for (int b = 0; b < NB; b++) tma_load_3d(sQ + b * kBlockBytes, &tmQ, b * 64, row0, zc, bar_tma);
     }
     wait_phase(bar_tma, ph_tma);
 
-    const int my_row = tid;                                   // rows warps: accumulator row / TMEM lane
-    const int brow = c * L.npc + row0 + my_row;               // batch row in the padded numbering the filter uses
+    const int my_row = tid;                      // row warps: accumulator row / TMEM lane
+    const int brow = c * L.npc + row0 + my_row;  // batch row in the padded numbering the filter uses
     float run_m = -INFINITY, run_l = 0.f, lse = 0.f;
 
     // ---- sweep 1: logsumexp --------------------------------------------------------------------------------------
@@ -220,8 +229,13 @@ __global__ void __launch_bounds__(kThreads, 1)
                     v[j] = live ? __expf(v[j] - lse) : 0.f;
                 }
 #pragma unroll
-                for (int q = 0; q < 8; q++) {
-                    *reinterpret_cast<float4*>(sP + swz_offset(my_row, cb * 32 + q * 4)) = make_float4(v[4 * q], v[4 * q + 1], v[4 * q + 2], v[4 * q + 3]);
+                for (int q = 0; q < 4; q++) {  // 8 halves = one 16-byte chunk
+                    uint4 pk;
+                    pk.x = pack_half2(v[8 * q + 0], v[8 * q + 1]);
+                    pk.y = pack_half2(v[8 * q + 2], v[8 * q + 3]);
+                    pk.z = pack_half2(v[8 * q + 4], v[8 * q + 5]);
+                    pk.w = pack_half2(v[8 * q + 6], v[8 * q + 7]);
+                    *reinterpret_cast<uint4*>(sP + swz_chunk_offset(my_row, cb * 32 + q * 8)) = pk;
                 }
             }
             fence_proxy_async_smem();  // P was written with ordinary stores; the MMA reads it through the async proxy
@@ -231,11 +245,11 @@ __global__ void __launch_bounds__(kThreads, 1)
         if (tid == kCtl) {
             tc_fence_after();
 #pragma unroll
-            for (int ks = 0; ks < BN / 8; ks++)  // dQ += P K, k runs over the tile's negatives
-                mma_tf32_ss(tdQ, desc_kmajor(aP, ks), desc_mnmajor(aK, ks), kIdescDQ, (t > 0 || ks > 0) ? 1u : 0u);
+            for (int ks = 0; ks < BN / kMmaK; ks++)  // dQ += P K, k runs over the tile's negatives
+                mma_f16_ss(tdQ, desc_kmajor(aP, ks), desc_mnmajor(aK, ks), kIdescDQ, (t > 0 || ks > 0) ? 1u : 0u);
 #pragma unroll
-            for (int ks = 0; ks < BM / 8; ks++)  // dK = P^T Q, k runs over the block's rows
-                mma_tf32_ss(tdK, desc_mnmajor(aP, ks), desc_mnmajor(aQ, ks), kIdescDK, ks > 0);
+            for (int ks = 0; ks < BM / kMmaK; ks++)  // dK = P^T Q, k runs over the block's rows
+                mma_f16_ss(tdK, desc_mnmajor(aP, ks), desc_mnmajor(aQ, ks), kIdescDK, ks > 0);
             mma_commit(bar_mma);
         }
         wait_phase(bar_mma, ph_mma);
@@ -303,16 +317,16 @@ EncodeTiledFn encode_fn() {
     return fn;
 }
 
-// [S*C matrices][rows][ld floats] viewed as a 3-D tensor; box = 32 floats x 128 rows of one matrix, 128-byte swizzle,
+// [S*C matrices][rows][ld halves] viewed as a 3-D tensor; box = 64 halves x 128 rows of one matrix, 128-byte swizzle,
 // rows past the matrix end read as zero
-int make_map(CUtensorMap* map, float* base, int ld, int rows, int mats) {
+int make_map(CUtensorMap* map, __half* base, int ld, int rows, int mats) {
     EncodeTiledFn fn = encode_fn();
     if (fn == nullptr) return GE2_ERR_CUDA;
     cuuint64_t dims[3] = {(cuuint64_t)ld, (cuuint64_t)rows, (cuuint64_t)mats};
-    cuuint64_t strides[2] = {(cuuint64_t)ld * 4, (cuuint64_t)rows * ld * 4};
-    cuuint32_t box[3] = {32, 128, 1};
+    cuuint64_t strides[2] = {(cuuint64_t)ld * 2, (cuuint64_t)rows * ld * 2};
+    cuuint32_t box[3] = {64, 128, 1};
     cuuint32_t estr[3] = {1, 1, 1};
-    CUresult r = fn(map, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 3, base, dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+    CUresult r = fn(map, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 3, base, dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
                     CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
     if (r != CUDA_SUCCESS) {
         g_last_cuda_error = (int)r;
@@ -323,22 +337,23 @@ int make_map(CUtensorMap* map, float* base, int ld, int rows, int mats) {
 
 template <int DP>
 int launch(const LpKernelArgs& a, cudaStream_t stream) {
+    if (a.L.Qh == nullptr || a.L.Kh == nullptr) return GE2_ERR_WORKSPACE;
     CUtensorMap tmQ, tmK;
-    int rc = make_map(&tmQ, a.L.Q, DP, a.L.npc, a.L.S * a.d.C);
+    int rc = make_map(&tmQ, a.L.Qh, DP, a.L.npc, a.L.S * a.d.C);
     if (rc != GE2_OK) return rc;
-    rc = make_map(&tmK, a.L.K, DP, a.d.N, a.L.S * a.d.C);
+    rc = make_map(&tmK, a.L.Kh, DP, a.d.N, a.L.S * a.d.C);
     if (rc != GE2_OK) return rc;
     const int smem = Layout<DP>::kDynamic;
-    GE2_CUDA_TRY(cudaFuncSetAttribute(lp_scores_tf32_kernel<DP>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
+    GE2_CUDA_TRY(cudaFuncSetAttribute(lp_scores_f16_kernel<DP>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
     dim3 grid((unsigned)ceil_div(a.L.npc, BM), (unsigned)a.d.C, (unsigned)a.L.S);
-    lp_scores_tf32_kernel<DP><<<grid, kThreads, smem, stream>>>(tmQ, tmK, a);
+    lp_scores_f16_kernel<DP><<<grid, kThreads, smem, stream>>>(tmQ, tmK, a);
     GE2_LAUNCH_CHECK();
     return GE2_OK;
 }
 
 }  // namespace
 
-int lp_scores_tf32(const LpKernelArgs& a, cudaStream_t stream) {
+int lp_scores_f16(const LpKernelArgs& a, cudaStream_t stream) {
     if (a.L.ld == 64) return launch<64>(a, stream);
     if (a.L.ld == 128) return launch<128>(a, stream);
     return GE2_ERR_UNSUPPORTED;

@@ -1,5 +1,5 @@
 // Link-prediction training step (forward scores, softmax cross-entropy, backward) -- gather / scatter halves.
-// The contraction-heavy middle lives in lp_scores_fp32.cu / lp_scores_tf32.cu.
+// The contraction-heavy middle lives in lp_scores_fp32.cu / lp_scores_f16.cu.
 //
 // Follows, in the reference project: Model::train_batch up to loss.backward() (cpp/src/nn/model.cpp:362-397),
 // mod_node_corrupt_forward RNS branch (cpp/src/nn/decoders/edge/decoder_methods.cpp:724-806,933-946,1089-1097),
@@ -74,8 +74,12 @@ __global__ void __launch_bounds__(256) lp_prep_kernel(LpKernelArgs a) {
             const int s = (int)(w / L.Bp);
             const int i = (int)(w - (int64_t)s * L.Bp);
             float* q = L.Q + ((int64_t)s * L.Bp + i) * ld;
+            __half* qh = L.Qh != nullptr ? L.Qh + ((int64_t)s * L.Bp + i) * ld : nullptr;
             if (i >= d.B) {  // zero rows appended by pad_and_reshape; their positive score is padded with 0
-                for (int k = lane; k < ld; k += 32) q[k] = 0.f;
+                for (int k = lane; k < ld; k += 32) {
+                    q[k] = 0.f;
+                    if (qh != nullptr) qh[k] = __float2half_rn(0.f);
+                }
                 if (lane == 0) L.pos[(int64_t)s * L.Bp + i] = 0.f;
                 continue;
             }
@@ -89,7 +93,10 @@ __global__ void __launch_bounds__(256) lp_prep_kernel(LpKernelArgs a) {
             }
             if (!ok) {
                 if (lane == 0) or_status(d.status, GE2_STATUS_BAD_INDEX);
-                for (int k = lane; k < ld; k += 32) q[k] = 0.f;
+                for (int k = lane; k < ld; k += 32) {
+                    q[k] = 0.f;
+                    if (qh != nullptr) qh[k] = __float2half_rn(0.f);
+                }
                 if (lane == 0) L.pos[(int64_t)s * L.Bp + i] = 0.f;
                 continue;
             }
@@ -112,6 +119,7 @@ __global__ void __launch_bounds__(256) lp_prep_kernel(LpKernelArgs a) {
                     dot += v * eb[k];
                 }
                 q[k] = v;
+                if (qh != nullptr) qh[k] = __float2half_rn(v);
             }
             dot = warp_sum(dot);
             if (lane == 0) L.pos[(int64_t)s * L.Bp + i] = dot;
@@ -121,13 +129,15 @@ __global__ void __launch_bounds__(256) lp_prep_kernel(LpKernelArgs a) {
             const int64_t j = e - (int64_t)s * L.CN;
             const int64_t id = (s == 0 ? d.dst_negs : d.src_negs)[j];
             float* krow = L.K + e * ld;
-            if (id < 0 || id >= d.U) {
-                if (lane == 0) or_status(d.status, GE2_STATUS_BAD_INDEX);
-                for (int k = lane; k < ld; k += 32) krow[k] = 0.f;
-                continue;
+            __half* khrow = L.Kh != nullptr ? L.Kh + e * ld : nullptr;
+            const bool bad = id < 0 || id >= d.U;
+            if (bad && lane == 0) or_status(d.status, GE2_STATUS_BAD_INDEX);
+            const float* src = bad ? nullptr : emb_row(d, id);
+            for (int k = lane; k < ld; k += 32) {
+                const float v = (!bad && k < D) ? src[k] : 0.f;
+                krow[k] = v;
+                if (khrow != nullptr) khrow[k] = __float2half_rn(v);
             }
-            const float* src = emb_row(d, id);
-            for (int k = lane; k < ld; k += 32) krow[k] = k < D ? src[k] : 0.f;
         }
     }
 }
@@ -235,7 +245,7 @@ int validate(const ge2_lp_desc* d) {
     if (d == nullptr) return GE2_ERR_INVALID_ARGUMENT;
     if (d->B <= 0 || d->C <= 0 || d->N <= 0 || d->D <= 0 || d->U <= 0) return GE2_ERR_INVALID_ARGUMENT;
     if (d->decoder != GE2_DECODER_DISTMULT && d->decoder != GE2_DECODER_COMPLEX) return GE2_ERR_INVALID_ARGUMENT;
-    if (d->precision != GE2_PRECISION_FP32 && d->precision != GE2_PRECISION_TF32) return GE2_ERR_INVALID_ARGUMENT;
+    if (d->precision != GE2_PRECISION_FP32 && d->precision != GE2_PRECISION_F16) return GE2_ERR_INVALID_ARGUMENT;
     if (d->use_inverse && !d->has_relations) return GE2_ERR_INVALID_ARGUMENT;
     if (d->D > 128) return GE2_ERR_UNSUPPORTED;
     // the reference's complex operator splits the row in D/2 and D - D/2 columns and multiplies them element-wise: D must be even
@@ -305,7 +315,7 @@ extern "C" int ge2_lp_step(const ge2_lp_desc* desc, ge2_stream_t stream_) {
     }
 
     if (phases & 2) {
-        rc = desc->precision == GE2_PRECISION_TF32 ? lp_scores_tf32(a, stream) : lp_scores_fp32(a, stream);
+        rc = desc->precision == GE2_PRECISION_F16 ? lp_scores_f16(a, stream) : lp_scores_fp32(a, stream);
         if (rc != GE2_OK) return rc;
     }
     if (!(phases & 4)) return GE2_OK;

@@ -82,7 +82,8 @@ GE2_API int ge2_pack_ids(const int64_t *const parts[4], const int64_t lens[4], c
 #define GE2_DECODER_COMPLEX 1  /* complex Hadamard: first D/2 columns real, remaining D - D/2 imaginary         */
 
 #define GE2_PRECISION_FP32 0 /* CUDA-core FFMA contraction, fp32 throughout (1e-4 relative parity)      */
-#define GE2_PRECISION_TF32 1 /* tcgen05 kind::tf32 tiles, fp32 accumulate in TMEM (1e-2 relative parity) */
+#define GE2_PRECISION_F16 1  /* tcgen05 kind::f16 tiles (fp16 operands, 11-bit significand like TF32), fp32
+                                accumulate in TMEM, fp32 everywhere else (1e-2 relative parity)         */
 
 typedef struct ge2_lp_desc {
     int32_t decoder;       /* GE2_DECODER_*                                                       */
