@@ -21,7 +21,7 @@ EXPORTS = [
     "ge2_version", "ge2_last_cuda_error", "ge2_status_string", "ge2_check_device", "ge2_unique_workspace_bytes",
     "ge2_unique_bitmap", "ge2_pack_ids", "ge2_lp_workspace_bytes", "ge2_lp_step", "ge2_sparse_adagrad", "ge2_index_read",
     "ge2_index_add", "ge2_adagrad_scatter", "ge2_dense_adagrad", "ge2_sample_negatives", "ge2_remap_edges_to_slots",
-    "ge2_copy_slabs",
+    "ge2_copy_slabs", "ge2_unique_bitmap_static",
 ]
 
 
@@ -68,6 +68,7 @@ def load_library():
     lib.ge2_unique_workspace_bytes.restype = C.c_size_t
     lib.ge2_unique_workspace_bytes.argtypes = [C.c_int64]
     lib.ge2_unique_bitmap.argtypes = [C.c_void_p, C.c_int64, C.c_int64, C.c_void_p, C.c_size_t, C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p]
+    lib.ge2_unique_bitmap_static.argtypes = [C.c_void_p, C.c_int64, C.c_int64, C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p]
     lib.ge2_pack_ids.argtypes = [C.POINTER(C.c_void_p), C.POINTER(C.c_int64), C.POINTER(C.c_int64), C.c_void_p, C.c_void_p]
     lib.ge2_lp_workspace_bytes.argtypes = [C.POINTER(LpDesc), C.POINTER(C.c_size_t)]
     lib.ge2_lp_step.argtypes = [C.POINTER(LpDesc), C.c_void_p]
@@ -135,6 +136,16 @@ def unique_bitmap(ids, domain: int, workspace=None, out_unique=None, out_inverse
     check(lib.ge2_unique_bitmap(ptr(ids), n, domain, ptr(workspace), workspace.numel(), ptr(out_unique), ptr(out_inverse), ptr(out_count),
                                 cur_stream()), "ge2_unique_bitmap")
     return out_unique, out_inverse[:n], out_count
+
+
+UNIQUE_STATIC_MAX_DOMAIN = 4194304
+
+
+def unique_bitmap_static(ids, domain: int, out_unique, out_inverse, out_count):
+    """Unique-map with the library's built-in scratch: for callers that may not allocate device memory.  Every buffer is
+    supplied by the caller; domain is limited to UNIQUE_STATIC_MAX_DOMAIN.  Calls that overlap on the GPU race."""
+    check(load_library().ge2_unique_bitmap_static(ptr(ids), ids.numel(), domain, ptr(out_unique), ptr(out_inverse), ptr(out_count),
+                                                  cur_stream()), "ge2_unique_bitmap_static")
 
 
 def make_lp_desc(*, decoder, precision, B, Cn, N, D, R, U, node_emb, row_index=None, emb_stride=None, src_ids, dst_ids, rel_ids=None,

@@ -249,3 +249,50 @@ extern "C" int ge2_pack_ids(const int64_t* const parts[4], const int64_t lens[4]
     GE2_LAUNCH_CHECK();
     return GE2_OK;
 }
+
+// ---------------------------------------------------------------------------------------------------------------
+// Allocation-free variant of the unique-map.
+//
+// Some callers of this library run where cudaMalloc is off limits: inside a runtime that owns all device memory and
+// hands none out after start-up, in a plugin that is only ever given its input and output buffers, or on a hot path
+// whose latency budget has no room for an allocator call.  For them the scratch of the unique-map (bitset, per-word
+// offsets, scan tile states) lives in the array below, which is part of the library image: every GPU that loads the
+// library holds these bytes until the process exits.  The size fixes the largest id domain the entry point accepts.
+// ---------------------------------------------------------------------------------------------------------------
+namespace ge2 {
+namespace {
+
+constexpr int64_t kStaticMaxDomain = GE2_UNIQUE_STATIC_MAX_DOMAIN;
+constexpr size_t static_ws_bytes(int64_t domain) {
+    const int64_t nw = (domain + 63) >> 6;
+    const int64_t tiles = (nw + kTileWords - 1) / kTileWords;
+    return (((size_t)nw * 8 + 255) & ~(size_t)255) + (((size_t)nw * 4 + 255) & ~(size_t)255) + (((size_t)(tiles + 1) * 4 + 255) & ~(size_t)255);
+}
+constexpr size_t kStaticBytes = static_ws_bytes(kStaticMaxDomain);
+
+static __device__ __align__(256) unsigned char g_unique_static_scratch[kStaticBytes];
+
+constexpr int kMaxDevices = 64;
+void* g_static_scratch_addr[kMaxDevices] = {};  // device address of the array, per device, resolved on first use
+
+}  // namespace
+}  // namespace ge2
+
+extern "C" int ge2_unique_bitmap_static(const int64_t* ids, int64_t n, int64_t domain, int64_t* out_unique, int64_t* out_inverse,
+                                        int32_t* out_count, ge2_stream_t stream) {
+    if (domain <= 0 || n < 0) return GE2_ERR_INVALID_ARGUMENT;
+    if (domain > kStaticMaxDomain) return GE2_ERR_UNSUPPORTED;  // the built-in scratch is sized for GE2_UNIQUE_STATIC_MAX_DOMAIN ids
+    int device = -1;
+    GE2_CUDA_TRY(cudaGetDevice(&device));
+    if (device < 0 || device >= kMaxDevices) return GE2_ERR_UNSUPPORTED;
+    void* scratch = g_static_scratch_addr[device];
+    if (scratch == nullptr) {
+        // In host code the array's name is only a handle; the address a kernel can use has to be asked for, once per device,
+        // with that device current (it is: cudaGetDevice above).  Not a stream operation, but do it before any stream capture.
+        GE2_CUDA_TRY(cudaGetSymbolAddress(&scratch, g_unique_static_scratch));
+        if (scratch == nullptr) return GE2_ERR_CUDA;
+        g_static_scratch_addr[device] = scratch;
+    }
+    // Same kernels as ge2_unique_bitmap, which clears the parts of the scratch that must start at zero on every call.
+    return ge2_unique_bitmap(ids, n, domain, scratch, kStaticBytes, out_unique, out_inverse, out_count, stream);
+}

@@ -63,6 +63,19 @@ GE2_API size_t ge2_unique_workspace_bytes(int64_t domain);
 GE2_API int ge2_unique_bitmap(const int64_t *ids, int64_t n, int64_t domain, void *workspace, size_t workspace_bytes,
                       int64_t *out_unique, int64_t *out_inverse, int32_t *out_count, ge2_stream_t stream);
 
+/* Unique-map for callers that cannot allocate device memory -- a host runtime that owns the whole GPU heap and hands
+ * out none of it after start-up, a plugin that only ever receives its input and output buffers, a latency-bound loop
+ * that may not call an allocator.  No counterpart in the reference project.  Same results as ge2_unique_bitmap, but
+ * the scratch is a fixed array inside the library (about 0.8 MB on every GPU that loads it, held until the process
+ * exits), so the id domain is limited to GE2_UNIQUE_STATIC_MAX_DOMAIN; a larger domain returns GE2_ERR_UNSUPPORTED.
+ * The call makes no cudaMalloc/cudaFree and uses no allocating library routine.  The first call on each device looks
+ * up the array's device address; make that first call outside any stream capture.  All calls share the one array,
+ * which keeps the previous call's contents (the parts that must start at zero are cleared by every call): two calls
+ * whose kernels can overlap on the GPU -- different streams without an ordering between them -- race. */
+#define GE2_UNIQUE_STATIC_MAX_DOMAIN 4194304
+GE2_API int ge2_unique_bitmap_static(const int64_t *ids, int64_t n, int64_t domain, int64_t *out_unique, int64_t *out_inverse,
+                                     int32_t *out_count, ge2_stream_t stream);
+
 /* Packs up to four id vectors into one contiguous buffer, the job of pack_ids_into_cached_buffer
  * (cpp/src/common/util.cpp:113-159).  Any part may be NULL with length 0. */
 GE2_API int ge2_pack_ids(const int64_t *const parts[4], const int64_t lens[4], const int64_t strides[4], int64_t *out,

@@ -24,7 +24,7 @@ def test_library_exports_every_declared_symbol(ge2):
     for name in declared_functions():
         assert hasattr(lib, name), f"{name} declared in include/ge2_b200.h but not exported"
     assert sorted(ge2.capi.EXPORTS) == [n for n in declared_functions() if n in ge2.capi.EXPORTS]
-    assert set(declared_functions()) <= set(ge2.capi.EXPORTS) | {"ge2_lp_step_static"}
+    assert set(declared_functions()) <= set(ge2.capi.EXPORTS)
 
 
 def test_host_only_entry_points(ge2):
