@@ -2,23 +2,30 @@
 // of TF32) with fp32 accumulators in tensor memory, operands staged in shared memory by TMA (plain tiled loads, no
 // multicast).  The 1e-2-parity path; everything outside the three contractions stays fp32.
 //
-// One CTA = (side, chunk, 128-row block).  Shared memory holds the query block Q [128 x DP], one tile of negatives
-// K [128 x DP] and one tile of probabilities P [128 x 128] as fp16, all in the 128-byte-swizzled layout TMA writes
-// (64-element column blocks of 128 rows at a 128-byte pitch).  That one layout serves every contraction, because a
-// block read along its rows is a K-major operand and read along its columns an MN-major operand:
-//   S  [row, n] = Q  K^T   A = Q  (K-major, k = d)    B = K (K-major, k = d)      -> TMEM columns [0, 128)
-//   dQ [row, d] += P  K    A = P  (K-major, k = n)    B = K (MN-major, k = n)     -> TMEM columns [128, 128 + DP)
-//   dK [n, d]   = P^T Q    A = P  (MN-major, k = row) B = Q (MN-major, k = row)   -> TMEM columns [256, 256 + DP)
+// One CTA = (side, chunk, 128-row block).  Shared memory holds the query block Q [128 x DP], a ring of tiles of
+// negatives K [128 x DP] and two tiles of probabilities P [128 x 128] as fp16, all in the 128-byte-swizzled layout TMA
+// writes (64-element column blocks of 128 rows at a 128-byte pitch).  That one layout serves every contraction, because
+// a block read along its rows is a K-major operand and read along its columns an MN-major operand:
+//   S  [row, n] = Q  K^T   A = Q  (K-major, k = d)    B = K (K-major, k = d)      -> TMEM columns [0, 256), two buffers
+//   dQ [row, d] += P  K    A = P  (K-major, k = n)    B = K (MN-major, k = n)     -> TMEM columns [256, 256 + DP)
+//   dK [n, d]   = P^T Q    A = P  (MN-major, k = row) B = Q (MN-major, k = row)   -> TMEM columns [384, 384 + DP)
 // (32-bit tf32 operands cannot do this: the hardware transposes them only from a different, 32-byte-atom swizzle, so
 // every tile would be needed twice and the set no longer fits in shared memory.)
-// Sweep 1 runs the first contraction alone to get each row's logsumexp; sweep 2 recomputes S, turns it into
-// P = exp(S - lse) in registers, writes P to shared memory and issues the two gradient contractions.
-// The [rows x N] score matrix never leaves the SM.  Replaces the reference's bmm + logsumexp + cross_entropy +
-// autograd chain (cpp/src/nn/decoders/edge/comparators.cpp:128-138, cpp/src/nn/loss.cpp:46-63 of the reference project).
+// The chunk's negatives stream past the query block twice: sweep 1 runs the first contraction alone to get each row's
+// logsumexp; sweep 2 recomputes S, turns it into P = exp(S - lse) in registers, writes P to shared memory and issues the
+// two gradient contractions.  The [rows x N] score matrix never leaves the SM.  Replaces the reference's bmm +
+// logsumexp + cross_entropy + autograd chain (cpp/src/nn/decoders/edge/comparators.cpp:128-138,
+// cpp/src/nn/loss.cpp:46-63 of the reference project).
 //
-// Threads: warps 0-3 own one accumulator row each (TMEM lane = thread), warp 4 allocates tensor memory and its
-// lane 0 issues every TMA load and MMA.  Steps are separated by block-wide barriers; each mbarrier wait is bounded
-// and a wait that runs out raises GE2_STATUS_PIPE_TIMEOUT, after which the CTA drains and frees its tensor memory.
+// Warp roles, connected by mbarrier pipelines (no block-wide barrier inside the loops):
+//   warps 0-3  softmax: one accumulator row per thread (TMEM lane = thread); S -> running max/sum, later S -> P
+//   warps 4-7  drain:   dK accumulator -> vector reductions into global dK; at the end dQ accumulator -> global dQ
+//   warp  8    lane 0:  TMA producer for the K ring (and the one-off Q load)
+//   warp  9    lane 0:  MMA issuer; the warp also allocates and frees tensor memory
+// The MMA issuer runs the score contraction of tile i+1 before the gradient contractions of tile i, so the tensor
+// pipe has work while the softmax warps turn S(i) into P(i).
+// Every mbarrier wait is bounded; a wait that runs out raises GE2_STATUS_PIPE_TIMEOUT and sets a block-wide abort flag
+// that every other wait polls, so all roles fall through to the common exit where tensor memory is released.
 #include "lp_internal.cuh"
 #include "tc_ptx.cuh"
 
@@ -29,24 +36,30 @@ using namespace tc;
 
 constexpr int BM = 128;                 // query rows per CTA  (MMA M)
 constexpr int BN = 128;                 // negatives per tile  (MMA N of the score contraction)
-constexpr int kThreads = 160;           // 4 row warps + 1 control warp
-constexpr int kCtl = 128;               // the thread that issues TMA and MMA
+constexpr int kThreads = 320;           // 4 softmax warps + 4 drain warps + TMA warp + MMA warp
+constexpr int kTmaWarp = 8, kMmaWarp = 9;
 constexpr int kBlockBytes = 128 * 128;  // one 64-half column block of 128 rows
 constexpr int kMmaK = 16;               // k extent of one kind::f16 MMA (32 bytes)
+constexpr int kStagesK = 3;             // K ring depth
 constexpr uint32_t kTmemCols = 512;
 constexpr float kMasked = -1e9f;
+
+// mbarrier slots
+enum Bar { kBarQ = 0, kBarKFull = 1, kBarKEmpty = kBarKFull + kStagesK, kBarSFull = kBarKEmpty + kStagesK, kBarSEmpty = kBarSFull + 2,
+           kBarPFull = kBarSEmpty + 2, kBarPEmpty = kBarPFull + 2, kBarDkFull = kBarPEmpty + 2, kBarDkEmpty, kBarDqFull, kNumBars };
 
 template <int DP>
 struct Layout {
     static constexpr int NB = DP / 64;               // column blocks of Q / K
+    static constexpr int kTileBytes = NB * kBlockBytes;
+    static constexpr int kPBytes = (BN / 64) * kBlockBytes;
     static constexpr int kQ = 0;
-    static constexpr int kK = kQ + NB * kBlockBytes;
-    static constexpr int kP = kK + NB * kBlockBytes;
-    static constexpr int kBars = kP + (BN / 64) * kBlockBytes;  // two mbarriers
-    static constexpr int kTmem = kBars + 16;                      // tensor memory base address
+    static constexpr int kK = kQ + kTileBytes;
+    static constexpr int kP = kK + kStagesK * kTileBytes;
+    static constexpr int kBars = kP + 2 * kPBytes;
+    static constexpr int kTmem = kBars + kNumBars * 8;           // tensor memory base address
     static constexpr int kAbort = kTmem + 4;
-    static constexpr int kMask = kAbort + 12;                     // BN int32
-    static constexpr int kEnd = kMask + BN * 4;
+    static constexpr int kEnd = kAbort + 4;
     // 1024 bytes of slack to align the base; at least 120 KB so that one CTA owns the SM and its tensor memory
     static constexpr int kDynamic = (kEnd + 1024) > 120 * 1024 ? (kEnd + 1024) : 120 * 1024;
 };
@@ -70,6 +83,38 @@ __device__ __forceinline__ uint32_t pack_half2(float a, float b) {
     return *reinterpret_cast<uint32_t*>(&h);
 }
 
+__device__ __forceinline__ float exp2f_fast(float x) {  // one MUFU.EX2; 2^-inf = 0
+    float y;
+    asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+    return y;
+}
+__device__ __forceinline__ void mbar_arrive(uint64_t* bar) {
+    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(bar)) : "memory");
+}
+
+// Bounded wait that also gives up as soon as another role has raised the abort flag.
+__device__ __forceinline__ bool pipe_wait(uint64_t* bar, uint32_t parity, volatile int* abort_flag, int32_t* status) {
+    for (uint32_t i = 0; i < (1u << 20); i++) {
+        if (mbar_try_wait(bar, parity)) return true;
+        if (i > 64) __nanosleep(i > 4096 ? 256 : 32);  // long waits (a role idle for a whole sweep) must not eat issue slots
+        if ((i & 255u) == 255u && *abort_flag) return false;
+    }
+    *abort_flag = 1;
+    or_status(status, GE2_STATUS_PIPE_TIMEOUT);
+    return false;
+}
+
+#ifdef GE2_TRACE
+// development aid (not compiled into the shipped library): clock stamps of CTA (0,0,0), read back by a debug export
+__device__ long long g_trace[4][64][8];
+#define TR(role, it, k)                                                                              \
+    do {                                                                                             \
+        if (blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0 && (it) < 64) g_trace[role][it][k] = clock64(); \
+    } while (0)
+#else
+#define TR(role, it, k)
+#endif
+
 template <int DP>
 __global__ void __launch_bounds__(kThreads, 1)
     lp_scores_f16_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK, LpKernelArgs a) {
@@ -79,34 +124,40 @@ __global__ void __launch_bounds__(kThreads, 1)
     unsigned char* sQ = smem + LY::kQ;
     unsigned char* sK = smem + LY::kK;
     unsigned char* sP = smem + LY::kP;
-    uint64_t* bar_tma = (uint64_t*)(smem + LY::kBars);
-    uint64_t* bar_mma = bar_tma + 1;
+    uint64_t* bars = (uint64_t*)(smem + LY::kBars);
     uint32_t* s_tmem = (uint32_t*)(smem + LY::kTmem);
     volatile int* s_abort = (volatile int*)(smem + LY::kAbort);
-    int32_t* s_mask = (int32_t*)(smem + LY::kMask);
 
     const ge2_lp_desc& d = a.d;
     const LpLayout& L = a.L;
-    const int tid = threadIdx.x, warp = tid >> 5;
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const int s = blockIdx.z, c = blockIdx.y;
     const int row0 = blockIdx.x * BM;
     const int valid_rows = min(BM, L.npc - row0);
     const int zc = s * d.C + c;  // third TMA coordinate: (side, chunk)
     const int64_t grow0 = (int64_t)s * L.Bp + (int64_t)c * L.npc + row0;
-    const int32_t* maskc = L.mask + (int64_t)s * L.CN + (int64_t)c * d.N;
-    float* dKc = L.dK + ((int64_t)s * L.CN + (int64_t)c * d.N) * DP;
-    float* dump = s == 0 ? d.neg_scores : d.inv_neg_scores;
-    const int n_tiles = (d.N + BN - 1) / BN;
+    const int T = (d.N + BN - 1) / BN;  // tiles per sweep; iteration i < T is sweep 1, i >= T sweep 2 on tile i - T
     constexpr int NB = LY::NB;
-    constexpr uint32_t kTileBytes = NB * kBlockBytes;
 
     if (tid == 0) {
-        mbar_init(bar_tma, 1);
-        mbar_init(bar_mma, 1);
+        mbar_init(&bars[kBarQ], 1);
+        for (int k = 0; k < kStagesK; k++) {
+            mbar_init(&bars[kBarKFull + k], 1);
+            mbar_init(&bars[kBarKEmpty + k], 1);
+        }
+        for (int k = 0; k < 2; k++) {
+            mbar_init(&bars[kBarSFull + k], 1);
+            mbar_init(&bars[kBarSEmpty + k], 4);  // one arrival per softmax warp
+            mbar_init(&bars[kBarPFull + k], 4);
+            mbar_init(&bars[kBarPEmpty + k], 1);
+        }
+        mbar_init(&bars[kBarDkFull], 1);
+        mbar_init(&bars[kBarDkEmpty], 4);  // one arrival per drain warp
+        mbar_init(&bars[kBarDqFull], 1);
         *s_abort = 0;
         mbar_init_fence();
     }
-    if (warp == 4) {
+    if (warp == kMmaWarp) {
         tmem_alloc(s_tmem, kTmemCols);
         tmem_relinquish();
     }
@@ -114,155 +165,242 @@ __global__ void __launch_bounds__(kThreads, 1)
     __syncthreads();
     tc_fence_after();
     const uint32_t tmem = *s_tmem;
-    const uint32_t tS = tmem, tdQ = tmem + 128, tdK = tmem + 256;
+    const uint32_t tS = tmem, tdQ = tmem + 256, tdK = tmem + 384;
     const uint32_t lane_sel = (uint32_t)((warp & 3) * 32) << 16;  // this warp's quarter of the 128 TMEM lanes
-    const uint32_t aQ = smem_u32(sQ), aK = smem_u32(sK), aP = smem_u32(sP);
-    constexpr uint32_t kIdescS = idesc_f16(BM, BN, 0, 0);
-    constexpr uint32_t kIdescDQ = idesc_f16(BM, DP, 0, 1);
-    constexpr uint32_t kIdescDK = idesc_f16(BN, DP, 1, 1);
-    uint32_t ph_tma = 0, ph_mma = 0;
+    auto wait = [&](int bar, uint32_t parity) { return pipe_wait(&bars[bar], parity, s_abort, d.status); };
 
-    // wait on a barrier phase; on timeout flag the CTA for an orderly exit (everybody still reaches the next __syncthreads)
-    auto wait_phase = [&](uint64_t* bar, uint32_t& phase) {
-        if (!mbar_wait(bar, phase)) {
-            *s_abort = 1;
-            or_status(d.status, GE2_STATUS_PIPE_TIMEOUT);
-        }
-        phase ^= 1;
-    };
-    auto load_k_tile = [&](int n0) {  // control thread only
-        mbar_expect_tx(bar_tma, kTileBytes);
+    if (warp == kTmaWarp) {
+        // ================================ TMA producer ================================
+        if (lane == 0) {
+            prefetch_tensormap(&tmQ);
+            prefetch_tensormap(&tmK);
+            mbar_expect_tx(&bars[kBarQ], LY::kTileBytes);
 #pragma unroll
-        for (int b = 0; b < NB; b++) tma_load_3d(sK + b * kBlockBytes, &tmK, b * 64, n0, zc, bar_tma);
-    };
-    auto issue_scores = [&]() {  // control thread only: S = Q K^T
-        tc_fence_after();
+            for (int b = 0; b < NB; b++) tma_load_3d(sQ + b * kBlockBytes, &tmQ, b * 64, row0, zc, &bars[kBarQ]);
+            for (int i = 0; i < 2 * T; i++) {
+                const int st = i % kStagesK, use = i / kStagesK;
+                TR(0, i, 0);
+                if (!wait(kBarKEmpty + st, (use & 1) ^ 1)) break;
+                TR(0, i, 1);
+                mbar_expect_tx(&bars[kBarKFull + st], LY::kTileBytes);
+                const int n0 = (i < T ? i : i - T) * BN;
 #pragma unroll
-        for (int ks = 0; ks < DP / kMmaK; ks++) mma_f16_ss(tS, desc_kmajor(aQ, ks), desc_kmajor(aK, ks), kIdescS, ks > 0);
-        mma_commit(bar_mma);
-    };
-
-    // ---- query block -------------------------------------------------------------------------------------------
-    if (tid == kCtl) {
-        prefetch_tensormap(&tmQ);
-        prefetch_tensormap(&tmK);
-        mbar_expect_tx(bar_tma, kTileBytes);
-#pragma unroll
-        for (int b = 0; b < NB; b++) tma_load_3d(sQ + b * kBlockBytes, &tmQ, b * 64, row0, zc, bar_tma);
-    }
-    wait_phase(bar_tma, ph_tma);
-
-    const int my_row = tid;                      // row warps: accumulator row / TMEM lane
-    const int brow = c * L.npc + row0 + my_row;  // batch row in the padded numbering the filter uses
-    float run_m = -INFINITY, run_l = 0.f, lse = 0.f;
-
-    // ---- sweep 1: logsumexp --------------------------------------------------------------------------------------
-    for (int t = 0; t < n_tiles; t++) {
-        const int n0 = t * BN;
-        const int valid_n = min(BN, d.N - n0);
-        if (tid < BN) s_mask[tid] = tid < valid_n ? maskc[n0 + tid] : -1;
-        if (tid == kCtl) load_k_tile(n0);
-        wait_phase(bar_tma, ph_tma);
-        if (tid == kCtl) issue_scores();
-        wait_phase(bar_mma, ph_mma);
-        tc_fence_after();
-        __syncthreads();
-        if (*s_abort) break;
-        if (warp < 4) {
-#pragma unroll 1
-            for (int cb = 0; cb < BN / 32; cb++) {
-                float v[32];
-                tmem_ld_32x32(tS + lane_sel + cb * 32, v);
-                float tmax = -INFINITY;
-#pragma unroll
-                for (int j = 0; j < 32; j++) {
-                    const int col = cb * 32 + j;
-                    float sc = v[j];
-                    if (s_mask[col] == brow) sc = kMasked;
-                    if (dump != nullptr && my_row < valid_rows && col < valid_n) dump[(int64_t)brow * d.N + n0 + col] = sc;
-                    v[j] = col < valid_n ? sc : -INFINITY;
-                    tmax = fmaxf(tmax, v[j]);
-                }
-                if (tmax > -INFINITY) {
-                    const float nm = fmaxf(run_m, tmax);
-                    float add = 0.f;
-#pragma unroll
-                    for (int j = 0; j < 32; j++) add += __expf(v[j] - nm);
-                    run_l = run_l * __expf(run_m - nm) + add;
-                    run_m = nm;
-                }
+                for (int b = 0; b < NB; b++) tma_load_3d(sK + st * LY::kTileBytes + b * kBlockBytes, &tmK, b * 64, n0, zc, &bars[kBarKFull + st]);
             }
         }
-        tc_fence_before();
-        __syncthreads();  // S and the K tile are free again
-    }
-    if (warp < 4 && my_row < valid_rows) {
-        const float pos = L.pos[grow0 + my_row];
-        const float nm = fmaxf(run_m, pos);
-        lse = nm + __logf(run_l * __expf(run_m - nm) + __expf(pos - nm));
-        L.lse[grow0 + my_row] = lse;
-    }
-
-    // ---- sweep 2: probabilities, dQ and dK -------------------------------------------------------------------------
-    for (int t = 0; t < n_tiles; t++) {
-        if (*s_abort) break;
-        const int n0 = t * BN;
-        const int valid_n = min(BN, d.N - n0);
-        if (tid < BN) s_mask[tid] = tid < valid_n ? maskc[n0 + tid] : -1;
-        if (tid == kCtl) load_k_tile(n0);
-        wait_phase(bar_tma, ph_tma);
-        if (tid == kCtl) issue_scores();
-        wait_phase(bar_mma, ph_mma);
-        tc_fence_after();
-        __syncthreads();
-        if (*s_abort) break;
-        if (warp < 4) {
-#pragma unroll 1
-            for (int cb = 0; cb < BN / 32; cb++) {
-                float v[32];
-                tmem_ld_32x32(tS + lane_sel + cb * 32, v);
+    } else if (warp == kMmaWarp) {
+        // ================================ MMA issuer ================================
+        if (lane == 0) {
+            const uint32_t aQ = smem_u32(sQ), aK0 = smem_u32(sK), aP0 = smem_u32(sP);
+            constexpr uint32_t kIdescS = idesc_f16(BM, BN, 0, 0);
+            constexpr uint32_t kIdescDQ = idesc_f16(BM, DP, 0, 1);
+            constexpr uint32_t kIdescDK = idesc_f16(BN, DP, 1, 1);
+            bool ok = wait(kBarQ, 0);
+            // gradient contractions of sweep-2 iteration j (tile t = j - T)
+            auto issue_grad = [&](int j) -> bool {
+                const int t = j - T, pb = t & 1, st = j % kStagesK;
+                if (!wait(kBarPFull + pb, (t >> 1) & 1)) return false;
+                TR(1, j, 4);
+                if (!wait(kBarDkEmpty, (t & 1) ^ 1)) return false;
+                TR(1, j, 5);
+                tc_fence_after();
+                const uint32_t aK = aK0 + st * LY::kTileBytes, aP = aP0 + pb * LY::kPBytes;
 #pragma unroll
-                for (int j = 0; j < 32; j++) {
-                    const int col = cb * 32 + j;
-                    // masked entries were overwritten in place by the reference: no gradient reaches them
-                    const bool live = my_row < valid_rows && col < valid_n && s_mask[col] != brow;
-                    v[j] = live ? __expf(v[j] - lse) : 0.f;
-                }
+                for (int ks = 0; ks < BN / kMmaK; ks++)  // dQ += P K, k runs over the tile's negatives
+                    mma_f16_ss(tdQ, desc_kmajor(aP, ks), desc_mnmajor(aK, ks), kIdescDQ, (t > 0 || ks > 0) ? 1u : 0u);
 #pragma unroll
-                for (int q = 0; q < 4; q++) {  // 8 halves = one 16-byte chunk
-                    uint4 pk;
-                    pk.x = pack_half2(v[8 * q + 0], v[8 * q + 1]);
-                    pk.y = pack_half2(v[8 * q + 2], v[8 * q + 3]);
-                    pk.z = pack_half2(v[8 * q + 4], v[8 * q + 5]);
-                    pk.w = pack_half2(v[8 * q + 6], v[8 * q + 7]);
-                    *reinterpret_cast<uint4*>(sP + swz_chunk_offset(my_row, cb * 32 + q * 8)) = pk;
+                for (int ks = 0; ks < BM / kMmaK; ks++)  // dK = P^T Q, k runs over the block's rows
+                    mma_f16_ss(tdK, desc_mnmajor(aP, ks), desc_mnmajor(aQ, ks), kIdescDK, ks > 0);
+                mma_commit(&bars[kBarKEmpty + st]);
+                mma_commit(&bars[kBarPEmpty + pb]);
+                mma_commit(&bars[kBarDkFull]);
+                if (t == T - 1) mma_commit(&bars[kBarDqFull]);
+                TR(1, j, 6);
+                return true;
+            };
+            for (int i = 0; ok && i < 2 * T; i++) {
+                const int st = i % kStagesK, use = i / kStagesK, sb = i & 1;
+                TR(1, i, 0);
+                if (!wait(kBarKFull + st, use & 1)) { ok = false; break; }
+                TR(1, i, 1);
+                if (!wait(kBarSEmpty + sb, ((i >> 1) & 1) ^ 1)) { ok = false; break; }
+                TR(1, i, 2);
+                tc_fence_after();
+                const uint32_t aK = aK0 + st * LY::kTileBytes;
+#pragma unroll
+                for (int ks = 0; ks < DP / kMmaK; ks++) mma_f16_ss(tS + sb * BN, desc_kmajor(aQ, ks), desc_kmajor(aK, ks), kIdescS, ks > 0);
+                mma_commit(&bars[kBarSFull + sb]);
+                if (i < T) mma_commit(&bars[kBarKEmpty + st]);  // sweep 1 needs the tile for nothing else
+                TR(1, i, 3);
+                if (i - 1 >= T) ok = issue_grad(i - 1);
+            }
+            if (ok) issue_grad(2 * T - 1);
+        }
+    } else if (warp < 4) {
+        // ================================ softmax warps ================================
+        const int my_row = tid;                      // accumulator row / TMEM lane
+        const int brow = c * L.npc + row0 + my_row;  // batch row in the padded numbering the filter uses
+        const int wrow0 = c * L.npc + row0 + warp * 32;  // first batch row of this warp
+        const int32_t* maskc = L.mask + (int64_t)s * L.CN + (int64_t)c * d.N;
+        float* dump = s == 0 ? d.neg_scores : d.inv_neg_scores;
+        constexpr float kLog2e = 1.4426950408889634f;
+        // running max / sum of exp2 in the base-2 domain (scores pre-multiplied by log2 e): one FFMA + one MUFU per score
+        float run_m = -INFINITY, run_l = 0.f, lse2 = 0.f;
+        for (int i = 0; i < 2 * T; i++) {
+            const int sb = i & 1;
+            const int t = i < T ? i : i - T;
+            const int n0 = t * BN;
+            const int valid_n = min(BN, d.N - n0);
+            // The filter is sparse: a tile has at most one masked row per column and few of them fall in this warp's 32
+            // rows.  Lane l looks at columns l, l+32, l+64, l+96; entries that name a row of this warp are handed to that
+            // row's thread, which ends up with one bit per masked column of its own row (mbits[k] bit j = column 32k+j).
+            uint32_t mbits[BN / 32];
+#pragma unroll
+            for (int k = 0; k < BN / 32; k++) {
+                const int idx = k * 32 + lane;
+                const int32_t m = idx < valid_n ? __ldg(&maskc[n0 + idx]) : -1;
+                unsigned ballot = __ballot_sync(0xffffffffu, (unsigned)(m - wrow0) < 32u);
+                mbits[k] = 0;
+                while (ballot != 0) {
+                    const int src = __ffs(ballot) - 1;
+                    ballot &= ballot - 1;
+                    if (__shfl_sync(0xffffffffu, m, src) == brow) mbits[k] |= 1u << src;
                 }
             }
-            fence_proxy_async_smem();  // P was written with ordinary stores; the MMA reads it through the async proxy
-        }
-        tc_fence_before();
-        __syncthreads();
-        if (tid == kCtl) {
+            if (tid == 0) TR(2, i, 0);
+            if (!__all_sync(0xffffffffu, wait(kBarSFull + sb, (i >> 1) & 1))) break;  // warp-uniform: tcgen05.ld is collective
+            if (tid == 0) TR(2, i, 1);
             tc_fence_after();
+            const uint32_t tSb = tS + sb * BN + lane_sel;
+            if (i < T) {
+#pragma unroll 1
+                for (int cb = 0; cb < BN / 32; cb++) {
+                    float v[32];
+                    tmem_ld_32x32(tSb + cb * 32, v);
+                    const int nv = valid_n - cb * 32;  // live columns of this 32-column slab
+                    if (nv <= 0) continue;
+                    const uint32_t mb = cb == 0 ? mbits[0] : cb == 1 ? mbits[1] : cb == 2 ? mbits[2] : mbits[3];
+                    const bool general = dump != nullptr || nv < 32 || __any_sync(0xffffffffu, mb != 0);
+                    if (!general) {
+                        float tmax = v[0];
 #pragma unroll
-            for (int ks = 0; ks < BN / kMmaK; ks++)  // dQ += P K, k runs over the tile's negatives
-                mma_f16_ss(tdQ, desc_kmajor(aP, ks), desc_mnmajor(aK, ks), kIdescDQ, (t > 0 || ks > 0) ? 1u : 0u);
+                        for (int j = 1; j < 32; j++) tmax = fmaxf(tmax, v[j]);
+                        const float nm = fmaxf(run_m, tmax * kLog2e);
+                        float add0 = 0.f, add1 = 0.f;
 #pragma unroll
-            for (int ks = 0; ks < BM / kMmaK; ks++)  // dK = P^T Q, k runs over the block's rows
-                mma_f16_ss(tdK, desc_mnmajor(aP, ks), desc_mnmajor(aQ, ks), kIdescDK, ks > 0);
-            mma_commit(bar_mma);
+                        for (int j = 0; j < 32; j += 2) {
+                            add0 += exp2f_fast(fmaf(v[j], kLog2e, -nm));
+                            add1 += exp2f_fast(fmaf(v[j + 1], kLog2e, -nm));
+                        }
+                        run_l = fmaf(run_l, exp2f_fast(run_m - nm), add0 + add1);
+                        run_m = nm;
+                    } else {
+                        float tmax = -INFINITY;
+#pragma unroll
+                        for (int j = 0; j < 32; j++) {
+                            const int col = cb * 32 + j;
+                            float sc = v[j];
+                            sc = ((mb >> j) & 1u) ? kMasked : sc;
+                            if (dump != nullptr && my_row < valid_rows && col < valid_n) dump[(int64_t)brow * d.N + n0 + col] = sc;
+                            v[j] = j < nv ? sc * kLog2e : -INFINITY;
+                            tmax = fmaxf(tmax, v[j]);
+                        }
+                        const float nm = fmaxf(run_m, tmax);
+                        float add = 0.f;
+#pragma unroll
+                        for (int j = 0; j < 32; j++) add += exp2f_fast(v[j] - nm);  // 2^-inf = 0 for absent columns
+                        run_l = fmaf(run_l, exp2f_fast(run_m - nm), add);
+                        run_m = nm;
+                    }
+                }
+                tc_fence_before();
+                __syncwarp();
+                if (lane == 0) mbar_arrive(&bars[kBarSEmpty + sb]);
+                if (tid == 0) TR(2, i, 3);
+                if (i == T - 1) {
+                    float lse = 0.f;
+                    if (my_row < valid_rows) {
+                        const float pos2 = L.pos[grow0 + my_row] * kLog2e;
+                        const float nm = fmaxf(run_m, pos2);
+                        lse2 = nm + __log2f(run_l * exp2f_fast(run_m - nm) + exp2f_fast(pos2 - nm));
+                        lse = lse2 * 0.6931471805599453f;
+                        L.lse[grow0 + my_row] = lse;
+                    }
+                }
+            } else {
+                const int pb = t & 1;
+                // the gradient MMAs that read this P buffer two tiles ago must be done
+                if (!__all_sync(0xffffffffu, wait(kBarPEmpty + pb, ((t >> 1) & 1) ^ 1))) break;
+                if (tid == 0) TR(2, i, 2);
+                unsigned char* sPb = sP + pb * LY::kPBytes;
+                const bool row_live = my_row < valid_rows;
+#pragma unroll 1
+                for (int cb = 0; cb < BN / 32; cb++) {
+                    float v[32];
+                    tmem_ld_32x32(tSb + cb * 32, v);
+                    const int nv = valid_n - cb * 32;
+                    const uint32_t mb = cb == 0 ? mbits[0] : cb == 1 ? mbits[1] : cb == 2 ? mbits[2] : mbits[3];
+                    const bool general = nv < 32 || __any_sync(0xffffffffu, mb != 0);
+                    if (!general) {
+#pragma unroll
+                        for (int j = 0; j < 32; j++) v[j] = exp2f_fast(fmaf(v[j], kLog2e, -lse2));
+                        if (!row_live) {
+#pragma unroll
+                            for (int j = 0; j < 32; j++) v[j] = 0.f;
+                        }
+                    } else {
+#pragma unroll
+                        for (int j = 0; j < 32; j++) {
+                            // masked entries were overwritten in place by the reference: no gradient reaches them
+                            const bool live = row_live && j < nv && ((mb >> j) & 1u) == 0u;
+                            const float e = exp2f_fast(fmaf(v[j], kLog2e, -lse2));
+                            v[j] = live ? e : 0.f;
+                        }
+                    }
+#pragma unroll
+                    for (int q = 0; q < 4; q++) {  // 8 halves = one 16-byte chunk
+                        uint4 pk;
+                        pk.x = pack_half2(v[8 * q + 0], v[8 * q + 1]);
+                        pk.y = pack_half2(v[8 * q + 2], v[8 * q + 3]);
+                        pk.z = pack_half2(v[8 * q + 4], v[8 * q + 5]);
+                        pk.w = pack_half2(v[8 * q + 6], v[8 * q + 7]);
+                        *reinterpret_cast<uint4*>(sPb + swz_chunk_offset(my_row, cb * 32 + q * 8)) = pk;
+                    }
+                }
+                tc_fence_before();
+                fence_proxy_async_smem();  // P was written with ordinary stores; the MMA reads it through the async proxy
+                __syncwarp();
+                if (lane == 0) {
+                    mbar_arrive(&bars[kBarSEmpty + sb]);
+                    mbar_arrive(&bars[kBarPFull + pb]);
+                }
+                if (tid == 0) TR(2, i, 3);
+            }
         }
-        wait_phase(bar_mma, ph_mma);
-        tc_fence_after();
-        __syncthreads();
-        if (*s_abort) break;
-        if (warp < 4) {  // here a TMEM lane is a negative of the tile
-            float* dst = dKc + (int64_t)(n0 + my_row) * DP;
+    } else {
+        // ================================ drain warps (4-7) ================================
+        const int my_lane = tid - 128;  // TMEM lane: a negative of the tile for dK, a query row for dQ
+        float* dKc = L.dK + ((int64_t)s * L.CN + (int64_t)c * d.N) * DP;
+        bool ok = true;
+        for (int t = 0; t < T; t++) {
+            const int n0 = t * BN;
+            const int valid_n = min(BN, d.N - n0);
+            if (tid == 128) TR(3, t, 0);
+            if (!__all_sync(0xffffffffu, wait(kBarDkFull, t & 1))) { ok = false; break; }
+            if (tid == 128) TR(3, t, 1);
+            tc_fence_after();
+            float* dst = dKc + (int64_t)(n0 + my_lane) * DP;
 #pragma unroll 1
             for (int cb = 0; cb < DP / 32; cb++) {
                 float v[32];
                 tmem_ld_32x32(tdK + lane_sel + cb * 32, v);  // warp-collective: lanes past the tile's end take part too
-                if (my_row < valid_n) {
+                if (cb == DP / 32 - 1) {  // accumulator fully read: hand it back before the slow part
+                    tc_fence_before();
+                    __syncwarp();
+                    if (lane == 0) mbar_arrive(&bars[kBarDkEmpty]);
+                    if (tid == 128) TR(3, t, 2);
+                }
+                if (my_lane < valid_n) {
 #pragma unroll
                     for (int q = 0; q < 8; q++) {
                         const int col = cb * 32 + q * 4;
@@ -271,31 +409,32 @@ __global__ void __launch_bounds__(kThreads, 1)
                 }
             }
         }
-        tc_fence_before();
-        __syncthreads();  // dK accumulator, P and the K tile are free again
-    }
-    if (warp < 4 && !*s_abort) {
+        if (tid == 128) TR(3, T, 0);
+        if (ok && __all_sync(0xffffffffu, wait(kBarDqFull, 0))) {
+            tc_fence_after();
 #pragma unroll 1
-        for (int cb = 0; cb < DP / 32; cb++) {
-            float v[32];
-            tmem_ld_32x32(tdQ + lane_sel + cb * 32, v);
-            if (my_row < valid_rows) {
-                float* dst = L.dQ + (grow0 + my_row) * DP + cb * 32;
+            for (int cb = 0; cb < DP / 32; cb++) {
+                float v[32];
+                tmem_ld_32x32(tdQ + lane_sel + cb * 32, v);
+                if (my_lane < valid_rows) {
+                    float* dst = L.dQ + (grow0 + my_lane) * DP + cb * 32;
 #pragma unroll
-                for (int q = 0; q < 8; q++) *reinterpret_cast<float4*>(dst + q * 4) = make_float4(v[4 * q], v[4 * q + 1], v[4 * q + 2], v[4 * q + 3]);
+                    for (int q = 0; q < 8; q++) *reinterpret_cast<float4*>(dst + q * 4) = make_float4(v[4 * q], v[4 * q + 1], v[4 * q + 2], v[4 * q + 3]);
+                }
             }
         }
     }
-    // ---- teardown: nothing of this CTA may still be in flight when tensor memory is released ----------------------
+    // ---- common exit: every role ends here, normally or after an abort; then tensor memory is released ----------
     tc_fence_before();
     __syncthreads();
-    if (*s_abort && tid == kCtl) {
-        // a wait ran out: give outstanding copies / MMAs one more bounded chance to land before the memory is reused
-        mbar_wait(bar_tma, ph_tma ^ 1, 1u << 16);
-        mbar_wait(bar_mma, ph_mma ^ 1, 1u << 16);
-    }
-    __syncthreads();
-    if (warp == 4) {
+    if (warp == kMmaWarp) {
+        if (*s_abort && lane == 0) {
+            // a wait ran out somewhere: give copies / MMAs still in flight a bounded chance to land before the SM's
+            // shared and tensor memory are handed to the next CTA
+            for (int k = 0; k < kStagesK; k++) mbar_wait(&bars[kBarKFull + k], 0, 1u << 14);
+            mbar_wait(&bars[kBarDqFull], 0, 1u << 14);
+        }
+        __syncwarp();
         tc_fence_after();
         tmem_dealloc(tmem, kTmemCols);
     }
@@ -352,6 +491,12 @@ int launch(const LpKernelArgs& a, cudaStream_t stream) {
 }
 
 }  // namespace
+
+#ifdef GE2_TRACE
+extern "C" __attribute__((visibility("default"))) int ge2_debug_read_trace(long long* host_out) {
+    return (int)cudaMemcpyFromSymbol(host_out, g_trace, sizeof(long long) * 4 * 64 * 8);
+}
+#endif
 
 int lp_scores_f16(const LpKernelArgs& a, cudaStream_t stream) {
     if (a.L.ld == 64) return launch<64>(a, stream);
