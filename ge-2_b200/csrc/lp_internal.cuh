@@ -29,6 +29,7 @@ struct LpLayout {
     int32_t* mask;    // [S][CN]  batch row whose score in this (chunk, column) is masked, or -1
     __half* Qh;       // [S][Bp][ld]  fp16 copy of Q, operand of the tensor-core path (null on the fp32 path)
     __half* Kh;       // [S][CN][ld]  fp16 copy of K
+    float* part;      // [S][Bp][4][2] per-row partial (max, sum) of sweep 1 when a chunk's tiles are split over CTAs
     size_t bytes;
     size_t zero_begin, zero_bytes;  // dK range
 };
@@ -66,6 +67,7 @@ inline LpLayout lp_make_layout(const ge2_lp_desc& d, void* base) {
     const bool half_copies = d.precision == GE2_PRECISION_F16;
     size_t oQh = half_copies ? take((size_t)L.S * L.Bp * L.ld * 2) : 0;
     size_t oKh = half_copies ? take((size_t)L.S * L.CN * L.ld * 2) : 0;
+    size_t opart = half_copies ? take((size_t)L.S * L.Bp * 8 * 4) : 0;
     L.Q = (float*)(p + oQ);
     L.K = (float*)(p + oK);
     L.dQ = (float*)(p + odQ);
@@ -75,6 +77,7 @@ inline LpLayout lp_make_layout(const ge2_lp_desc& d, void* base) {
     L.mask = (int32_t*)(p + omask);
     L.Qh = half_copies ? (__half*)(p + oQh) : nullptr;
     L.Kh = half_copies ? (__half*)(p + oKh) : nullptr;
+    L.part = half_copies ? (float*)(p + opart) : nullptr;
     L.zero_begin = odK;
     L.zero_bytes = (size_t)L.S * L.CN * L.ld * 4;
     L.bytes = off;

@@ -26,6 +26,8 @@
 // pipe has work while the softmax warps turn S(i) into P(i).
 // Every mbarrier wait is bounded; a wait that runs out raises GE2_STATUS_PIPE_TIMEOUT and sets a block-wide abort flag
 // that every other wait polls, so all roles fall through to the common exit where tensor memory is released.
+#include <stdlib.h>
+
 #include "lp_internal.cuh"
 #include "tc_ptx.cuh"
 
@@ -117,7 +119,7 @@ __device__ long long g_trace[4][64][8];
 
 template <int DP>
 __global__ void __launch_bounds__(kThreads, 1)
-    lp_scores_f16_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK, LpKernelArgs a) {
+    lp_scores_f16_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK, LpKernelArgs a, int mode, int nsplit) {
     using LY = Layout<DP>;
     extern __shared__ unsigned char smem_raw[];
     unsigned char* smem = (unsigned char*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
@@ -132,11 +134,19 @@ __global__ void __launch_bounds__(kThreads, 1)
     const LpLayout& L = a.L;
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const int s = blockIdx.z, c = blockIdx.y;
-    const int row0 = blockIdx.x * BM;
+    // blockIdx.x = row block * nsplit + h: with nsplit > 1 the chunk's negative tiles are dealt round-robin to nsplit CTAs
+    const int split_h = blockIdx.x % nsplit;
+    const int row0 = (blockIdx.x / nsplit) * BM;
     const int valid_rows = min(BM, L.npc - row0);
     const int zc = s * d.C + c;  // third TMA coordinate: (side, chunk)
     const int64_t grow0 = (int64_t)s * L.Bp + (int64_t)c * L.npc + row0;
-    const int T = (d.N + BN - 1) / BN;  // tiles per sweep; iteration i < T is sweep 1, i >= T sweep 2 on tile i - T
+    const int T_all = (d.N + BN - 1) / BN;                         // tiles of the chunk
+    const int T_loc = (T_all - split_h + nsplit - 1) / nsplit;       // tiles of this CTA: split_h, split_h + nsplit, ...
+    // mode 0: both sweeps in one launch (nsplit == 1); mode 1: sweep 1 only, leaves per-row partial (max, sum);
+    // mode 2: sweep 2 only, starts from the partials.  Iteration i < nA is sweep 1 on local tile i, later ones sweep 2.
+    const int nA = mode == 2 ? 0 : T_loc, nB = mode == 1 ? 0 : T_loc;
+    const int n_iter = nA + nB;
+    auto tile_n0 = [&](int i) { return (split_h + nsplit * (i < nA ? i : i - nA)) * BN; };
     constexpr int NB = LY::NB;
 
     if (tid == 0) {
@@ -177,13 +187,13 @@ __global__ void __launch_bounds__(kThreads, 1)
             mbar_expect_tx(&bars[kBarQ], LY::kTileBytes);
 #pragma unroll
             for (int b = 0; b < NB; b++) tma_load_3d(sQ + b * kBlockBytes, &tmQ, b * 64, row0, zc, &bars[kBarQ]);
-            for (int i = 0; i < 2 * T; i++) {
+            for (int i = 0; i < n_iter; i++) {
                 const int st = i % kStagesK, use = i / kStagesK;
                 TR(0, i, 0);
                 if (!wait(kBarKEmpty + st, (use & 1) ^ 1)) break;
                 TR(0, i, 1);
                 mbar_expect_tx(&bars[kBarKFull + st], LY::kTileBytes);
-                const int n0 = (i < T ? i : i - T) * BN;
+                const int n0 = tile_n0(i);
 #pragma unroll
                 for (int b = 0; b < NB; b++) tma_load_3d(sK + st * LY::kTileBytes + b * kBlockBytes, &tmK, b * 64, n0, zc, &bars[kBarKFull + st]);
             }
@@ -198,7 +208,7 @@ __global__ void __launch_bounds__(kThreads, 1)
             bool ok = wait(kBarQ, 0);
             // gradient contractions of sweep-2 iteration j (tile t = j - T)
             auto issue_grad = [&](int j) -> bool {
-                const int t = j - T, pb = t & 1, st = j % kStagesK;
+                const int t = j - nA, pb = t & 1, st = j % kStagesK;
                 if (!wait(kBarPFull + pb, (t >> 1) & 1)) return false;
                 TR(1, j, 4);
                 if (!wait(kBarDkEmpty, (t & 1) ^ 1)) return false;
@@ -214,11 +224,11 @@ __global__ void __launch_bounds__(kThreads, 1)
                 mma_commit(&bars[kBarKEmpty + st]);
                 mma_commit(&bars[kBarPEmpty + pb]);
                 mma_commit(&bars[kBarDkFull]);
-                if (t == T - 1) mma_commit(&bars[kBarDqFull]);
+                if (t == nB - 1) mma_commit(&bars[kBarDqFull]);
                 TR(1, j, 6);
                 return true;
             };
-            for (int i = 0; ok && i < 2 * T; i++) {
+            for (int i = 0; ok && i < n_iter; i++) {
                 const int st = i % kStagesK, use = i / kStagesK, sb = i & 1;
                 TR(1, i, 0);
                 if (!wait(kBarKFull + st, use & 1)) { ok = false; break; }
@@ -230,11 +240,11 @@ __global__ void __launch_bounds__(kThreads, 1)
 #pragma unroll
                 for (int ks = 0; ks < DP / kMmaK; ks++) mma_f16_ss(tS + sb * BN, desc_kmajor(aQ, ks), desc_kmajor(aK, ks), kIdescS, ks > 0);
                 mma_commit(&bars[kBarSFull + sb]);
-                if (i < T) mma_commit(&bars[kBarKEmpty + st]);  // sweep 1 needs the tile for nothing else
+                if (i < nA) mma_commit(&bars[kBarKEmpty + st]);  // sweep 1 needs the tile for nothing else
                 TR(1, i, 3);
-                if (i - 1 >= T) ok = issue_grad(i - 1);
+                if (i - 1 >= nA) ok = issue_grad(i - 1);
             }
-            if (ok) issue_grad(2 * T - 1);
+            if (ok && nB > 0) issue_grad(n_iter - 1);
         }
     } else if (warp < 4) {
         // ================================ softmax warps ================================
@@ -246,10 +256,26 @@ __global__ void __launch_bounds__(kThreads, 1)
         constexpr float kLog2e = 1.4426950408889634f;
         // running max / sum of exp2 in the base-2 domain (scores pre-multiplied by log2 e): one FFMA + one MUFU per score
         float run_m = -INFINITY, run_l = 0.f, lse2 = 0.f;
-        for (int i = 0; i < 2 * T; i++) {
+        if (mode == 2 && my_row < valid_rows) {  // sweep 1 ran in an earlier launch: combine its partial (max, sum) pairs
+            float m = -INFINITY, l = 0.f;
+            const float2* part = reinterpret_cast<const float2*>(L.part) + (grow0 + my_row) * 4;
+            for (int k = 0; k < nsplit; k++) {
+                const float2 pk = part[k];
+                const float nm = fmaxf(m, pk.x);
+                if (nm > -INFINITY) {
+                    l = l * exp2f_fast(m - nm) + pk.y * exp2f_fast(pk.x - nm);
+                    m = nm;
+                }
+            }
+            const float pos2 = L.pos[grow0 + my_row] * kLog2e;
+            const float nm = fmaxf(m, pos2);
+            lse2 = nm + __log2f(l * exp2f_fast(m - nm) + exp2f_fast(pos2 - nm));
+            if (split_h == 0) L.lse[grow0 + my_row] = lse2 * 0.6931471805599453f;
+        }
+        for (int i = 0; i < n_iter; i++) {
             const int sb = i & 1;
-            const int t = i < T ? i : i - T;
-            const int n0 = t * BN;
+            const int t = i < nA ? i : i - nA;  // local tile index within its sweep
+            const int n0 = tile_n0(i);
             const int valid_n = min(BN, d.N - n0);
             // The filter is sparse: a tile has at most one masked row per column and few of them fall in this warp's 32
             // rows.  Lane l looks at columns l, l+32, l+64, l+96; entries that name a row of this warp are handed to that
@@ -272,7 +298,7 @@ __global__ void __launch_bounds__(kThreads, 1)
             if (tid == 0) TR(2, i, 1);
             tc_fence_after();
             const uint32_t tSb = tS + sb * BN + lane_sel;
-            if (i < T) {
+            if (i < nA) {
 #pragma unroll 1
                 for (int cb = 0; cb < BN / 32; cb++) {
                     float v[32];
@@ -317,14 +343,14 @@ __global__ void __launch_bounds__(kThreads, 1)
                 __syncwarp();
                 if (lane == 0) mbar_arrive(&bars[kBarSEmpty + sb]);
                 if (tid == 0) TR(2, i, 3);
-                if (i == T - 1) {
-                    float lse = 0.f;
-                    if (my_row < valid_rows) {
+                if (i == nA - 1 && my_row < valid_rows) {
+                    if (mode == 1) {  // hand the partial over to the sweep-2 launch
+                        reinterpret_cast<float2*>(L.part)[(grow0 + my_row) * 4 + split_h] = make_float2(run_m, run_l);
+                    } else {
                         const float pos2 = L.pos[grow0 + my_row] * kLog2e;
                         const float nm = fmaxf(run_m, pos2);
                         lse2 = nm + __log2f(run_l * exp2f_fast(run_m - nm) + exp2f_fast(pos2 - nm));
-                        lse = lse2 * 0.6931471805599453f;
-                        L.lse[grow0 + my_row] = lse;
+                        L.lse[grow0 + my_row] = lse2 * 0.6931471805599453f;
                     }
                 }
             } else {
@@ -382,8 +408,8 @@ __global__ void __launch_bounds__(kThreads, 1)
         const int my_lane = tid - 128;  // TMEM lane: a negative of the tile for dK, a query row for dQ
         float* dKc = L.dK + ((int64_t)s * L.CN + (int64_t)c * d.N) * DP;
         bool ok = true;
-        for (int t = 0; t < T; t++) {
-            const int n0 = t * BN;
+        for (int t = 0; t < nB; t++) {
+            const int n0 = tile_n0(nA + t);
             const int valid_n = min(BN, d.N - n0);
             if (tid == 128) TR(3, t, 0);
             if (!__all_sync(0xffffffffu, wait(kBarDkFull, t & 1))) { ok = false; break; }
@@ -409,8 +435,7 @@ __global__ void __launch_bounds__(kThreads, 1)
                 }
             }
         }
-        if (tid == 128) TR(3, T, 0);
-        if (ok && __all_sync(0xffffffffu, wait(kBarDqFull, 0))) {
+        if (ok && nB > 0 && __all_sync(0xffffffffu, wait(kBarDqFull, 0))) {
             tc_fence_after();
 #pragma unroll 1
             for (int cb = 0; cb < DP / 32; cb++) {
@@ -418,8 +443,14 @@ __global__ void __launch_bounds__(kThreads, 1)
                 tmem_ld_32x32(tdQ + lane_sel + cb * 32, v);
                 if (my_lane < valid_rows) {
                     float* dst = L.dQ + (grow0 + my_lane) * DP + cb * 32;
+                    if (nsplit == 1) {
 #pragma unroll
-                    for (int q = 0; q < 8; q++) *reinterpret_cast<float4*>(dst + q * 4) = make_float4(v[4 * q], v[4 * q + 1], v[4 * q + 2], v[4 * q + 3]);
+                        for (int q = 0; q < 8; q++) *reinterpret_cast<float4*>(dst + q * 4) = make_float4(v[4 * q], v[4 * q + 1], v[4 * q + 2], v[4 * q + 3]);
+                    } else {  // the row's dQ is the sum over the CTAs that share the chunk's tiles (dQ was zeroed by the host side)
+#pragma unroll
+                        for (int q = 0; q < 8; q++)
+                            if (cb * 32 + q * 4 < d.D) atomicAdd(reinterpret_cast<float4*>(dst + q * 4), make_float4(v[4 * q], v[4 * q + 1], v[4 * q + 2], v[4 * q + 3]));
+                    }
                 }
             }
         }
@@ -474,6 +505,27 @@ int make_map(CUtensorMap* map, __half* base, int ld, int rows, int mats) {
     return GE2_OK;
 }
 
+// How many CTAs share one (side, chunk, row block): work items are indivisible, so 160 items on 148 SMs cost two full
+// rounds; dealing each item's tiles to 2 or 4 CTAs (sweep 1 and sweep 2 then run as two launches) shortens the tail at the
+// price of a fixed per-CTA overhead (Q load, barrier and tensor-memory set-up), taken as 12 % of a whole item here.
+int choose_nsplit(int items, int tiles) {
+    if (const char* e = getenv("GE2_F16_NSPLIT")) {
+        const int v = atoi(e);
+        if ((v == 1 || v == 2 || v == 4) && v <= tiles) return v;
+    }
+    int best = 1;
+    double best_cost = 1e30;
+    for (int ns = 1; ns <= 4 && ns <= tiles; ns *= 2) {
+        const double rounds = (double)((items * ns + kNumSMs - 1) / kNumSMs);
+        const double cost = rounds * (1.0 / ns + 0.12) + (ns > 1 ? 0.1 : 0.0);
+        if (cost < best_cost) {
+            best_cost = cost;
+            best = ns;
+        }
+    }
+    return best;
+}
+
 template <int DP>
 int launch(const LpKernelArgs& a, cudaStream_t stream) {
     if (a.L.Qh == nullptr || a.L.Kh == nullptr) return GE2_ERR_WORKSPACE;
@@ -484,9 +536,20 @@ int launch(const LpKernelArgs& a, cudaStream_t stream) {
     if (rc != GE2_OK) return rc;
     const int smem = Layout<DP>::kDynamic;
     GE2_CUDA_TRY(cudaFuncSetAttribute(lp_scores_f16_kernel<DP>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
-    dim3 grid((unsigned)ceil_div(a.L.npc, BM), (unsigned)a.d.C, (unsigned)a.L.S);
-    lp_scores_f16_kernel<DP><<<grid, kThreads, smem, stream>>>(tmQ, tmK, a);
-    GE2_LAUNCH_CHECK();
+    const int row_blocks = ceil_div(a.L.npc, BM);
+    const int nsplit = choose_nsplit(row_blocks * a.d.C * a.L.S, ceil_div(a.d.N, BN));
+    dim3 grid((unsigned)(row_blocks * nsplit), (unsigned)a.d.C, (unsigned)a.L.S);
+    if (nsplit == 1) {
+        lp_scores_f16_kernel<DP><<<grid, kThreads, smem, stream>>>(tmQ, tmK, a, 0, 1);
+        GE2_LAUNCH_CHECK();
+    } else {
+        // dQ is reduced across the CTAs of a split: it starts from zero (dK next to it is zeroed by the caller already)
+        GE2_CUDA_TRY(cudaMemsetAsync(a.L.dQ, 0, (size_t)a.L.S * a.L.Bp * DP * sizeof(float), stream));
+        lp_scores_f16_kernel<DP><<<grid, kThreads, smem, stream>>>(tmQ, tmK, a, 1, nsplit);
+        GE2_LAUNCH_CHECK();
+        lp_scores_f16_kernel<DP><<<grid, kThreads, smem, stream>>>(tmQ, tmK, a, 2, nsplit);
+        GE2_LAUNCH_CHECK();
+    }
     return GE2_OK;
 }
 

@@ -153,6 +153,7 @@ __global__ void __launch_bounds__(256) lp_finish_kernel(LpKernelArgs a) {
     const int64_t e_rows = (int64_t)L.S * d.B;
     const int64_t total = e_rows + (int64_t)L.S * L.CN;
     const int D = d.D, h = D / 2, ld = L.ld;
+    const bool vec4 = (D % 4 == 0) && (((uintptr_t)d.node_grad | (uintptr_t)d.rel_grad | (uintptr_t)d.inv_rel_grad) & 15) == 0;
     for (int64_t w = ((int64_t)blockIdx.x * blockDim.x + threadIdx.x) >> 5; w < total; w += warps) {
         if (w < e_rows) {
             const int s = (int)(w / d.B);
@@ -177,25 +178,45 @@ __global__ void __launch_bounds__(256) lp_finish_kernel(LpKernelArgs a) {
             const float dpos = __expf(L.pos[qrow] - L.lse[qrow]) - 1.0f;  // d loss / d pos_i = softmax prob of the positive - 1
             float* ga = d.node_grad + aid * D;
             float* gb = d.node_grad + bid * D;
-            for (int k = lane; k < D; k += 32) {
-                atomicAdd(&gb[k], dpos * q[k]);
+            // per column k: contribution to the compared endpoint (gb), the relation-adjusted endpoint (ga) and the relation row (gr)
+            auto column = [&](int k, float& vb, float& va, float& vr) {
+                vb = dpos * q[k];
                 const float g = dq[k] + dpos * eb[k];  // d loss / d adjusted embedding
                 if (r == nullptr) {
-                    atomicAdd(&ga[k], g);
+                    va = g;
+                    vr = 0.f;
                 } else if (d.decoder == GE2_DECODER_DISTMULT) {
-                    atomicAdd(&ga[k], g * r[k]);
-                    atomicAdd(&rg[k], g * ea[k]);
+                    va = g * r[k];
+                    vr = g * ea[k];
                 } else {
                     // complex Hadamard backward: needs the gradient of the partner component too
                     const int kp = k < h ? k + h : k - h;
                     const float gp = dq[kp] + dpos * eb[kp];
                     if (k < h) {  // real component: g = g_re, gp = g_im
-                        atomicAdd(&ga[k], g * r[k] + gp * r[kp]);
-                        atomicAdd(&rg[k], g * ea[k] + gp * ea[kp]);
+                        va = g * r[k] + gp * r[kp];
+                        vr = g * ea[k] + gp * ea[kp];
                     } else {  // imaginary component: g = g_im, gp = g_re
-                        atomicAdd(&ga[k], -gp * r[k] + g * r[kp]);
-                        atomicAdd(&rg[k], -gp * ea[k] + g * ea[kp]);
+                        va = -gp * r[k] + g * r[kp];
+                        vr = -gp * ea[k] + g * ea[kp];
                     }
+                }
+            };
+            if (vec4) {  // 16-byte vector reductions: a quarter of the atomic operations
+                for (int k = lane * 4; k < D; k += 128) {
+                    float vb[4], va[4], vr[4];
+#pragma unroll
+                    for (int e = 0; e < 4; e++) column(k + e, vb[e], va[e], vr[e]);
+                    atomicAdd(reinterpret_cast<float4*>(gb + k), make_float4(vb[0], vb[1], vb[2], vb[3]));
+                    atomicAdd(reinterpret_cast<float4*>(ga + k), make_float4(va[0], va[1], va[2], va[3]));
+                    if (rg != nullptr) atomicAdd(reinterpret_cast<float4*>(rg + k), make_float4(vr[0], vr[1], vr[2], vr[3]));
+                }
+            } else {
+                for (int k = lane; k < D; k += 32) {
+                    float vb, va, vr;
+                    column(k, vb, va, vr);
+                    atomicAdd(&gb[k], vb);
+                    atomicAdd(&ga[k], va);
+                    if (rg != nullptr) atomicAdd(&rg[k], vr);
                 }
             }
         } else {
@@ -206,9 +227,16 @@ __global__ void __launch_bounds__(256) lp_finish_kernel(LpKernelArgs a) {
             if (id < 0 || id >= d.U) continue;
             const float* dk = L.dK + e * ld;
             float* g = d.node_grad + id * D;
-            for (int k = lane; k < D; k += 32) {
-                const float v = dk[k];
-                if (v != 0.f) atomicAdd(&g[k], v);
+            if (vec4) {
+                for (int k = lane * 4; k < D; k += 128) {
+                    const float4 v = *reinterpret_cast<const float4*>(dk + k);
+                    if (v.x != 0.f || v.y != 0.f || v.z != 0.f || v.w != 0.f) atomicAdd(reinterpret_cast<float4*>(g + k), v);
+                }
+            } else {
+                for (int k = lane; k < D; k += 32) {
+                    const float v = dk[k];
+                    if (v != 0.f) atomicAdd(&g[k], v);
+                }
             }
         }
     }

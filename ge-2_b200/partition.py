@@ -1,0 +1,236 @@
+"""Partition buffer across GPUs: schedule of partition-disjoint supersteps, bucket assignment, and partition swaps as
+NCCL send/recv (one process per GPU, torch.distributed for the plumbing).
+
+Mirrors, in the reference project (paths relative to gege/src/cpp/src): the partition buffer of
+storage/buffer.cpp and storage/storage.cpp:359-757 (MemPartitionBufferStorage, capacity 4, performNextSwap :576-689),
+the disjoint per-device states of data/ordering.cpp:1647-1670 / data/dataloader.cpp:709-844, and the relation-gradient
+exchange of nn/model.cpp:174-204.  Differences, on purpose:
+  * every partition has a home slab on one GPU (p % world), so a swap never touches host memory, also when
+    world * capacity < num_partitions (the reference's peer relay requires equality and otherwise stages through the host);
+  * an admitted partition is fetched from wherever it currently is -- another rank's active buffer (the reference's relay
+    copy) or its home -- and evicted partitions go home; all of it is one batch of NCCL point-to-point operations;
+  * the schedule is a round-robin design over pairs of partitions (every two partitions share a state at least once per
+    epoch, states of one superstep are disjoint); the reference's own ordering code can be plugged in instead, the buffer
+    only needs the list of states.
+"""
+from __future__ import annotations
+
+from dataclasses import dataclass, field
+from typing import Dict, List, Optional, Sequence, Tuple
+
+CAPACITY = 4  # buffer_capacity of the reference (buffer.cpp:950,1106; ordering.cpp:1753)
+
+
+# ----------------------------------------------------------------------------------------------------------------
+# schedule
+# ----------------------------------------------------------------------------------------------------------------
+def round_robin_states(num_partitions: int) -> List[List[List[int]]]:
+    """Rounds of pairwise-disjoint 4-partition states such that every two partitions meet in some state.
+
+    Partitions are paired into units (2k, 2k+1); a state is two units; the rounds are the 1-factorisation of the
+    complete graph on the units (circle method), so each round uses every partition exactly once.
+    Returns rounds[r][s] = sorted list of 4 partition ids.  num_partitions must be a multiple of 4."""
+    if num_partitions % 4 != 0 or num_partitions < 4:
+        raise ValueError("num_partitions must be a positive multiple of 4")
+    units = num_partitions // 2
+    if units == 2:
+        return [[[0, 1, 2, 3]]]
+    ids = list(range(units))
+    rounds = []
+    for _ in range(units - 1):
+        pairs = [(ids[k], ids[units - 1 - k]) for k in range(units // 2)]
+        rounds.append([sorted([2 * a, 2 * a + 1, 2 * b, 2 * b + 1]) for a, b in pairs])
+        ids = [ids[0]] + [ids[-1]] + ids[1:-1]
+    return rounds
+
+
+def make_supersteps(num_partitions: int, world: int) -> List[List[Optional[List[int]]]]:
+    """supersteps[k][rank] = state (4 partition ids) trained by `rank` in superstep k, or None when the lane idles.
+    States of one superstep are pairwise disjoint."""
+    out = []
+    for rnd in round_robin_states(num_partitions):
+        for i in range(0, len(rnd), world):
+            lane = rnd[i:i + world]
+            out.append(lane + [None] * (world - len(lane)))
+    return out
+
+
+def assign_buckets(supersteps, num_partitions: int) -> Dict[Tuple[int, int], Tuple[int, int]]:
+    """Every ordered bucket (src partition, dst partition) -> (superstep, rank) of the first state holding both,
+    the rule of the reference's greedy bucket assignment (ordering.cpp:1350-1370)."""
+    owner = {}
+    for k, lanes in enumerate(supersteps):
+        for rank, st in enumerate(lanes):
+            if st is None:
+                continue
+            for a in st:
+                for b in st:
+                    owner.setdefault((a, b), (k, rank))
+    missing = [(a, b) for a in range(num_partitions) for b in range(num_partitions) if (a, b) not in owner]
+    if missing:
+        raise ValueError(f"schedule does not cover buckets {missing[:4]}...")
+    return owner
+
+
+# ----------------------------------------------------------------------------------------------------------------
+# swap plan
+# ----------------------------------------------------------------------------------------------------------------
+@dataclass
+class Move:
+    partition: int
+    src_rank: int
+    src_kind: str  # "buf" | "home"
+    src_index: int  # buffer slot, or index into the rank's home list
+    dst_rank: int
+    dst_kind: str
+    dst_index: int
+
+
+@dataclass
+class Placement:
+    """Where every partition's current data lives, and what each rank's buffer slots hold."""
+    world: int
+    num_partitions: int
+    slots: List[List[int]] = field(default_factory=list)  # slots[rank][slot] = partition or -1
+    in_buffer: Dict[int, Tuple[int, int]] = field(default_factory=dict)  # partition -> (rank, slot)
+
+    @staticmethod
+    def initial(world: int, num_partitions: int) -> "Placement":
+        return Placement(world, num_partitions, [[-1] * CAPACITY for _ in range(world)], {})
+
+    def home_rank(self, p: int) -> int:
+        return p % self.world
+
+    def home_index(self, p: int) -> int:
+        return p // self.world
+
+
+def plan_swap(place: Placement, next_states: Sequence[Optional[Sequence[int]]]) -> Tuple[List[Move], List[List[int]]]:
+    """Moves that turn the current placement into `next_states` (one state per rank, None = keep the buffer as it is).
+
+    Like the relay branch of performNextSwap (storage.cpp:599-652) each admitted partition is copied from its current
+    holder; unlike it a partition that stays on its rank keeps its slot, and partitions nobody holds next go home.
+    Returns (moves, new slot tables).  Raises if two ranks claim one partition (states must be disjoint)."""
+    world = place.world
+    claimed = {}
+    for r, st in enumerate(next_states):
+        if st is None:
+            continue
+        if len(st) > CAPACITY or len(set(st)) != len(st):
+            raise ValueError("a state holds at most 4 distinct partitions")
+        for p in st:
+            if p in claimed:
+                raise ValueError(f"partition {p} claimed by ranks {claimed[p]} and {r}: states of a superstep must be disjoint")
+            claimed[p] = r
+    new_slots = [list(s) for s in place.slots]
+    moves: List[Move] = []
+    # 1. evictions: resident partitions that their rank does not keep
+    for r in range(world):
+        st = next_states[r]
+        keep = set(st) if st is not None else set(p for p in place.slots[r] if p >= 0)
+        for slot, p in enumerate(place.slots[r]):
+            if p >= 0 and p not in keep:
+                new_slots[r][slot] = -1
+                if p not in claimed:  # nobody needs it next: back to its home slab
+                    moves.append(Move(p, r, "buf", slot, place.home_rank(p), "home", place.home_index(p)))
+    # 2. admissions into free slots, lowest slot first, partitions in ascending order (deterministic on every rank)
+    for r in range(world):
+        st = next_states[r]
+        if st is None:
+            continue
+        have = set(p for p in new_slots[r] if p >= 0)
+        free = [k for k, p in enumerate(new_slots[r]) if p < 0]
+        for p in sorted(st):
+            if p in have:
+                continue
+            slot = free.pop(0)
+            new_slots[r][slot] = p
+            if p in place.in_buffer:
+                sr, ss = place.in_buffer[p]
+                moves.append(Move(p, sr, "buf", ss, r, "buf", slot))
+            else:
+                moves.append(Move(p, place.home_rank(p), "home", place.home_index(p), r, "buf", slot))
+    return moves, new_slots
+
+
+def apply_plan(place: Placement, new_slots: List[List[int]]) -> Placement:
+    inb = {p: (r, k) for r, row in enumerate(new_slots) for k, p in enumerate(row) if p >= 0}
+    return Placement(place.world, place.num_partitions, [list(s) for s in new_slots], inb)
+
+
+# ----------------------------------------------------------------------------------------------------------------
+# the buffer itself (one per rank)
+# ----------------------------------------------------------------------------------------------------------------
+class PartitionBuffer:
+    """Active buffer [4 * partition_rows, D] plus home slabs for the partitions this rank is home of, for one or more
+    tables moved together (embeddings and Adagrad state, graph_storage.h:247-281 of the reference moves both)."""
+
+    def __init__(self, tables_home: Sequence, partition_rows: int, num_partitions: int, rank: int, world: int, dist=None):
+        """tables_home[t]: tensor [n_home * partition_rows, D] with this rank's home partitions (p % world == rank, ascending).
+        dist: torch.distributed module (None for a single process)."""
+        import torch
+
+        self.rank, self.world, self.dist = rank, world, dist
+        self.rows = partition_rows
+        self.num_partitions = num_partitions
+        self.home = list(tables_home)
+        self.buf = [torch.empty((CAPACITY * partition_rows, t.shape[1]), dtype=t.dtype, device=t.device) for t in self.home]
+        self.staging = [torch.empty_like(b) for b in self.buf]
+        self.place = Placement.initial(world, num_partitions)
+
+    def _slab(self, kind: str, index: int, t: int, staged: bool = False):
+        base = (self.staging[t] if staged else self.buf[t]) if kind == "buf" else self.home[t]
+        return base[index * self.rows:(index + 1) * self.rows]
+
+    def swap(self, next_states: Sequence[Optional[Sequence[int]]], stream=None):
+        """Performs the swap for every rank's next state (all ranks call this with the same argument).
+        Local moves are device copies; moves between ranks are point-to-point sends/receives batched into one group.
+        Incoming slabs land in a staging buffer and are copied into place after all outgoing data has left, so a slot
+        can be overwritten by the partition that replaces it while its old content is still being sent."""
+        import torch
+
+        moves, new_slots = plan_swap(self.place, next_states)
+        ops, reqs, local, staged_in = [], [], [], []
+        for m in moves:  # same order on every rank: sends and receives pair up per peer in that order
+            for t in range(len(self.home)):
+                if m.src_rank == self.rank and m.dst_rank == self.rank:
+                    local.append((m, t))
+                elif m.src_rank == self.rank:
+                    ops.append(("send", self._slab(m.src_kind, m.src_index, t), m.dst_rank))
+                elif m.dst_rank == self.rank:
+                    dst = self._slab(m.dst_kind, m.dst_index, t, staged=m.dst_kind == "buf")
+                    ops.append(("recv", dst, m.src_rank))
+                    if m.dst_kind == "buf":
+                        staged_in.append((m, t))
+        # local moves out of the buffer read the old content: stage them too
+        for m, t in local:
+            if m.dst_kind == "buf":
+                self._slab("buf", m.dst_index, t, staged=True).copy_(self._slab(m.src_kind, m.src_index, t))
+                staged_in.append((m, t))
+        if ops:
+            d = self.dist
+            p2p = [d.P2POp(d.isend if kind == "send" else d.irecv, ten, peer) for kind, ten, peer in ops]
+            reqs = d.batch_isend_irecv(p2p)
+            for r in reqs:
+                r.wait()
+        for m, t in local:
+            if m.dst_kind == "home":
+                self._slab("home", m.dst_index, t).copy_(self._slab("buf", m.src_index, t))
+        for m, t in staged_in:
+            self._slab("buf", m.dst_index, t).copy_(self._slab("buf", m.dst_index, t, staged=True))
+        self.place = apply_plan(self.place, new_slots)
+        return moves
+
+    def flush(self):
+        """Sends every resident partition home (end of training / before evaluation), the counterpart of the reference's
+        unload(write=true)."""
+        return self.swap([[] for _ in range(self.world)])
+
+    def slot_table(self):
+        """partition -> slot of this rank's buffer (-1 when not resident): the map mapEdgesWithPartitionSlots_ indexes
+        (graph_storage.cpp:270-303 of the reference)."""
+        tab = [-1] * self.num_partitions
+        for slot, p in enumerate(self.place.slots[self.rank]):
+            if p >= 0:
+                tab[p] = slot
+        return tab

@@ -1,0 +1,120 @@
+"""Host logic of the partition buffer: schedule, bucket assignment, swap plans, and the swap protocol itself run as
+two gloo ranks on CPU (the NCCL path uses the same code with CUDA tensors)."""
+import importlib
+import os
+import sys
+
+import numpy as np
+import pytest
+import torch
+import torch.multiprocessing as mp
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+sys.path[:0] = [ROOT, os.path.join(ROOT, "oracle")]
+import ge2_oracle as O  # noqa: E402
+
+partition = importlib.import_module("ge-2_b200.partition")
+
+
+@pytest.mark.parametrize("P", [4, 8, 16, 32])
+def test_round_robin_covers_all_pairs(P):
+    rounds = partition.round_robin_states(P)
+    seen = set()
+    for rnd in rounds:
+        flat = [p for st in rnd for p in st]
+        assert sorted(flat) == list(range(P))  # a round uses every partition exactly once: its states are disjoint
+        for st in rnd:
+            assert len(st) == 4
+            seen |= {(a, b) for a in st for b in st}
+    assert len(seen) == P * P
+
+
+@pytest.mark.parametrize("P,world", [(16, 2), (16, 4), (32, 8), (8, 2)])
+def test_supersteps_and_bucket_assignment(P, world):
+    steps = partition.make_supersteps(P, world)
+    for lanes in steps:
+        used = [p for st in lanes if st is not None for p in st]
+        assert len(used) == len(set(used)) and len(lanes) == world
+    owner = partition.assign_buckets(steps, P)
+    assert len(owner) == P * P
+    for (a, b), (k, r) in owner.items():
+        assert a in steps[k][r] and b in steps[k][r]
+
+
+def test_plan_swap_matches_reference_relay_when_everything_is_resident():
+    """world * 4 == P: every admitted partition comes from the rank and slot that hold it now, which is the owner lookup
+    of the reference's relay (oracle.relay_swap_plan)."""
+    place = partition.Placement.initial(2, 8)
+    moves, slots = partition.plan_swap(place, [[0, 1, 2, 3], [4, 5, 6, 7]])
+    assert all(m.src_kind == "home" for m in moves) and slots == [[0, 1, 2, 3], [4, 5, 6, 7]]
+    place = partition.apply_plan(place, slots)
+    nxt = [[0, 1, 4, 5], [2, 3, 6, 7]]
+    moves, slots2 = partition.plan_swap(place, nxt)
+    ref = O.relay_swap_plan(slots, [sorted(s) for s in nxt])
+    ref_src = {p: (sd, ss) for lanes in ref for (_slot, p, sd, ss) in lanes}
+    for m in moves:
+        assert m.src_kind == "buf" and (m.src_rank, m.src_index) == ref_src[m.partition]
+    assert sorted(slots2[0]) == [0, 1, 4, 5] and slots2[0][:2] == [0, 1]  # partitions that stay keep their slot
+    with pytest.raises(ValueError):
+        partition.plan_swap(place, [[0, 1, 2, 3], [3, 5, 6, 7]])  # overlapping states
+
+
+def _worker(rank, world, P, rows, D, port, out):
+    import torch.distributed as dist
+
+    os.environ["MASTER_ADDR"], os.environ["MASTER_PORT"] = "127.0.0.1", str(port)
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    try:
+        home_parts = [p for p in range(P) if p % world == rank]
+        emb = torch.cat([torch.full((rows, D), float(p * 100)) + torch.arange(rows).view(-1, 1) for p in home_parts])
+        state = emb * 0.5
+        buf = partition.PartitionBuffer([emb, state], rows, P, rank, world, dist)
+        steps = partition.make_supersteps(P, world)
+        for k, lanes in enumerate(steps):
+            buf.swap(lanes)
+            st = lanes[rank]
+            if st is not None:
+                tab = buf.slot_table()
+                for p in st:  # "training": a partition- and superstep-specific update of the resident rows
+                    s = tab[p]
+                    assert s >= 0
+                    buf.buf[0][s * rows:(s + 1) * rows] += (k + 1) * 0.25 + p
+                    buf.buf[1][s * rows:(s + 1) * rows] += 1.0
+            dist.barrier()
+        buf.flush()
+        out.put((rank, emb.numpy().copy(), state.numpy().copy()))
+    finally:
+        dist.destroy_process_group()
+
+
+@pytest.mark.parametrize("P,world", [(8, 2), (16, 2)])
+def test_swap_protocol_two_gloo_ranks(P, world):
+    rows, D = 3, 2
+    ctx = mp.get_context("spawn")
+    out = ctx.Queue()
+    port = 29500 + (os.getpid() % 500) + P
+    procs = [ctx.Process(target=_worker, args=(r, world, P, rows, D, port, out)) for r in range(world)]
+    for p in procs:
+        p.start()
+    got = {}
+    for _ in range(world):
+        r, e, s = out.get(timeout=120)
+        got[r] = (e, s)
+    for p in procs:
+        p.join(timeout=60)
+        assert p.exitcode == 0
+    # single-process expectation
+    steps = partition.make_supersteps(P, world)
+    exp_e = {p: np.full((rows, D), p * 100.0, np.float32) + np.arange(rows, dtype=np.float32)[:, None] for p in range(P)}
+    exp_s = {p: exp_e[p] * 0.5 for p in range(P)}
+    for k, lanes in enumerate(steps):
+        for st in lanes:
+            if st is None:
+                continue
+            for p in st:
+                exp_e[p] = exp_e[p] + ((k + 1) * 0.25 + p)
+                exp_s[p] = exp_s[p] + 1.0
+    for r in range(world):
+        parts = [p for p in range(P) if p % world == r]
+        assert np.array_equal(got[r][0], np.concatenate([exp_e[p] for p in parts]))
+        assert np.array_equal(got[r][1], np.concatenate([exp_s[p] for p in parts]))
