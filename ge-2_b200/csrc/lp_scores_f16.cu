@@ -2,13 +2,14 @@
 // of TF32) with fp32 accumulators in tensor memory, operands staged in shared memory by TMA (plain tiled loads, no
 // multicast).  The 1e-2-parity path; everything outside the three contractions stays fp32.
 //
-// One CTA = (side, chunk, 128-row block).  Shared memory holds the query block Q [128 x DP], a ring of tiles of
+// One CTA = (side, chunk, 128-row block) -- or, when the grid would otherwise leave SMs idle in its last round, a share of
+// that block's tiles (see choose_nsplit).  Shared memory holds the query block Q [128 x DP], a ring of three tiles of
 // negatives K [128 x DP] and two tiles of probabilities P [128 x 128] as fp16, all in the 128-byte-swizzled layout TMA
 // writes (64-element column blocks of 128 rows at a 128-byte pitch).  That one layout serves every contraction, because
 // a block read along its rows is a K-major operand and read along its columns an MN-major operand:
-//   S  [row, n] = Q  K^T   A = Q  (K-major, k = d)    B = K (K-major, k = d)      -> TMEM columns [0, 256), two buffers
-//   dQ [row, d] += P  K    A = P  (K-major, k = n)    B = K (MN-major, k = n)     -> TMEM columns [256, 256 + DP)
-//   dK [n, d]   = P^T Q    A = P  (MN-major, k = row) B = Q (MN-major, k = row)   -> TMEM columns [384, 384 + DP)
+//   S  [row, n] = Q  K^T   A = Q  (K-major, k = d)    B = K (K-major, k = d)      -> TMEM columns [0, 128)
+//   dQ [row, d] += P  K    A = P  (K-major, k = n)    B = K (MN-major, k = n)     -> TMEM columns [128, 128 + DP)
+//   dK [n, d]   = P^T Q    A = P  (MN-major, k = row) B = Q (MN-major, k = row)   -> TMEM columns [256, ..) and [384, ..), alternating
 // (32-bit tf32 operands cannot do this: the hardware transposes them only from a different, 32-byte-atom swizzle, so
 // every tile would be needed twice and the set no longer fits in shared memory.)
 // The chunk's negatives stream past the query block twice: sweep 1 runs the first contraction alone to get each row's
@@ -18,12 +19,15 @@
 // cpp/src/nn/loss.cpp:46-63 of the reference project).
 //
 // Warp roles, connected by mbarrier pipelines (no block-wide barrier inside the loops):
-//   warps 0-3  softmax: one accumulator row per thread (TMEM lane = thread); S -> running max/sum, later S -> P
-//   warps 4-7  drain:   dK accumulator -> vector reductions into global dK; at the end dQ accumulator -> global dQ
-//   warp  8    lane 0:  TMA producer for the K ring (and the one-off Q load)
-//   warp  9    lane 0:  MMA issuer; the warp also allocates and frees tensor memory
+//   warps 0-7   softmax: thread = accumulator row (TMEM lane), warps 0-3 columns [0,64) and 4-7 columns [64,128) of a tile;
+//               S -> registers (the S accumulator is handed back at once) -> running max/sum in the exp2 domain, later -> P
+//   warps 8-11  drain: dK accumulator -> swizzled staging in shared memory -> one TMA reduce-add per 32 x 32 slab into
+//               global dK (row blocks of a chunk add up there); at the end dQ accumulator -> global dQ
+//   warp  12    lane 0: TMA producer for the K ring (and the one-off Q load)
+//   warp  13    lane 0: MMA issuer; the warp also allocates and frees tensor memory
 // The MMA issuer runs the score contraction of tile i+1 before the gradient contractions of tile i, so the tensor
-// pipe has work while the softmax warps turn S(i) into P(i).
+// pipe has work while the softmax warps turn S(i) into P(i); with two dK accumulators the drain of tile i overlaps the
+// contractions of tile i+1.
 // Every mbarrier wait is bounded; a wait that runs out raises GE2_STATUS_PIPE_TIMEOUT and sets a block-wide abort flag
 // that every other wait polls, so all roles fall through to the common exit where tensor memory is released.
 #include <stdlib.h>
@@ -38,8 +42,8 @@ using namespace tc;
 
 constexpr int BM = 128;                 // query rows per CTA  (MMA M)
 constexpr int BN = 128;                 // negatives per tile  (MMA N of the score contraction)
-constexpr int kThreads = 320;           // 4 softmax warps + 4 drain warps + TMA warp + MMA warp
-constexpr int kTmaWarp = 8, kMmaWarp = 9;
+constexpr int kThreads = 448;           // 8 softmax warps + 4 drain warps + TMA warp + MMA warp
+constexpr int kDrainWarp0 = 8, kTmaWarp = 12, kMmaWarp = 13;
 constexpr int kBlockBytes = 128 * 128;  // one 64-half column block of 128 rows
 constexpr int kMmaK = 16;               // k extent of one kind::f16 MMA (32 bytes)
 constexpr int kStagesK = 3;             // K ring depth
@@ -47,8 +51,9 @@ constexpr uint32_t kTmemCols = 512;
 constexpr float kMasked = -1e9f;
 
 // mbarrier slots
-enum Bar { kBarQ = 0, kBarKFull = 1, kBarKEmpty = kBarKFull + kStagesK, kBarSFull = kBarKEmpty + kStagesK, kBarSEmpty = kBarSFull + 2,
-           kBarPFull = kBarSEmpty + 2, kBarPEmpty = kBarPFull + 2, kBarDkFull = kBarPEmpty + 2, kBarDkEmpty, kBarDqFull, kNumBars };
+enum Bar { kBarQ = 0, kBarKFull = 1, kBarKEmpty = kBarKFull + kStagesK, kBarSFull = kBarKEmpty + kStagesK, kBarSEmpty = kBarSFull + 1,
+           kBarPFull = kBarSEmpty + 1, kBarPEmpty = kBarPFull + 2, kBarDkFull = kBarPEmpty + 2, kBarDkEmpty = kBarDkFull + 2, kBarDqFull = kBarDkEmpty + 2,
+           kBarXch, kNumBars };
 
 template <int DP>
 struct Layout {
@@ -61,18 +66,24 @@ struct Layout {
     static constexpr int kBars = kP + 2 * kPBytes;
     static constexpr int kTmem = kBars + kNumBars * 8;           // tensor memory base address
     static constexpr int kAbort = kTmem + 4;
-    static constexpr int kEnd = kAbort + 4;
+    // 4 drain warps x 2 buffers x (32 rows x 128 bytes): staging for the TMA reductions of dK, 128-byte swizzled.
+    // The half-row (max, sum) exchange at the end of sweep 1 (2 x 128 float2) borrows the same bytes: no drain runs before sweep 2.
+    static constexpr int kDrain = ((kAbort + 4 + 1023) / 1024) * 1024;
+    static constexpr int kXch = kDrain;
+    static constexpr int kEnd = kDrain + 4 * 2 * 4096;
     // 1024 bytes of slack to align the base; at least 120 KB so that one CTA owns the SM and its tensor memory
     static constexpr int kDynamic = (kEnd + 1024) > 120 * 1024 ? (kEnd + 1024) : 120 * 1024;
 };
 
+// Descriptors are built once per tile; a k-step only adds its byte offset (>> 4) to the start-address field, which cannot
+// carry out of the field because shared-memory addresses stay below 256 KB.
 // K-major operand: k-step `ks` (16 halves = 32 bytes) sits in column block ks/4 at byte (ks%4)*32; 8-row groups are 1024 bytes apart
-__device__ __forceinline__ uint64_t desc_kmajor(uint32_t tile, int ks) {
-    return smem_desc_sw128(tile + (ks >> 2) * kBlockBytes + (ks & 3) * 32, 16, 1024);
-}
+__device__ __forceinline__ uint64_t desc_kmajor_base(uint32_t tile) { return smem_desc_sw128(tile, 16, 1024); }
+__host__ __device__ constexpr uint64_t koff_kmajor(int ks) { return (uint64_t)(((ks >> 2) * kBlockBytes + (ks & 3) * 32) >> 4); }
 // MN-major operand: k-step `ks` is rows [16 ks, 16 ks + 16) = two 8-row groups of 1024 bytes; the 64-element MN blocks are
 // kBlockBytes apart
-__device__ __forceinline__ uint64_t desc_mnmajor(uint32_t tile, int ks) { return smem_desc_sw128(tile + ks * 2048, kBlockBytes, 1024); }
+__device__ __forceinline__ uint64_t desc_mnmajor_base(uint32_t tile) { return smem_desc_sw128(tile, kBlockBytes, 1024); }
+__host__ __device__ constexpr uint64_t koff_mnmajor(int ks) { return (uint64_t)((ks * 2048) >> 4); }
 
 // byte offset of the 16-byte chunk holding halves [col, col + 8) of row `row` in the swizzled block layout (col % 8 == 0)
 __device__ __forceinline__ uint32_t swz_chunk_offset(int row, int col) {
@@ -109,6 +120,12 @@ __device__ __forceinline__ bool pipe_wait(uint64_t* bar, uint32_t parity, volati
 #ifdef GE2_TRACE
 // development aid (not compiled into the shipped library): clock stamps of CTA (0,0,0), read back by a debug export
 __device__ long long g_trace[4][64][8];
+__device__ unsigned long long g_cta_times[2048][2];
+__device__ __forceinline__ unsigned long long global_ns() {
+    unsigned long long t;
+    asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t));
+    return t;
+}
 #define TR(role, it, k)                                                                              \
     do {                                                                                             \
         if (blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0 && (it) < 64) g_trace[role][it][k] = clock64(); \
@@ -119,7 +136,8 @@ __device__ long long g_trace[4][64][8];
 
 template <int DP>
 __global__ void __launch_bounds__(kThreads, 1)
-    lp_scores_f16_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK, LpKernelArgs a, int mode, int nsplit) {
+    lp_scores_f16_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK, const __grid_constant__ CUtensorMap tmDK,
+                         LpKernelArgs a, int mode, int nsplit) {
     using LY = Layout<DP>;
     extern __shared__ unsigned char smem_raw[];
     unsigned char* smem = (unsigned char*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
@@ -146,9 +164,16 @@ __global__ void __launch_bounds__(kThreads, 1)
     // mode 2: sweep 2 only, starts from the partials.  Iteration i < nA is sweep 1 on local tile i, later ones sweep 2.
     const int nA = mode == 2 ? 0 : T_loc, nB = mode == 1 ? 0 : T_loc;
     const int n_iter = nA + nB;
-    auto tile_n0 = [&](int i) { return (split_h + nsplit * (i < nA ? i : i - nA)) * BN; };
+    // The row blocks of one chunk run side by side and all reduce into the same dK rows; each starts its sweeps at a
+    // different tile so that at any moment they touch different rows instead of queueing on the same L2 lines.
+    const int rot = (blockIdx.x / nsplit) % T_loc;
+    auto tile_n0 = [&](int i) { return (split_h + nsplit * (((i < nA ? i : i - nA) + rot) % T_loc)) * BN; };
     constexpr int NB = LY::NB;
 
+#ifdef GE2_TRACE
+    const int cta_lin = blockIdx.x + gridDim.x * (blockIdx.y + gridDim.y * blockIdx.z) + (mode == 2 ? 1024 : 0);
+    if (tid == 0 && cta_lin < 2048) g_cta_times[cta_lin][0] = global_ns();
+#endif
     if (tid == 0) {
         mbar_init(&bars[kBarQ], 1);
         for (int k = 0; k < kStagesK; k++) {
@@ -156,14 +181,15 @@ __global__ void __launch_bounds__(kThreads, 1)
             mbar_init(&bars[kBarKEmpty + k], 1);
         }
         for (int k = 0; k < 2; k++) {
-            mbar_init(&bars[kBarSFull + k], 1);
-            mbar_init(&bars[kBarSEmpty + k], 4);  // one arrival per softmax warp
-            mbar_init(&bars[kBarPFull + k], 4);
+            mbar_init(&bars[kBarDkFull + k], 1);
+            mbar_init(&bars[kBarDkEmpty + k], 4);  // one arrival per drain warp
+            mbar_init(&bars[kBarPFull + k], 8);
             mbar_init(&bars[kBarPEmpty + k], 1);
         }
-        mbar_init(&bars[kBarDkFull], 1);
-        mbar_init(&bars[kBarDkEmpty], 4);  // one arrival per drain warp
+        mbar_init(&bars[kBarSFull], 1);
+        mbar_init(&bars[kBarSEmpty], 8);  // one arrival per softmax warp
         mbar_init(&bars[kBarDqFull], 1);
+        mbar_init(&bars[kBarXch], 8);  // the two halves of every row exchange their (max, sum) once, after sweep 1
         *s_abort = 0;
         mbar_init_fence();
     }
@@ -175,7 +201,9 @@ __global__ void __launch_bounds__(kThreads, 1)
     __syncthreads();
     tc_fence_after();
     const uint32_t tmem = *s_tmem;
-    const uint32_t tS = tmem, tdQ = tmem + 256, tdK = tmem + 384;
+    // tensor memory: S [0,128) (single buffer: the softmax warps copy it to registers at once and hand it back),
+    // dQ [128, 128+DP), two dK accumulators at 256 and 384 so the drain of tile t overlaps the contractions of tile t+1
+    const uint32_t tS = tmem, tdQ = tmem + 128, tdK = tmem + 256;
     const uint32_t lane_sel = (uint32_t)((warp & 3) * 32) << 16;  // this warp's quarter of the 128 TMEM lanes
     auto wait = [&](int bar, uint32_t parity) { return pipe_wait(&bars[bar], parity, s_abort, d.status); };
 
@@ -206,57 +234,63 @@ __global__ void __launch_bounds__(kThreads, 1)
             constexpr uint32_t kIdescDQ = idesc_f16(BM, DP, 0, 1);
             constexpr uint32_t kIdescDK = idesc_f16(BN, DP, 1, 1);
             bool ok = wait(kBarQ, 0);
+            const uint64_t dQk = desc_kmajor_base(aQ), dQm = desc_mnmajor_base(aQ);
             // gradient contractions of sweep-2 iteration j (tile t = j - T)
             auto issue_grad = [&](int j) -> bool {
                 const int t = j - nA, pb = t & 1, st = j % kStagesK;
                 if (!wait(kBarPFull + pb, (t >> 1) & 1)) return false;
                 TR(1, j, 4);
-                if (!wait(kBarDkEmpty, (t & 1) ^ 1)) return false;
+                if (!wait(kBarDkEmpty + (t & 1), ((t >> 1) & 1) ^ 1)) return false;
                 TR(1, j, 5);
                 tc_fence_after();
                 const uint32_t aK = aK0 + st * LY::kTileBytes, aP = aP0 + pb * LY::kPBytes;
+                const uint64_t dPk = desc_kmajor_base(aP), dPm = desc_mnmajor_base(aP), dKm = desc_mnmajor_base(aK);
 #pragma unroll
                 for (int ks = 0; ks < BN / kMmaK; ks++)  // dQ += P K, k runs over the tile's negatives
-                    mma_f16_ss(tdQ, desc_kmajor(aP, ks), desc_mnmajor(aK, ks), kIdescDQ, (t > 0 || ks > 0) ? 1u : 0u);
+                    mma_f16_ss(tdQ, dPk + koff_kmajor(ks), dKm + koff_mnmajor(ks), kIdescDQ, (t > 0 || ks > 0) ? 1u : 0u);
 #pragma unroll
                 for (int ks = 0; ks < BM / kMmaK; ks++)  // dK = P^T Q, k runs over the block's rows
-                    mma_f16_ss(tdK, desc_mnmajor(aP, ks), desc_mnmajor(aQ, ks), kIdescDK, ks > 0);
+                    mma_f16_ss(tdK + (t & 1) * 128, dPm + koff_mnmajor(ks), dQm + koff_mnmajor(ks), kIdescDK, ks > 0);
                 mma_commit(&bars[kBarKEmpty + st]);
                 mma_commit(&bars[kBarPEmpty + pb]);
-                mma_commit(&bars[kBarDkFull]);
+                mma_commit(&bars[kBarDkFull + (t & 1)]);
                 if (t == nB - 1) mma_commit(&bars[kBarDqFull]);
                 TR(1, j, 6);
                 return true;
             };
             for (int i = 0; ok && i < n_iter; i++) {
-                const int st = i % kStagesK, use = i / kStagesK, sb = i & 1;
+                const int st = i % kStagesK, use = i / kStagesK;
                 TR(1, i, 0);
                 if (!wait(kBarKFull + st, use & 1)) { ok = false; break; }
                 TR(1, i, 1);
-                if (!wait(kBarSEmpty + sb, ((i >> 1) & 1) ^ 1)) { ok = false; break; }
+                if (!wait(kBarSEmpty, (i & 1) ^ 1)) { ok = false; break; }
                 TR(1, i, 2);
                 tc_fence_after();
-                const uint32_t aK = aK0 + st * LY::kTileBytes;
+                const uint64_t dKk = desc_kmajor_base(aK0 + st * LY::kTileBytes);
 #pragma unroll
-                for (int ks = 0; ks < DP / kMmaK; ks++) mma_f16_ss(tS + sb * BN, desc_kmajor(aQ, ks), desc_kmajor(aK, ks), kIdescS, ks > 0);
-                mma_commit(&bars[kBarSFull + sb]);
+                for (int ks = 0; ks < DP / kMmaK; ks++) mma_f16_ss(tS, dQk + koff_kmajor(ks), dKk + koff_kmajor(ks), kIdescS, ks > 0);
+                mma_commit(&bars[kBarSFull]);
                 if (i < nA) mma_commit(&bars[kBarKEmpty + st]);  // sweep 1 needs the tile for nothing else
                 TR(1, i, 3);
                 if (i - 1 >= nA) ok = issue_grad(i - 1);
             }
             if (ok && nB > 0) issue_grad(n_iter - 1);
         }
-    } else if (warp < 4) {
-        // ================================ softmax warps ================================
-        const int my_row = tid;                      // accumulator row / TMEM lane
-        const int brow = c * L.npc + row0 + my_row;  // batch row in the padded numbering the filter uses
-        const int wrow0 = c * L.npc + row0 + warp * 32;  // first batch row of this warp
+    } else if (warp < kDrainWarp0) {
+        // ================================ softmax warps (0-7) ================================
+        // Two warps per scheduler so one computes while the other waits on tensor memory or a dependent chain: warps 0-3
+        // take columns [0, 64) of every tile, warps 4-7 columns [64, 128), both for rows 32*(warp & 3) ... + 31.
+        const int half = warp >> 2;                      // which 64 columns of a tile
+        const int my_row = tid & 127;                    // accumulator row / TMEM lane
+        const int brow = c * L.npc + row0 + my_row;      // batch row in the padded numbering the filter uses
+        const int wrow0 = c * L.npc + row0 + (warp & 3) * 32;  // first batch row of this warp
         const int32_t* maskc = L.mask + (int64_t)s * L.CN + (int64_t)c * d.N;
         float* dump = s == 0 ? d.neg_scores : d.inv_neg_scores;
         constexpr float kLog2e = 1.4426950408889634f;
+        const bool row_live = my_row < valid_rows;
         // running max / sum of exp2 in the base-2 domain (scores pre-multiplied by log2 e): one FFMA + one MUFU per score
         float run_m = -INFINITY, run_l = 0.f, lse2 = 0.f;
-        if (mode == 2 && my_row < valid_rows) {  // sweep 1 ran in an earlier launch: combine its partial (max, sum) pairs
+        if (mode == 2 && row_live) {  // sweep 1 ran in an earlier launch: combine its partial (max, sum) pairs
             float m = -INFINITY, l = 0.f;
             const float2* part = reinterpret_cast<const float2*>(L.part) + (grow0 + my_row) * 4;
             for (int k = 0; k < nsplit; k++) {
@@ -270,171 +304,181 @@ __global__ void __launch_bounds__(kThreads, 1)
             const float pos2 = L.pos[grow0 + my_row] * kLog2e;
             const float nm = fmaxf(m, pos2);
             lse2 = nm + __log2f(l * exp2f_fast(m - nm) + exp2f_fast(pos2 - nm));
-            if (split_h == 0) L.lse[grow0 + my_row] = lse2 * 0.6931471805599453f;
+            if (split_h == 0 && half == 0) L.lse[grow0 + my_row] = lse2 * 0.6931471805599453f;
         }
+        // The filter is sparse: a tile has at most one masked row per column and few of them fall in this warp's 32 rows.
+        // Lane l looks at columns l and l+32 of the warp's half tile; entries that name a row of this warp are handed to
+        // that row's thread, which ends up with one bit per masked column of its own row.  The words of the next tile are
+        // fetched while the current one is processed.
+        auto load_mask = [&](int i, int32_t (&m)[2]) {
+            if (i < n_iter) {
+                const int n0 = tile_n0(i);
+                const int vn = min(BN, d.N - n0);
+#pragma unroll
+                for (int k = 0; k < 2; k++) {
+                    const int idx = half * 64 + k * 32 + lane;
+                    m[k] = idx < vn ? __ldg(&maskc[n0 + idx]) : -1;
+                }
+            } else {
+                m[0] = m[1] = -1;
+            }
+        };
+        int32_t mnext[2];
+        load_mask(0, mnext);
         for (int i = 0; i < n_iter; i++) {
-            const int sb = i & 1;
             const int t = i < nA ? i : i - nA;  // local tile index within its sweep
             const int n0 = tile_n0(i);
-            const int valid_n = min(BN, d.N - n0);
-            // The filter is sparse: a tile has at most one masked row per column and few of them fall in this warp's 32
-            // rows.  Lane l looks at columns l, l+32, l+64, l+96; entries that name a row of this warp are handed to that
-            // row's thread, which ends up with one bit per masked column of its own row (mbits[k] bit j = column 32k+j).
-            uint32_t mbits[BN / 32];
+            const int nv = min(BN, d.N - n0) - half * 64;  // live columns among this warp's 64
+            const int32_t mcur[2] = {mnext[0], mnext[1]};
+            load_mask(i + 1, mnext);
+            uint32_t mb[2] = {0u, 0u};  // mb[k] bit j = column half*64 + 32k + j of this tile is masked for my row
 #pragma unroll
-            for (int k = 0; k < BN / 32; k++) {
-                const int idx = k * 32 + lane;
-                const int32_t m = idx < valid_n ? __ldg(&maskc[n0 + idx]) : -1;
-                unsigned ballot = __ballot_sync(0xffffffffu, (unsigned)(m - wrow0) < 32u);
-                mbits[k] = 0;
+            for (int k = 0; k < 2; k++) {
+                unsigned ballot = __ballot_sync(0xffffffffu, (unsigned)(mcur[k] - wrow0) < 32u);
                 while (ballot != 0) {
                     const int src = __ffs(ballot) - 1;
                     ballot &= ballot - 1;
-                    if (__shfl_sync(0xffffffffu, m, src) == brow) mbits[k] |= 1u << src;
+                    if (__shfl_sync(0xffffffffu, mcur[k], src) == brow) mb[k] |= 1u << src;
                 }
             }
+            const bool general = nv < 64 || dump != nullptr || __any_sync(0xffffffffu, (mb[0] | mb[1]) != 0u);
             if (tid == 0) TR(2, i, 0);
-            if (!__all_sync(0xffffffffu, wait(kBarSFull + sb, (i >> 1) & 1))) break;  // warp-uniform: tcgen05.ld is collective
+            if (!__all_sync(0xffffffffu, wait(kBarSFull, i & 1))) break;  // warp-uniform: tcgen05.ld is collective
             if (tid == 0) TR(2, i, 1);
             tc_fence_after();
-            const uint32_t tSb = tS + sb * BN + lane_sel;
+            float v[64];
+            tmem_ld_32x64(tS + half * 64 + lane_sel, v);
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(&bars[kBarSEmpty]);  // the tile is in registers: the S accumulator is free again
             if (i < nA) {
-#pragma unroll 1
-                for (int cb = 0; cb < BN / 32; cb++) {
-                    float v[32];
-                    tmem_ld_32x32(tSb + cb * 32, v);
-                    const int nv = valid_n - cb * 32;  // live columns of this 32-column slab
-                    if (nv <= 0) continue;
-                    const uint32_t mb = cb == 0 ? mbits[0] : cb == 1 ? mbits[1] : cb == 2 ? mbits[2] : mbits[3];
-                    const bool general = dump != nullptr || nv < 32 || __any_sync(0xffffffffu, mb != 0);
-                    if (!general) {
-                        float tmax = v[0];
+                if (nv > 0) {
+                    if (general) {
 #pragma unroll
-                        for (int j = 1; j < 32; j++) tmax = fmaxf(tmax, v[j]);
-                        const float nm = fmaxf(run_m, tmax * kLog2e);
-                        float add0 = 0.f, add1 = 0.f;
-#pragma unroll
-                        for (int j = 0; j < 32; j += 2) {
-                            add0 += exp2f_fast(fmaf(v[j], kLog2e, -nm));
-                            add1 += exp2f_fast(fmaf(v[j + 1], kLog2e, -nm));
+                        for (int j = 0; j < 64; j++) {
+                            float sc = ((mb[j >> 5] >> (j & 31)) & 1u) ? kMasked : v[j];
+                            if (dump != nullptr && row_live && j < nv) dump[(int64_t)brow * d.N + n0 + half * 64 + j] = sc;
+                            v[j] = j < nv ? sc : -INFINITY;
                         }
-                        run_l = fmaf(run_l, exp2f_fast(run_m - nm), add0 + add1);
-                        run_m = nm;
-                    } else {
-                        float tmax = -INFINITY;
-#pragma unroll
-                        for (int j = 0; j < 32; j++) {
-                            const int col = cb * 32 + j;
-                            float sc = v[j];
-                            sc = ((mb >> j) & 1u) ? kMasked : sc;
-                            if (dump != nullptr && my_row < valid_rows && col < valid_n) dump[(int64_t)brow * d.N + n0 + col] = sc;
-                            v[j] = j < nv ? sc * kLog2e : -INFINITY;
-                            tmax = fmaxf(tmax, v[j]);
-                        }
-                        const float nm = fmaxf(run_m, tmax);
-                        float add = 0.f;
-#pragma unroll
-                        for (int j = 0; j < 32; j++) add += exp2f_fast(v[j] - nm);  // 2^-inf = 0 for absent columns
-                        run_l = fmaf(run_l, exp2f_fast(run_m - nm), add);
-                        run_m = nm;
                     }
+                    float mx[8];
+#pragma unroll
+                    for (int k = 0; k < 8; k++) mx[k] = v[k];
+#pragma unroll
+                    for (int j = 8; j < 64; j++) mx[j & 7] = fmaxf(mx[j & 7], v[j]);
+                    const float tmax = fmaxf(fmaxf(fmaxf(mx[0], mx[1]), fmaxf(mx[2], mx[3])), fmaxf(fmaxf(mx[4], mx[5]), fmaxf(mx[6], mx[7])));
+                    const float nm = fmaxf(run_m, tmax * kLog2e);
+                    float add[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+                    for (int j = 0; j < 64; j++) add[j & 3] += exp2f_fast(fmaf(v[j], kLog2e, -nm));  // 2^-inf = 0 for absent columns
+                    run_l = fmaf(run_l, exp2f_fast(run_m - nm), (add[0] + add[1]) + (add[2] + add[3]));
+                    run_m = nm;
                 }
-                tc_fence_before();
-                __syncwarp();
-                if (lane == 0) mbar_arrive(&bars[kBarSEmpty + sb]);
                 if (tid == 0) TR(2, i, 3);
-                if (i == nA - 1 && my_row < valid_rows) {
-                    if (mode == 1) {  // hand the partial over to the sweep-2 launch
-                        reinterpret_cast<float2*>(L.part)[(grow0 + my_row) * 4 + split_h] = make_float2(run_m, run_l);
-                    } else {
-                        const float pos2 = L.pos[grow0 + my_row] * kLog2e;
-                        const float nm = fmaxf(run_m, pos2);
-                        lse2 = nm + __log2f(run_l * exp2f_fast(run_m - nm) + exp2f_fast(pos2 - nm));
-                        L.lse[grow0 + my_row] = lse2 * 0.6931471805599453f;
+                if (i == nA - 1) {
+                    // the two halves of a row meet in shared memory; the wait is an mbarrier (bounded), not a named barrier
+                    float2* xch = reinterpret_cast<float2*>(smem + LY::kXch);
+                    xch[half * 128 + my_row] = make_float2(run_m, run_l);
+                    __syncwarp();
+                    if (lane == 0) mbar_arrive(&bars[kBarXch]);  // used once per launch: 8 arrivals, one per softmax warp
+                    if (!__all_sync(0xffffffffu, wait(kBarXch, 0))) break;
+                    const float2 other = xch[(half ^ 1) * 128 + my_row];
+                    const float nm = fmaxf(run_m, other.x);
+                    float l = 0.f;
+                    if (nm > -INFINITY) l = run_l * exp2f_fast(run_m - nm) + other.y * exp2f_fast(other.x - nm);
+                    if (row_live) {
+                        if (mode == 1) {  // hand the partial over to the sweep-2 launch
+                            if (half == 0) reinterpret_cast<float2*>(L.part)[(grow0 + my_row) * 4 + split_h] = make_float2(nm, l);
+                        } else {
+                            const float pos2 = L.pos[grow0 + my_row] * kLog2e;
+                            const float nm2 = fmaxf(nm, pos2);
+                            lse2 = nm2 + __log2f(l * exp2f_fast(nm - nm2) + exp2f_fast(pos2 - nm2));
+                            if (half == 0) L.lse[grow0 + my_row] = lse2 * 0.6931471805599453f;
+                        }
                     }
                 }
             } else {
                 const int pb = t & 1;
+                // scores to probabilities first (registers only), so the wait for the P buffer overlaps with the arithmetic
+#pragma unroll
+                for (int j = 0; j < 64; j++) v[j] = exp2f_fast(fmaf(v[j], kLog2e, -lse2));
+                if (general || !row_live) {
+#pragma unroll
+                    for (int j = 0; j < 64; j++) {
+                        // masked entries were overwritten in place by the reference: no gradient reaches them
+                        const bool live = row_live && j < nv && ((mb[j >> 5] >> (j & 31)) & 1u) == 0u;
+                        v[j] = live ? v[j] : 0.f;
+                    }
+                }
                 // the gradient MMAs that read this P buffer two tiles ago must be done
                 if (!__all_sync(0xffffffffu, wait(kBarPEmpty + pb, ((t >> 1) & 1) ^ 1))) break;
                 if (tid == 0) TR(2, i, 2);
                 unsigned char* sPb = sP + pb * LY::kPBytes;
-                const bool row_live = my_row < valid_rows;
-#pragma unroll 1
-                for (int cb = 0; cb < BN / 32; cb++) {
-                    float v[32];
-                    tmem_ld_32x32(tSb + cb * 32, v);
-                    const int nv = valid_n - cb * 32;
-                    const uint32_t mb = cb == 0 ? mbits[0] : cb == 1 ? mbits[1] : cb == 2 ? mbits[2] : mbits[3];
-                    const bool general = nv < 32 || __any_sync(0xffffffffu, mb != 0);
-                    if (!general) {
 #pragma unroll
-                        for (int j = 0; j < 32; j++) v[j] = exp2f_fast(fmaf(v[j], kLog2e, -lse2));
-                        if (!row_live) {
-#pragma unroll
-                            for (int j = 0; j < 32; j++) v[j] = 0.f;
-                        }
-                    } else {
-#pragma unroll
-                        for (int j = 0; j < 32; j++) {
-                            // masked entries were overwritten in place by the reference: no gradient reaches them
-                            const bool live = row_live && j < nv && ((mb >> j) & 1u) == 0u;
-                            const float e = exp2f_fast(fmaf(v[j], kLog2e, -lse2));
-                            v[j] = live ? e : 0.f;
-                        }
-                    }
-#pragma unroll
-                    for (int q = 0; q < 4; q++) {  // 8 halves = one 16-byte chunk
-                        uint4 pk;
-                        pk.x = pack_half2(v[8 * q + 0], v[8 * q + 1]);
-                        pk.y = pack_half2(v[8 * q + 2], v[8 * q + 3]);
-                        pk.z = pack_half2(v[8 * q + 4], v[8 * q + 5]);
-                        pk.w = pack_half2(v[8 * q + 6], v[8 * q + 7]);
-                        *reinterpret_cast<uint4*>(sPb + swz_chunk_offset(my_row, cb * 32 + q * 8)) = pk;
-                    }
+                for (int q = 0; q < 8; q++) {  // 8 halves = one 16-byte chunk
+                    uint4 pk;
+                    pk.x = pack_half2(v[8 * q + 0], v[8 * q + 1]);
+                    pk.y = pack_half2(v[8 * q + 2], v[8 * q + 3]);
+                    pk.z = pack_half2(v[8 * q + 4], v[8 * q + 5]);
+                    pk.w = pack_half2(v[8 * q + 6], v[8 * q + 7]);
+                    *reinterpret_cast<uint4*>(sPb + swz_chunk_offset(my_row, half * 64 + q * 8)) = pk;
                 }
-                tc_fence_before();
                 fence_proxy_async_smem();  // P was written with ordinary stores; the MMA reads it through the async proxy
                 __syncwarp();
-                if (lane == 0) {
-                    mbar_arrive(&bars[kBarSEmpty + sb]);
-                    mbar_arrive(&bars[kBarPFull + pb]);
-                }
+                if (lane == 0) mbar_arrive(&bars[kBarPFull + pb]);
                 if (tid == 0) TR(2, i, 3);
             }
         }
     } else {
-        // ================================ drain warps (4-7) ================================
-        const int my_lane = tid - 128;  // TMEM lane: a negative of the tile for dK, a query row for dQ
+        // ================================ drain warps (8-11) ================================
+        const int my_lane = tid - kDrainWarp0 * 32;  // TMEM lane: a negative of the tile for dK, a query row for dQ
         float* dKc = L.dK + ((int64_t)s * L.CN + (int64_t)c * d.N) * DP;
         bool ok = true;
         for (int t = 0; t < nB; t++) {
             const int n0 = tile_n0(nA + t);
             const int valid_n = min(BN, d.N - n0);
-            if (tid == 128) TR(3, t, 0);
-            if (!__all_sync(0xffffffffu, wait(kBarDkFull, t & 1))) { ok = false; break; }
-            if (tid == 128) TR(3, t, 1);
+            if (tid == kDrainWarp0 * 32) TR(3, t, 0);
+            if (!__all_sync(0xffffffffu, wait(kBarDkFull + (t & 1), (t >> 1) & 1))) { ok = false; break; }
+            if (tid == kDrainWarp0 * 32) TR(3, t, 1);
             tc_fence_after();
-            float* dst = dKc + (int64_t)(n0 + my_lane) * DP;
+            // Each 32 x 32 slab of the accumulator goes through a per-warp staging buffer in shared memory (128-byte rows,
+            // 16-byte chunks XOR-swizzled by row: conflict-free stores, and the layout a SWIZZLE_128B tensor map expects) and
+            // from there to global dK as ONE TMA reduce-add per slab: the load/store units only see the shared-memory
+            // stores, rows past the chunk's last negative are clipped by the tensor map, and the accumulator is handed
+            // back as soon as its last slab is in registers.  Two staging buffers alternate, so a slab is written while
+            // the TMA engine still reads the previous one.
+            unsigned char* scr0 = smem + LY::kDrain + (warp - kDrainWarp0) * 8192;
 #pragma unroll 1
             for (int cb = 0; cb < DP / 32; cb++) {
                 float v[32];
-                tmem_ld_32x32(tdK + lane_sel + cb * 32, v);  // warp-collective: lanes past the tile's end take part too
-                if (cb == DP / 32 - 1) {  // accumulator fully read: hand it back before the slow part
+                if (tid == kDrainWarp0 * 32 && t == 1) TR(3, 32 + cb, 0);
+                tmem_ld_32x32(tdK + (t & 1) * 128 + lane_sel + cb * 32, v);  // warp-collective
+                if (tid == kDrainWarp0 * 32 && t == 1) TR(3, 32 + cb, 1);
+                if (cb == DP / 32 - 1) {
                     tc_fence_before();
                     __syncwarp();
-                    if (lane == 0) mbar_arrive(&bars[kBarDkEmpty]);
-                    if (tid == 128) TR(3, t, 2);
+                    if (lane == 0) mbar_arrive(&bars[kBarDkEmpty + (t & 1)]);
+                    if (tid == kDrainWarp0 * 32) TR(3, t, 2);
                 }
-                if (my_lane < valid_n) {
+                if (cb * 32 >= d.D) continue;  // padding columns only: nothing to add
+                unsigned char* scr = scr0 + (cb & 1) * 4096;
+                if (lane == 0) bulk_wait_group_read<1>();  // the reduction that last used this buffer (two slabs ago) has read it
+                __syncwarp();
 #pragma unroll
-                    for (int q = 0; q < 8; q++) {
-                        const int col = cb * 32 + q * 4;
-                        if (col < d.D) atomicAdd(reinterpret_cast<float4*>(dst + col), make_float4(v[4 * q], v[4 * q + 1], v[4 * q + 2], v[4 * q + 3]));
-                    }
+                for (int q = 0; q < 8; q++)
+                    *reinterpret_cast<float4*>(scr + lane * 128 + ((q ^ (lane & 7)) << 4)) = make_float4(v[4 * q], v[4 * q + 1], v[4 * q + 2], v[4 * q + 3]);
+                fence_proxy_async_smem();
+                __syncwarp();
+                if (tid == kDrainWarp0 * 32 && t == 1) TR(3, 32 + cb, 2);
+                if (lane == 0) {
+                    tma_reduce_add_3d(&tmDK, cb * 32, n0 + (warp - kDrainWarp0) * 32, zc, scr);
+                    bulk_commit_group();
                 }
+                if (tid == kDrainWarp0 * 32 && t == 1) TR(3, 32 + cb, 3);
             }
         }
+        if (lane == 0) bulk_wait_group<0>();  // all of this warp's reductions have landed before the CTA can exit
+        __syncwarp();
         if (ok && nB > 0 && __all_sync(0xffffffffu, wait(kBarDqFull, 0))) {
             tc_fence_after();
 #pragma unroll 1
@@ -469,6 +513,9 @@ __global__ void __launch_bounds__(kThreads, 1)
         tc_fence_after();
         tmem_dealloc(tmem, kTmemCols);
     }
+#ifdef GE2_TRACE
+    if (tid == 0 && cta_lin < 2048) g_cta_times[cta_lin][1] = global_ns();
+#endif
 }
 
 typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*, const cuuint32_t*,
@@ -526,6 +573,23 @@ int choose_nsplit(int items, int tiles) {
     return best;
 }
 
+// dK [S*C][N][ld floats] as a 3-D tensor for the reduce-add stores: box = 32 floats x 32 rows, 128-byte swizzle
+int make_map_f32_slab(CUtensorMap* map, float* base, int ld, int rows, int mats) {
+    EncodeTiledFn fn = encode_fn();
+    if (fn == nullptr) return GE2_ERR_CUDA;
+    cuuint64_t dims[3] = {(cuuint64_t)ld, (cuuint64_t)rows, (cuuint64_t)mats};
+    cuuint64_t strides[2] = {(cuuint64_t)ld * 4, (cuuint64_t)rows * ld * 4};
+    cuuint32_t box[3] = {32, 32, 1};
+    cuuint32_t estr[3] = {1, 1, 1};
+    CUresult r = fn(map, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 3, base, dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                    CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_NONE, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS) {
+        g_last_cuda_error = (int)r;
+        return GE2_ERR_CUDA;
+    }
+    return GE2_OK;
+}
+
 template <int DP>
 int launch(const LpKernelArgs& a, cudaStream_t stream) {
     if (a.L.Qh == nullptr || a.L.Kh == nullptr) return GE2_ERR_WORKSPACE;
@@ -534,20 +598,23 @@ int launch(const LpKernelArgs& a, cudaStream_t stream) {
     if (rc != GE2_OK) return rc;
     rc = make_map(&tmK, a.L.Kh, DP, a.d.N, a.L.S * a.d.C);
     if (rc != GE2_OK) return rc;
+    CUtensorMap tmDK;
+    rc = make_map_f32_slab(&tmDK, a.L.dK, DP, a.d.N, a.L.S * a.d.C);
+    if (rc != GE2_OK) return rc;
     const int smem = Layout<DP>::kDynamic;
     GE2_CUDA_TRY(cudaFuncSetAttribute(lp_scores_f16_kernel<DP>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
     const int row_blocks = ceil_div(a.L.npc, BM);
     const int nsplit = choose_nsplit(row_blocks * a.d.C * a.L.S, ceil_div(a.d.N, BN));
     dim3 grid((unsigned)(row_blocks * nsplit), (unsigned)a.d.C, (unsigned)a.L.S);
     if (nsplit == 1) {
-        lp_scores_f16_kernel<DP><<<grid, kThreads, smem, stream>>>(tmQ, tmK, a, 0, 1);
+        lp_scores_f16_kernel<DP><<<grid, kThreads, smem, stream>>>(tmQ, tmK, tmDK, a, 0, 1);
         GE2_LAUNCH_CHECK();
     } else {
         // dQ is reduced across the CTAs of a split: it starts from zero (dK next to it is zeroed by the caller already)
         GE2_CUDA_TRY(cudaMemsetAsync(a.L.dQ, 0, (size_t)a.L.S * a.L.Bp * DP * sizeof(float), stream));
-        lp_scores_f16_kernel<DP><<<grid, kThreads, smem, stream>>>(tmQ, tmK, a, 1, nsplit);
+        lp_scores_f16_kernel<DP><<<grid, kThreads, smem, stream>>>(tmQ, tmK, tmDK, a, 1, nsplit);
         GE2_LAUNCH_CHECK();
-        lp_scores_f16_kernel<DP><<<grid, kThreads, smem, stream>>>(tmQ, tmK, a, 2, nsplit);
+        lp_scores_f16_kernel<DP><<<grid, kThreads, smem, stream>>>(tmQ, tmK, tmDK, a, 2, nsplit);
         GE2_LAUNCH_CHECK();
     }
     return GE2_OK;
@@ -558,6 +625,9 @@ int launch(const LpKernelArgs& a, cudaStream_t stream) {
 #ifdef GE2_TRACE
 extern "C" __attribute__((visibility("default"))) int ge2_debug_read_trace(long long* host_out) {
     return (int)cudaMemcpyFromSymbol(host_out, g_trace, sizeof(long long) * 4 * 64 * 8);
+}
+extern "C" __attribute__((visibility("default"))) int ge2_debug_read_cta_times(unsigned long long* host_out) {
+    return (int)cudaMemcpyFromSymbol(host_out, g_cta_times, sizeof(unsigned long long) * 2048 * 2);
 }
 #endif
 
