@@ -221,6 +221,7 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--precision", default=os.environ.get("GE2_PRECISION", "fp32"), choices=["fp32", "f16"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--no-graph", action="store_true", help="issue every launch from the host instead of replaying a CUDA graph")
     ap.add_argument("--cpu-budget", type=float, default=15.0)
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3)
@@ -275,43 +276,66 @@ def main():
             dist.barrier()
         torch.cuda.synchronize()
 
-    def batch(i):
-        return edges[i * B:(i + 1) * B]
+    num_batches = n_edges // B
+    use_graph = world == 1 and not args.no_graph  # NCCL all-reduce stays outside graph capture in this build
 
-    # ---- device-resident timing (`value`) --------------------------------------------------------------------
+    # ---- warm-up, then an event-bracketed pass that times the scores kernel alone (roofline) ---------------------
     for i in range(W):
-        pipe.step(batch(i), i, rel_hook=rel_hook)
+        pipe.enqueue_resident(edges, num_batches, rel_hook=rel_hook)
     pipe.check_status()
     ev_pairs = [(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)) for _ in range(K)]
+    barrier()
+    for i in range(K):
+        pipe.enqueue_resident(edges, num_batches, scores_events=ev_pairs[i], rel_hook=rel_hook)
+    barrier()
+    scores_ms = float(np.mean([a.elapsed_time(b) for a, b in ev_pairs]))
+
+    # ---- device-resident timing (`value`): K steps, one CUDA-graph launch per step -----------------------------------
+    if use_graph:
+        graph = pipe.capture_resident(edges, num_batches)
+        for _ in range(W):
+            graph.replay()
     start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     clocks = ClockSampler(local_rank)
     barrier()
     clocks.start()
     start.record()
     for i in range(K):
-        pipe.step(batch(W + i), W + i, scores_events=ev_pairs[i], rel_hook=rel_hook)
+        if use_graph:
+            graph.replay()
+        else:
+            pipe.enqueue_resident(edges, num_batches, rel_hook=rel_hook)
     end.record()
     barrier()
     ms = start.elapsed_time(end)
-    scores_ms = float(np.mean([a.elapsed_time(b) for a, b in ev_pairs]))
     pipe.check_status()
 
     # ---- end-to-end timing (`e2e`): host edges in, loss out, through the same public step call -----------------
+    first = int(pipe.step_dev.item()) % num_batches
+    idx = (first + torch.arange(K)) % num_batches
     host_edges = torch.empty((K, B, 3), dtype=torch.int64).pin_memory()
-    host_edges.copy_(edges[W * B:(W + K) * B].reshape(K, B, 3).cpu())
+    host_edges.copy_(edges.reshape(num_batches, B, 3)[idx.to(device)].cpu())
     host_loss = torch.zeros(K, dtype=torch.float32).pin_memory()
     stage = torch.empty((B, 3), dtype=torch.int64, device=device)
-    for i in range(min(W, K)):
+    stage.copy_(host_edges[0])
+    if use_graph:
+        graph_e2e = pipe.capture_resident(stage, 1)
+
+    def e2e_step(i):
         stage.copy_(host_edges[i], non_blocking=True)
-        pipe.step(stage, 10_000 + i, rel_hook=rel_hook)
+        if use_graph:
+            graph_e2e.replay()
+        else:
+            pipe.enqueue_resident(stage, 1, rel_hook=rel_hook)
         host_loss[i:i + 1].copy_(pipe.loss, non_blocking=True)
+
+    for i in range(min(W, K)):
+        e2e_step(i)
     s2, e2 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     barrier()
     s2.record()
     for i in range(K):
-        stage.copy_(host_edges[i], non_blocking=True)
-        pipe.step(stage, 20_000 + i, rel_hook=rel_hook)
-        host_loss[i:i + 1].copy_(pipe.loss, non_blocking=True)
+        e2e_step(i)
     e2.record()
     barrier()
     ms_e2e = s2.elapsed_time(e2)
@@ -334,14 +358,16 @@ def main():
             ms_per_step=ms / K, higher_is_better=True, scaling="weak", vs_baseline=None,
             dtype="f32" if args.precision == "fp32" else "f16 tensor tiles, f32 accumulate and storage", data="synthetic",
             config=dict(workload=cfg["name"], per_gpu_batch=B, global_batch=B * world, precision=args.precision,
-                        l2="tables (0.8 GB) and edge list larger than L2; rows touched per step are random", parallelism=f"dp{world}" if world > 1 else "single"),
+                        l2="tables (0.8 GB) and edge list larger than L2; rows touched per step are random", parallelism=f"dp{world}" if world > 1 else "single",
+                        launch="one CUDA graph replay per step" if use_graph else "host-issued launches"),
             e2e=dict(value=world * K * B / (ms_e2e * 1e-3), unit="edges/s", h2d_bytes_per_step=B * 3 * 8, d2h_bytes_per_step=4,
                      note="pinned host edges -> H2D, step, loss -> pinned host, all stream-ordered; one synchronize at the end"),
-            gpu_launches=K * pipe.launches_per_step(),
+            gpu_launches=K * (pipe.launches_per_step() + 1),
             clocks=clock_info,
             roofline=dict(bound="tensor", kernel="lp_scores_%s" % args.precision, achieved=achieved, peak=pk["tf"], unit="TFLOP/s",
                           frac=achieved / pk["tf"], traffic=None, peak_source=pk["src"] + " bf16 dense",
-                          ms_per_launch=scores_ms, flops_per_launch=flops),
+                          ms_per_launch=scores_ms, flops_per_launch=flops,
+                          timing="CUDA events around the scores launch(es) in an event-bracketed pass of the same K steps"),
         )
         if world == 1 and not args.no_cpu_baseline:
             cpu = CpuReference(cfg, 20262)

@@ -21,7 +21,7 @@ EXPORTS = [
     "ge2_version", "ge2_last_cuda_error", "ge2_status_string", "ge2_check_device", "ge2_unique_workspace_bytes",
     "ge2_unique_bitmap", "ge2_pack_ids", "ge2_lp_workspace_bytes", "ge2_lp_step", "ge2_sparse_adagrad", "ge2_index_read",
     "ge2_index_add", "ge2_adagrad_scatter", "ge2_dense_adagrad", "ge2_sample_negatives", "ge2_remap_edges_to_slots",
-    "ge2_copy_slabs", "ge2_unique_bitmap_static",
+    "ge2_copy_slabs", "ge2_unique_bitmap_static", "ge2_sample_batch", "ge2_advance_step",
 ]
 
 
@@ -80,6 +80,9 @@ def load_library():
     lib.ge2_dense_adagrad.argtypes = [C.c_void_p, C.c_void_p, C.c_void_p, C.c_int64, C.c_float, C.c_float, C.c_float, C.c_int32, C.c_void_p]
     lib.ge2_sample_negatives.argtypes = [C.c_void_p, C.c_void_p, C.c_int64, C.c_int32, C.c_int32, C.c_int32, C.c_int32, C.c_int64, C.c_int32,
                                          C.c_uint64, C.c_uint64, C.c_void_p, C.c_void_p, C.c_void_p]
+    lib.ge2_sample_batch.argtypes = [C.c_void_p, C.c_int32, C.c_int64, C.c_void_p, C.c_int32, C.c_int32, C.c_int32, C.c_int32, C.c_int64, C.c_int32,
+                                     C.c_uint64, C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p]
+    lib.ge2_advance_step.argtypes = [C.c_void_p, C.c_void_p]
     lib.ge2_remap_edges_to_slots.argtypes = [C.c_void_p, C.c_int64, C.c_int32, C.c_void_p, C.c_int32, C.c_int64, C.c_void_p, C.c_void_p, C.c_void_p]
     lib.ge2_copy_slabs.argtypes = [C.c_void_p, C.c_void_p, C.POINTER(C.c_int32), C.c_int32, C.c_int64, C.c_void_p]
     lib.ge2_check_device.argtypes = [C.c_int]
@@ -235,6 +238,15 @@ def dense_adagrad(param, sum_state, grad, lr: float, eps: float = 1e-10, grad_sc
 def sample_negatives(src_ids, dst_ids, edge_stride, B, Cn, N, n_deg, domain, want_src, seed, batch_index, out_packed, out_deg_rows):
     check(load_library().ge2_sample_negatives(ptr(src_ids), ptr(dst_ids), edge_stride, B, Cn, N, n_deg, domain, 1 if want_src else 0, seed,
                                               batch_index, ptr(out_packed), ptr(out_deg_rows), cur_stream()), "ge2_sample_negatives")
+
+
+def sample_batch(edges, num_batches, step_dev, B, Cn, N, n_deg, domain, want_src, seed, out_packed, out_deg_rows, out_rel):
+    check(load_library().ge2_sample_batch(ptr(edges), edges.shape[1], num_batches, ptr(step_dev), B, Cn, N, n_deg, domain, 1 if want_src else 0,
+                                          seed, ptr(out_packed), ptr(out_deg_rows), ptr(out_rel), cur_stream()), "ge2_sample_batch")
+
+
+def advance_step(step_dev):
+    check(load_library().ge2_advance_step(ptr(step_dev), cur_stream()), "ge2_advance_step")
 
 
 def remap_edges_to_slots(edges, partition_to_slot, partition_size, out=None, status=None):

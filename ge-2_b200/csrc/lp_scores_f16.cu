@@ -1,6 +1,6 @@
 // Tensor-core scores kernel of the link-prediction step: tcgen05.mma kind::f16 (fp16 operands, the 11-bit significand
-// of TF32) with fp32 accumulators in tensor memory, operands staged in shared memory by TMA (plain tiled loads, no
-// multicast).  The 1e-2-parity path; everything outside the three contractions stays fp32.
+// of TF32) with fp32 accumulators in tensor memory, operands staged in shared memory by TMA (every CTA issues its own plain tiled
+// loads).  The 1e-2-parity path; everything outside the three contractions stays fp32.
 //
 // One CTA = (side, chunk, 128-row block) -- or, when the grid would otherwise leave SMs idle in its last round, a share of
 // that block's tiles (see choose_nsplit).  Shared memory holds the query block Q [128 x DP], a ring of three tiles of
@@ -552,24 +552,18 @@ int make_map(CUtensorMap* map, __half* base, int ld, int rows, int mats) {
     return GE2_OK;
 }
 
-// How many CTAs share one (side, chunk, row block): work items are indivisible, so 160 items on 148 SMs cost two full
-// rounds; dealing each item's tiles to 2 or 4 CTAs (sweep 1 and sweep 2 then run as two launches) shortens the tail at the
-// price of a fixed per-CTA overhead (Q load, barrier and tensor-memory set-up), taken as 12 % of a whole item here.
+// How many CTAs share one (side, chunk, row block).  A small batch has fewer such blocks than the GPU has SMs; dealing
+// each block's tiles to 2 or 4 CTAs (sweep 1 and sweep 2 then run as two launches) fills the machine.  Once the grid
+// covers every SM, splitting only adds per-CTA set-up (Q load, barriers, tensor memory) and a second launch -- measured
+// on B200: 160 blocks take 85 us unsplit, 90 us split in two -- so the largest split that still fits one round is used.
 int choose_nsplit(int items, int tiles) {
     if (const char* e = getenv("GE2_F16_NSPLIT")) {
         const int v = atoi(e);
         if ((v == 1 || v == 2 || v == 4) && v <= tiles) return v;
     }
     int best = 1;
-    double best_cost = 1e30;
-    for (int ns = 1; ns <= 4 && ns <= tiles; ns *= 2) {
-        const double rounds = (double)((items * ns + kNumSMs - 1) / kNumSMs);
-        const double cost = rounds * (1.0 / ns + 0.12) + (ns > 1 ? 0.1 : 0.0);
-        if (cost < best_cost) {
-            best_cost = cost;
-            best = ns;
-        }
-    }
+    for (int ns = 2; ns <= 4 && ns <= tiles; ns *= 2)
+        if (items * ns <= kNumSMs) best = ns;
     return best;
 }
 

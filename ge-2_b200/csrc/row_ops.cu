@@ -220,7 +220,18 @@ __device__ __forceinline__ uint64_t splitmix64(uint64_t x) {
 __global__ void __launch_bounds__(256) sample_negatives_kernel(const int64_t* __restrict__ src_ids, const int64_t* __restrict__ dst_ids,
                                                                int64_t edge_stride, int B, int C, int N, int n_deg, int64_t domain,
                                                                int want_src, uint64_t key, int64_t* __restrict__ packed,
-                                                               int64_t* __restrict__ deg_rows) {
+                                                               int64_t* __restrict__ deg_rows, const uint64_t* __restrict__ step_dev,
+                                                               int64_t num_batches, const int64_t* __restrict__ rel_ids,
+                                                               int64_t* __restrict__ out_rel) {
+    // graph-replay form: the batch index lives on the device, so the same launch serves every batch of the epoch
+    if (step_dev != nullptr) {
+        const uint64_t step = *step_dev;
+        const int64_t off = (int64_t)(step % (uint64_t)num_batches) * B * edge_stride;
+        src_ids += off;
+        dst_ids += off;
+        if (rel_ids != nullptr) rel_ids += off;
+        key += step * 0x9E3779B97F4A7C15ull;
+    }
     const int64_t CN = (int64_t)C * N;
     const int64_t total = 2 * (int64_t)B + CN;
     int64_t* out_src_neg = packed + 2 * (int64_t)B;
@@ -229,6 +240,7 @@ __global__ void __launch_bounds__(256) sample_negatives_kernel(const int64_t* __
     for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += stride) {
         if (i < B) {
             packed[i] = src_ids[i * edge_stride];
+            if (out_rel != nullptr) out_rel[i] = rel_ids[i * edge_stride];
         } else if (i < 2 * (int64_t)B) {
             packed[i] = dst_ids[(i - B) * edge_stride];
         } else {
@@ -338,7 +350,33 @@ extern "C" int ge2_sample_negatives(const int64_t* src_ids, const int64_t* dst_i
     const int64_t total = 2 * (int64_t)B + (int64_t)C * N;
     const uint64_t key = seed * 0xD1342543DE82EF95ull + batch_index * 0x9E3779B97F4A7C15ull + 0x632BE59BD9B4E019ull;
     sample_negatives_kernel<<<stream_grid(total, 256), 256, 0, as_stream(stream_)>>>(src_ids, dst_ids, edge_stride, B, C, N, n_deg, domain,
-                                                                                   want_src_negs, key, out_packed_ids, out_deg_rows);
+                                                                                   want_src_negs, key, out_packed_ids, out_deg_rows, nullptr, 1,
+                                                                                   nullptr, nullptr);
+    GE2_LAUNCH_CHECK();
+    return GE2_OK;
+}
+
+extern "C" int ge2_sample_batch(const int64_t* edges, int32_t cols, int64_t num_batches, const uint64_t* step_dev, int32_t B, int32_t C,
+                                int32_t N, int32_t n_deg, int64_t domain, int32_t want_src_negs, uint64_t seed, int64_t* out_packed_ids,
+                                int64_t* out_deg_rows, int64_t* out_rel_ids, ge2_stream_t stream_) {
+    if (B <= 0 || C <= 0 || N <= 0 || n_deg < 0 || n_deg > N || domain <= 0 || num_batches <= 0 || (cols != 2 && cols != 3))
+        return GE2_ERR_INVALID_ARGUMENT;
+    if (edges == nullptr || step_dev == nullptr || out_packed_ids == nullptr) return GE2_ERR_INVALID_ARGUMENT;
+    if ((n_deg > 0 && out_deg_rows == nullptr) || (cols == 3 && out_rel_ids == nullptr)) return GE2_ERR_INVALID_ARGUMENT;
+    const int64_t total = 2 * (int64_t)B + (int64_t)C * N;
+    const uint64_t key = seed * 0xD1342543DE82EF95ull + 0x632BE59BD9B4E019ull;
+    sample_negatives_kernel<<<stream_grid(total, 256), 256, 0, as_stream(stream_)>>>(
+        edges, edges + cols - 1, cols, B, C, N, n_deg, domain, want_src_negs, key, out_packed_ids, out_deg_rows, step_dev, num_batches,
+        cols == 3 ? edges + 1 : nullptr, cols == 3 ? out_rel_ids : nullptr);
+    GE2_LAUNCH_CHECK();
+    return GE2_OK;
+}
+
+__global__ void advance_step_kernel(uint64_t* step) { *step += 1; }
+
+extern "C" int ge2_advance_step(uint64_t* step_dev, ge2_stream_t stream_) {
+    if (step_dev == nullptr) return GE2_ERR_INVALID_ARGUMENT;
+    advance_step_kernel<<<1, 1, 0, as_stream(stream_)>>>(step_dev);
     GE2_LAUNCH_CHECK();
     return GE2_OK;
 }

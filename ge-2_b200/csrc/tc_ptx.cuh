@@ -1,4 +1,4 @@
-// Thin inline-PTX wrappers for the Blackwell (sm_100a) tensor path: mbarrier, TMA tiled loads (never multicast),
+// Thin inline-PTX wrappers for the Blackwell (sm_100a) tensor path: mbarrier, TMA tiled loads (one CTA, one destination),
 // tensor memory allocation, tcgen05.mma with shared-memory descriptors, tcgen05.ld.
 // Every wait is bounded: it returns false after a fixed number of polls instead of spinning forever.
 #pragma once

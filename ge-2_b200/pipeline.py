@@ -87,17 +87,22 @@ class BatchPipeline:
             self.src_negs_local = self.inverse[off:off + CN]
             off += CN
         self.dst_negs_local = self.inverse[off:off + CN]
+        self.step_dev = torch.zeros(1, dtype=torch.int64, device=dev)  # device-side batch counter of the graph-replay form
+        self.rel_ids = torch.empty(max(B, 1), **i64)                    # the batch's relation column, copied by the sampler
+        self._graph = None
         self._desc = None
         self._ws = None
         self.grad_scale = 1.0  # 1 / #GPUs when relation gradients are all-reduced (model.cpp:188-192 of the reference project)
 
-    def _make_desc(self, edges):
+    def _make_desc(self, edges, rel_ids=None, rel_stride=None):
         cfg = self.cfg
         cols = edges.shape[1]
+        if rel_ids is None and cfg.has_relations:
+            rel_ids, rel_stride = edges[:, 1], cols
         d = capi.make_lp_desc(
             decoder=cfg.decoder, precision=cfg.precision, B=cfg.B, Cn=cfg.C, N=cfg.N, D=cfg.D, R=cfg.R if cfg.has_relations else 0,
             U=self.cap, node_emb=self.table, row_index=self.unique, emb_stride=cfg.D, src_ids=self.src_local, dst_ids=self.dst_local,
-            rel_ids=edges[:, 1] if cfg.has_relations else None, edge_stride=1, rel_stride=cols, dst_negs=self.dst_negs_local,
+            rel_ids=rel_ids if cfg.has_relations else None, edge_stride=1, rel_stride=rel_stride or 1, dst_negs=self.dst_negs_local,
             src_negs=self.src_negs_local, deg_sample_rows=self.deg_rows if cfg.n_deg > 0 else None, n_deg=cfg.n_deg,
             rel=self.rel, inv_rel=self.inv_rel if cfg.sides == 2 else None, node_grad=self.node_grad, rel_grad=self.rel_grad,
             inv_rel_grad=self.inv_rel_grad, loss=self.loss, status=self.status)
@@ -118,7 +123,10 @@ class BatchPipeline:
         capi.sample_negatives(edges, edges[:, cols - 1], cols, cfg.B, cfg.C, cfg.N, cfg.n_deg, cfg.domain, cfg.sides == 2, cfg.seed,
                               batch_index, self.packed, self.deg_rows if cfg.n_deg > 0 else None)
         capi.unique_bitmap(self.packed, cfg.domain, workspace=self.uws, out_unique=self.unique, out_inverse=self.inverse, out_count=self.count)
-        desc = self._make_desc(edges)
+        self._backward_and_update(self._make_desc(edges), scores_events, rel_hook)
+
+    def _backward_and_update(self, desc, scores_events=None, rel_hook=None):
+        cfg = self.cfg
         if scores_events is None:
             capi.lp_step(desc)
         else:  # same kernels, issued phase by phase so the scores kernel can be bracketed by events
@@ -139,11 +147,38 @@ class BatchPipeline:
             if cfg.sides == 2:
                 capi.dense_adagrad(self.inv_rel, self.inv_rel_state, self.inv_rel_grad, dl, grad_scale=self.grad_scale, clear_grad=True)
 
+    # ---- graph-replay form: the whole step is a fixed launch list that reads its batch index from device memory ----------
+    def enqueue_resident(self, edges_all, num_batches: int, scores_events=None, rel_hook=None):
+        """One training step on batch (*step_dev % num_batches) of the resident edge list edges_all[num_batches * B, cols];
+        advances the device-side counter at the end.  No argument changes from step to step, so the launch list can be
+        captured once into a CUDA graph (capture_resident) and replayed."""
+        cfg = self.cfg
+        capi.sample_batch(edges_all, num_batches, self.step_dev, cfg.B, cfg.C, cfg.N, cfg.n_deg, cfg.domain, cfg.sides == 2, cfg.seed,
+                          self.packed, self.deg_rows if cfg.n_deg > 0 else None, self.rel_ids if cfg.has_relations else None)
+        capi.unique_bitmap(self.packed, cfg.domain, workspace=self.uws, out_unique=self.unique, out_inverse=self.inverse, out_count=self.count)
+        self._backward_and_update(self._make_desc(edges_all, self.rel_ids, 1), scores_events, rel_hook)
+        capi.advance_step(self.step_dev)
+
+    def capture_resident(self, edges_all, num_batches: int):
+        """Captures one resident step into a CUDA graph (after one eager step, which also resolves driver entry points and
+        function attributes outside the capture).  replay() then costs a single graph launch per step."""
+        self.enqueue_resident(edges_all, num_batches)
+        torch.cuda.synchronize(self.device)
+        self._graph_edges = edges_all  # keep the captured pointers alive
+        g = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(g):
+            self.enqueue_resident(edges_all, num_batches)
+        self._graph = g
+        return g
+
+    def replay(self):
+        self._graph.replay()
+
     # kernels of libge2_b200.so launched per step (memsets not counted): sample, mark, scan, inverse, [mask], prep, scores,
     # finish, loss, adagrad_scatter, dense adagrad per relation table
     def launches_per_step(self) -> int:
         cfg = self.cfg
-        return 4 + (1 if cfg.n_deg > 0 else 0) + 4 + 1 + (cfg.sides if cfg.has_relations else 0)
+        return 4 + (1 if cfg.n_deg > 0 else 0) + 4 + 1 + (cfg.sides if cfg.has_relations else 0)  # (+1 counter bump and up to +1 scores launch in the resident form)
 
     def check_status(self):
         """Synchronises and raises if any kernel flagged bad data (call between epochs, not per batch)."""

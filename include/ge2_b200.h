@@ -212,6 +212,16 @@ GE2_API int ge2_sample_negatives(const int64_t *src_ids, const int64_t *dst_ids,
                          int32_t n_deg, int64_t domain, int32_t want_src_negs, uint64_t seed, uint64_t batch_index,
                          int64_t *out_packed_ids, int64_t *out_deg_rows, ge2_stream_t stream);
 
+/* The same producer in a form a captured CUDA graph can replay for every batch of an epoch: the batch is batch number
+ * (*step_dev % num_batches) of the resident, already shuffled edge list edges[num_batches * B, cols] (the reference slices
+ * its shuffled active edges the same way, cpp/src/data/dataloader.cpp:671-689), the generator is keyed by (seed, *step_dev),
+ * and the batch's relation column is copied to out_rel_ids[B] (cols == 3) so that no later kernel needs the edge pointer.
+ * ge2_advance_step increments the device-side counter (one launch at the end of the step). */
+GE2_API int ge2_sample_batch(const int64_t *edges, int32_t cols, int64_t num_batches, const uint64_t *step_dev, int32_t B, int32_t C,
+                             int32_t N, int32_t n_deg, int64_t domain, int32_t want_src_negs, uint64_t seed, int64_t *out_packed_ids,
+                             int64_t *out_deg_rows, int64_t *out_rel_ids, ge2_stream_t stream);
+GE2_API int ge2_advance_step(uint64_t *step_dev, ge2_stream_t stream);
+
 /* GraphModelStorage::mapEdgesWithPartitionSlots_ (cpp/src/storage/graph_storage.cpp:270-303):
  * id -> slot[id / partition_size] * partition_size + id % partition_size on the first and last column of
  * edges[n, cols] (int64, in place or out of place).  A non-resident partition sets GE2_STATUS_BAD_INDEX. */

@@ -52,3 +52,39 @@ def test_three_steps_match_oracle(ge2, cuda_device, decoder, D, R, deg):
         if has_rel:
             assert np.abs(d_rel.cpu().numpy() - rel).max() <= 1e-4 * np.abs(rel).max()
             assert np.abs(d_inv.cpu().numpy() - inv_rel).max() <= 1e-4 * np.abs(inv_rel).max()
+
+
+def test_graph_replay_equals_host_issued_steps(ge2, cuda_device):
+    """The resident form reads its batch index from device memory; a captured CUDA graph replayed three times must leave
+    the tables where three host-issued steps leave them (up to the order of the gradient atomics)."""
+    from importlib import import_module
+
+    pipeline = import_module("ge-2_b200.pipeline")
+    rng = np.random.default_rng(21)
+    nodes, B, C, N, D, R, nb = 6000, 512, 2, 256, 100, 17, 5
+    table = (0.3 * rng.standard_normal((nodes, D))).astype(np.float32)
+    state = (0.01 + 0.05 * rng.random((nodes, D))).astype(np.float32)
+    rel = (1 + 0.2 * rng.standard_normal((R, D))).astype(np.float32)
+    edges = np.stack([workloads.zipf_ids(rng, nb * B, nodes, 1.0), workloads.zipf_ids(rng, nb * B, R, 1.2),
+                      workloads.zipf_ids(rng, nb * B, nodes, 1.0)], axis=1).astype(np.int64)
+    d_edges = torch.from_numpy(edges).to(cuda_device)
+    results = []
+    for mode in ("host", "graph"):
+        cfg = pipeline.PipelineConfig("COMPLEX", B, C, N, 0.5, D, R, nodes, lr=0.1, precision="fp32")
+        t = lambda a: torch.from_numpy(a.copy()).to(cuda_device)
+        d_table, d_state, d_rel, d_inv = t(table), t(state), t(rel), t(rel)
+        pipe = pipeline.BatchPipeline(cfg, d_table, d_state, d_rel, torch.zeros_like(d_rel), d_inv, torch.zeros_like(d_inv))
+        if mode == "host":
+            for _ in range(3):
+                pipe.enqueue_resident(d_edges, nb)
+        else:
+            g = pipe.capture_resident(d_edges, nb)  # one host-issued step, then the capture
+            g.replay()
+            g.replay()
+        pipe.check_status()
+        assert int(pipe.step_dev) == 3
+        results.append((d_table.cpu().numpy(), d_state.cpu().numpy(), d_rel.cpu().numpy(), float(pipe.loss)))
+    for a, b in zip(results[0][:3], results[1][:3]):
+        assert np.abs(a - b).max() <= 1e-5 * np.abs(a).max()
+    assert abs(results[0][3] - results[1][3]) <= 1e-5 * abs(results[0][3])
+    assert np.abs(results[0][0] - table).max() > 0  # and the steps did train
