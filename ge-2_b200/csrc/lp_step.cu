@@ -15,11 +15,6 @@ __device__ __forceinline__ const float* emb_row(const ge2_lp_desc& d, int64_t lo
     return d.node_emb + row * d.emb_stride;
 }
 
-__device__ __forceinline__ float warp_sum(float v) {
-#pragma unroll
-    for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
-    return v;
-}
 
 // ---------------------------------------------------------------------------------------------------
 // mask: one int per (side, chunk, column) = the batch row whose score there is overwritten with -1e9
@@ -58,104 +53,198 @@ __global__ void __launch_bounds__(256) mask_from_deg_rows_kernel(const int64_t* 
     }
 }
 
+// four consecutive columns [k, k+4) of a row of length D; columns past D read as zero.  `vec` = the row start is
+// 16-byte aligned and D % 4 == 0, so one vector load serves; otherwise 8-byte pairs (k even) or scalars.
+__device__ __forceinline__ float4 load4(const float* __restrict__ row, int k, int D, bool vec) {
+    if (vec && k + 3 < D) return __ldg(reinterpret_cast<const float4*>(row + k));
+    float4 v;
+    if ((k & 1) == 0 && k + 3 < D && (((uintptr_t)(row + k)) & 7) == 0) {
+        const float2 a = __ldg(reinterpret_cast<const float2*>(row + k)), b = __ldg(reinterpret_cast<const float2*>(row + k + 2));
+        return make_float4(a.x, a.y, b.x, b.y);
+    }
+    v.x = k < D ? __ldg(row + k) : 0.f;
+    v.y = k + 1 < D ? __ldg(row + k + 1) : 0.f;
+    v.z = k + 2 < D ? __ldg(row + k + 2) : 0.f;
+    v.w = k + 3 < D ? __ldg(row + k + 3) : 0.f;
+    return v;
+}
+
+__device__ __forceinline__ void store_half4(__half* dst, float4 v) {
+    const __half2 lo = __floats2half2_rn(v.x, v.y), hi = __floats2half2_rn(v.z, v.w);
+    uint2 pk;
+    pk.x = *reinterpret_cast<const uint32_t*>(&lo);
+    pk.y = *reinterpret_cast<const uint32_t*>(&hi);
+    *reinterpret_cast<uint2*>(dst) = pk;
+}
+
 // ---------------------------------------------------------------------------------------------------
-// prep: one warp per output row.  Rows [0, S*Bp) are query rows, rows [S*Bp, S*Bp + S*CN) negative rows.
+// prep: eight lanes per output row (four rows in flight per warp, so the dependent loads id -> row index -> embedding
+// row overlap), each lane 4 columns at a time.  Rows [0, S*Bp) are query rows, rows [S*Bp, S*Bp + S*CN) negative rows.
 // ---------------------------------------------------------------------------------------------------
 __global__ void __launch_bounds__(256) lp_prep_kernel(LpKernelArgs a) {
     const ge2_lp_desc& d = a.d;
     const LpLayout& L = a.L;
-    const int lane = threadIdx.x & 31;
-    const int64_t warps = ((int64_t)gridDim.x * blockDim.x) >> 5;
+    const int tid = threadIdx.x;
+    const int gl = tid & 7;                              // lane within the row group
+    const unsigned gmask = 0xFFu << ((tid & 31) & ~7);   // the 8 lanes of this group inside the warp
+    const int64_t groups = ((int64_t)gridDim.x * blockDim.x) >> 3;
     const int64_t q_rows = (int64_t)L.S * L.Bp;
     const int64_t total = q_rows + (int64_t)L.S * L.CN;
+    const int64_t total_pad = round_up<int64_t>(total, 4);  // whole warps stay in the loop for the shuffles
     const int D = d.D, h = D / 2, ld = L.ld;
-    for (int64_t w = ((int64_t)blockIdx.x * blockDim.x + threadIdx.x) >> 5; w < total; w += warps) {
+    const bool vec_e = (d.emb_stride % 4 == 0) && (((uintptr_t)d.node_emb) & 15) == 0 && D % 4 == 0;
+    const bool vec_r = D % 4 == 0 && ((((uintptr_t)d.rel) | ((uintptr_t)d.inv_rel)) & 15) == 0;
+    const bool write_k32 = d.precision != GE2_PRECISION_F16;  // the tensor path reads only the fp16 copy of the negatives
+    for (int64_t w = ((int64_t)blockIdx.x * blockDim.x + tid) >> 3; w < total_pad; w += groups) {
+        if (w >= total) continue;
         if (w < q_rows) {
             const int s = (int)(w / L.Bp);
             const int i = (int)(w - (int64_t)s * L.Bp);
             float* q = L.Q + ((int64_t)s * L.Bp + i) * ld;
             __half* qh = L.Qh != nullptr ? L.Qh + ((int64_t)s * L.Bp + i) * ld : nullptr;
-            if (i >= d.B) {  // zero rows appended by pad_and_reshape; their positive score is padded with 0
-                for (int k = lane; k < ld; k += 32) {
-                    q[k] = 0.f;
-                    if (qh != nullptr) qh[k] = __float2half_rn(0.f);
+            bool ok = i < d.B;  // rows past B: zero rows appended by pad_and_reshape; their positive score is padded with 0
+            int64_t sid = 0, did = 0, rid = 0;
+            if (ok) {
+                sid = d.src_ids[(int64_t)i * d.edge_stride];
+                did = d.dst_ids[(int64_t)i * d.edge_stride];
+                ok = sid >= 0 && sid < d.U && did >= 0 && did < d.U;
+                if (d.has_relations) {
+                    rid = d.rel_ids[(int64_t)i * d.rel_stride];
+                    ok = ok && rid >= 0 && rid < d.R;
                 }
-                if (lane == 0) L.pos[(int64_t)s * L.Bp + i] = 0.f;
-                continue;
+                if (!ok && gl == 0) or_status(d.status, GE2_STATUS_BAD_INDEX);
             }
-            const int64_t sid = d.src_ids[(int64_t)i * d.edge_stride];
-            const int64_t did = d.dst_ids[(int64_t)i * d.edge_stride];
-            bool ok = sid >= 0 && sid < d.U && did >= 0 && did < d.U;
-            int64_t rid = 0;
-            if (d.has_relations) {
-                rid = d.rel_ids[(int64_t)i * d.rel_stride];
-                ok = ok && rid >= 0 && rid < d.R;
-            }
-            if (!ok) {
-                if (lane == 0) or_status(d.status, GE2_STATUS_BAD_INDEX);
-                for (int k = lane; k < ld; k += 32) {
-                    q[k] = 0.f;
-                    if (qh != nullptr) qh[k] = __float2half_rn(0.f);
-                }
-                if (lane == 0) L.pos[(int64_t)s * L.Bp + i] = 0.f;
-                continue;
-            }
-            const float* ea = emb_row(d, s == 0 ? sid : did);  // the endpoint the relation is applied to
-            const float* eb = emb_row(d, s == 0 ? did : sid);  // the endpoint it is compared with
-            const float* r = d.has_relations ? (s == 0 ? d.rel : d.inv_rel) + rid * D : nullptr;
+            const float* ea = ok ? emb_row(d, s == 0 ? sid : did) : nullptr;  // the endpoint the relation is applied to
+            const float* eb = ok ? emb_row(d, s == 0 ? did : sid) : nullptr;  // the endpoint it is compared with
+            const float* r = (ok && d.has_relations) ? (s == 0 ? d.rel : d.inv_rel) + rid * D : nullptr;
             float dot = 0.f;
-            for (int k = lane; k < ld; k += 32) {
-                float v = 0.f;
-                if (k < D) {
+            for (int k = gl * 4; k < ld; k += 32) {
+                float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
+                if (ok) {
+                    const float4 x = load4(ea, k, D, vec_e);
                     if (r == nullptr) {
-                        v = ea[k];
-                    } else if (d.decoder == GE2_DECODER_DISTMULT) {
-                        v = ea[k] * r[k];
-                    } else if (k < h) {
-                        v = ea[k] * r[k] - ea[k + h] * r[k + h];
+                        v = x;
                     } else {
-                        v = ea[k - h] * r[k] + ea[k] * r[k - h];
+                        const float4 rr = load4(r, k, D, vec_r);
+                        if (d.decoder == GE2_DECODER_DISTMULT) {
+                            v = make_float4(x.x * rr.x, x.y * rr.y, x.z * rr.z, x.w * rr.w);
+                        } else {
+                            // complex Hadamard: columns [0, h) real, [h, D) imaginary; the partner component comes from the
+                            // same two rows (just loaded, so these scalar reads hit L1)
+                            float xv[4] = {x.x, x.y, x.z, x.w}, rv[4] = {rr.x, rr.y, rr.z, rr.w}, o[4];
+#pragma unroll
+                            for (int e2 = 0; e2 < 4; e2++) {
+                                const int c = k + e2;
+                                o[e2] = 0.f;
+                                if (c < D) {
+                                    const int cp = c < h ? c + h : c - h;
+                                    const float xp = __ldg(ea + cp), rp = __ldg(r + cp);
+                                    o[e2] = c < h ? xv[e2] * rv[e2] - xp * rp   // real: e_re r_re - e_im r_im
+                                                  : xp * rv[e2] + xv[e2] * rp;  // imaginary: e_re r_im + e_im r_re
+                                }
+                            }
+                            v = make_float4(o[0], o[1], o[2], o[3]);
+                        }
                     }
-                    dot += v * eb[k];
+                    const float4 y = load4(eb, k, D, vec_e);
+                    dot += v.x * y.x + v.y * y.y + v.z * y.z + v.w * y.w;
                 }
-                q[k] = v;
-                if (qh != nullptr) qh[k] = __float2half_rn(v);
+                *reinterpret_cast<float4*>(q + k) = v;
+                if (qh != nullptr) store_half4(qh + k, v);
             }
-            dot = warp_sum(dot);
-            if (lane == 0) L.pos[(int64_t)s * L.Bp + i] = dot;
+#pragma unroll
+            for (int o = 4; o > 0; o >>= 1) dot += __shfl_xor_sync(gmask, dot, o);
+            if (gl == 0) L.pos[(int64_t)s * L.Bp + i] = dot;
         } else {
             const int64_t e = w - q_rows;
             const int s = (int)(e / L.CN);
             const int64_t j = e - (int64_t)s * L.CN;
             const int64_t id = (s == 0 ? d.dst_negs : d.src_negs)[j];
-            float* krow = L.K + e * ld;
-            __half* khrow = L.Kh != nullptr ? L.Kh + e * ld : nullptr;
             const bool bad = id < 0 || id >= d.U;
-            if (bad && lane == 0) or_status(d.status, GE2_STATUS_BAD_INDEX);
+            if (bad && gl == 0) or_status(d.status, GE2_STATUS_BAD_INDEX);
             const float* src = bad ? nullptr : emb_row(d, id);
-            for (int k = lane; k < ld; k += 32) {
-                const float v = (!bad && k < D) ? src[k] : 0.f;
-                krow[k] = v;
-                if (khrow != nullptr) khrow[k] = __float2half_rn(v);
+            for (int k = gl * 4; k < ld; k += 32) {
+                const float4 v = bad ? make_float4(0.f, 0.f, 0.f, 0.f) : load4(src, k, D, vec_e);
+                if (write_k32) *reinterpret_cast<float4*>(L.K + e * ld + k) = v;
+                if (L.Kh != nullptr) store_half4(L.Kh + e * ld + k, v);
             }
         }
     }
 }
 
 // ---------------------------------------------------------------------------------------------------
-// finish: one warp per edge row and side, then one warp per negative row.
+// finish: relation-operator backward and the duplicate-reducing scatter of every gradient row.
+// Eight lanes share a row (16 columns each for ld = 128), so a warp has four rows in flight and the chain of dependent
+// loads (ids -> row index -> embedding row) overlaps four ways.  A CTA walks a contiguous range of rows and first folds
+// gradients for frequently hit rows (hub nodes under a power-law degree distribution, popular relations) into a small
+// shared-memory table; what does not find a slot goes to global memory with 16-byte vector atomics, and the table is
+// flushed once at the end.  Sums are the same as the reference's index_add backward up to fp32 addition order.
 // ---------------------------------------------------------------------------------------------------
-__global__ void __launch_bounds__(256) lp_finish_kernel(LpKernelArgs a) {
+constexpr int kFinSlots = 32;     // hot rows cached per CTA
+constexpr int kFinLanes = 8;      // lanes per row
+constexpr long long kFinEmpty = -1;
+
+struct FinishSmem {
+    float acc[kFinSlots][128];
+    long long tag[kFinSlots];  // 0 <= key < 2^40: node row; (1 + side) << 40 | relation id: relation row
+};
+
+__device__ __forceinline__ int fin_slot_of(long long key) { return (int)(((unsigned long long)key * 0x9E3779B97F4A7C15ull) >> 59); }  // top 5 bits
+
+__global__ void __launch_bounds__(256) lp_finish_kernel(LpKernelArgs a, int rows_per_cta) {
+    __shared__ FinishSmem sm;
     const ge2_lp_desc& d = a.d;
     const LpLayout& L = a.L;
-    const int lane = threadIdx.x & 31;
-    const int64_t warps = ((int64_t)gridDim.x * blockDim.x) >> 5;
+    const int tid = threadIdx.x;
+    const int gl = tid & (kFinLanes - 1);                 // lane within the row group
+    const int group = tid / kFinLanes;                    // 32 groups per CTA
+    const unsigned gmask = 0xFFu << ((tid & 31) & ~7);    // the 8 lanes of this group inside the warp
+    const int gleader = (tid & 31) & ~7;
     const int64_t e_rows = (int64_t)L.S * d.B;
     const int64_t total = e_rows + (int64_t)L.S * L.CN;
     const int D = d.D, h = D / 2, ld = L.ld;
     const bool vec4 = (D % 4 == 0) && (((uintptr_t)d.node_grad | (uintptr_t)d.rel_grad | (uintptr_t)d.inv_rel_grad) & 15) == 0;
-    for (int64_t w = ((int64_t)blockIdx.x * blockDim.x + threadIdx.x) >> 5; w < total; w += warps) {
-        if (w < e_rows) {
+    const bool vec_e = (d.emb_stride % 4 == 0) && (((uintptr_t)d.node_emb) & 15) == 0 && D % 4 == 0;
+    const bool vec_r = D % 4 == 0 && ((((uintptr_t)d.rel) | ((uintptr_t)d.inv_rel)) & 15) == 0;
+
+    for (int k = tid; k < kFinSlots * 128; k += 256) (&sm.acc[0][0])[k] = 0.f;
+    if (tid < kFinSlots) sm.tag[tid] = kFinEmpty;
+    __syncthreads();
+
+    // claims (or finds) the shared slot of `key`; -1 when the slot belongs to another row.  Group-uniform result.
+    auto claim = [&](long long key) -> int {
+        int slot = -1;
+        if ((tid & 31) == gleader) {
+            const int sidx = fin_slot_of(key);
+            const long long old = (long long)atomicCAS((unsigned long long*)&sm.tag[sidx], (unsigned long long)kFinEmpty, (unsigned long long)key);
+            slot = (old == kFinEmpty || old == key) ? sidx : -1;
+        }
+        return __shfl_sync(gmask, slot, gleader);
+    };
+    // adds four consecutive columns [k, k+4) of a gradient row either into the shared slot or straight into global memory
+    auto add4 = [&](int slot, float* grow, int k, float4 v) {
+        if (v.x == 0.f && v.y == 0.f && v.z == 0.f && v.w == 0.f) return;
+        if (slot >= 0) {
+            atomicAdd(&sm.acc[slot][k], v.x);
+            atomicAdd(&sm.acc[slot][k + 1], v.y);
+            atomicAdd(&sm.acc[slot][k + 2], v.z);
+            atomicAdd(&sm.acc[slot][k + 3], v.w);
+        } else if (vec4) {
+            atomicAdd(reinterpret_cast<float4*>(grow + k), v);
+        } else {
+            if (k < D) atomicAdd(grow + k, v.x);
+            if (k + 1 < D) atomicAdd(grow + k + 1, v.y);
+            if (k + 2 < D) atomicAdd(grow + k + 2, v.z);
+            if (k + 3 < D) atomicAdd(grow + k + 3, v.w);
+        }
+    };
+
+    const int64_t row_begin = (int64_t)blockIdx.x * rows_per_cta;
+    const int64_t row_end = row_begin + rows_per_cta < total ? row_begin + rows_per_cta : total;
+    for (int64_t w0 = row_begin; w0 < row_end; w0 += 32) {
+        const int64_t w = w0 + group;  // whole warps stay in the loop (shuffles below), rows past the end do nothing
+        const bool live = w < row_end;
+        if (live && w < e_rows) {
             const int s = (int)(w / d.B);
             const int i = (int)(w - (int64_t)s * d.B);
             const int64_t sid = d.src_ids[(int64_t)i * d.edge_stride];
@@ -166,78 +255,85 @@ __global__ void __launch_bounds__(256) lp_finish_kernel(LpKernelArgs a) {
                 rid = d.rel_ids[(int64_t)i * d.rel_stride];
                 ok = ok && rid >= 0 && rid < d.R;
             }
-            if (!ok) continue;  // already flagged by prep
-            const int64_t aid = s == 0 ? sid : did, bid = s == 0 ? did : sid;
-            const float* ea = emb_row(d, aid);
-            const float* eb = emb_row(d, bid);
-            const float* r = d.has_relations ? (s == 0 ? d.rel : d.inv_rel) + rid * D : nullptr;
-            float* rg = d.has_relations ? (s == 0 ? d.rel_grad : d.inv_rel_grad) + rid * D : nullptr;
-            const int64_t qrow = (int64_t)s * L.Bp + i;
-            const float* q = L.Q + qrow * ld;
-            const float* dq = L.dQ + qrow * ld;
-            const float dpos = __expf(L.pos[qrow] - L.lse[qrow]) - 1.0f;  // d loss / d pos_i = softmax prob of the positive - 1
-            float* ga = d.node_grad + aid * D;
-            float* gb = d.node_grad + bid * D;
-            // per column k: contribution to the compared endpoint (gb), the relation-adjusted endpoint (ga) and the relation row (gr)
-            auto column = [&](int k, float& vb, float& va, float& vr) {
-                vb = dpos * q[k];
-                const float g = dq[k] + dpos * eb[k];  // d loss / d adjusted embedding
-                if (r == nullptr) {
-                    va = g;
-                    vr = 0.f;
-                } else if (d.decoder == GE2_DECODER_DISTMULT) {
-                    va = g * r[k];
-                    vr = g * ea[k];
-                } else {
-                    // complex Hadamard backward: needs the gradient of the partner component too
-                    const int kp = k < h ? k + h : k - h;
-                    const float gp = dq[kp] + dpos * eb[kp];
-                    if (k < h) {  // real component: g = g_re, gp = g_im
-                        va = g * r[k] + gp * r[kp];
-                        vr = g * ea[k] + gp * ea[kp];
-                    } else {  // imaginary component: g = g_im, gp = g_re
-                        va = -gp * r[k] + g * r[kp];
-                        vr = -gp * ea[k] + g * ea[kp];
-                    }
-                }
-            };
-            if (vec4) {  // 16-byte vector reductions: a quarter of the atomic operations
-                for (int k = lane * 4; k < D; k += 128) {
-                    float vb[4], va[4], vr[4];
+            if (ok) {  // bad rows were flagged by prep
+                const int64_t aid = s == 0 ? sid : did, bid = s == 0 ? did : sid;
+                const float* ea = emb_row(d, aid);
+                const float* eb = emb_row(d, bid);
+                const float* r = d.has_relations ? (s == 0 ? d.rel : d.inv_rel) + rid * D : nullptr;
+                float* rg = d.has_relations ? (s == 0 ? d.rel_grad : d.inv_rel_grad) + rid * D : nullptr;
+                const int64_t qrow = (int64_t)s * L.Bp + i;
+                const float* q = L.Q + qrow * ld;
+                const float* dq = L.dQ + qrow * ld;
+                const float dpos = __expf(L.pos[qrow] - L.lse[qrow]) - 1.0f;  // d loss / d pos_i = softmax prob of the positive - 1
+                const int slot_a = claim(aid), slot_b = claim(bid);
+                const int slot_r = r != nullptr ? claim(((long long)(1 + s) << 40) | rid) : -1;
+                for (int k = gl * 4; k < D; k += kFinLanes * 4) {
+                    const float4 q4 = *reinterpret_cast<const float4*>(q + k);
+                    const float4 dq4 = *reinterpret_cast<const float4*>(dq + k);
+                    const float4 eb4 = load4(eb, k, D, vec_e);
+                    const float qv[4] = {q4.x, q4.y, q4.z, q4.w}, dqv[4] = {dq4.x, dq4.y, dq4.z, dq4.w}, ebv[4] = {eb4.x, eb4.y, eb4.z, eb4.w};
+                    float vb[4], va[4], vr[4] = {0.f, 0.f, 0.f, 0.f};
+                    if (r == nullptr) {
 #pragma unroll
-                    for (int e = 0; e < 4; e++) column(k + e, vb[e], va[e], vr[e]);
-                    atomicAdd(reinterpret_cast<float4*>(gb + k), make_float4(vb[0], vb[1], vb[2], vb[3]));
-                    atomicAdd(reinterpret_cast<float4*>(ga + k), make_float4(va[0], va[1], va[2], va[3]));
-                    if (rg != nullptr) atomicAdd(reinterpret_cast<float4*>(rg + k), make_float4(vr[0], vr[1], vr[2], vr[3]));
-                }
-            } else {
-                for (int k = lane; k < D; k += 32) {
-                    float vb, va, vr;
-                    column(k, vb, va, vr);
-                    atomicAdd(&gb[k], vb);
-                    atomicAdd(&ga[k], va);
-                    if (rg != nullptr) atomicAdd(&rg[k], vr);
+                        for (int e = 0; e < 4; e++) {
+                            vb[e] = dpos * qv[e];
+                            va[e] = dqv[e] + dpos * ebv[e];  // d loss / d adjusted embedding
+                        }
+                    } else {
+                        const float4 ea4 = load4(ea, k, D, vec_e), r4 = load4(r, k, D, vec_r);
+                        const float eav[4] = {ea4.x, ea4.y, ea4.z, ea4.w}, rv[4] = {r4.x, r4.y, r4.z, r4.w};
+#pragma unroll
+                        for (int e = 0; e < 4; e++) {
+                            const int c = k + e;
+                            vb[e] = dpos * qv[e];
+                            const float g = dqv[e] + dpos * ebv[e];
+                            if (d.decoder == GE2_DECODER_DISTMULT) {
+                                va[e] = g * rv[e];
+                                vr[e] = g * eav[e];
+                            } else if (c < D) {
+                                // complex Hadamard backward: needs the gradient of the partner component too
+                                const int cp = c < h ? c + h : c - h;
+                                const float gp = dq[cp] + dpos * __ldg(eb + cp);
+                                const float rp = __ldg(r + cp), eap = __ldg(ea + cp);
+                                if (c < h) {  // real component: g = g_re, gp = g_im
+                                    va[e] = g * rv[e] + gp * rp;
+                                    vr[e] = g * eav[e] + gp * eap;
+                                } else {  // imaginary component: g = g_im, gp = g_re
+                                    va[e] = -gp * rv[e] + g * rp;
+                                    vr[e] = -gp * eav[e] + g * eap;
+                                }
+                            } else {
+                                va[e] = 0.f;
+                            }
+                        }
+                    }
+                    add4(slot_b, d.node_grad + bid * D, k, make_float4(vb[0], vb[1], vb[2], vb[3]));
+                    add4(slot_a, d.node_grad + aid * D, k, make_float4(va[0], va[1], va[2], va[3]));
+                    if (rg != nullptr) add4(slot_r, rg, k, make_float4(vr[0], vr[1], vr[2], vr[3]));
                 }
             }
-        } else {
+        } else if (live) {
             const int64_t e = w - e_rows;
             const int s = (int)(e / L.CN);
             const int64_t j = e - (int64_t)s * L.CN;
             const int64_t id = (s == 0 ? d.dst_negs : d.src_negs)[j];
-            if (id < 0 || id >= d.U) continue;
-            const float* dk = L.dK + e * ld;
-            float* g = d.node_grad + id * D;
-            if (vec4) {
-                for (int k = lane * 4; k < D; k += 128) {
-                    const float4 v = *reinterpret_cast<const float4*>(dk + k);
-                    if (v.x != 0.f || v.y != 0.f || v.z != 0.f || v.w != 0.f) atomicAdd(reinterpret_cast<float4*>(g + k), v);
-                }
-            } else {
-                for (int k = lane; k < D; k += 32) {
-                    const float v = dk[k];
-                    if (v != 0.f) atomicAdd(&g[k], v);
-                }
+            if (id >= 0 && id < d.U) {
+                const float* dk = L.dK + e * ld;
+                const int slot = claim(id);
+                for (int k = gl * 4; k < D; k += kFinLanes * 4) add4(slot, d.node_grad + id * D, k, *reinterpret_cast<const float4*>(dk + k));
             }
+        }
+    }
+    __syncthreads();
+    // flush: group g writes slot g
+    if (group < kFinSlots) {
+        const long long key = sm.tag[group];
+        if (key != kFinEmpty) {
+            const int kind = (int)(key >> 40);
+            const long long id = key & ((1ll << 40) - 1);
+            float* grow = kind == 0 ? d.node_grad + id * D : (kind == 1 ? d.rel_grad : d.inv_rel_grad) + id * D;
+            for (int k = gl * 4; k < D; k += kFinLanes * 4)
+                add4(-1, grow, k, make_float4(sm.acc[group][k], sm.acc[group][k + 1], sm.acc[group][k + 2], sm.acc[group][k + 3]));
         }
     }
 }
@@ -338,7 +434,7 @@ extern "C" int ge2_lp_step(const ge2_lp_desc* desc, ge2_stream_t stream_) {
     }
 
     const int64_t prep_rows = (int64_t)L.S * L.Bp + (int64_t)L.S * L.CN;
-    lp_prep_kernel<<<stream_grid(prep_rows, 8, 8), 256, 0, stream>>>(a);
+    lp_prep_kernel<<<stream_grid(prep_rows, 32, 8), 256, 0, stream>>>(a);
     GE2_LAUNCH_CHECK();
     }
 
@@ -349,7 +445,10 @@ extern "C" int ge2_lp_step(const ge2_lp_desc* desc, ge2_stream_t stream_) {
     if (!(phases & 4)) return GE2_OK;
 
     const int64_t fin_rows = (int64_t)L.S * desc->B + (int64_t)L.S * L.CN;
-    lp_finish_kernel<<<stream_grid(fin_rows, 8, 8), 256, 0, stream>>>(a);
+    // contiguous row ranges per CTA (so that repeated rows meet in a CTA's shared table), two CTAs per SM worth of ranges
+    const int fin_ctas = (int)(fin_rows < (int64_t)kNumSMs * 4 * 32 ? ceil_div<int64_t>(fin_rows, 32) : (int64_t)kNumSMs * 4);
+    const int rows_per_cta = (int)round_up<int64_t>(ceil_div<int64_t>(fin_rows, fin_ctas), 32);
+    lp_finish_kernel<<<(unsigned)ceil_div<int64_t>(fin_rows, rows_per_cta), 256, 0, stream>>>(a, rows_per_cta);
     GE2_LAUNCH_CHECK();
     lp_loss_kernel<<<1, 1024, 0, stream>>>(L.lse, L.pos, (int64_t)L.S * L.Bp, desc->loss);
     GE2_LAUNCH_CHECK();
