@@ -221,6 +221,7 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--precision", default=os.environ.get("GE2_PRECISION", "fp32"), choices=["fp32", "f16"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--steps-per-state", type=int, default=50, help="N > 1: training steps between partition swaps")
     ap.add_argument("--no-graph", action="store_true", help="issue every launch from the host instead of replaying a CUDA graph")
     ap.add_argument("--cpu-budget", type=float, default=15.0)
     args = ap.parse_args()
@@ -256,8 +257,23 @@ def main():
     edges = make_graph(cfg, n_edges, 20262 + rank, device)  # each rank: its own edge share (weak scaling)
     edges = edges[torch.randperm(n_edges, device=device)]    # epoch shuffle (dataloader.cpp:613-616 of the reference project)
     gen = torch.Generator(device=device).manual_seed(7 + rank)
-    table = (torch.rand((nodes, D), device=device, generator=gen) - 0.5) * 0.2
-    state = torch.zeros((nodes, D), device=device)
+    pbuf, supersteps = None, None
+    if world == 1:
+        table = (torch.rand((nodes, D), device=device, generator=gen) - 0.5) * 0.2
+        state = torch.zeros((nodes, D), device=device)
+    else:
+        # Partition buffer (the reference's multi-GPU layout): 4 * world node partitions, every rank trains on the 4 that are
+        # resident in its buffer (same per-GPU domain and batch as the single-GPU run: weak scaling); between supersteps the
+        # partitions change hands over NCCL.  Edge endpoints are buffer-local ids, as after the reference's slot remap.
+        partition = importlib.import_module("ge-2_b200.partition")
+        P, psize = 4 * world, nodes // 4
+        home_emb = (torch.rand((4 * psize, D), device=device, generator=gen) - 0.5) * 0.2
+        home_state = torch.zeros((4 * psize, D), device=device)
+        pbuf = partition.PartitionBuffer([home_emb, home_state], psize, P, rank, world, dist)
+        supersteps = partition.make_supersteps(P, world)
+        pbuf.swap(supersteps[0])  # initial load; also sets up the NCCL point-to-point connections before anything is timed
+        pbuf.swap(supersteps[1 % len(supersteps)])
+        table, state = pbuf.buf[0], pbuf.buf[1]
     rel = torch.zeros((R, D), device=device)
     rel[:, : D // 2] = 1  # ComplEx relation init (complex.cpp:18-20 of the reference project)
     inv_rel = rel.clone()
@@ -268,8 +284,7 @@ def main():
         pipe.grad_scale = 1.0 / world
 
         def rel_hook(p):  # Model::all_reduce of the reference (model.cpp:174-204): sum of the replicas' relation gradients
-            dist.all_reduce(p.rel_grad)
-            dist.all_reduce(p.inv_rel_grad)
+            dist.all_reduce(p.rel_grads)  # both tables in one call
 
     def barrier():
         if dist is not None:
@@ -277,7 +292,15 @@ def main():
         torch.cuda.synchronize()
 
     num_batches = n_edges // B
-    use_graph = world == 1 and not args.no_graph  # NCCL all-reduce stays outside graph capture in this build
+    use_graph = not args.no_graph  # N > 1: two graphs per step with the host-issued NCCL all-reduce between them
+    sps = args.steps_per_state
+    swaps = [0]
+
+    def maybe_swap(i):
+        """superstep boundary: every `sps` steps the ranks exchange partitions (performNextSwap of the reference)"""
+        if pbuf is not None and i > 0 and i % sps == 0:
+            swaps[0] += 1
+            pbuf.swap(supersteps[(1 + swaps[0]) % len(supersteps)])
 
     # ---- warm-up, then an event-bracketed pass that times the scores kernel alone (roofline) ---------------------
     for i in range(W):
@@ -292,7 +315,7 @@ def main():
 
     # ---- device-resident timing (`value`): K steps, one CUDA-graph launch per step -----------------------------------
     if use_graph:
-        graph = pipe.capture_resident(edges, num_batches)
+        graph = pipe.capture_resident(edges, num_batches) if world == 1 else pipe.capture_resident_split(edges, num_batches, rel_hook)
         for _ in range(W):
             graph.replay()
     start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
@@ -301,6 +324,7 @@ def main():
     clocks.start()
     start.record()
     for i in range(K):
+        maybe_swap(i)
         if use_graph:
             graph.replay()
         else:
@@ -319,9 +343,10 @@ def main():
     stage = torch.empty((B, 3), dtype=torch.int64, device=device)
     stage.copy_(host_edges[0])
     if use_graph:
-        graph_e2e = pipe.capture_resident(stage, 1)
+        graph_e2e = pipe.capture_resident(stage, 1) if world == 1 else pipe.capture_resident_split(stage, 1, rel_hook)
 
     def e2e_step(i):
+        maybe_swap(i)
         stage.copy_(host_edges[i], non_blocking=True)
         if use_graph:
             graph_e2e.replay()
@@ -359,7 +384,9 @@ def main():
             dtype="f32" if args.precision == "fp32" else "f16 tensor tiles, f32 accumulate and storage", data="synthetic",
             config=dict(workload=cfg["name"], per_gpu_batch=B, global_batch=B * world, precision=args.precision,
                         l2="tables (0.8 GB) and edge list larger than L2; rows touched per step are random", parallelism=f"dp{world}" if world > 1 else "single",
-                        launch="one CUDA graph replay per step" if use_graph else "host-issued launches"),
+                        launch=("one CUDA graph replay per step" if world == 1 else "two CUDA graph replays + one NCCL all-reduce per step") if use_graph else "host-issued launches",
+                        partitions=None if pbuf is None else dict(count=4 * world, rows=nodes // 4, steps_per_state=sps, swaps_in_timed_region=(K - 1) // sps,
+                                                                  exchange="NCCL send/recv of partition slabs + all-reduce of relation gradients every step")),
             e2e=dict(value=world * K * B / (ms_e2e * 1e-3), unit="edges/s", h2d_bytes_per_step=B * 3 * 8, d2h_bytes_per_step=4,
                      note="pinned host edges -> H2D, step, loss -> pinned host, all stream-ordered; one synchronize at the end"),
             gpu_launches=K * (pipe.launches_per_step() + 1),

@@ -74,8 +74,10 @@ class BatchPipeline:
         self.loss = torch.zeros(1, dtype=torch.float32, device=dev)
         self.uws = capi.unique_workspace(cfg.domain, dev)
         if cfg.has_relations:
-            self.rel_grad = torch.zeros_like(rel)
-            self.inv_rel_grad = torch.zeros_like(inv_rel) if cfg.sides == 2 else None
+            # one contiguous buffer for both relation-gradient tables: a single all-reduce serves them in the multi-GPU trainer
+            self.rel_grads = torch.zeros((cfg.sides,) + tuple(rel.shape), dtype=rel.dtype, device=dev)
+            self.rel_grad = self.rel_grads[0]
+            self.inv_rel_grad = self.rel_grads[1] if cfg.sides == 2 else None
         else:
             self.rel_grad = self.inv_rel_grad = None
         B = cfg.B
@@ -126,7 +128,12 @@ class BatchPipeline:
         self._backward_and_update(self._make_desc(edges), scores_events, rel_hook)
 
     def _backward_and_update(self, desc, scores_events=None, rel_hook=None):
-        cfg = self.cfg
+        self._backward(desc, scores_events)
+        if rel_hook is not None:
+            rel_hook(self)
+        self._update()
+
+    def _backward(self, desc, scores_events=None):
         if scores_events is None:
             capi.lp_step(desc)
         else:  # same kernels, issued phase by phase so the scores kernel can be bracketed by events
@@ -138,8 +145,9 @@ class BatchPipeline:
             scores_events[1].record()
             desc.phases = 4
             capi.lp_step(desc)
-        if rel_hook is not None:
-            rel_hook(self)
+
+    def _update(self):
+        cfg = self.cfg
         capi.adagrad_scatter(self.table, self.state, self.unique, self.node_grad, cfg.lr, U=self.cap, U_dev=self.count, status=self.status)
         if cfg.has_relations:
             dl = cfg.lr if cfg.dense_lr is None else cfg.dense_lr
@@ -159,17 +167,44 @@ class BatchPipeline:
         self._backward_and_update(self._make_desc(edges_all, self.rel_ids, 1), scores_events, rel_hook)
         capi.advance_step(self.step_dev)
 
-    def capture_resident(self, edges_all, num_batches: int):
+    def capture_resident(self, edges_all, num_batches: int, rel_hook=None):
         """Captures one resident step into a CUDA graph (after one eager step, which also resolves driver entry points and
         function attributes outside the capture).  replay() then costs a single graph launch per step."""
-        self.enqueue_resident(edges_all, num_batches)
+        self.enqueue_resident(edges_all, num_batches, rel_hook=rel_hook)
         torch.cuda.synchronize(self.device)
         self._graph_edges = edges_all  # keep the captured pointers alive
         g = torch.cuda.CUDAGraph()
         with torch.cuda.graph(g):
-            self.enqueue_resident(edges_all, num_batches)
+            self.enqueue_resident(edges_all, num_batches, rel_hook=rel_hook)
         self._graph = g
         return g
+
+    def capture_resident_split(self, edges_all, num_batches: int, rel_hook):
+        """Multi-GPU form: the step is captured as two graphs with the relation-gradient all-reduce (rel_hook, a host-issued
+        NCCL call) between them -- sample/unique/forward/backward, then the optimizer updates and the counter bump."""
+        self.enqueue_resident(edges_all, num_batches, rel_hook=rel_hook)
+        torch.cuda.synchronize(self.device)
+        self._graph_edges = edges_all
+        cfg = self.cfg
+        ga, gb = torch.cuda.CUDAGraph(), torch.cuda.CUDAGraph()
+        with torch.cuda.graph(ga):
+            capi.sample_batch(edges_all, num_batches, self.step_dev, cfg.B, cfg.C, cfg.N, cfg.n_deg, cfg.domain, cfg.sides == 2, cfg.seed,
+                              self.packed, self.deg_rows if cfg.n_deg > 0 else None, self.rel_ids if cfg.has_relations else None)
+            capi.unique_bitmap(self.packed, cfg.domain, workspace=self.uws, out_unique=self.unique, out_inverse=self.inverse,
+                               out_count=self.count)
+            self._backward(self._make_desc(edges_all, self.rel_ids, 1))
+        with torch.cuda.graph(gb):
+            self._update()
+            capi.advance_step(self.step_dev)
+
+        class _Split:
+            def replay(_self):
+                ga.replay()
+                rel_hook(self)
+                gb.replay()
+
+        self._split = (ga, gb)
+        return _Split()
 
     def replay(self):
         self._graph.replay()
