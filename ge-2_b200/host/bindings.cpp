@@ -1,0 +1,49 @@
+// Python binding of the host layer (module ge2_host), used by the tests; same class and member names as the reference's
+// own pybind modules (python_bindings/ of the reference project) for the members that exist here.
+#include <torch/extension.h>
+
+#include "ge2_host.h"
+
+using namespace ge2host;
+
+PYBIND11_MODULE(ge2_host, m) {
+    py::register_exception<GegeRuntimeException>(m, "GegeRuntimeException");
+    m.def("map_tensors", &map_tensors, py::arg("unmapped_tensors"), py::arg("sorted") = true, py::arg("value_domain_size") = -1);
+    m.def("map_tensors_unique_inverse_cuda", &map_tensors_unique_inverse_cuda, py::arg("all_ids"), py::arg("sorted") = true,
+          py::arg("value_domain_size") = -1);
+    py::class_<Batch, std::shared_ptr<Batch>>(m, "Batch")
+        .def(py::init<>())
+        .def_readwrite("unique_node_indices", &Batch::unique_node_indices_)
+        .def_readwrite("node_embeddings", &Batch::node_embeddings_)
+        .def_readwrite("node_gradients", &Batch::node_gradients_)
+        .def_readwrite("node_embeddings_state", &Batch::node_embeddings_state_)
+        .def_readwrite("node_state_update", &Batch::node_state_update_)
+        .def_readwrite("src_neg_indices_mapping", &Batch::src_neg_indices_mapping_)
+        .def_readwrite("dst_neg_indices_mapping", &Batch::dst_neg_indices_mapping_)
+        .def_readwrite("edges", &Batch::edges_)
+        .def_readwrite("src_neg_filter", &Batch::src_neg_filter_)
+        .def_readwrite("dst_neg_filter", &Batch::dst_neg_filter_)
+        .def_readwrite("loss", &Batch::loss_)
+        .def("accumulateGradients", &Batch::accumulateGradients)
+        .def("clear", &Batch::clear);
+    py::enum_<DecoderType>(m, "DecoderType").value("DISTMULT", DecoderType::DISTMULT).value("COMPLEX", DecoderType::COMPLEX);
+    py::class_<Model, std::shared_ptr<Model>>(m, "Model")
+        .def(py::init<DecoderType, int64_t, int64_t, bool, float, float, torch::Device, const std::string&>(), py::arg("type"),
+             py::arg("num_relations"), py::arg("dim"), py::arg("use_inverse_relations"), py::arg("dense_lr"), py::arg("sparse_lr"),
+             py::arg("device"), py::arg("precision") = "fp32")
+        .def("train_batch", &Model::train_batch, py::arg("batch"), py::arg("call_step") = true)
+        .def("step", &Model::step)
+        .def("clear_grad", &Model::clear_grad)
+        .def("step_after_all_reduce", &Model::step_after_all_reduce)
+        .def_readwrite("relations", &Model::relations_)
+        .def_readwrite("inverse_relations", &Model::inverse_relations_)
+        .def_readwrite("relations_grad", &Model::relations_grad_)
+        .def_readwrite("inverse_relations_grad", &Model::inverse_relations_grad_)
+        .def_readwrite("relations_state", &Model::relations_state_)
+        .def_readwrite("inverse_relations_state", &Model::inverse_relations_state_);
+    py::class_<InMemory, std::shared_ptr<InMemory>>(m, "InMemory")
+        .def(py::init<torch::Tensor>())
+        .def("indexRead", &InMemory::indexRead)
+        .def("indexAdd", &InMemory::indexAdd)
+        .def_readwrite("data", &InMemory::data_);
+}
