@@ -212,6 +212,69 @@ def reference_arm(args):
     print(json.dumps(line), flush=True)
 
 
+def aten_chain_ms(cfg, table, state, rel, inv_rel, edges, steps, device):
+    """For context only (never the product path): the reference's per-batch op chain restated with the same ATen calls it makes
+    on the GPU -- randint negatives, unique, index_select gathers, bmm scores, logsumexp + cross_entropy, autograd backward,
+    Adagrad element-wise ops, index_add_ (decoder_methods.cpp:724-946, loss.cpp:46-63, batch.cpp:264-266, storage.cpp:1216 of the
+    reference project) -- timed on this GPU.  It is what the reference's build would launch, minus its host-side bookkeeping, so
+    it flatters the reference; the reference itself needs its CMake build and an omegaconf-based config loader and is not run."""
+    B, C, N, D, n = cfg["B"], cfg["C"], cfg["N"], cfg["D"], cfg["nodes"]
+    nd = int(N * cfg["degree_fraction"])
+    h = D // 2
+    rel_p = rel.clone().requires_grad_(True)
+    inv_p = inv_rel.clone().requires_grad_(True)
+    rs, irs = torch.zeros_like(rel), torch.zeros_like(rel)
+    tab, st = table.clone(), state.clone()
+
+    def cmul(e, r):
+        out = torch.zeros_like(e)
+        out[:, :h] = e[:, :h] * r[:, :h] - e[:, h:] * r[:, h:]
+        out[:, h:] = e[:, :h] * r[:, h:] + e[:, h:] * r[:, :h]
+        return out
+
+    def one(i):
+        e = edges[i * B:(i + 1) * B]
+        uni = torch.randint(n, (C, N - nd), device=device)
+        rows = torch.randint(0, B, (C, nd), device=device)
+        dneg, sneg = torch.cat([e[:, 2][rows], uni], 1), torch.cat([e[:, 0][rows], uni], 1)
+        ids = torch.cat([e[:, 0], e[:, 2], sneg.reshape(-1), dneg.reshape(-1)])
+        uniq, inv = torch.unique(ids, sorted=True, return_inverse=True)
+        emb = tab.index_select(0, uniq).requires_grad_(True)
+        s_l, d_l = inv[:B], inv[B:2 * B]
+        src, dst = emb.index_select(0, s_l), emb.index_select(0, d_l)
+        loss = 0
+        for q_e, o_e, r_tab, negs in ((src, dst, rel_p, inv[2 * B + C * N:]), (dst, src, inv_p, inv[2 * B:2 * B + C * N])):
+            q = cmul(q_e, r_tab.index_select(0, e[:, 1]))
+            pos = (q * o_e).sum(-1)
+            ne = emb.index_select(0, negs).reshape(C, N, D)
+            neg = q.view(C, B // C, D).bmm(ne.transpose(-1, -2)).flatten(0, 1)
+            y = torch.cat([pos.unsqueeze(1), neg.logsumexp(1, True)], -1)
+            loss = loss + torch.nn.functional.cross_entropy(y, torch.zeros(B, dtype=torch.int64, device=device), reduction="sum")
+        loss.backward()
+        with torch.no_grad():
+            for p_, s_ in ((rel_p, rs), (inv_p, irs)):
+                s_.addcmul_(p_.grad, p_.grad, value=1.0)
+                p_.addcdiv_(p_.grad, s_.sqrt().add_(1e-10), value=-cfg["lr"])
+                p_.grad = None
+            g = emb.grad
+            upd = g.pow(2)
+            stl = st.index_select(0, uniq).add_(upd)
+            delta = -cfg["lr"] * (g / stl.sqrt().add_(1e-10))
+            tab.index_add_(0, uniq, delta)
+            st.index_add_(0, uniq, upd)
+
+    for i in range(3):
+        one(i)
+    a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    torch.cuda.synchronize()
+    a.record()
+    for i in range(steps):
+        one(3 + i)
+    b.record()
+    torch.cuda.synchronize()
+    return a.elapsed_time(b) / steps
+
+
 # ----------------------------------------------------------------------------------------------------------------
 def main():
     ap = argparse.ArgumentParser()
@@ -221,6 +284,7 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--precision", default=os.environ.get("GE2_PRECISION", "fp32"), choices=["fp32", "f16"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--no-aten-chain", action="store_true", help="skip the ATen restatement of the reference's GPU op chain (context figure)")
     ap.add_argument("--steps-per-state", type=int, default=50, help="N > 1: training steps between partition swaps")
     ap.add_argument("--no-graph", action="store_true", help="issue every launch from the host instead of replaying a CUDA graph")
     ap.add_argument("--cpu-budget", type=float, default=15.0)
@@ -396,6 +460,14 @@ def main():
                           ms_per_launch=scores_ms, flops_per_launch=flops,
                           timing="CUDA events around the scores launch(es) in an event-bracketed pass of the same K steps"),
         )
+        if world == 1 and not args.no_aten_chain:
+            try:
+                ms_chain = aten_chain_ms(cfg, table, state, rel, inv_rel, edges, min(K, 20), device)
+                line["aten_chain"] = dict(value=B / (ms_chain * 1e-3), unit="edges/s", ms_per_step=ms_chain,
+                                          note="the reference's GPU op chain restated with the same ATen calls (torch library kernels), same workload, "
+                                               "same GPU; context for the speed-up, not the reference build and not part of the product path")
+            except Exception as ex:  # context only: never let it break the bench line
+                line["aten_chain"] = dict(unavailable=str(ex)[:120])
         if world == 1 and not args.no_cpu_baseline:
             cpu = CpuReference(cfg, 20262)
             v, k, dt = cpu.timed(args.cpu_budget)
