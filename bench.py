@@ -34,6 +34,11 @@ CFG = dict(name="kg-1M-entities/1k-relations/20M-triples ComplEx d=100 B=10000 n
            triples=20_000_000, decoder="COMPLEX", D=100, B=10_000, C=10, N=1000, degree_fraction=0.5, lr=0.1, alpha_nodes=1.1, alpha_rel=1.2)
 
 
+# dram__bytes_read.sum + dram__bytes_write.sum of one launch of the scores kernel on this workload, from the ncu capture
+# summarised in profiles/lp_scores_f16_config2.md (operands and partial gradients stay in the 126 MB L2)
+NCU_TRAFFIC = {"f16": 20_729_344, "fp32": None}
+
+
 def peaks():
     f = ROOT / "MEASURED_PEAKS.json"
     if f.exists():
@@ -282,8 +287,10 @@ def main():
     ap.add_argument("--steps", type=int, default=100)
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
-    ap.add_argument("--precision", default=os.environ.get("GE2_PRECISION", "fp32"), choices=["fp32", "f16"])
+    ap.add_argument("--precision", default=os.environ.get("GE2_PRECISION", "f16"), choices=["fp32", "f16"],
+                    help="f16: tcgen05 fp16-operand tiles with fp32 accumulation (1e-2 parity, the designed path); fp32: CUDA-core path (1e-4 parity)")
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--no-fp32-path", action="store_true", help="skip the side measurement of the fp32 CUDA-core path")
     ap.add_argument("--no-aten-chain", action="store_true", help="skip the ATen restatement of the reference's GPU op chain (context figure)")
     ap.add_argument("--steps-per-state", type=int, default=50, help="N > 1: training steps between partition swaps")
     ap.add_argument("--no-graph", action="store_true", help="issue every launch from the host instead of replaying a CUDA graph")
@@ -456,10 +463,26 @@ def main():
             gpu_launches=K * (pipe.launches_per_step() + 1),
             clocks=clock_info,
             roofline=dict(bound="tensor", kernel="lp_scores_%s" % args.precision, achieved=achieved, peak=pk["tf"], unit="TFLOP/s",
-                          frac=achieved / pk["tf"], traffic=None, peak_source=pk["src"] + " bf16 dense",
+                          frac=achieved / pk["tf"], traffic=NCU_TRAFFIC.get(args.precision), peak_source=pk["src"] + " bf16 dense",
                           ms_per_launch=scores_ms, flops_per_launch=flops,
                           timing="CUDA events around the scores launch(es) in an event-bracketed pass of the same K steps"),
         )
+        if world == 1 and args.precision == "f16" and not args.no_fp32_path:
+            # the same step on the fp32 CUDA-core path (1e-4 parity), for reference next to the headline
+            pc32 = pipeline.PipelineConfig(cfg["decoder"], B, C, N, cfg["degree_fraction"], D, R, nodes, lr=cfg["lr"], precision="fp32")
+            p32 = pipeline.BatchPipeline(pc32, table, state, rel, torch.zeros_like(rel), inv_rel, torch.zeros_like(inv_rel))
+            g32 = p32.capture_resident(edges, num_batches)
+            for _ in range(3):
+                g32.replay()
+            a32, b32 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            k32 = max(10, K // 5)
+            torch.cuda.synchronize()
+            a32.record()
+            for _ in range(k32):
+                g32.replay()
+            b32.record()
+            torch.cuda.synchronize()
+            line["fp32_path"] = dict(value=k32 * B / (a32.elapsed_time(b32) * 1e-3), unit="edges/s", ms_per_step=a32.elapsed_time(b32) / k32, steps=k32)
         if world == 1 and not args.no_aten_chain:
             try:
                 ms_chain = aten_chain_ms(cfg, table, state, rel, inv_rel, edges, min(K, 20), device)
