@@ -38,7 +38,7 @@ class LpDesc(C.Structure):
         ("src_ids", C.c_void_p), ("rel_ids", C.c_void_p), ("dst_ids", C.c_void_p), ("edge_stride", C.c_int64), ("rel_stride", C.c_int64),
         ("dst_negs", C.c_void_p), ("src_negs", C.c_void_p),
         ("dst_filter", C.c_void_p), ("dst_filter_n", C.c_int64), ("src_filter", C.c_void_p), ("src_filter_n", C.c_int64),
-        ("deg_sample_rows", C.c_void_p), ("n_deg", C.c_int32), ("reserved1", C.c_int32),
+        ("deg_sample_rows", C.c_void_p), ("n_deg", C.c_int32), ("flags", C.c_int32),
         ("rel", C.c_void_p), ("inv_rel", C.c_void_p),
         ("node_grad", C.c_void_p), ("rel_grad", C.c_void_p), ("inv_rel_grad", C.c_void_p), ("loss", C.c_void_p),
         ("pos_scores", C.c_void_p), ("neg_scores", C.c_void_p), ("inv_pos_scores", C.c_void_p), ("inv_neg_scores", C.c_void_p),
@@ -154,7 +154,7 @@ def unique_bitmap_static(ids, domain: int, out_unique, out_inverse, out_count):
 def make_lp_desc(*, decoder, precision, B, Cn, N, D, R, U, node_emb, row_index=None, emb_stride=None, src_ids, dst_ids, rel_ids=None,
                  edge_stride=1, rel_stride=1, dst_negs, src_negs=None, dst_filter=None, src_filter=None, deg_sample_rows=None, n_deg=0,
                  rel=None, inv_rel=None, node_grad, rel_grad=None, inv_rel_grad=None, loss, pos_scores=None, neg_scores=None,
-                 inv_pos_scores=None, inv_neg_scores=None, status=None, workspace=None) -> LpDesc:
+                 inv_pos_scores=None, inv_neg_scores=None, status=None, workspace=None, node_grad_is_zero=False) -> LpDesc:
     d = LpDesc()
     d.decoder = DECODER[decoder] if isinstance(decoder, str) else decoder
     d.precision = PRECISION[precision] if isinstance(precision, str) else precision
@@ -173,6 +173,7 @@ def make_lp_desc(*, decoder, precision, B, Cn, N, D, R, U, node_emb, row_index=N
     if d.src_filter_n == 0:
         d.src_filter = None
     d.deg_sample_rows, d.n_deg = ptr(deg_sample_rows), n_deg
+    d.flags = 1 if node_grad_is_zero else 0
     d.rel, d.inv_rel = ptr(rel), ptr(inv_rel)
     d.node_grad, d.rel_grad, d.inv_rel_grad, d.loss = ptr(node_grad), ptr(rel_grad), ptr(inv_rel_grad), ptr(loss)
     d.pos_scores, d.neg_scores = ptr(pos_scores), ptr(neg_scores)

@@ -29,6 +29,7 @@ struct LpLayout {
     int32_t* mask;    // [S][CN]  batch row whose score in this (chunk, column) is masked, or -1
     __half* Qh;       // [S][Bp][ld]  fp16 copy of Q, operand of the tensor-core path (null on the fp32 path)
     __half* Kh;       // [S][CN][ld]  fp16 copy of K
+    double* loss_acc; // [1] sum over rows of (lse - pos): zeroed by the prepare kernel, added to by the scores kernels
     float* part;      // [S][Bp][4][2] per-row partial (max, sum) of sweep 1 when a chunk's tiles are split over CTAs
     size_t bytes;
     size_t zero_begin, zero_bytes;  // dK range
@@ -64,6 +65,7 @@ inline LpLayout lp_make_layout(const ge2_lp_desc& d, void* base) {
     size_t opos = take((size_t)L.S * L.Bp * 4);
     size_t olse = take((size_t)L.S * L.Bp * 4);
     size_t omask = take((size_t)L.S * L.CN * 4);
+    size_t oloss = take(8);
     const bool half_copies = d.precision == GE2_PRECISION_F16;
     size_t oQh = half_copies ? take((size_t)L.S * L.Bp * L.ld * 2) : 0;
     size_t oKh = half_copies ? take((size_t)L.S * L.CN * L.ld * 2) : 0;
@@ -75,6 +77,7 @@ inline LpLayout lp_make_layout(const ge2_lp_desc& d, void* base) {
     L.pos = (float*)(p + opos);
     L.lse = (float*)(p + olse);
     L.mask = (int32_t*)(p + omask);
+    L.loss_acc = (double*)(p + oloss);
     L.Qh = half_copies ? (__half*)(p + oQh) : nullptr;
     L.Kh = half_copies ? (__half*)(p + oKh) : nullptr;
     L.part = half_copies ? (float*)(p + opart) : nullptr;

@@ -289,7 +289,13 @@ __global__ void __launch_bounds__(kThreads, 1)
         constexpr float kLog2e = 1.4426950408889634f;
         const bool row_live = my_row < valid_rows;
         // running max / sum of exp2 in the base-2 domain (scores pre-multiplied by log2 e): one FFMA + one MUFU per score
-        float run_m = -INFINITY, run_l = 0.f, lse2 = 0.f;
+        float run_m = -INFINITY, run_l = 0.f, lse2 = 0.f, my_loss = 0.f;
+        // the step's loss = sum over rows of (lse - pos): one double-precision atomic per warp
+        auto add_row_loss = [&](float v) {
+#pragma unroll
+            for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+            if (lane == 0) atomicAdd(L.loss_acc, (double)v);
+        };
         if (mode == 2 && row_live) {  // sweep 1 ran in an earlier launch: combine its partial (max, sum) pairs
             float m = -INFINITY, l = 0.f;
             const float2* part = reinterpret_cast<const float2*>(L.part) + (grow0 + my_row) * 4;
@@ -305,7 +311,9 @@ __global__ void __launch_bounds__(kThreads, 1)
             const float nm = fmaxf(m, pos2);
             lse2 = nm + __log2f(l * exp2f_fast(m - nm) + exp2f_fast(pos2 - nm));
             if (split_h == 0 && half == 0) L.lse[grow0 + my_row] = lse2 * 0.6931471805599453f;
+            my_loss = (lse2 - pos2) * 0.6931471805599453f;
         }
+        if (mode == 2 && split_h == 0 && half == 0) add_row_loss(my_loss);
         // The filter is sparse: a tile has at most one masked row per column and few of them fall in this warp's 32 rows.
         // Lane l looks at columns l and l+32 of the warp's half tile; entries that name a row of this warp are handed to
         // that row's thread, which ends up with one bit per masked column of its own row.  The words of the next tile are
@@ -394,8 +402,10 @@ __global__ void __launch_bounds__(kThreads, 1)
                             const float nm2 = fmaxf(nm, pos2);
                             lse2 = nm2 + __log2f(l * exp2f_fast(nm - nm2) + exp2f_fast(pos2 - nm2));
                             if (half == 0) L.lse[grow0 + my_row] = lse2 * 0.6931471805599453f;
+                            my_loss = (lse2 - pos2) * 0.6931471805599453f;
                         }
                     }
+                    if (mode == 0 && half == 0) add_row_loss(my_loss);
                 }
             } else {
                 const int pb = t & 1;

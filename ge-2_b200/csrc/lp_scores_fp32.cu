@@ -25,6 +25,7 @@ struct Smem {
     float k[BN][DP + 4];
     float p[BM][BN + 4];
     float lse[BM];
+    float loss[BM];  // per-row lse - pos, summed by one thread
     int32_t mask[BN];
 };
 
@@ -148,11 +149,20 @@ __global__ void __launch_bounds__(kThreads, 2) lp_scores_fp32_kernel(LpKernelArg
                 const float z = l * expf(m - nm) + expf(pos - nm);
                 lse = nm + logf(z);
                 L.lse[grow0 + lr] = lse;
+                sm.loss[lr] = lse - pos;
+            } else {
+                sm.loss[lr] = 0.f;
             }
             sm.lse[lr] = lse;
         }
     }
 
+    __syncthreads();
+    if (tid == 0) {  // one double-precision add per CTA into the step's loss
+        double acc = 0.0;
+        for (int r = 0; r < BM; r++) acc += (double)sm.loss[r];
+        atomicAdd(L.loss_acc, acc);
+    }
     // ---- sweep 2: probabilities, dQ and dK ---------------------------------------------------------
     constexpr int H = DP / 64;  // column groups of 64 floats; thread owns columns tx*4 + 64*h
     float dq[4][H][4];

@@ -95,6 +95,7 @@ __global__ void __launch_bounds__(256) lp_prep_kernel(LpKernelArgs a) {
     const bool vec_e = (d.emb_stride % 4 == 0) && (((uintptr_t)d.node_emb) & 15) == 0 && D % 4 == 0;
     const bool vec_r = D % 4 == 0 && ((((uintptr_t)d.rel) | ((uintptr_t)d.inv_rel)) & 15) == 0;
     const bool write_k32 = d.precision != GE2_PRECISION_F16;  // the tensor path reads only the fp16 copy of the negatives
+    if (blockIdx.x == 0 && tid == 0) *L.loss_acc = 0.0;        // the scores kernel of this step adds every row's loss term to it
     for (int64_t w = ((int64_t)blockIdx.x * blockDim.x + tid) >> 3; w < total_pad; w += groups) {
         if (w >= total) continue;
         if (w < q_rows) {
@@ -207,6 +208,8 @@ __global__ void __launch_bounds__(256) lp_finish_kernel(LpKernelArgs a, int rows
     const bool vec_e = (d.emb_stride % 4 == 0) && (((uintptr_t)d.node_emb) & 15) == 0 && D % 4 == 0;
     const bool vec_r = D % 4 == 0 && ((((uintptr_t)d.rel) | ((uintptr_t)d.inv_rel)) & 15) == 0;
 
+    // loss = sum over sides and padded rows of (lse - pos), accumulated in double by the scores kernel that ran before
+    if (blockIdx.x == 0 && tid == 0) *d.loss = (float)*L.loss_acc;
     for (int k = tid; k < kFinSlots * 128; k += 256) (&sm.acc[0][0])[k] = 0.f;
     if (tid < kFinSlots) sm.tag[tid] = kFinEmpty;
     __syncthreads();
@@ -338,24 +341,6 @@ __global__ void __launch_bounds__(256) lp_finish_kernel(LpKernelArgs a, int rows
     }
 }
 
-// loss = sum over sides and padded rows of (lse - pos); fixed reduction order so the value is reproducible
-__global__ void __launch_bounds__(1024) lp_loss_kernel(const float* __restrict__ lse, const float* __restrict__ pos, int64_t n,
-                                                       float* __restrict__ loss) {
-    __shared__ double s_part[32];
-    double acc = 0.0;
-    for (int64_t i = threadIdx.x; i < n; i += blockDim.x) acc += (double)lse[i] - (double)pos[i];
-#pragma unroll
-    for (int o = 16; o > 0; o >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, o);
-    if ((threadIdx.x & 31) == 0) s_part[threadIdx.x >> 5] = acc;
-    __syncthreads();
-    if (threadIdx.x < 32) {
-        double v = threadIdx.x < (blockDim.x >> 5) ? s_part[threadIdx.x] : 0.0;
-#pragma unroll
-        for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
-        if (threadIdx.x == 0) *loss = (float)v;
-    }
-}
-
 __global__ void __launch_bounds__(256) copy_pos_kernel(const float* __restrict__ pos, int Bp, float* __restrict__ out0, float* __restrict__ out1,
                                                        int S) {
     const int i = blockIdx.x * blockDim.x + threadIdx.x;
@@ -413,7 +398,8 @@ extern "C" int ge2_lp_step(const ge2_lp_desc* desc, ge2_stream_t stream_) {
 
     const int phases = desc->phases == 0 ? 7 : desc->phases;
     if (phases & 2) GE2_CUDA_TRY(cudaMemsetAsync(L.dK, 0, L.zero_bytes, stream));
-    if (phases & 4) GE2_CUDA_TRY(cudaMemsetAsync(desc->node_grad, 0, (size_t)desc->U * desc->D * 4, stream));
+    if ((phases & 4) && !(desc->flags & GE2_LP_NODE_GRAD_IS_ZERO))
+        GE2_CUDA_TRY(cudaMemsetAsync(desc->node_grad, 0, (size_t)desc->U * desc->D * 4, stream));
     if (phases & 1) {
     GE2_CUDA_TRY(cudaMemsetAsync(L.mask, 0xFF, (size_t)L.S * L.CN * 4, stream));
     if (desc->deg_sample_rows != nullptr) {
@@ -449,8 +435,6 @@ extern "C" int ge2_lp_step(const ge2_lp_desc* desc, ge2_stream_t stream_) {
     const int fin_ctas = (int)(fin_rows < (int64_t)kNumSMs * 4 * 32 ? ceil_div<int64_t>(fin_rows, 32) : (int64_t)kNumSMs * 4);
     const int rows_per_cta = (int)round_up<int64_t>(ceil_div<int64_t>(fin_rows, fin_ctas), 32);
     lp_finish_kernel<<<(unsigned)ceil_div<int64_t>(fin_rows, rows_per_cta), 256, 0, stream>>>(a, rows_per_cta);
-    GE2_LAUNCH_CHECK();
-    lp_loss_kernel<<<1, 1024, 0, stream>>>(L.lse, L.pos, (int64_t)L.S * L.Bp, desc->loss);
     GE2_LAUNCH_CHECK();
     if (desc->pos_scores != nullptr || desc->inv_pos_scores != nullptr) {
         copy_pos_kernel<<<ceil_div(L.Bp, 256), 256, 0, stream>>>(L.pos, L.Bp, desc->pos_scores, desc->inv_pos_scores, L.S);

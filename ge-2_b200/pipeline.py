@@ -107,7 +107,7 @@ class BatchPipeline:
             rel_ids=rel_ids if cfg.has_relations else None, edge_stride=1, rel_stride=rel_stride or 1, dst_negs=self.dst_negs_local,
             src_negs=self.src_negs_local, deg_sample_rows=self.deg_rows if cfg.n_deg > 0 else None, n_deg=cfg.n_deg,
             rel=self.rel, inv_rel=self.inv_rel if cfg.sides == 2 else None, node_grad=self.node_grad, rel_grad=self.rel_grad,
-            inv_rel_grad=self.inv_rel_grad, loss=self.loss, status=self.status)
+            inv_rel_grad=self.inv_rel_grad, loss=self.loss, status=self.status, node_grad_is_zero=True)
         if self._ws is None:
             self._ws = torch.empty(capi.lp_workspace_bytes(d), dtype=torch.uint8, device=self.device)
         d.workspace, d.workspace_bytes = self._ws.data_ptr(), self._ws.numel()
@@ -148,7 +148,9 @@ class BatchPipeline:
 
     def _update(self):
         cfg = self.cfg
-        capi.adagrad_scatter(self.table, self.state, self.unique, self.node_grad, cfg.lr, U=self.cap, U_dev=self.count, status=self.status)
+        # clear_grad: the rows just consumed are zeroed in the same pass, so the next step needs no memset of the gradient buffer
+        capi.adagrad_scatter(self.table, self.state, self.unique, self.node_grad, cfg.lr, U=self.cap, U_dev=self.count, clear_grad=True,
+                             status=self.status)
         if cfg.has_relations:
             dl = cfg.lr if cfg.dense_lr is None else cfg.dense_lr
             capi.dense_adagrad(self.rel, self.rel_state, self.rel_grad, dl, grad_scale=self.grad_scale, clear_grad=True)

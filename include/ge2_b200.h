@@ -94,6 +94,10 @@ GE2_API int ge2_pack_ids(const int64_t *const parts[4], const int64_t lens[4], c
 #define GE2_DECODER_DISTMULT 0 /* Hadamard relation operator; with has_relations == 0 this is the "Dot" decoder */
 #define GE2_DECODER_COMPLEX 1  /* complex Hadamard: first D/2 columns real, remaining D - D/2 imaginary         */
 
+/* ge2_lp_desc.flags: the caller guarantees node_grad is all zero on entry (e.g. ge2_adagrad_scatter with clear_grad
+ * consumed the previous batch's gradients), so the step skips its own memset of U * D floats */
+#define GE2_LP_NODE_GRAD_IS_ZERO 1
+
 #define GE2_PRECISION_FP32 0 /* CUDA-core FFMA contraction, fp32 throughout (1e-4 relative parity)      */
 #define GE2_PRECISION_F16 1  /* tcgen05 kind::f16 tiles (fp16 operands, 11-bit significand like TF32), fp32
                                 accumulate in TMEM, fp32 everywhere else (1e-2 relative parity)         */
@@ -141,13 +145,13 @@ typedef struct ge2_lp_desc {
     int64_t src_filter_n;
     const int64_t *deg_sample_rows;
     int32_t n_deg;
-    int32_t reserved1;
+    int32_t flags;        /* GE2_LP_* bits */
 
     const float *rel;     /* [R, D] relation_embeddings                                           */
     const float *inv_rel; /* [R, D] inverse_relation_embeddings                                   */
 
     /* outputs */
-    float *node_grad;    /* [U, D]  d loss / d node_emb, overwritten                               */
+    float *node_grad;    /* [U, D]  d loss / d node_emb, overwritten (zeroed first unless GE2_LP_NODE_GRAD_IS_ZERO) */
     float *rel_grad;     /* [R, D]  accumulated into (+=), like autograd's .grad                   */
     float *inv_rel_grad; /* [R, D]  accumulated into (+=)                                          */
     float *loss;         /* [1]     overwritten                                                    */
