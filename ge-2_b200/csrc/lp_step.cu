@@ -201,7 +201,7 @@ __global__ void __launch_bounds__(256) lp_finish_kernel(LpKernelArgs a, int rows
     const int group = tid / kFinLanes;                    // 32 groups per CTA
     const unsigned gmask = 0xFFu << ((tid & 31) & ~7);    // the 8 lanes of this group inside the warp
     const int gleader = (tid & 31) & ~7;
-    const int64_t e_rows = (int64_t)L.S * d.B;
+    const int64_t e_rows = d.B;  // one row group per edge (both sides), then one per negative
     const int64_t total = e_rows + (int64_t)L.S * L.CN;
     const int D = d.D, h = D / 2, ld = L.ld;
     const bool vec4 = (D % 4 == 0) && (((uintptr_t)d.node_grad | (uintptr_t)d.rel_grad | (uintptr_t)d.inv_rel_grad) & 15) == 0;
@@ -248,8 +248,10 @@ __global__ void __launch_bounds__(256) lp_finish_kernel(LpKernelArgs a, int rows
         const int64_t w = w0 + group;  // whole warps stay in the loop (shuffles below), rows past the end do nothing
         const bool live = w < row_end;
         if (live && w < e_rows) {
-            const int s = (int)(w / d.B);
-            const int i = (int)(w - (int64_t)s * d.B);
+            // one edge, both corruption sides at once: side 0 applies the relation to the source and compares with the
+            // destination, side 1 the inverse relation to the destination and compares with the source, so each endpoint
+            // receives one combined row instead of two
+            const int i = (int)w;
             const int64_t sid = d.src_ids[(int64_t)i * d.edge_stride];
             const int64_t did = d.dst_ids[(int64_t)i * d.edge_stride];
             bool ok = sid >= 0 && sid < d.U && did >= 0 && did < d.U;
@@ -259,60 +261,76 @@ __global__ void __launch_bounds__(256) lp_finish_kernel(LpKernelArgs a, int rows
                 ok = ok && rid >= 0 && rid < d.R;
             }
             if (ok) {  // bad rows were flagged by prep
-                const int64_t aid = s == 0 ? sid : did, bid = s == 0 ? did : sid;
-                const float* ea = emb_row(d, aid);
-                const float* eb = emb_row(d, bid);
-                const float* r = d.has_relations ? (s == 0 ? d.rel : d.inv_rel) + rid * D : nullptr;
-                float* rg = d.has_relations ? (s == 0 ? d.rel_grad : d.inv_rel_grad) + rid * D : nullptr;
-                const int64_t qrow = (int64_t)s * L.Bp + i;
-                const float* q = L.Q + qrow * ld;
-                const float* dq = L.dQ + qrow * ld;
-                const float dpos = __expf(L.pos[qrow] - L.lse[qrow]) - 1.0f;  // d loss / d pos_i = softmax prob of the positive - 1
-                const int slot_a = claim(aid), slot_b = claim(bid);
-                const int slot_r = r != nullptr ? claim(((long long)(1 + s) << 40) | rid) : -1;
-                for (int k = gl * 4; k < D; k += kFinLanes * 4) {
-                    const float4 q4 = *reinterpret_cast<const float4*>(q + k);
-                    const float4 dq4 = *reinterpret_cast<const float4*>(dq + k);
-                    const float4 eb4 = load4(eb, k, D, vec_e);
-                    const float qv[4] = {q4.x, q4.y, q4.z, q4.w}, dqv[4] = {dq4.x, dq4.y, dq4.z, dq4.w}, ebv[4] = {eb4.x, eb4.y, eb4.z, eb4.w};
-                    float vb[4], va[4], vr[4] = {0.f, 0.f, 0.f, 0.f};
-                    if (r == nullptr) {
+                const float* es = emb_row(d, sid);
+                const float* ed = emb_row(d, did);
+                const int slot_s = claim(sid), slot_d = claim(did);
+                int slot_r[2] = {-1, -1};
+                const float *r[2] = {nullptr, nullptr}, *q[2], *dq[2];
+                float* rg[2] = {nullptr, nullptr};
+                float dpos[2];
 #pragma unroll
-                        for (int e = 0; e < 4; e++) {
-                            vb[e] = dpos * qv[e];
-                            va[e] = dqv[e] + dpos * ebv[e];  // d loss / d adjusted embedding
+                for (int s = 0; s < 2; s++) {
+                    if (s >= L.S) break;
+                    const int64_t qrow = (int64_t)s * L.Bp + i;
+                    q[s] = L.Q + qrow * ld;
+                    dq[s] = L.dQ + qrow * ld;
+                    dpos[s] = __expf(L.pos[qrow] - L.lse[qrow]) - 1.0f;  // d loss / d pos_i = softmax prob of the positive - 1
+                    if (d.has_relations) {
+                        r[s] = (s == 0 ? d.rel : d.inv_rel) + rid * D;
+                        rg[s] = (s == 0 ? d.rel_grad : d.inv_rel_grad) + rid * D;
+                        slot_r[s] = claim(((long long)(1 + s) << 40) | rid);
+                    }
+                }
+                for (int k = gl * 4; k < D; k += kFinLanes * 4) {
+                    const float4 s4 = load4(es, k, D, vec_e), d4 = load4(ed, k, D, vec_e);
+                    const float sv[4] = {s4.x, s4.y, s4.z, s4.w}, dv[4] = {d4.x, d4.y, d4.z, d4.w};
+                    float gs[4] = {0.f, 0.f, 0.f, 0.f}, gd[4] = {0.f, 0.f, 0.f, 0.f};  // gradient rows of the source / destination node
+#pragma unroll
+                    for (int s = 0; s < 2; s++) {
+                        if (s >= L.S) break;
+                        const float* ea = s == 0 ? es : ed;            // endpoint the relation is applied to
+                        const float* eb = s == 0 ? ed : es;            // endpoint it is compared with
+                        const float* eav = s == 0 ? sv : dv;
+                        const float* ebv = s == 0 ? dv : sv;
+                        float* ga = s == 0 ? gs : gd;
+                        float* gb = s == 0 ? gd : gs;
+                        const float4 q4 = *reinterpret_cast<const float4*>(q[s] + k);
+                        const float4 dq4 = *reinterpret_cast<const float4*>(dq[s] + k);
+                        const float qv[4] = {q4.x, q4.y, q4.z, q4.w}, dqv[4] = {dq4.x, dq4.y, dq4.z, dq4.w};
+                        float vr[4] = {0.f, 0.f, 0.f, 0.f};
+                        float rv[4] = {0.f, 0.f, 0.f, 0.f};
+                        if (r[s] != nullptr) {
+                            const float4 r4 = load4(r[s], k, D, vec_r);
+                            rv[0] = r4.x; rv[1] = r4.y; rv[2] = r4.z; rv[3] = r4.w;
                         }
-                    } else {
-                        const float4 ea4 = load4(ea, k, D, vec_e), r4 = load4(r, k, D, vec_r);
-                        const float eav[4] = {ea4.x, ea4.y, ea4.z, ea4.w}, rv[4] = {r4.x, r4.y, r4.z, r4.w};
 #pragma unroll
                         for (int e = 0; e < 4; e++) {
                             const int c = k + e;
-                            vb[e] = dpos * qv[e];
-                            const float g = dqv[e] + dpos * ebv[e];
-                            if (d.decoder == GE2_DECODER_DISTMULT) {
-                                va[e] = g * rv[e];
+                            gb[e] += dpos[s] * qv[e];
+                            const float g = dqv[e] + dpos[s] * ebv[e];  // d loss / d adjusted embedding
+                            if (r[s] == nullptr) {
+                                ga[e] += g;
+                            } else if (d.decoder == GE2_DECODER_DISTMULT) {
+                                ga[e] += g * rv[e];
                                 vr[e] = g * eav[e];
                             } else if (c < D) {
                                 // complex Hadamard backward: needs the gradient of the partner component too
                                 const int cp = c < h ? c + h : c - h;
-                                const float gp = dq[cp] + dpos * __ldg(eb + cp);
-                                const float rp = __ldg(r + cp), eap = __ldg(ea + cp);
+                                const float gp = dq[s][cp] + dpos[s] * __ldg(eb + cp);
+                                const float rp = __ldg(r[s] + cp), eap = __ldg(ea + cp);
                                 if (c < h) {  // real component: g = g_re, gp = g_im
-                                    va[e] = g * rv[e] + gp * rp;
+                                    ga[e] += g * rv[e] + gp * rp;
                                     vr[e] = g * eav[e] + gp * eap;
                                 } else {  // imaginary component: g = g_im, gp = g_re
-                                    va[e] = -gp * rv[e] + g * rp;
+                                    ga[e] += -gp * rv[e] + g * rp;
                                     vr[e] = -gp * eav[e] + g * eap;
                                 }
-                            } else {
-                                va[e] = 0.f;
                             }
                         }
+                        if (rg[s] != nullptr) add4(slot_r[s], rg[s], k, make_float4(vr[0], vr[1], vr[2], vr[3]));
                     }
-                    add4(slot_b, d.node_grad + bid * D, k, make_float4(vb[0], vb[1], vb[2], vb[3]));
-                    add4(slot_a, d.node_grad + aid * D, k, make_float4(va[0], va[1], va[2], va[3]));
-                    if (rg != nullptr) add4(slot_r, rg, k, make_float4(vr[0], vr[1], vr[2], vr[3]));
+                    add4(slot_s, d.node_grad + sid * D, k, make_float4(gs[0], gs[1], gs[2], gs[3]));
+                    add4(slot_d, d.node_grad + did * D, k, make_float4(gd[0], gd[1], gd[2], gd[3]));
                 }
             }
         } else if (live) {
@@ -430,7 +448,7 @@ extern "C" int ge2_lp_step(const ge2_lp_desc* desc, ge2_stream_t stream_) {
     }
     if (!(phases & 4)) return GE2_OK;
 
-    const int64_t fin_rows = (int64_t)L.S * desc->B + (int64_t)L.S * L.CN;
+    const int64_t fin_rows = (int64_t)desc->B + (int64_t)L.S * L.CN;
     // contiguous row ranges per CTA (so that repeated rows meet in a CTA's shared table), two CTAs per SM worth of ranges
     const int fin_ctas = (int)(fin_rows < (int64_t)kNumSMs * 4 * 32 ? ceil_div<int64_t>(fin_rows, 32) : (int64_t)kNumSMs * 4);
     const int rows_per_cta = (int)round_up<int64_t>(ceil_div<int64_t>(fin_rows, fin_ctas), 32);
