@@ -150,7 +150,7 @@ __global__ void __launch_bounds__(256) lp_prep_kernel(LpKernelArgs a) {
                     const float4 y = load4(eb, k, D, vec_e);
                     dot += v.x * y.x + v.y * y.y + v.z * y.z + v.w * y.w;
                 }
-                *reinterpret_cast<float4*>(q + k) = v;
+                if (write_k32) *reinterpret_cast<float4*>(q + k) = v;  // only the fp32 scores kernel reads the fp32 copies
                 if (qh != nullptr) store_half4(qh + k, v);
             }
 #pragma unroll
@@ -265,14 +265,13 @@ __global__ void __launch_bounds__(256) lp_finish_kernel(LpKernelArgs a, int rows
                 const float* ed = emb_row(d, did);
                 const int slot_s = claim(sid), slot_d = claim(did);
                 int slot_r[2] = {-1, -1};
-                const float *r[2] = {nullptr, nullptr}, *q[2], *dq[2];
+                const float *r[2] = {nullptr, nullptr}, *dq[2];
                 float* rg[2] = {nullptr, nullptr};
                 float dpos[2];
 #pragma unroll
                 for (int s = 0; s < 2; s++) {
                     if (s >= L.S) break;
                     const int64_t qrow = (int64_t)s * L.Bp + i;
-                    q[s] = L.Q + qrow * ld;
                     dq[s] = L.dQ + qrow * ld;
                     dpos[s] = __expf(L.pos[qrow] - L.lse[qrow]) - 1.0f;  // d loss / d pos_i = softmax prob of the positive - 1
                     if (d.has_relations) {
@@ -294,9 +293,9 @@ __global__ void __launch_bounds__(256) lp_finish_kernel(LpKernelArgs a, int rows
                         const float* ebv = s == 0 ? dv : sv;
                         float* ga = s == 0 ? gs : gd;
                         float* gb = s == 0 ? gd : gs;
-                        const float4 q4 = *reinterpret_cast<const float4*>(q[s] + k);
+                        // the relation-adjusted embedding q = op(ea, r) is recomputed from rows that are loaded anyway
                         const float4 dq4 = *reinterpret_cast<const float4*>(dq[s] + k);
-                        const float qv[4] = {q4.x, q4.y, q4.z, q4.w}, dqv[4] = {dq4.x, dq4.y, dq4.z, dq4.w};
+                        const float dqv[4] = {dq4.x, dq4.y, dq4.z, dq4.w};
                         float vr[4] = {0.f, 0.f, 0.f, 0.f};
                         float rv[4] = {0.f, 0.f, 0.f, 0.f};
                         if (r[s] != nullptr) {
@@ -306,22 +305,25 @@ __global__ void __launch_bounds__(256) lp_finish_kernel(LpKernelArgs a, int rows
 #pragma unroll
                         for (int e = 0; e < 4; e++) {
                             const int c = k + e;
-                            gb[e] += dpos[s] * qv[e];
                             const float g = dqv[e] + dpos[s] * ebv[e];  // d loss / d adjusted embedding
                             if (r[s] == nullptr) {
+                                gb[e] += dpos[s] * eav[e];
                                 ga[e] += g;
                             } else if (d.decoder == GE2_DECODER_DISTMULT) {
+                                gb[e] += dpos[s] * (eav[e] * rv[e]);
                                 ga[e] += g * rv[e];
                                 vr[e] = g * eav[e];
                             } else if (c < D) {
-                                // complex Hadamard backward: needs the gradient of the partner component too
+                                // complex Hadamard forward and backward: both need the partner component
                                 const int cp = c < h ? c + h : c - h;
                                 const float gp = dq[s][cp] + dpos[s] * __ldg(eb + cp);
                                 const float rp = __ldg(r[s] + cp), eap = __ldg(ea + cp);
                                 if (c < h) {  // real component: g = g_re, gp = g_im
+                                    gb[e] += dpos[s] * (eav[e] * rv[e] - eap * rp);
                                     ga[e] += g * rv[e] + gp * rp;
                                     vr[e] = g * eav[e] + gp * eap;
                                 } else {  // imaginary component: g = g_im, gp = g_re
+                                    gb[e] += dpos[s] * (eap * rv[e] + eav[e] * rp);
                                     ga[e] += -gp * rv[e] + g * rp;
                                     vr[e] = -gp * eav[e] + g * eap;
                                 }
