@@ -294,6 +294,7 @@ def main():
     ap.add_argument("--no-aten-chain", action="store_true", help="skip the ATen restatement of the reference's GPU op chain (context figure)")
     ap.add_argument("--steps-per-state", type=int, default=50, help="N > 1: training steps between partition swaps")
     ap.add_argument("--no-graph", action="store_true", help="issue every launch from the host instead of replaying a CUDA graph")
+    ap.add_argument("--no-pipeline", action="store_true", help="do not draw batch t+1 on a side stream while batch t trains")
     ap.add_argument("--cpu-budget", type=float, default=15.0)
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3)
@@ -367,11 +368,13 @@ def main():
     sps = args.steps_per_state
     swaps = [0]
 
-    def maybe_swap(i):
+    def maybe_swap(i, runner=None):
         """superstep boundary: every `sps` steps the ranks exchange partitions (performNextSwap of the reference)"""
         if pbuf is not None and i > 0 and i % sps == 0:
             swaps[0] += 1
             pbuf.swap(supersteps[(1 + swaps[0]) % len(supersteps)])
+            if runner is not None and hasattr(runner, "refill"):
+                runner.refill()  # a new state brings a new edge bucket: the batch drawn ahead is drawn again
 
     # ---- warm-up, then an event-bracketed pass that times the scores kernel alone (roofline) ---------------------
     for i in range(W):
@@ -385,8 +388,12 @@ def main():
     scores_ms = float(np.mean([a.elapsed_time(b) for a, b in ev_pairs]))
 
     # ---- device-resident timing (`value`): K steps, one CUDA-graph launch per step -----------------------------------
-    if use_graph:
+    pipelined = use_graph and not args.no_pipeline
+    if pipelined:
+        graph = pipe.capture_pipelined(edges, num_batches, rel_hook=rel_hook)
+    elif use_graph:
         graph = pipe.capture_resident(edges, num_batches) if world == 1 else pipe.capture_resident_split(edges, num_batches, rel_hook)
+    if use_graph:
         for _ in range(W):
             graph.replay()
     start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
@@ -395,7 +402,7 @@ def main():
     clocks.start()
     start.record()
     for i in range(K):
-        maybe_swap(i)
+        maybe_swap(i, graph if use_graph else None)
         if use_graph:
             graph.replay()
         else:
@@ -406,23 +413,32 @@ def main():
     pipe.check_status()
 
     # ---- end-to-end timing (`e2e`): host edges in, loss out, through the same public step call -----------------
-    first = int(pipe.step_dev.item()) % num_batches
+    first = int(pipe.step_dev[0].item()) % num_batches
     idx = (first + torch.arange(K)) % num_batches
     host_edges = torch.empty((K, B, 3), dtype=torch.int64).pin_memory()
     host_edges.copy_(edges.reshape(num_batches, B, 3)[idx.to(device)].cpu())
     host_loss = torch.zeros(K, dtype=torch.float32).pin_memory()
     stage = torch.empty((B, 3), dtype=torch.int64, device=device)
     stage.copy_(host_edges[0])
-    if use_graph:
+    if pipelined:
+        # two staging slots: while batch i trains, the ids of batch i+1 are drawn from the slot copied during step i-1
+        graph_e2e = pipeline.HostFeed(pipe, 3, rel_hook=rel_hook)
+        graph_e2e.start(host_edges[K - 1], host_edges[0])
+    elif use_graph:
         graph_e2e = pipe.capture_resident(stage, 1) if world == 1 else pipe.capture_resident_split(stage, 1, rel_hook)
 
     def e2e_step(i):
-        maybe_swap(i)
-        stage.copy_(host_edges[i], non_blocking=True)
-        if use_graph:
-            graph_e2e.replay()
+        if pipelined:
+            maybe_swap(i, graph_e2e)
+            graph_e2e.step(host_edges[(i + 1) % K], host_loss[i:i + 1])  # trains batch i, copies and draws batch i+1
+            return
         else:
-            pipe.enqueue_resident(stage, 1, rel_hook=rel_hook)
+            maybe_swap(i)
+            stage.copy_(host_edges[i], non_blocking=True)
+            if use_graph:
+                graph_e2e.replay()
+            else:
+                pipe.enqueue_resident(stage, 1, rel_hook=rel_hook)
         host_loss[i:i + 1].copy_(pipe.loss, non_blocking=True)
 
     for i in range(min(W, K)):
@@ -432,6 +448,8 @@ def main():
     s2.record()
     for i in range(K):
         e2e_step(i)
+    if pipelined:
+        graph_e2e.drain()
     e2.record()
     barrier()
     ms_e2e = s2.elapsed_time(e2)
@@ -456,10 +474,12 @@ def main():
             config=dict(workload=cfg["name"], per_gpu_batch=B, global_batch=B * world, precision=args.precision,
                         l2="tables (0.8 GB) and edge list larger than L2; rows touched per step are random", parallelism=f"dp{world}" if world > 1 else "single",
                         launch=("one CUDA graph replay per step" if world == 1 else "two CUDA graph replays + one NCCL all-reduce per step") if use_graph else "host-issued launches",
+                        pipelined="ids of batch t+1 are drawn and deduplicated on a side stream while batch t trains" if pipelined else None,
                         partitions=None if pbuf is None else dict(count=4 * world, rows=nodes // 4, steps_per_state=sps, swaps_in_timed_region=(K - 1) // sps,
                                                                   exchange="NCCL send/recv of partition slabs + all-reduce of relation gradients every step")),
             e2e=dict(value=world * K * B / (ms_e2e * 1e-3), unit="edges/s", h2d_bytes_per_step=B * 3 * 8, d2h_bytes_per_step=4,
-                     note="pinned host edges -> H2D, step, loss -> pinned host, all stream-ordered; one synchronize at the end"),
+                     note="pinned host edges -> H2D, step, loss -> pinned host, all stream-ordered; one synchronize at the end"
+                          + ("; the H2D copy issued in step i carries batch i+1 (drawn ahead while batch i trains) and runs on a copy stream, the loss read-back on another" if pipelined else "")),
             gpu_launches=K * (pipe.launches_per_step() + 1),
             clocks=clock_info,
             roofline=dict(bound="tensor", kernel="lp_scores_%s" % args.precision, achieved=achieved, peak=pk["tf"], unit="TFLOP/s",

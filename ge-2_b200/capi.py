@@ -82,7 +82,7 @@ def load_library():
                                          C.c_uint64, C.c_uint64, C.c_void_p, C.c_void_p, C.c_void_p]
     lib.ge2_sample_batch.argtypes = [C.c_void_p, C.c_int32, C.c_int64, C.c_void_p, C.c_int32, C.c_int32, C.c_int32, C.c_int32, C.c_int64, C.c_int32,
                                      C.c_uint64, C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p]
-    lib.ge2_advance_step.argtypes = [C.c_void_p, C.c_void_p]
+    lib.ge2_advance_step.argtypes = [C.c_void_p, C.c_int32, C.c_void_p]
     lib.ge2_remap_edges_to_slots.argtypes = [C.c_void_p, C.c_int64, C.c_int32, C.c_void_p, C.c_int32, C.c_int64, C.c_void_p, C.c_void_p, C.c_void_p]
     lib.ge2_copy_slabs.argtypes = [C.c_void_p, C.c_void_p, C.POINTER(C.c_int32), C.c_int32, C.c_int64, C.c_void_p]
     lib.ge2_check_device.argtypes = [C.c_int]
@@ -246,8 +246,8 @@ def sample_batch(edges, num_batches, step_dev, B, Cn, N, n_deg, domain, want_src
                                           seed, ptr(out_packed), ptr(out_deg_rows), ptr(out_rel), cur_stream()), "ge2_sample_batch")
 
 
-def advance_step(step_dev):
-    check(load_library().ge2_advance_step(ptr(step_dev), cur_stream()), "ge2_advance_step")
+def advance_step(step_dev, n=1):
+    check(load_library().ge2_advance_step(ptr(step_dev), n, cur_stream()), "ge2_advance_step")
 
 
 def remap_edges_to_slots(edges, partition_to_slot, partition_size, out=None, status=None):

@@ -372,11 +372,13 @@ extern "C" int ge2_sample_batch(const int64_t* edges, int32_t cols, int64_t num_
     return GE2_OK;
 }
 
-__global__ void advance_step_kernel(uint64_t* step) { *step += 1; }
+__global__ void advance_step_kernel(uint64_t* step, int n) {
+    if ((int)threadIdx.x < n) step[threadIdx.x] += 1;
+}
 
-extern "C" int ge2_advance_step(uint64_t* step_dev, ge2_stream_t stream_) {
-    if (step_dev == nullptr) return GE2_ERR_INVALID_ARGUMENT;
-    advance_step_kernel<<<1, 1, 0, as_stream(stream_)>>>(step_dev);
+extern "C" int ge2_advance_step(uint64_t* step_dev, int32_t n, ge2_stream_t stream_) {
+    if (step_dev == nullptr || n < 1 || n > 32) return GE2_ERR_INVALID_ARGUMENT;
+    advance_step_kernel<<<1, 32, 0, as_stream(stream_)>>>(step_dev, n);
     GE2_LAUNCH_CHECK();
     return GE2_OK;
 }

@@ -50,6 +50,31 @@ class PipelineConfig:
         return 2 * self.B + self.sides * self.C * self.N
 
 
+class _IdSet:
+    """The per-batch id buffers: packed ids, unique map, inverse (and its column slices), device-side count, degree rows,
+    relation column.  The pipeline owns two sets so that batch t+1 can be sampled and deduplicated while batch t trains."""
+
+    def __init__(self, cfg: "PipelineConfig", cap: int, dev):
+        n_ids, CN, B = cfg.n_ids, cfg.C * cfg.N, cfg.B
+        i64 = dict(dtype=torch.int64, device=dev)
+        self.packed = torch.empty(n_ids, **i64)
+        self.deg_rows = torch.empty((cfg.C, max(cfg.n_deg, 1)), **i64)
+        self.unique = torch.empty(cap, **i64)
+        self.inverse = torch.empty(n_ids, **i64)
+        self.count = torch.zeros(2, dtype=torch.int32, device=dev)
+        self.rel_ids = torch.empty(max(B, 1), **i64)  # the batch's relation column, copied by the sampler
+        self.loss = torch.zeros(1, dtype=torch.float32, device=dev)  # loss of the batch trained from this set
+        self.uws = capi.unique_workspace(cfg.domain, dev)  # one per set: two unique-maps may be in flight at the same time
+        self.src_local = self.inverse[0:B]
+        self.dst_local = self.inverse[B:2 * B]
+        off = 2 * B
+        self.src_negs_local = None
+        if cfg.sides == 2:
+            self.src_negs_local = self.inverse[off:off + CN]
+            off += CN
+        self.dst_negs_local = self.inverse[off:off + CN]
+
+
 class BatchPipeline:
     """Owns the per-batch scratch (ids, unique map, gradients, workspaces); tables are owned by the caller."""
 
@@ -63,16 +88,14 @@ class BatchPipeline:
         assert table.is_cuda and table.dtype == torch.float32 and table.shape[1] == cfg.D and table.is_contiguous()
         n_ids, CN = cfg.n_ids, cfg.C * cfg.N
         self.cap = min(n_ids, cfg.domain)
-        i64 = dict(dtype=torch.int64, device=dev)
-        self.packed = torch.empty(n_ids, **i64)
-        self.deg_rows = torch.empty((cfg.C, max(cfg.n_deg, 1)), **i64)
-        self.unique = torch.empty(self.cap, **i64)
-        self.inverse = torch.empty(n_ids, **i64)
-        self.count = torch.zeros(2, dtype=torch.int32, device=dev)
+        self.ids = [_IdSet(cfg, self.cap, dev), _IdSet(cfg, self.cap, dev)]
+        first = self.ids[0]  # the non-pipelined forms use the first set only; its buffers keep their plain names
+        self.packed, self.deg_rows, self.unique, self.inverse, self.count, self.rel_ids = (
+            first.packed, first.deg_rows, first.unique, first.inverse, first.count, first.rel_ids)
         self.status = torch.zeros(1, dtype=torch.int32, device=dev)
         self.node_grad = torch.zeros((self.cap, cfg.D), dtype=torch.float32, device=dev)
-        self.loss = torch.zeros(1, dtype=torch.float32, device=dev)
-        self.uws = capi.unique_workspace(cfg.domain, dev)
+        self.loss = first.loss
+        self.uws = first.uws
         if cfg.has_relations:
             # one contiguous buffer for both relation-gradient tables: a single all-reduce serves them in the multi-GPU trainer
             self.rel_grads = torch.zeros((cfg.sides,) + tuple(rel.shape), dtype=rel.dtype, device=dev)
@@ -80,34 +103,26 @@ class BatchPipeline:
             self.inv_rel_grad = self.rel_grads[1] if cfg.sides == 2 else None
         else:
             self.rel_grad = self.inv_rel_grad = None
-        B = cfg.B
-        self.src_local = self.inverse[0:B]
-        self.dst_local = self.inverse[B:2 * B]
-        off = 2 * B
-        self.src_negs_local = None
-        if cfg.sides == 2:
-            self.src_negs_local = self.inverse[off:off + CN]
-            off += CN
-        self.dst_negs_local = self.inverse[off:off + CN]
-        self.step_dev = torch.zeros(1, dtype=torch.int64, device=dev)  # device-side batch counter of the graph-replay form
-        self.rel_ids = torch.empty(max(B, 1), **i64)                    # the batch's relation column, copied by the sampler
+        # device-side batch counters of the graph-replay forms: {t, t + 1}
+        self.step_dev = torch.tensor([0, 1], dtype=torch.int64, device=dev)
         self._graph = None
         self._desc = None
         self._ws = None
         self.grad_scale = 1.0  # 1 / #GPUs when relation gradients are all-reduced (model.cpp:188-192 of the reference project)
 
-    def _make_desc(self, edges, rel_ids=None, rel_stride=None):
+    def _make_desc(self, edges, rel_ids=None, rel_stride=None, ids: Optional[_IdSet] = None):
         cfg = self.cfg
+        ids = ids or self.ids[0]
         cols = edges.shape[1]
         if rel_ids is None and cfg.has_relations:
             rel_ids, rel_stride = edges[:, 1], cols
         d = capi.make_lp_desc(
             decoder=cfg.decoder, precision=cfg.precision, B=cfg.B, Cn=cfg.C, N=cfg.N, D=cfg.D, R=cfg.R if cfg.has_relations else 0,
-            U=self.cap, node_emb=self.table, row_index=self.unique, emb_stride=cfg.D, src_ids=self.src_local, dst_ids=self.dst_local,
-            rel_ids=rel_ids if cfg.has_relations else None, edge_stride=1, rel_stride=rel_stride or 1, dst_negs=self.dst_negs_local,
-            src_negs=self.src_negs_local, deg_sample_rows=self.deg_rows if cfg.n_deg > 0 else None, n_deg=cfg.n_deg,
+            U=self.cap, node_emb=self.table, row_index=ids.unique, emb_stride=cfg.D, src_ids=ids.src_local, dst_ids=ids.dst_local,
+            rel_ids=rel_ids if cfg.has_relations else None, edge_stride=1, rel_stride=rel_stride or 1, dst_negs=ids.dst_negs_local,
+            src_negs=ids.src_negs_local, deg_sample_rows=ids.deg_rows if cfg.n_deg > 0 else None, n_deg=cfg.n_deg,
             rel=self.rel, inv_rel=self.inv_rel if cfg.sides == 2 else None, node_grad=self.node_grad, rel_grad=self.rel_grad,
-            inv_rel_grad=self.inv_rel_grad, loss=self.loss, status=self.status, node_grad_is_zero=True)
+            inv_rel_grad=self.inv_rel_grad, loss=ids.loss, status=self.status, node_grad_is_zero=True)
         if self._ws is None:
             self._ws = torch.empty(capi.lp_workspace_bytes(d), dtype=torch.uint8, device=self.device)
         d.workspace, d.workspace_bytes = self._ws.data_ptr(), self._ws.numel()
@@ -146,10 +161,11 @@ class BatchPipeline:
             desc.phases = 4
             capi.lp_step(desc)
 
-    def _update(self):
+    def _update(self, ids: Optional[_IdSet] = None):
         cfg = self.cfg
+        ids = ids or self.ids[0]
         # clear_grad: the rows just consumed are zeroed in the same pass, so the next step needs no memset of the gradient buffer
-        capi.adagrad_scatter(self.table, self.state, self.unique, self.node_grad, cfg.lr, U=self.cap, U_dev=self.count, clear_grad=True,
+        capi.adagrad_scatter(self.table, self.state, ids.unique, self.node_grad, cfg.lr, U=self.cap, U_dev=ids.count, clear_grad=True,
                              status=self.status)
         if cfg.has_relations:
             dl = cfg.lr if cfg.dense_lr is None else cfg.dense_lr
@@ -167,7 +183,7 @@ class BatchPipeline:
                           self.packed, self.deg_rows if cfg.n_deg > 0 else None, self.rel_ids if cfg.has_relations else None)
         capi.unique_bitmap(self.packed, cfg.domain, workspace=self.uws, out_unique=self.unique, out_inverse=self.inverse, out_count=self.count)
         self._backward_and_update(self._make_desc(edges_all, self.rel_ids, 1), scores_events, rel_hook)
-        capi.advance_step(self.step_dev)
+        capi.advance_step(self.step_dev, 2)
 
     def capture_resident(self, edges_all, num_batches: int, rel_hook=None):
         """Captures one resident step into a CUDA graph (after one eager step, which also resolves driver entry points and
@@ -197,7 +213,7 @@ class BatchPipeline:
             self._backward(self._make_desc(edges_all, self.rel_ids, 1))
         with torch.cuda.graph(gb):
             self._update()
-            capi.advance_step(self.step_dev)
+            capi.advance_step(self.step_dev, 2)
 
         class _Split:
             def replay(_self):
@@ -207,6 +223,75 @@ class BatchPipeline:
 
         self._split = (ga, gb)
         return _Split()
+
+    # ---- pipelined form: batch t+1 is sampled and deduplicated on a side stream while batch t trains -----------------
+    def _front(self, ids: _IdSet, edges_all, num_batches: int, counter):
+        """sampler + unique-map into one id set; `counter` is the device counter holding the batch number to use"""
+        cfg = self.cfg
+        capi.sample_batch(edges_all, num_batches, counter, cfg.B, cfg.C, cfg.N, cfg.n_deg, cfg.domain, cfg.sides == 2, cfg.seed,
+                          ids.packed, ids.deg_rows if cfg.n_deg > 0 else None, ids.rel_ids if cfg.has_relations else None)
+        capi.unique_bitmap(ids.packed, cfg.domain, workspace=ids.uws, out_unique=ids.unique, out_inverse=ids.inverse, out_count=ids.count)
+
+    def capture_pipelined(self, edges_all, num_batches: int, rel_hook=None):
+        """Software-pipelined steps: while the decoder step of batch t runs (its scores kernel leaves most SMs idle in its
+        second round), the ids of batch t+1 are drawn and deduplicated on a side stream into the other id set; the optimizer
+        updates of batch t follow the join, so batch t+1 gathers the updated rows.  Two graphs alternate (one per id set);
+        with rel_hook (the multi-GPU all-reduce, host-issued) each step is two graph launches around the hook.
+        Returns an object with replay().  The same batches, negatives and arithmetic as the plain resident form."""
+        self.enqueue_resident(edges_all, num_batches, rel_hook=rel_hook)  # warm-up: driver entry points, function attributes
+        torch.cuda.synchronize(self.device)
+        self._graph_edges = edges_all
+        cfg = self.cfg
+        ctr_now, ctr_next = self.step_dev[0:1], self.step_dev[1:2]
+        self._front(self.ids[0], edges_all, num_batches, ctr_now)  # ids of the first pipelined batch
+        torch.cuda.synchronize(self.device)
+        graphs = []
+        for p in (0, 1):
+            cur, nxt = self.ids[p], self.ids[1 - p]
+            ga = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(ga):
+                main = torch.cuda.current_stream()
+                side = torch.cuda.Stream(device=self.device)
+                side.wait_stream(main)
+                with torch.cuda.stream(side):
+                    self._front(nxt, edges_all, num_batches, ctr_next)
+                self._backward(self._make_desc(edges_all, cur.rel_ids, 1, ids=cur))
+                main.wait_stream(side)
+                if rel_hook is None:
+                    self._update(cur)
+                    capi.advance_step(self.step_dev, 2)
+            gb = None
+            if rel_hook is not None:
+                gb = torch.cuda.CUDAGraph()
+                with torch.cuda.graph(gb):
+                    self._update(cur)
+                    capi.advance_step(self.step_dev, 2)
+            graphs.append((ga, gb))
+        pipe = self
+
+        class _Pipelined:
+            parity = 0
+
+            def replay(_self):
+                ga, gb = graphs[_self.parity]
+                ga.replay()
+                if gb is not None:
+                    rel_hook(pipe)
+                    gb.replay()
+                _self.parity ^= 1
+
+            @property
+            def loss(_self):
+                """device scalar holding the loss of the batch trained by the last replay"""
+                return pipe.ids[_self.parity ^ 1].loss
+
+            def refill(_self):
+                """Draws the ids of the coming batch again (host-issued): call after the resident edge list was replaced,
+                e.g. at a partition swap, since the batch sampled ahead came from the old list."""
+                pipe._front(pipe.ids[_self.parity], edges_all, num_batches, ctr_now)
+
+        self._pipelined = graphs
+        return _Pipelined()
 
     def replay(self):
         self._graph.replay()
@@ -220,6 +305,65 @@ class BatchPipeline:
     def check_status(self):
         """Synchronises and raises if any kernel flagged bad data (call between epochs, not per batch)."""
         torch.cuda.synchronize(self.device)
-        word = int(self.status.item()) | int(self.count[1].item())
+        word = int(self.status.item()) | int(self.ids[0].count[1].item()) | int(self.ids[1].count[1].item())
         if word:
             raise capi.Ge2Error("device status: " + capi.decode_status(word))
+
+
+class HostFeed:
+    """Trains batches that arrive in pinned host memory through the pipelined graphs, with the copies off the critical path.
+
+    start(batch0, batch1) trains batch0 (host-issued, also the warm-up the capture needs) and draws the ids of batch1;
+    every later step(next_batch, loss_out) trains the batch drawn ahead while, on a side stream, next_batch is drawn.
+    The host-to-device copy of next_batch runs on its own stream during the previous step; the 4-byte loss read-back runs on
+    a third stream.  Each loss slot and each staging slot is reused every second step; events order the reuse.
+    Batches are trained exactly once, in the order given, with the same sampler counters as the resident forms."""
+
+    def __init__(self, pipe: BatchPipeline, cols: int, rel_hook=None):
+        self.pipe, self.rel_hook = pipe, rel_hook
+        dev = pipe.device
+        self.stage = torch.empty((2, pipe.cfg.B, cols), dtype=torch.int64, device=dev)
+        self.h2d, self.d2h = torch.cuda.Stream(device=dev), torch.cuda.Stream(device=dev)
+        self.copied = [torch.cuda.Event() for _ in range(2)]
+        self.done = [torch.cuda.Event() for _ in range(2)]
+        self.read = [torch.cuda.Event() for _ in range(2)]
+        self.runner, self.j = None, 0
+
+    def start(self, batch0, batch1):
+        pipe = self.pipe
+        c = int(pipe.step_dev[0].item())
+        self.stage[c % 2].copy_(batch0)
+        self.stage[(c + 1) % 2].copy_(batch1)
+        self.slot0 = c + 2
+        self.runner = pipe.capture_pipelined(self.stage.view(2 * pipe.cfg.B, -1), 2, rel_hook=self.rel_hook)
+        torch.cuda.synchronize(pipe.device)
+        self.j = 0
+
+    def step(self, next_batch, loss_out=None):
+        """next_batch: pinned host tensor [B, cols] (the batch after the one trained by this call);
+        loss_out: pinned host tensor of one float receiving this step's loss (valid after a synchronize)."""
+        j, main = self.j, torch.cuda.current_stream()
+        k = j % 2
+        if j >= 2:
+            self.h2d.wait_event(self.done[k])  # the sampler of step j-2 was the last reader of this staging slot
+        with torch.cuda.stream(self.h2d):
+            self.stage[(self.slot0 + j) % 2].copy_(next_batch, non_blocking=True)
+            self.copied[k].record()
+        main.wait_event(self.copied[k])
+        if j >= 2 and loss_out is not None:
+            main.wait_event(self.read[k])      # this step overwrites the loss slot read back two steps ago
+        self.runner.replay()
+        self.done[k].record()
+        if loss_out is not None:
+            self.d2h.wait_event(self.done[k])
+            with torch.cuda.stream(self.d2h):
+                loss_out.copy_(self.runner.loss, non_blocking=True)
+                self.read[k].record()
+        self.j = j + 1
+
+    def drain(self):
+        """makes the current stream wait for the loss read-backs still in flight (call before timing stops or before reading them)"""
+        torch.cuda.current_stream().wait_stream(self.d2h)
+
+    def refill(self):
+        self.runner.refill()

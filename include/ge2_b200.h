@@ -220,11 +220,12 @@ GE2_API int ge2_sample_negatives(const int64_t *src_ids, const int64_t *dst_ids,
  * (*step_dev % num_batches) of the resident, already shuffled edge list edges[num_batches * B, cols] (the reference slices
  * its shuffled active edges the same way, cpp/src/data/dataloader.cpp:671-689), the generator is keyed by (seed, *step_dev),
  * and the batch's relation column is copied to out_rel_ids[B] (cols == 3) so that no later kernel needs the edge pointer.
- * ge2_advance_step increments the device-side counter (one launch at the end of the step). */
+ * ge2_advance_step increments n consecutive device-side counters (one launch at the end of the step; a pipelined host
+ * keeps {t, t + 1} so that batch t + 1 can be sampled while batch t is still training). */
 GE2_API int ge2_sample_batch(const int64_t *edges, int32_t cols, int64_t num_batches, const uint64_t *step_dev, int32_t B, int32_t C,
                              int32_t N, int32_t n_deg, int64_t domain, int32_t want_src_negs, uint64_t seed, int64_t *out_packed_ids,
                              int64_t *out_deg_rows, int64_t *out_rel_ids, ge2_stream_t stream);
-GE2_API int ge2_advance_step(uint64_t *step_dev, ge2_stream_t stream);
+GE2_API int ge2_advance_step(uint64_t *step_dev, int32_t n, ge2_stream_t stream);
 
 /* GraphModelStorage::mapEdgesWithPartitionSlots_ (cpp/src/storage/graph_storage.cpp:270-303):
  * id -> slot[id / partition_size] * partition_size + id % partition_size on the first and last column of

@@ -69,7 +69,7 @@ def test_graph_replay_equals_host_issued_steps(ge2, cuda_device):
                       workloads.zipf_ids(rng, nb * B, nodes, 1.0)], axis=1).astype(np.int64)
     d_edges = torch.from_numpy(edges).to(cuda_device)
     results = []
-    for mode in ("host", "graph"):
+    for mode in ("host", "graph", "pipelined"):
         cfg = pipeline.PipelineConfig("COMPLEX", B, C, N, 0.5, D, R, nodes, lr=0.1, precision="fp32")
         t = lambda a: torch.from_numpy(a.copy()).to(cuda_device)
         d_table, d_state, d_rel, d_inv = t(table), t(state), t(rel), t(rel)
@@ -78,13 +78,56 @@ def test_graph_replay_equals_host_issued_steps(ge2, cuda_device):
             for _ in range(3):
                 pipe.enqueue_resident(d_edges, nb)
         else:
-            g = pipe.capture_resident(d_edges, nb)  # one host-issued step, then the capture
+            # one host-issued step, then the capture; the pipelined form draws batch t+1 on a side stream during step t
+            g = pipe.capture_resident(d_edges, nb) if mode == "graph" else pipe.capture_pipelined(d_edges, nb)
             g.replay()
             g.replay()
         pipe.check_status()
-        assert int(pipe.step_dev) == 3
-        results.append((d_table.cpu().numpy(), d_state.cpu().numpy(), d_rel.cpu().numpy(), float(pipe.loss)))
-    for a, b in zip(results[0][:3], results[1][:3]):
-        assert np.abs(a - b).max() <= 1e-5 * np.abs(a).max()
-    assert abs(results[0][3] - results[1][3]) <= 1e-5 * abs(results[0][3])
+        assert pipe.step_dev.tolist() == [3, 4]
+        results.append((d_table.cpu().numpy(), d_state.cpu().numpy(), d_rel.cpu().numpy(), float(g.loss if mode == "pipelined" else pipe.loss)))
+    for other in results[1:]:
+        for a, b in zip(results[0][:3], other[:3]):
+            assert np.abs(a - b).max() <= 1e-5 * np.abs(a).max()
+        assert abs(results[0][3] - other[3]) <= 1e-5 * abs(results[0][3])
     assert np.abs(results[0][0] - table).max() > 0  # and the steps did train
+
+
+@pytest.mark.gpu
+def test_host_feed_trains_the_same_batches_as_the_resident_form(cuda_device):
+    """Batches fed from pinned host memory through the pipelined graphs (copies on side streams) give the tables and the
+    per-step losses of the resident form stepping over the same batches in the same order."""
+    from importlib import import_module
+
+    pipeline = import_module("ge-2_b200.pipeline")
+    rng = np.random.default_rng(33)
+    nodes, B, C, N, D, R, nb = 5000, 384, 2, 128, 64, 11, 6
+    table = (0.3 * rng.standard_normal((nodes, D))).astype(np.float32)
+    state = (0.01 + 0.05 * rng.random((nodes, D))).astype(np.float32)
+    rel = (1 + 0.2 * rng.standard_normal((R, D))).astype(np.float32)
+    edges = np.stack([workloads.zipf_ids(rng, nb * B, nodes, 1.0), workloads.zipf_ids(rng, nb * B, R, 1.2),
+                      workloads.zipf_ids(rng, nb * B, nodes, 1.0)], axis=1).astype(np.int64)
+    host = torch.from_numpy(edges).reshape(nb, B, 3).pin_memory()
+    d_edges = torch.from_numpy(edges).to(cuda_device)
+    out = []
+    for mode in ("resident", "host_feed"):
+        cfg = pipeline.PipelineConfig("DISTMULT", B, C, N, 0.5, D, R, nodes, lr=0.1, precision="fp32")
+        t = lambda a: torch.from_numpy(a.copy()).to(cuda_device)
+        d_table, d_state, d_rel, d_inv = t(table), t(state), t(rel), t(rel)
+        pipe = pipeline.BatchPipeline(cfg, d_table, d_state, d_rel, torch.zeros_like(d_rel), d_inv, torch.zeros_like(d_inv))
+        losses = torch.zeros(nb, dtype=torch.float32).pin_memory()
+        if mode == "resident":
+            for i in range(nb - 1):
+                pipe.enqueue_resident(d_edges, nb)
+                losses[i:i + 1].copy_(pipe.loss)
+        else:
+            feed = pipeline.HostFeed(pipe, 3)
+            feed.start(host[0], host[1])  # trains batch 0
+            losses[0:1].copy_(pipe.loss)
+            for i in range(1, nb - 1):
+                feed.step(host[i + 1], losses[i:i + 1])  # trains batch i, draws batch i+1
+            feed.drain()
+        pipe.check_status()
+        out.append((d_table.cpu().numpy(), d_state.cpu().numpy(), d_rel.cpu().numpy(), losses.numpy().copy()))
+    for a, b in zip(out[0], out[1]):
+        assert np.abs(a - b).max() <= 1e-5 * np.abs(a).max()
+    assert (out[0][3][: nb - 1] > 0).all()
