@@ -167,7 +167,11 @@ __global__ void __launch_bounds__(kThreads, 1)
     // The row blocks of one chunk run side by side and all reduce into the same dK rows; each starts its sweeps at a
     // different tile so that at any moment they touch different rows instead of queueing on the same L2 lines.
     const int rot = (blockIdx.x / nsplit) % T_loc;
-    auto tile_n0 = [&](int i) { return (split_h + nsplit * (((i < nA ? i : i - nA) + rot) % T_loc)) * BN; };
+    auto tile_n0 = [&](int i) {
+        int lt = (i < nA ? i : i - nA) + rot;  // both terms are below T_loc: one conditional subtraction instead of a modulo
+        lt = lt >= T_loc ? lt - T_loc : lt;
+        return (split_h + nsplit * lt) * BN;
+    };
     constexpr int NB = LY::NB;
 
 #ifdef GE2_TRACE
@@ -206,6 +210,16 @@ __global__ void __launch_bounds__(kThreads, 1)
     const uint32_t tS = tmem, tdQ = tmem + 128, tdK = tmem + 256;
     const uint32_t lane_sel = (uint32_t)((warp & 3) * 32) << 16;  // this warp's quarter of the 128 TMEM lanes
     auto wait = [&](int bar, uint32_t parity) { return pipe_wait(&bars[bar], parity, s_abort, d.status); };
+    // Whole-warp wait: one lane polls until the phase completes (32 lanes polling the same mbarrier slow every other role's
+    // polls down); then every lane observes the completed phase with a single try_wait of its own, which the ordering of
+    // its later tensor-memory and shared-memory reads hangs on.
+    auto warp_wait = [&](int bar, uint32_t parity) -> bool {
+        int ok = 1;
+        if (lane == 0) ok = wait(bar, parity) ? 1 : 0;
+        ok = __shfl_sync(0xffffffffu, ok, 0);
+        if (ok) ok = mbar_try_wait(&bars[bar], parity) ? 1 : 0;
+        return __all_sync(0xffffffffu, ok) != 0;
+    };
 
     if (warp == kTmaWarp) {
         // ================================ TMA producer ================================
@@ -231,8 +245,11 @@ __global__ void __launch_bounds__(kThreads, 1)
         if (lane == 0) {
             const uint32_t aQ = smem_u32(sQ), aK0 = smem_u32(sK), aP0 = smem_u32(sP);
             constexpr uint32_t kIdescS = idesc_f16(BM, BN, 0, 0);
-            constexpr uint32_t kIdescDQ = idesc_f16(BM, DP, 0, 1);
-            constexpr uint32_t kIdescDK = idesc_f16(BN, DP, 1, 1);
+            // the embedding dimension rounded up to the MMA k step, not to the 64-column block: D = 100 costs 7/8 of DP = 128
+            // (only the N extent of the two gradient contractions is trimmed; the score contraction keeps its DP / 16 steps)
+            const int D16 = ((d.D + kMmaK - 1) / kMmaK) * kMmaK;
+            const uint32_t kIdescDQ = idesc_f16(BM, D16, 0, 1);
+            const uint32_t kIdescDK = idesc_f16(BN, D16, 1, 1);
             bool ok = wait(kBarQ, 0);
             const uint64_t dQk = desc_kmajor_base(aQ), dQm = desc_mnmajor_base(aQ);
             // gradient contractions of sweep-2 iteration j (tile t = j - T)
@@ -349,9 +366,11 @@ __global__ void __launch_bounds__(kThreads, 1)
                     if (__shfl_sync(0xffffffffu, mcur[k], src) == brow) mb[k] |= 1u << src;
                 }
             }
-            const bool general = nv < 64 || dump != nullptr || __any_sync(0xffffffffu, (mb[0] | mb[1]) != 0u);
+            // which 8-column groups of the half tile hold a masked entry for any row of this warp (usually one or two of the 8)
+            const uint32_t wor[2] = {__reduce_or_sync(0xffffffffu, mb[0]), __reduce_or_sync(0xffffffffu, mb[1])};
+            const bool general = nv < 64 || dump != nullptr;  // ragged last tile, or the score dump of the tests
             if (tid == 0) TR(2, i, 0);
-            if (!__all_sync(0xffffffffu, wait(kBarSFull, i & 1))) break;  // warp-uniform: tcgen05.ld is collective
+            if (!warp_wait(kBarSFull, i & 1)) break;  // warp-uniform: tcgen05.ld is collective
             if (tid == 0) TR(2, i, 1);
             tc_fence_after();
             float v[64];
@@ -367,6 +386,14 @@ __global__ void __launch_bounds__(kThreads, 1)
                             float sc = ((mb[j >> 5] >> (j & 31)) & 1u) ? kMasked : v[j];
                             if (dump != nullptr && row_live && j < nv) dump[(int64_t)brow * d.N + n0 + half * 64 + j] = sc;
                             v[j] = j < nv ? sc : -INFINITY;
+                        }
+                    } else {
+#pragma unroll
+                        for (int q = 0; q < 8; q++) {
+                            if ((wor[q >> 2] >> ((q & 3) * 8)) & 0xffu) {  // warp-uniform
+#pragma unroll
+                                for (int j = 8 * q; j < 8 * q + 8; j++) v[j] = ((mb[j >> 5] >> (j & 31)) & 1u) ? kMasked : v[j];
+                            }
                         }
                     }
                     float mx[8];
@@ -389,7 +416,7 @@ __global__ void __launch_bounds__(kThreads, 1)
                     xch[half * 128 + my_row] = make_float2(run_m, run_l);
                     __syncwarp();
                     if (lane == 0) mbar_arrive(&bars[kBarXch]);  // used once per launch: 8 arrivals, one per softmax warp
-                    if (!__all_sync(0xffffffffu, wait(kBarXch, 0))) break;
+                    if (!warp_wait(kBarXch, 0)) break;
                     const float2 other = xch[(half ^ 1) * 128 + my_row];
                     const float nm = fmaxf(run_m, other.x);
                     float l = 0.f;
@@ -412,16 +439,19 @@ __global__ void __launch_bounds__(kThreads, 1)
                 // scores to probabilities first (registers only), so the wait for the P buffer overlaps with the arithmetic
 #pragma unroll
                 for (int j = 0; j < 64; j++) v[j] = exp2f_fast(fmaf(v[j], kLog2e, -lse2));
-                if (general || !row_live) {
+                // Masked entries were overwritten in place by the reference: no gradient reaches them.  Nothing else needs
+                // zeroing: a column past the chunk's last negative meets an all-zero row of K in dQ and is clipped from dK by
+                // the tensor map, and a row past the block's last query has an all-zero row of Q (out-of-range rows of both
+                // tiles are zero-filled by the loads) whose dQ is never stored; exp2 of their zero scores is finite.
 #pragma unroll
-                    for (int j = 0; j < 64; j++) {
-                        // masked entries were overwritten in place by the reference: no gradient reaches them
-                        const bool live = row_live && j < nv && ((mb[j >> 5] >> (j & 31)) & 1u) == 0u;
-                        v[j] = live ? v[j] : 0.f;
+                for (int q = 0; q < 8; q++) {
+                    if ((wor[q >> 2] >> ((q & 3) * 8)) & 0xffu) {  // warp-uniform
+#pragma unroll
+                        for (int j = 8 * q; j < 8 * q + 8; j++) v[j] = ((mb[j >> 5] >> (j & 31)) & 1u) ? 0.f : v[j];
                     }
                 }
                 // the gradient MMAs that read this P buffer two tiles ago must be done
-                if (!__all_sync(0xffffffffu, wait(kBarPEmpty + pb, ((t >> 1) & 1) ^ 1))) break;
+                if (!warp_wait(kBarPEmpty + pb, ((t >> 1) & 1) ^ 1)) break;
                 if (tid == 0) TR(2, i, 2);
                 unsigned char* sPb = sP + pb * LY::kPBytes;
 #pragma unroll
@@ -448,7 +478,7 @@ __global__ void __launch_bounds__(kThreads, 1)
             const int n0 = tile_n0(nA + t);
             const int valid_n = min(BN, d.N - n0);
             if (tid == kDrainWarp0 * 32) TR(3, t, 0);
-            if (!__all_sync(0xffffffffu, wait(kBarDkFull + (t & 1), (t >> 1) & 1))) { ok = false; break; }
+            if (!warp_wait(kBarDkFull + (t & 1), (t >> 1) & 1)) { ok = false; break; }
             if (tid == kDrainWarp0 * 32) TR(3, t, 1);
             tc_fence_after();
             // Each 32 x 32 slab of the accumulator goes through a per-warp staging buffer in shared memory (128-byte rows,
@@ -471,6 +501,11 @@ __global__ void __launch_bounds__(kThreads, 1)
                     if (tid == kDrainWarp0 * 32) TR(3, t, 2);
                 }
                 if (cb * 32 >= d.D) continue;  // padding columns only: nothing to add
+                {
+                    const int dlim = ((d.D + kMmaK - 1) / kMmaK) * kMmaK - cb * 32;  // accumulator columns past this were never written
+#pragma unroll
+                    for (int j = 0; j < 32; j++) v[j] = j < dlim ? v[j] : 0.f;
+                }
                 unsigned char* scr = scr0 + (cb & 1) * 4096;
                 if (lane == 0) bulk_wait_group_read<1>();  // the reduction that last used this buffer (two slabs ago) has read it
                 __syncwarp();
@@ -489,7 +524,7 @@ __global__ void __launch_bounds__(kThreads, 1)
         }
         if (lane == 0) bulk_wait_group<0>();  // all of this warp's reductions have landed before the CTA can exit
         __syncwarp();
-        if (ok && nB > 0 && __all_sync(0xffffffffu, wait(kBarDqFull, 0))) {
+        if (ok && nB > 0 && warp_wait(kBarDqFull, 0)) {
             tc_fence_after();
 #pragma unroll 1
             for (int cb = 0; cb < DP / 32; cb++) {
@@ -499,7 +534,9 @@ __global__ void __launch_bounds__(kThreads, 1)
                     float* dst = L.dQ + (grow0 + my_lane) * DP + cb * 32;
                     if (nsplit == 1) {
 #pragma unroll
-                        for (int q = 0; q < 8; q++) *reinterpret_cast<float4*>(dst + q * 4) = make_float4(v[4 * q], v[4 * q + 1], v[4 * q + 2], v[4 * q + 3]);
+                        for (int q = 0; q < 8; q++)  // columns up to D rounded to the MMA step were computed; the rest of the row is never read
+                            if (cb * 32 + q * 4 < ((d.D + kMmaK - 1) / kMmaK) * kMmaK)
+                                *reinterpret_cast<float4*>(dst + q * 4) = make_float4(v[4 * q], v[4 * q + 1], v[4 * q + 2], v[4 * q + 3]);
                     } else {  // the row's dQ is the sum over the CTAs that share the chunk's tiles (dQ was zeroed by the host side)
 #pragma unroll
                         for (int q = 0; q < 8; q++)
