@@ -19,15 +19,16 @@
 // cpp/src/nn/loss.cpp:46-63 of the reference project).
 //
 // Warp roles, connected by mbarrier pipelines (no block-wide barrier inside the loops):
-//   warps 0-7   softmax: thread = accumulator row (TMEM lane), warps 0-3 columns [0,64) and 4-7 columns [64,128) of a tile;
-//               S -> registers (the S accumulator is handed back at once) -> running max/sum in the exp2 domain, later -> P
-//   warps 8-11  drain: dK accumulator -> swizzled staging in shared memory -> one TMA reduce-add per 32 x 32 slab into
+//   warps 0-15  softmax, two groups of 8 that take alternate tiles: thread = accumulator row (TMEM lane), 64 columns per warp;
+//               S -> registers (then the S accumulator is handed back) -> running max/sum in the exp2 domain, later -> P
+//   warps 16-19 drain: dK accumulator -> swizzled staging in shared memory -> one TMA reduce-add per 32 x 32 slab into
 //               global dK (row blocks of a chunk add up there); at the end dQ accumulator -> global dQ
-//   warp  12    lane 0: TMA producer for the K ring (and the one-off Q load)
-//   warp  13    lane 0: MMA issuer; the warp also allocates and frees tensor memory
-// The MMA issuer runs the score contraction of tile i+1 before the gradient contractions of tile i, so the tensor
-// pipe has work while the softmax warps turn S(i) into P(i); with two dK accumulators the drain of tile i overlaps the
-// contractions of tile i+1.
+//   warp  20    lane 0: TMA producer for the K ring (and the one-off Q load)
+//   warp  21    lane 0: issues the score contractions; the warp also allocates and frees tensor memory
+//   warp  22    lane 0: issues the gradient contractions of sweep 2
+// Two issuing threads, because one thread would sit in the wait for the probabilities of tile i while the score
+// contraction of tile i+1 could already run; with two dK accumulators the drain of tile i overlaps the contractions of
+// tile i+1, and in sweep 1 (no gradient accumulators yet) the scores alternate between two accumulators.
 // Every mbarrier wait is bounded; a wait that runs out raises GE2_STATUS_PIPE_TIMEOUT and sets a block-wide abort flag
 // that every other wait polls, so all roles fall through to the common exit where tensor memory is released.
 #include <stdlib.h>
@@ -42,8 +43,10 @@ using namespace tc;
 
 constexpr int BM = 128;                 // query rows per CTA  (MMA M)
 constexpr int BN = 128;                 // negatives per tile  (MMA N of the score contraction)
-constexpr int kThreads = 448;           // 8 softmax warps + 4 drain warps + TMA warp + MMA warp
-constexpr int kDrainWarp0 = 8, kTmaWarp = 12, kMmaWarp = 13;
+constexpr int kSoftmaxWarps = 16;       // 4 row quarters (tensor-memory lane groups) x 4 groups of 32 columns
+constexpr int kColGroups = kSoftmaxWarps / 4;
+constexpr int kThreads = 736;           // 16 softmax warps + 4 drain warps + TMA warp + two MMA warps
+constexpr int kDrainWarp0 = kSoftmaxWarps, kTmaWarp = kDrainWarp0 + 4, kMmaWarp = kTmaWarp + 1, kGradWarp = kMmaWarp + 1;
 constexpr int kBlockBytes = 128 * 128;  // one 64-half column block of 128 rows
 constexpr int kMmaK = 16;               // k extent of one kind::f16 MMA (32 bytes)
 constexpr int kStagesK = 3;             // K ring depth
@@ -51,8 +54,8 @@ constexpr uint32_t kTmemCols = 512;
 constexpr float kMasked = -1e9f;
 
 // mbarrier slots
-enum Bar { kBarQ = 0, kBarKFull = 1, kBarKEmpty = kBarKFull + kStagesK, kBarSFull = kBarKEmpty + kStagesK, kBarSEmpty = kBarSFull + 1,
-           kBarPFull = kBarSEmpty + 1, kBarPEmpty = kBarPFull + 2, kBarDkFull = kBarPEmpty + 2, kBarDkEmpty = kBarDkFull + 2, kBarDqFull = kBarDkEmpty + 2,
+enum Bar { kBarQ = 0, kBarKFull = 1, kBarKEmpty = kBarKFull + kStagesK, kBarSFull = kBarKEmpty + kStagesK, kBarSEmpty = kBarSFull + 3,
+           kBarPFull = kBarSEmpty + 3, kBarPEmpty = kBarPFull + 2, kBarDkFull = kBarPEmpty + 2, kBarDkEmpty = kBarDkFull + 2, kBarDqFull = kBarDkEmpty + 2,
            kBarXch, kNumBars };
 
 template <int DP>
@@ -67,7 +70,7 @@ struct Layout {
     static constexpr int kTmem = kBars + kNumBars * 8;           // tensor memory base address
     static constexpr int kAbort = kTmem + 4;
     // 4 drain warps x 2 buffers x (32 rows x 128 bytes): staging for the TMA reductions of dK, 128-byte swizzled.
-    // The half-row (max, sum) exchange at the end of sweep 1 (2 x 128 float2) borrows the same bytes: no drain runs before sweep 2.
+    // The per-column-group (max, sum) exchange at the end of sweep 1 (4 x 128 float2) borrows the same bytes: no drain runs before sweep 2.
     static constexpr int kDrain = ((kAbort + 4 + 1023) / 1024) * 1024;
     static constexpr int kXch = kDrain;
     static constexpr int kEnd = kDrain + 4 * 2 * 4096;
@@ -121,6 +124,7 @@ __device__ __forceinline__ bool pipe_wait(uint64_t* bar, uint32_t parity, volati
 // development aid (not compiled into the shipped library): clock stamps of CTA (0,0,0), read back by a debug export
 __device__ long long g_trace[4][64][8];
 __device__ unsigned long long g_cta_times[2048][2];
+__device__ long long g_wtrace[20][32][4];  // per softmax / drain warp of CTA (0,0,0): clock stamps per iteration
 __device__ __forceinline__ unsigned long long global_ns() {
     unsigned long long t;
     asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t));
@@ -130,14 +134,19 @@ __device__ __forceinline__ unsigned long long global_ns() {
     do {                                                                                             \
         if (blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0 && (it) < 64) g_trace[role][it][k] = clock64(); \
     } while (0)
+#define TRW(w, it, k)                                                                                \
+    do {                                                                                             \
+        if (blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0 && (it) < 32 && (threadIdx.x & 31) == 0) g_wtrace[w][it][k] = clock64(); \
+    } while (0)
 #else
 #define TR(role, it, k)
+#define TRW(w, it, k)
 #endif
 
 template <int DP>
 __global__ void __launch_bounds__(kThreads, 1)
     lp_scores_f16_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK, const __grid_constant__ CUtensorMap tmDK,
-                         LpKernelArgs a, int mode, int nsplit) {
+                         const __grid_constant__ CUtensorMap tmDKt, LpKernelArgs a, int mode, int nsplit) {
     using LY = Layout<DP>;
     extern __shared__ unsigned char smem_raw[];
     unsigned char* smem = (unsigned char*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
@@ -187,13 +196,17 @@ __global__ void __launch_bounds__(kThreads, 1)
         for (int k = 0; k < 2; k++) {
             mbar_init(&bars[kBarDkFull + k], 1);
             mbar_init(&bars[kBarDkEmpty + k], 4);  // one arrival per drain warp
-            mbar_init(&bars[kBarPFull + k], 8);
+            mbar_init(&bars[kBarPFull + k], kSoftmaxWarps);
             mbar_init(&bars[kBarPEmpty + k], 1);
         }
-        mbar_init(&bars[kBarSFull], 1);
-        mbar_init(&bars[kBarSEmpty], 8);  // one arrival per softmax warp
+        for (int k = 0; k < 2; k++) {
+            mbar_init(&bars[kBarSFull + k], 1);
+            mbar_init(&bars[kBarSEmpty + k], kSoftmaxWarps / 2);  // sweep 1: one arrival per warp of the group that owns the tile
+        }
+        mbar_init(&bars[kBarSFull + 2], 1);               // sweep 2: every softmax warp takes part in every tile
+        mbar_init(&bars[kBarSEmpty + 2], kSoftmaxWarps);
         mbar_init(&bars[kBarDqFull], 1);
-        mbar_init(&bars[kBarXch], 8);  // the two halves of every row exchange their (max, sum) once, after sweep 1
+        mbar_init(&bars[kBarXch], kSoftmaxWarps);  // the column groups of every row exchange their (max, sum) once, after sweep 1
         *s_abort = 0;
         mbar_init_fence();
     }
@@ -205,9 +218,14 @@ __global__ void __launch_bounds__(kThreads, 1)
     __syncthreads();
     tc_fence_after();
     const uint32_t tmem = *s_tmem;
-    // tensor memory: S [0,128) (single buffer: the softmax warps copy it to registers at once and hand it back),
-    // dQ [128, 128+DP), two dK accumulators at 256 and 384 so the drain of tile t overlaps the contractions of tile t+1
+    // tensor memory: S [0,128); dQ [128, 128+DP), which sweep 1 borrows as a second S buffer so the score contraction of
+    // tile i+1 never waits for the softmax warps; two dK accumulators at 256 and 384 so the drain of tile t overlaps the
+    // contractions of tile t+1
     const uint32_t tS = tmem, tdQ = tmem + 128, tdK = tmem + 256;
+    // S buffer and its use count for iteration i: sweep 1 alternates two buffers, sweep 2 has only the first
+    const int s_uses1 = (nA + 1) >> 1;  // uses of buffer 0 during sweep 1
+    auto s_buf = [&](int i) { return i < nA ? (i & 1) : 0; };
+    auto s_use = [&](int i) { return i < nA ? (i >> 1) : s_uses1 + (i - nA); };
     const uint32_t lane_sel = (uint32_t)((warp & 3) * 32) << 16;  // this warp's quarter of the 128 TMEM lanes
     auto wait = [&](int bar, uint32_t parity) { return pipe_wait(&bars[bar], parity, s_abort, d.status); };
     // Whole-warp wait: one lane polls until the phase completes (32 lanes polling the same mbarrier slow every other role's
@@ -241,23 +259,53 @@ __global__ void __launch_bounds__(kThreads, 1)
             }
         }
     } else if (warp == kMmaWarp) {
-        // ================================ MMA issuer ================================
+        // ================================ MMA issuer 1: score contractions ================================
         if (lane == 0) {
-            const uint32_t aQ = smem_u32(sQ), aK0 = smem_u32(sK), aP0 = smem_u32(sP);
+            const uint32_t aQ = smem_u32(sQ), aK0 = smem_u32(sK);
             constexpr uint32_t kIdescS = idesc_f16(BM, BN, 0, 0);
+            bool ok = wait(kBarQ, 0);
+            const uint64_t dQk = desc_kmajor_base(aQ);
+            for (int i = 0; ok && i < n_iter; i++) {
+                const int st = i % kStagesK, use = i / kStagesK;
+                const int sb = s_buf(i), su = s_use(i);
+                TR(1, i, 0);
+                if (!wait(kBarKFull + st, use & 1)) break;
+                TR(1, i, 1);
+                if (i < nA) {
+                    if (!wait(kBarSEmpty + sb, (su & 1) ^ 1)) break;
+                } else {
+                    // sweep 2 writes the first accumulator only: its last sweep-1 tile must have been read, then tile by tile
+                    if (i == nA && nA > 0 && !wait(kBarSEmpty + 0, (s_uses1 - 1) & 1)) break;
+                    if (!wait(kBarSEmpty + 2, ((i - nA) & 1) ^ 1)) break;
+                }
+                TR(1, i, 2);
+                tc_fence_after();
+                const uint64_t dKk = desc_kmajor_base(aK0 + st * LY::kTileBytes);
+#pragma unroll
+                for (int ks = 0; ks < DP / kMmaK; ks++) mma_f16_ss(tS + sb * 128, dQk + koff_kmajor(ks), dKk + koff_kmajor(ks), kIdescS, ks > 0);
+                mma_commit(&bars[i < nA ? kBarSFull + (i & 1) : kBarSFull + 2]);
+                if (i < nA) mma_commit(&bars[kBarKEmpty + st]);  // sweep 1 needs the tile for nothing else
+                TR(1, i, 3);
+            }
+        }
+    } else if (warp == kGradWarp) {
+        // ================================ MMA issuer 2: gradient contractions of sweep 2 ================================
+        // A thread of its own, so that the score contraction of the next tile is issued while this one still waits for
+        // the probabilities of the current tile.
+        if (lane == 0 && nB > 0) {
+            const uint32_t aQ = smem_u32(sQ), aK0 = smem_u32(sK), aP0 = smem_u32(sP);
             // the embedding dimension rounded up to the MMA k step, not to the 64-column block: D = 100 costs 7/8 of DP = 128
-            // (only the N extent of the two gradient contractions is trimmed; the score contraction keeps its DP / 16 steps)
             const int D16 = ((d.D + kMmaK - 1) / kMmaK) * kMmaK;
             const uint32_t kIdescDQ = idesc_f16(BM, D16, 0, 1);
             const uint32_t kIdescDK = idesc_f16(BN, D16, 1, 1);
             bool ok = wait(kBarQ, 0);
-            const uint64_t dQk = desc_kmajor_base(aQ), dQm = desc_mnmajor_base(aQ);
-            // gradient contractions of sweep-2 iteration j (tile t = j - T)
-            auto issue_grad = [&](int j) -> bool {
-                const int t = j - nA, pb = t & 1, st = j % kStagesK;
-                if (!wait(kBarPFull + pb, (t >> 1) & 1)) return false;
+            const uint64_t dQm = desc_mnmajor_base(aQ);
+            for (int t = 0; ok && t < nB; t++) {
+                const int j = nA + t, pb = t & 1, st = j % kStagesK;
+                // (no wait on the K stage: the probabilities were made from scores that were made from it)
+                if (!wait(kBarPFull + pb, (t >> 1) & 1)) break;
                 TR(1, j, 4);
-                if (!wait(kBarDkEmpty + (t & 1), ((t >> 1) & 1) ^ 1)) return false;
+                if (!wait(kBarDkEmpty + (t & 1), ((t >> 1) & 1) ^ 1)) break;
                 TR(1, j, 5);
                 tc_fence_after();
                 const uint32_t aK = aK0 + st * LY::kTileBytes, aP = aP0 + pb * LY::kPBytes;
@@ -273,31 +321,18 @@ __global__ void __launch_bounds__(kThreads, 1)
                 mma_commit(&bars[kBarDkFull + (t & 1)]);
                 if (t == nB - 1) mma_commit(&bars[kBarDqFull]);
                 TR(1, j, 6);
-                return true;
-            };
-            for (int i = 0; ok && i < n_iter; i++) {
-                const int st = i % kStagesK, use = i / kStagesK;
-                TR(1, i, 0);
-                if (!wait(kBarKFull + st, use & 1)) { ok = false; break; }
-                TR(1, i, 1);
-                if (!wait(kBarSEmpty, (i & 1) ^ 1)) { ok = false; break; }
-                TR(1, i, 2);
-                tc_fence_after();
-                const uint64_t dKk = desc_kmajor_base(aK0 + st * LY::kTileBytes);
-#pragma unroll
-                for (int ks = 0; ks < DP / kMmaK; ks++) mma_f16_ss(tS, dQk + koff_kmajor(ks), dKk + koff_kmajor(ks), kIdescS, ks > 0);
-                mma_commit(&bars[kBarSFull]);
-                if (i < nA) mma_commit(&bars[kBarKEmpty + st]);  // sweep 1 needs the tile for nothing else
-                TR(1, i, 3);
-                if (i - 1 >= nA) ok = issue_grad(i - 1);
             }
-            if (ok && nB > 0) issue_grad(n_iter - 1);
         }
     } else if (warp < kDrainWarp0) {
-        // ================================ softmax warps (0-7) ================================
-        // Two warps per scheduler so one computes while the other waits on tensor memory or a dependent chain: warps 0-3
-        // take columns [0, 64) of every tile, warps 4-7 columns [64, 128), both for rows 32*(warp & 3) ... + 31.
-        const int half = warp >> 2;                      // which 64 columns of a tile
+        // ================================ softmax warps (0-15) ================================
+        // Two groups of 8 warps take alternate tiles: group g = warp / 8 owns the tiles with (tile index & 1) == g of each
+        // sweep, so while one group waits for its scores or stores its probabilities the other keeps the exp unit busy (all 16
+        // warps on one tile would move through the same phase at the same time and leave the unit idle between tiles).
+        // Within a group, warp w takes rows 32*(w & 3) ... + 31 (its quarter of the tensor-memory lanes) and columns
+        // 64*((w >> 2) & 1) ... + 63 of the tile, as two passes of 32 columns.
+        const int grp = warp >> 3;                       // which tiles
+        const int ch = (warp >> 2) & 1;                  // which 64 columns of a tile
+        const int slot = grp * 2 + ch;                   // where this warp's partial (max, sum) goes in the exchange
         const int my_row = tid & 127;                    // accumulator row / TMEM lane
         const int brow = c * L.npc + row0 + my_row;      // batch row in the padded numbering the filter uses
         const int wrow0 = c * L.npc + row0 + (warp & 3) * 32;  // first batch row of this warp
@@ -307,6 +342,8 @@ __global__ void __launch_bounds__(kThreads, 1)
         const bool row_live = my_row < valid_rows;
         // running max / sum of exp2 in the base-2 domain (scores pre-multiplied by log2 e): one FFMA + one MUFU per score
         float run_m = -INFINITY, run_l = 0.f, lse2 = 0.f, my_loss = 0.f;
+        // fetched now (written by the kernel before this one), needed when the two sweeps meet
+        const float pos_mine = (mode != 1 && row_live) ? __ldg(&L.pos[grow0 + my_row]) : 0.f;
         // the step's loss = sum over rows of (lse - pos): one double-precision atomic per warp
         auto add_row_loss = [&](float v) {
 #pragma unroll
@@ -324,159 +361,227 @@ __global__ void __launch_bounds__(kThreads, 1)
                     m = nm;
                 }
             }
-            const float pos2 = L.pos[grow0 + my_row] * kLog2e;
+            const float pos2 = pos_mine * kLog2e;
             const float nm = fmaxf(m, pos2);
             lse2 = nm + __log2f(l * exp2f_fast(m - nm) + exp2f_fast(pos2 - nm));
-            if (split_h == 0 && half == 0) L.lse[grow0 + my_row] = lse2 * 0.6931471805599453f;
+            if (split_h == 0 && slot == 0) L.lse[grow0 + my_row] = lse2 * 0.6931471805599453f;
             my_loss = (lse2 - pos2) * 0.6931471805599453f;
         }
-        if (mode == 2 && split_h == 0 && half == 0) add_row_loss(my_loss);
         // The filter is sparse: a tile has at most one masked row per column and few of them fall in this warp's 32 rows.
-        // Lane l looks at columns l and l+32 of the warp's half tile; entries that name a row of this warp are handed to
-        // that row's thread, which ends up with one bit per masked column of its own row.  The words of the next tile are
-        // fetched while the current one is processed.
+        // Lane l looks at columns l and l + 32 of the warp's 64; an entry that names a row of this warp is handed to that
+        // row's thread, which ends up with one bit per masked column of its own row.  The words of the group's next tile
+        // are fetched while the current one is processed.
         auto load_mask = [&](int i, int32_t (&m)[2]) {
             if (i < n_iter) {
                 const int n0 = tile_n0(i);
                 const int vn = min(BN, d.N - n0);
 #pragma unroll
                 for (int k = 0; k < 2; k++) {
-                    const int idx = half * 64 + k * 32 + lane;
+                    const int idx = ch * 64 + k * 32 + lane;
                     m[k] = idx < vn ? __ldg(&maskc[n0 + idx]) : -1;
                 }
             } else {
                 m[0] = m[1] = -1;
             }
         };
-        int32_t mnext[2];
-        load_mask(0, mnext);
-        for (int i = 0; i < n_iter; i++) {
-            const int t = i < nA ? i : i - nA;  // local tile index within its sweep
-            const int n0 = tile_n0(i);
-            const int nv = min(BN, d.N - n0) - half * 64;  // live columns among this warp's 64
+        // per-tile preamble shared by both sweeps: mask bits of my row, then the wait for the tile's scores
+        uint32_t mb[2], wor[2];
+        int32_t mnext[2] = {-1, -1};
+        auto mask_bits = [&](int next_i) {
             const int32_t mcur[2] = {mnext[0], mnext[1]};
-            load_mask(i + 1, mnext);
-            uint32_t mb[2] = {0u, 0u};  // mb[k] bit j = column half*64 + 32k + j of this tile is masked for my row
+            load_mask(next_i, mnext);
 #pragma unroll
             for (int k = 0; k < 2; k++) {
+                mb[k] = 0u;  // bit j = column ch*64 + 32k + j of this tile is masked for my row
                 unsigned ballot = __ballot_sync(0xffffffffu, (unsigned)(mcur[k] - wrow0) < 32u);
                 while (ballot != 0) {
                     const int src = __ffs(ballot) - 1;
                     ballot &= ballot - 1;
                     if (__shfl_sync(0xffffffffu, mcur[k], src) == brow) mb[k] |= 1u << src;
                 }
+                // which 8-column groups hold a masked entry for any row of this warp (usually none or one of the 4)
+                wor[k] = __reduce_or_sync(0xffffffffu, mb[k]);
             }
-            // which 8-column groups of the half tile hold a masked entry for any row of this warp (usually one or two of the 8)
-            const uint32_t wor[2] = {__reduce_or_sync(0xffffffffu, mb[0]), __reduce_or_sync(0xffffffffu, mb[1])};
-            const bool general = nv < 64 || dump != nullptr;  // ragged last tile, or the score dump of the tests
+        };
+        bool alive = true;
+        // ---------------- sweep 1: running (max, sum) over the group's tiles ----------------
+        const int first1 = grp;  // the group's first sweep-1 iteration
+        load_mask(first1 < nA ? first1 : n_iter, mnext);
+        for (int i = first1; alive && i < nA; i += 2) {
+            const int n0 = tile_n0(i);
+            mask_bits(i + 2 < nA ? i + 2 : n_iter);
+            const int sb = s_buf(i);
             if (tid == 0) TR(2, i, 0);
-            if (!warp_wait(kBarSFull, i & 1)) break;  // warp-uniform: tcgen05.ld is collective
+            if (!warp_wait(kBarSFull + grp, (i >> 1) & 1)) { alive = false; break; }  // warp-uniform: tcgen05.ld is collective
             if (tid == 0) TR(2, i, 1);
+            TRW(warp, i, 0);
             tc_fence_after();
-            float v[64];
-            tmem_ld_32x64(tS + half * 64 + lane_sel, v);
-            tc_fence_before();
-            __syncwarp();
-            if (lane == 0) mbar_arrive(&bars[kBarSEmpty]);  // the tile is in registers: the S accumulator is free again
-            if (i < nA) {
-                if (nv > 0) {
-                    if (general) {
 #pragma unroll
-                        for (int j = 0; j < 64; j++) {
-                            float sc = ((mb[j >> 5] >> (j & 31)) & 1u) ? kMasked : v[j];
-                            if (dump != nullptr && row_live && j < nv) dump[(int64_t)brow * d.N + n0 + half * 64 + j] = sc;
-                            v[j] = j < nv ? sc : -INFINITY;
-                        }
-                    } else {
-#pragma unroll
-                        for (int q = 0; q < 8; q++) {
-                            if ((wor[q >> 2] >> ((q & 3) * 8)) & 0xffu) {  // warp-uniform
-#pragma unroll
-                                for (int j = 8 * q; j < 8 * q + 8; j++) v[j] = ((mb[j >> 5] >> (j & 31)) & 1u) ? kMasked : v[j];
-                            }
-                        }
-                    }
-                    float mx[8];
-#pragma unroll
-                    for (int k = 0; k < 8; k++) mx[k] = v[k];
-#pragma unroll
-                    for (int j = 8; j < 64; j++) mx[j & 7] = fmaxf(mx[j & 7], v[j]);
-                    const float tmax = fmaxf(fmaxf(fmaxf(mx[0], mx[1]), fmaxf(mx[2], mx[3])), fmaxf(fmaxf(mx[4], mx[5]), fmaxf(mx[6], mx[7])));
-                    const float nm = fmaxf(run_m, tmax * kLog2e);
-                    float add[4] = {0.f, 0.f, 0.f, 0.f};
-#pragma unroll
-                    for (int j = 0; j < 64; j++) add[j & 3] += exp2f_fast(fmaf(v[j], kLog2e, -nm));  // 2^-inf = 0 for absent columns
-                    run_l = fmaf(run_l, exp2f_fast(run_m - nm), (add[0] + add[1]) + (add[2] + add[3]));
-                    run_m = nm;
-                }
-                if (tid == 0) TR(2, i, 3);
-                if (i == nA - 1) {
-                    // the two halves of a row meet in shared memory; the wait is an mbarrier (bounded), not a named barrier
-                    float2* xch = reinterpret_cast<float2*>(smem + LY::kXch);
-                    xch[half * 128 + my_row] = make_float2(run_m, run_l);
+            for (int k = 0; k < 2; k++) {
+                const int nv = min(BN, d.N - n0) - ch * 64 - k * 32;  // live columns among these 32
+                float v[32];
+                tmem_ld_32x32(tS + sb * 128 + ch * 64 + k * 32 + lane_sel, v);
+                if (k == 1) {
+                    tc_fence_before();
                     __syncwarp();
-                    if (lane == 0) mbar_arrive(&bars[kBarXch]);  // used once per launch: 8 arrivals, one per softmax warp
-                    if (!warp_wait(kBarXch, 0)) break;
-                    const float2 other = xch[(half ^ 1) * 128 + my_row];
-                    const float nm = fmaxf(run_m, other.x);
-                    float l = 0.f;
-                    if (nm > -INFINITY) l = run_l * exp2f_fast(run_m - nm) + other.y * exp2f_fast(other.x - nm);
-                    if (row_live) {
-                        if (mode == 1) {  // hand the partial over to the sweep-2 launch
-                            if (half == 0) reinterpret_cast<float2*>(L.part)[(grow0 + my_row) * 4 + split_h] = make_float2(nm, l);
-                        } else {
-                            const float pos2 = L.pos[grow0 + my_row] * kLog2e;
-                            const float nm2 = fmaxf(nm, pos2);
-                            lse2 = nm2 + __log2f(l * exp2f_fast(nm - nm2) + exp2f_fast(pos2 - nm2));
-                            if (half == 0) L.lse[grow0 + my_row] = lse2 * 0.6931471805599453f;
-                            my_loss = (lse2 - pos2) * 0.6931471805599453f;
+                    if (lane == 0) mbar_arrive(&bars[kBarSEmpty + sb]);  // the tile is in registers: this S accumulator is free again
+                    TRW(warp, i, 1);
+                }
+                if (nv <= 0) continue;
+                if (nv < 32 || dump != nullptr) {  // ragged last tile, or the score dump of the tests
+#pragma unroll
+                    for (int j = 0; j < 32; j++) {
+                        float sc = ((mb[k] >> j) & 1u) ? kMasked : v[j];
+                        if (dump != nullptr && row_live && j < nv) dump[(int64_t)brow * d.N + n0 + ch * 64 + k * 32 + j] = sc;
+                        v[j] = j < nv ? sc : -INFINITY;
+                    }
+                } else {
+#pragma unroll
+                    for (int q = 0; q < 4; q++) {
+                        if ((wor[k] >> (q * 8)) & 0xffu) {  // warp-uniform
+#pragma unroll
+                            for (int j = 8 * q; j < 8 * q + 8; j++) v[j] = ((mb[k] >> j) & 1u) ? kMasked : v[j];
                         }
                     }
-                    if (mode == 0 && half == 0) add_row_loss(my_loss);
                 }
-            } else {
-                const int pb = t & 1;
-                // scores to probabilities first (registers only), so the wait for the P buffer overlaps with the arithmetic
+                float mx[4];
 #pragma unroll
-                for (int j = 0; j < 64; j++) v[j] = exp2f_fast(fmaf(v[j], kLog2e, -lse2));
-                // Masked entries were overwritten in place by the reference: no gradient reaches them.  Nothing else needs
-                // zeroing: a column past the chunk's last negative meets an all-zero row of K in dQ and is clipped from dK by
-                // the tensor map, and a row past the block's last query has an all-zero row of Q (out-of-range rows of both
-                // tiles are zero-filled by the loads) whose dQ is never stored; exp2 of their zero scores is finite.
+                for (int q = 0; q < 4; q++) mx[q] = v[q];
 #pragma unroll
-                for (int q = 0; q < 8; q++) {
-                    if ((wor[q >> 2] >> ((q & 3) * 8)) & 0xffu) {  // warp-uniform
+                for (int j = 4; j < 32; j++) mx[j & 3] = fmaxf(mx[j & 3], v[j]);
+                const float tmax = fmaxf(fmaxf(mx[0], mx[1]), fmaxf(mx[2], mx[3]));
+                const float nm = fmaxf(run_m, tmax * kLog2e);
+                float add[4] = {0.f, 0.f, 0.f, 0.f};
 #pragma unroll
-                        for (int j = 8 * q; j < 8 * q + 8; j++) v[j] = ((mb[j >> 5] >> (j & 31)) & 1u) ? 0.f : v[j];
+                for (int j = 0; j < 32; j++) add[j & 3] += exp2f_fast(fmaf(v[j], kLog2e, -nm));  // 2^-inf = 0 for absent columns
+                run_l = fmaf(run_l, exp2f_fast(run_m - nm), (add[0] + add[1]) + (add[2] + add[3]));
+                run_m = nm;
+            }
+            if (tid == 0) TR(2, i, 3);
+            TRW(warp, i, 3);
+        }
+        const int cg = warp >> 2;  // sweep 2: this warp's 32 columns of every tile
+        auto load_mask2 = [&](int i) -> int32_t {
+            if (i >= n_iter) return -1;
+            const int n0 = tile_n0(i);
+            const int idx = cg * 32 + lane;
+            return idx < min(BN, d.N - n0) ? __ldg(&maskc[n0 + idx]) : -1;
+        };
+        int32_t m2next = load_mask2(nA);  // fetched before the exchange below, used after it
+        if (alive && nA > 0) {
+            // the four partials of a row (two groups x two column halves) meet in shared memory; the wait is an mbarrier
+            // (bounded), not a named barrier
+            float2* xch = reinterpret_cast<float2*>(smem + LY::kXch);
+            xch[slot * 128 + my_row] = make_float2(run_m, run_l);
+            __syncwarp();
+            if (lane == 0) mbar_arrive(&bars[kBarXch]);  // used once per launch: one arrival per softmax warp
+            TRW(warp, 31, 0);
+            alive = warp_wait(kBarXch, 0);
+            TRW(warp, 31, 1);
+            if (alive) {
+                float2 pr[kColGroups];
+                float nm = -INFINITY;
+#pragma unroll
+                for (int k = 0; k < kColGroups; k++) {
+                    pr[k] = xch[k * 128 + my_row];
+                    nm = fmaxf(nm, pr[k].x);
+                }
+                float l = 0.f;
+                if (nm > -INFINITY) {
+#pragma unroll
+                    for (int k = 0; k < kColGroups; k++) l += pr[k].y * exp2f_fast(pr[k].x - nm);  // an empty partial has sum 0 and max -inf
+                }
+                if (row_live) {
+                    if (mode == 1) {  // hand the partial over to the sweep-2 launch
+                        if (slot == 0) reinterpret_cast<float2*>(L.part)[(grow0 + my_row) * 4 + split_h] = make_float2(nm, l);
+                    } else {
+                        const float pos2 = pos_mine * kLog2e;
+                        const float nm2 = fmaxf(nm, pos2);
+                        lse2 = nm2 + __log2f(l * exp2f_fast(nm - nm2) + exp2f_fast(pos2 - nm2));
+                        if (slot == 0) L.lse[grow0 + my_row] = lse2 * 0.6931471805599453f;
+                        my_loss = (lse2 - pos2) * 0.6931471805599453f;
                     }
                 }
-                // the gradient MMAs that read this P buffer two tiles ago must be done
-                if (!warp_wait(kBarPEmpty + pb, ((t >> 1) & 1) ^ 1)) break;
-                if (tid == 0) TR(2, i, 2);
-                unsigned char* sPb = sP + pb * LY::kPBytes;
-#pragma unroll
-                for (int q = 0; q < 8; q++) {  // 8 halves = one 16-byte chunk
-                    uint4 pk;
-                    pk.x = pack_half2(v[8 * q + 0], v[8 * q + 1]);
-                    pk.y = pack_half2(v[8 * q + 2], v[8 * q + 3]);
-                    pk.z = pack_half2(v[8 * q + 4], v[8 * q + 5]);
-                    pk.w = pack_half2(v[8 * q + 6], v[8 * q + 7]);
-                    *reinterpret_cast<uint4*>(sPb + swz_chunk_offset(my_row, half * 64 + q * 8)) = pk;
-                }
-                fence_proxy_async_smem();  // P was written with ordinary stores; the MMA reads it through the async proxy
-                __syncwarp();
-                if (lane == 0) mbar_arrive(&bars[kBarPFull + pb]);
-                if (tid == 0) TR(2, i, 3);
+                TRW(warp, 31, 2);
             }
         }
+        // ---------------- sweep 2: probabilities, all 16 warps on every tile ----------------
+        // There is one score accumulator now (the gradient accumulators fill tensor memory), so the tile is spread over all
+        // warps: each copies its 32 x 32 piece to registers and hands the accumulator back at once.  Warp w: rows 32*(w & 3)
+        // ... + 31, columns 32*(w >> 2) ... + 31.
+        for (int i = nA; alive && i < n_iter; i++) {
+            const int t = i - nA, pb = t & 1;
+            const int32_t mcur = m2next;
+            m2next = load_mask2(i + 1);
+            uint32_t mbits = 0u;  // bit j = column cg*32 + j of this tile is masked for my row
+            {
+                unsigned ballot = __ballot_sync(0xffffffffu, (unsigned)(mcur - wrow0) < 32u);
+                while (ballot != 0) {
+                    const int src = __ffs(ballot) - 1;
+                    ballot &= ballot - 1;
+                    if (__shfl_sync(0xffffffffu, mcur, src) == brow) mbits |= 1u << src;
+                }
+            }
+            const uint32_t wbits = __reduce_or_sync(0xffffffffu, mbits);
+            if (tid == 0) TR(2, i, 0);
+            if (!warp_wait(kBarSFull + 2, t & 1)) break;
+            if (tid == 0) TR(2, i, 1);
+            TRW(warp, i, 0);
+            tc_fence_after();
+            float v[32];
+            tmem_ld_32x32(tS + cg * 32 + lane_sel, v);
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(&bars[kBarSEmpty + 2]);  // the tile is in registers: the S accumulator is free again
+            TRW(warp, i, 1);
+#pragma unroll
+            for (int j = 0; j < 32; j++) v[j] = exp2f_fast(fmaf(v[j], kLog2e, -lse2));
+            // Masked entries were overwritten in place by the reference: no gradient reaches them.  Nothing else needs
+            // zeroing: a column past the chunk's last negative meets an all-zero row of K in dQ and is clipped from dK by
+            // the tensor map, and a row past the block's last query has an all-zero row of Q (out-of-range rows of both
+            // tiles are zero-filled by the loads) whose dQ is never stored; exp2 of their zero scores is finite.
+#pragma unroll
+            for (int q = 0; q < 4; q++) {
+                if ((wbits >> (q * 8)) & 0xffu) {  // warp-uniform
+#pragma unroll
+                    for (int j = 8 * q; j < 8 * q + 8; j++) v[j] = ((mbits >> j) & 1u) ? 0.f : v[j];
+                }
+            }
+            // the gradient MMAs that read this P buffer two tiles ago must be done
+            if (!warp_wait(kBarPEmpty + pb, ((t >> 1) & 1) ^ 1)) break;
+            if (tid == 0) TR(2, i, 2);
+            TRW(warp, i, 2);
+            unsigned char* sPb = sP + pb * LY::kPBytes;
+#pragma unroll
+            for (int q = 0; q < 4; q++) {  // 8 halves = one 16-byte chunk
+                uint4 pk;
+                pk.x = pack_half2(v[8 * q + 0], v[8 * q + 1]);
+                pk.y = pack_half2(v[8 * q + 2], v[8 * q + 3]);
+                pk.z = pack_half2(v[8 * q + 4], v[8 * q + 5]);
+                pk.w = pack_half2(v[8 * q + 6], v[8 * q + 7]);
+                *reinterpret_cast<uint4*>(sPb + swz_chunk_offset(my_row, cg * 32 + q * 8)) = pk;
+            }
+            fence_proxy_async_smem();  // P was written with ordinary stores; the MMA reads it through the async proxy
+            __syncwarp();
+            if (lane == 0) mbar_arrive(&bars[kBarPFull + pb]);
+            if (tid == 0) TR(2, i, 3);
+            TRW(warp, i, 3);
+        }
+        // the loss of this block's rows, off the path between the sweeps
+        if (alive && mode != 1 && slot == 0 && (mode == 0 || split_h == 0)) add_row_loss(my_loss);
     } else {
-        // ================================ drain warps (8-11) ================================
+        // ================================ drain warps (16-19) ================================
         const int my_lane = tid - kDrainWarp0 * 32;  // TMEM lane: a negative of the tile for dK, a query row for dQ
-        float* dKc = L.dK + ((int64_t)s * L.CN + (int64_t)c * d.N) * DP;
+        // columns of dK that are reduced into global memory: full 32-column slabs, then a narrow one
+        int full_slabs = d.D / 32, tail = ((d.D % 32) + 3) & ~3;
+        if (tail == 32) {
+            full_slabs++;
+            tail = 0;
+        }
+        const int n_slabs = full_slabs + (tail > 0 ? 1 : 0);
         bool ok = true;
         for (int t = 0; t < nB; t++) {
             const int n0 = tile_n0(nA + t);
-            const int valid_n = min(BN, d.N - n0);
             if (tid == kDrainWarp0 * 32) TR(3, t, 0);
             if (!warp_wait(kBarDkFull + (t & 1), (t >> 1) & 1)) { ok = false; break; }
             if (tid == kDrainWarp0 * 32) TR(3, t, 1);
@@ -487,36 +592,40 @@ __global__ void __launch_bounds__(kThreads, 1)
             // stores, rows past the chunk's last negative are clipped by the tensor map, and the accumulator is handed
             // back as soon as its last slab is in registers.  Two staging buffers alternate, so a slab is written while
             // the TMA engine still reads the previous one.
+            // Only real columns travel: D / 32 full slabs, then one narrow slab (its own tensor map, dense rows of `tail`
+            // floats) for the remainder rounded up to 4 -- with D = 100 that is 100 columns instead of the padded 128; the
+            // reductions into L2 are what bounds this sweep.
             unsigned char* scr0 = smem + LY::kDrain + (warp - kDrainWarp0) * 8192;
 #pragma unroll 1
-            for (int cb = 0; cb < DP / 32; cb++) {
+            for (int cb = 0; cb < n_slabs; cb++) {
                 float v[32];
                 if (tid == kDrainWarp0 * 32 && t == 1) TR(3, 32 + cb, 0);
                 tmem_ld_32x32(tdK + (t & 1) * 128 + lane_sel + cb * 32, v);  // warp-collective
                 if (tid == kDrainWarp0 * 32 && t == 1) TR(3, 32 + cb, 1);
-                if (cb == DP / 32 - 1) {
+                if (cb == n_slabs - 1) {
                     tc_fence_before();
                     __syncwarp();
                     if (lane == 0) mbar_arrive(&bars[kBarDkEmpty + (t & 1)]);
                     if (tid == kDrainWarp0 * 32) TR(3, t, 2);
                 }
-                if (cb * 32 >= d.D) continue;  // padding columns only: nothing to add
-                {
-                    const int dlim = ((d.D + kMmaK - 1) / kMmaK) * kMmaK - cb * 32;  // accumulator columns past this were never written
-#pragma unroll
-                    for (int j = 0; j < 32; j++) v[j] = j < dlim ? v[j] : 0.f;
-                }
                 unsigned char* scr = scr0 + (cb & 1) * 4096;
                 if (lane == 0) bulk_wait_group_read<1>();  // the reduction that last used this buffer (two slabs ago) has read it
                 __syncwarp();
+                const bool narrow = cb == full_slabs;
+                if (!narrow) {
 #pragma unroll
-                for (int q = 0; q < 8; q++)
-                    *reinterpret_cast<float4*>(scr + lane * 128 + ((q ^ (lane & 7)) << 4)) = make_float4(v[4 * q], v[4 * q + 1], v[4 * q + 2], v[4 * q + 3]);
+                    for (int q = 0; q < 8; q++)
+                        *reinterpret_cast<float4*>(scr + lane * 128 + ((q ^ (lane & 7)) << 4)) = make_float4(v[4 * q], v[4 * q + 1], v[4 * q + 2], v[4 * q + 3]);
+                } else {
+#pragma unroll
+                    for (int q = 0; q < 8; q++)
+                        if (q * 4 < tail) *reinterpret_cast<float4*>(scr + lane * (tail * 4) + q * 16) = make_float4(v[4 * q], v[4 * q + 1], v[4 * q + 2], v[4 * q + 3]);
+                }
                 fence_proxy_async_smem();
                 __syncwarp();
                 if (tid == kDrainWarp0 * 32 && t == 1) TR(3, 32 + cb, 2);
                 if (lane == 0) {
-                    tma_reduce_add_3d(&tmDK, cb * 32, n0 + (warp - kDrainWarp0) * 32, zc, scr);
+                    tma_reduce_add_3d(narrow ? &tmDKt : &tmDK, cb * 32, n0 + (warp - kDrainWarp0) * 32, zc, scr);
                     bulk_commit_group();
                 }
                 if (tid == kDrainWarp0 * 32 && t == 1) TR(3, 32 + cb, 3);
@@ -614,16 +723,18 @@ int choose_nsplit(int items, int tiles) {
     return best;
 }
 
-// dK [S*C][N][ld floats] as a 3-D tensor for the reduce-add stores: box = 32 floats x 32 rows, 128-byte swizzle
-int make_map_f32_slab(CUtensorMap* map, float* base, int ld, int rows, int mats) {
+// dK [S*C][N][ld floats] as a 3-D tensor for the reduce-add stores: box = 32 floats x 32 rows with the 128-byte swizzle, or
+// (narrow slab) box_cols < 32 floats x 32 rows, dense
+int make_map_f32_slab(CUtensorMap* map, float* base, int ld, int rows, int mats, int box_cols = 32) {
     EncodeTiledFn fn = encode_fn();
     if (fn == nullptr) return GE2_ERR_CUDA;
     cuuint64_t dims[3] = {(cuuint64_t)ld, (cuuint64_t)rows, (cuuint64_t)mats};
     cuuint64_t strides[2] = {(cuuint64_t)ld * 4, (cuuint64_t)rows * ld * 4};
-    cuuint32_t box[3] = {32, 32, 1};
+    cuuint32_t box[3] = {(cuuint32_t)box_cols, 32, 1};
     cuuint32_t estr[3] = {1, 1, 1};
     CUresult r = fn(map, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 3, base, dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
-                    CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_NONE, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+                    box_cols == 32 ? CU_TENSOR_MAP_SWIZZLE_128B : CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_NONE,
+                    CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
     if (r != CUDA_SUCCESS) {
         g_last_cuda_error = (int)r;
         return GE2_ERR_CUDA;
@@ -642,20 +753,26 @@ int launch(const LpKernelArgs& a, cudaStream_t stream) {
     CUtensorMap tmDK;
     rc = make_map_f32_slab(&tmDK, a.L.dK, DP, a.d.N, a.L.S * a.d.C);
     if (rc != GE2_OK) return rc;
+    CUtensorMap tmDKt = tmDK;  // narrow slab for the last D % 32 columns (rounded up to 4), when there are any
+    const int tail_cols = ((a.d.D % 32) + 3) & ~3;
+    if (tail_cols > 0 && tail_cols < 32) {
+        rc = make_map_f32_slab(&tmDKt, a.L.dK, DP, a.d.N, a.L.S * a.d.C, tail_cols);
+        if (rc != GE2_OK) return rc;
+    }
     const int smem = Layout<DP>::kDynamic;
     GE2_CUDA_TRY(cudaFuncSetAttribute(lp_scores_f16_kernel<DP>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
     const int row_blocks = ceil_div(a.L.npc, BM);
     const int nsplit = choose_nsplit(row_blocks * a.d.C * a.L.S, ceil_div(a.d.N, BN));
     dim3 grid((unsigned)(row_blocks * nsplit), (unsigned)a.d.C, (unsigned)a.L.S);
     if (nsplit == 1) {
-        lp_scores_f16_kernel<DP><<<grid, kThreads, smem, stream>>>(tmQ, tmK, tmDK, a, 0, 1);
+        lp_scores_f16_kernel<DP><<<grid, kThreads, smem, stream>>>(tmQ, tmK, tmDK, tmDKt, a, 0, 1);
         GE2_LAUNCH_CHECK();
     } else {
         // dQ is reduced across the CTAs of a split: it starts from zero (dK next to it is zeroed by the caller already)
         GE2_CUDA_TRY(cudaMemsetAsync(a.L.dQ, 0, (size_t)a.L.S * a.L.Bp * DP * sizeof(float), stream));
-        lp_scores_f16_kernel<DP><<<grid, kThreads, smem, stream>>>(tmQ, tmK, tmDK, a, 1, nsplit);
+        lp_scores_f16_kernel<DP><<<grid, kThreads, smem, stream>>>(tmQ, tmK, tmDK, tmDKt, a, 1, nsplit);
         GE2_LAUNCH_CHECK();
-        lp_scores_f16_kernel<DP><<<grid, kThreads, smem, stream>>>(tmQ, tmK, tmDK, a, 2, nsplit);
+        lp_scores_f16_kernel<DP><<<grid, kThreads, smem, stream>>>(tmQ, tmK, tmDK, tmDKt, a, 2, nsplit);
         GE2_LAUNCH_CHECK();
     }
     return GE2_OK;
@@ -666,6 +783,9 @@ int launch(const LpKernelArgs& a, cudaStream_t stream) {
 #ifdef GE2_TRACE
 extern "C" __attribute__((visibility("default"))) int ge2_debug_read_trace(long long* host_out) {
     return (int)cudaMemcpyFromSymbol(host_out, g_trace, sizeof(long long) * 4 * 64 * 8);
+}
+extern "C" __attribute__((visibility("default"))) int ge2_debug_read_wtrace(long long* host_out) {
+    return (int)cudaMemcpyFromSymbol(host_out, g_wtrace, sizeof(long long) * 20 * 32 * 4);
 }
 extern "C" __attribute__((visibility("default"))) int ge2_debug_read_cta_times(unsigned long long* host_out) {
     return (int)cudaMemcpyFromSymbol(host_out, g_cta_times, sizeof(unsigned long long) * 2048 * 2);
