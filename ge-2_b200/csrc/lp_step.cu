@@ -174,80 +174,68 @@ __global__ void __launch_bounds__(256) lp_prep_kernel(LpKernelArgs a) {
 }
 
 // ---------------------------------------------------------------------------------------------------
-// finish: relation-operator backward and the duplicate-reducing scatter of every gradient row.
-// Eight lanes share a row (16 columns each for ld = 128), so a warp has four rows in flight and the chain of dependent
-// loads (ids -> row index -> embedding row) overlaps four ways.  A CTA walks a contiguous range of rows and first folds
-// gradients for frequently hit rows (hub nodes under a power-law degree distribution, popular relations) into a small
-// shared-memory table; what does not find a slot goes to global memory with 16-byte vector atomics, and the table is
-// flushed once at the end.  Sums are the same as the reference's index_add backward up to fp32 addition order.
+// finish: relation-operator backward and the scatter of every gradient row.
+// One warp per row: an edge (both corruption sides at once) or one negative.  Lanes run along the embedding, so every
+// load and every atomic of a warp covers one contiguous 128-byte piece of a row, and the loads of a row (two endpoints, two
+// relation rows, two rows of dQ) are all issued before the first one is needed.  For ComplEx a lane holds the real and the
+// imaginary component of the same complex coordinate, so the operator's backward needs no second pass over the rows.
+// A CTA walks a contiguous range of rows and folds the gradients of relation rows (few rows, hit by every edge) into a
+// small shared-memory table that is flushed once at the end; node rows go straight to global memory (the batch-local
+// gradient buffer lives in L2).  Sums are the same as the reference's index_add backward up to fp32 addition order.
 // ---------------------------------------------------------------------------------------------------
-constexpr int kFinSlots = 32;     // hot rows cached per CTA
-constexpr int kFinLanes = 8;      // lanes per row
+constexpr int kFinSlots = 32;     // relation rows cached per CTA
+constexpr int kFinWarps = 8;
 constexpr long long kFinEmpty = -1;
 
 struct FinishSmem {
     float acc[kFinSlots][128];
-    long long tag[kFinSlots];  // 0 <= key < 2^40: node row; (1 + side) << 40 | relation id: relation row
+    long long tag[kFinSlots];  // (1 + side) << 40 | relation id
 };
 
 __device__ __forceinline__ int fin_slot_of(long long key) { return (int)(((unsigned long long)key * 0x9E3779B97F4A7C15ull) >> 59); }  // top 5 bits
 
-__global__ void __launch_bounds__(256) lp_finish_kernel(LpKernelArgs a, int rows_per_cta) {
+__global__ void __launch_bounds__(kFinWarps * 32) lp_finish_kernel(LpKernelArgs a, int edges_per_cta, int negs_per_cta) {
     __shared__ FinishSmem sm;
     const ge2_lp_desc& d = a.d;
     const LpLayout& L = a.L;
-    const int tid = threadIdx.x;
-    const int gl = tid & (kFinLanes - 1);                 // lane within the row group
-    const int group = tid / kFinLanes;                    // 32 groups per CTA
-    const unsigned gmask = 0xFFu << ((tid & 31) & ~7);    // the 8 lanes of this group inside the warp
-    const int gleader = (tid & 31) & ~7;
-    const int64_t e_rows = d.B;  // one row group per edge (both sides), then one per negative
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    const int64_t e_rows = d.B;  // one row per edge (both sides), then one per negative
     const int64_t total = e_rows + (int64_t)L.S * L.CN;
     const int D = d.D, h = D / 2, ld = L.ld;
-    const bool vec4 = (D % 4 == 0) && (((uintptr_t)d.node_grad | (uintptr_t)d.rel_grad | (uintptr_t)d.inv_rel_grad) & 15) == 0;
-    const bool vec_e = (d.emb_stride % 4 == 0) && (((uintptr_t)d.node_emb) & 15) == 0 && D % 4 == 0;
-    const bool vec_r = D % 4 == 0 && ((((uintptr_t)d.rel) | ((uintptr_t)d.inv_rel)) & 15) == 0;
+    const bool cplx = d.has_relations && d.decoder == GE2_DECODER_COMPLEX;
+    const int n_el = cplx ? h : D;       // coordinates a lane loop runs over: complex pairs, or plain columns
+    const int off2 = cplx ? h : 0;       // where the second component of a coordinate lives
+    const bool vec_g = (D % 4 == 0) && (((uintptr_t)d.node_grad) & 15) == 0;
 
     // loss = sum over sides and padded rows of (lse - pos), accumulated in double by the scores kernel that ran before
     if (blockIdx.x == 0 && tid == 0) *d.loss = (float)*L.loss_acc;
-    for (int k = tid; k < kFinSlots * 128; k += 256) (&sm.acc[0][0])[k] = 0.f;
-    if (tid < kFinSlots) sm.tag[tid] = kFinEmpty;
+    if (d.has_relations) {
+        for (int k = tid; k < kFinSlots * 128; k += kFinWarps * 32) (&sm.acc[0][0])[k] = 0.f;
+        if (tid < kFinSlots) sm.tag[tid] = kFinEmpty;
+    }
     __syncthreads();
 
-    // claims (or finds) the shared slot of `key`; -1 when the slot belongs to another row.  Group-uniform result.
+    // claims (or finds) the shared slot of `key`; -1 when the slot belongs to another row.  Warp-uniform result.
     auto claim = [&](long long key) -> int {
         int slot = -1;
-        if ((tid & 31) == gleader) {
+        if (lane == 0) {
             const int sidx = fin_slot_of(key);
             const long long old = (long long)atomicCAS((unsigned long long*)&sm.tag[sidx], (unsigned long long)kFinEmpty, (unsigned long long)key);
             slot = (old == kFinEmpty || old == key) ? sidx : -1;
         }
-        return __shfl_sync(gmask, slot, gleader);
-    };
-    // adds four consecutive columns [k, k+4) of a gradient row either into the shared slot or straight into global memory
-    auto add4 = [&](int slot, float* grow, int k, float4 v) {
-        if (v.x == 0.f && v.y == 0.f && v.z == 0.f && v.w == 0.f) return;
-        if (slot >= 0) {
-            atomicAdd(&sm.acc[slot][k], v.x);
-            atomicAdd(&sm.acc[slot][k + 1], v.y);
-            atomicAdd(&sm.acc[slot][k + 2], v.z);
-            atomicAdd(&sm.acc[slot][k + 3], v.w);
-        } else if (vec4) {
-            atomicAdd(reinterpret_cast<float4*>(grow + k), v);
-        } else {
-            if (k < D) atomicAdd(grow + k, v.x);
-            if (k + 1 < D) atomicAdd(grow + k + 1, v.y);
-            if (k + 2 < D) atomicAdd(grow + k + 2, v.z);
-            if (k + 3 < D) atomicAdd(grow + k + 3, v.w);
-        }
+        return __shfl_sync(0xffffffffu, slot, 0);
     };
 
-    const int64_t row_begin = (int64_t)blockIdx.x * rows_per_cta;
-    const int64_t row_end = row_begin + rows_per_cta < total ? row_begin + rows_per_cta : total;
-    for (int64_t w0 = row_begin; w0 < row_end; w0 += 32) {
-        const int64_t w = w0 + group;  // whole warps stay in the loop (shuffles below), rows past the end do nothing
-        const bool live = w < row_end;
-        if (live && w < e_rows) {
+    // Every CTA takes a contiguous share of the edges (heavy rows: six input rows, four output rows each) and a contiguous
+    // share of the negatives (one row in, one out), so the heavy rows are spread over the whole grid.
+    const int64_t e_begin = (int64_t)blockIdx.x * edges_per_cta;
+    const int64_t e_end = e_begin + edges_per_cta < e_rows ? e_begin + edges_per_cta : e_rows;
+    const int64_t n_begin = e_rows + (int64_t)blockIdx.x * negs_per_cta;
+    const int64_t n_end = n_begin + negs_per_cta < total ? n_begin + negs_per_cta : total;
+    const int64_t n_mine = (e_end > e_begin ? e_end - e_begin : 0) + (n_end > n_begin ? n_end - n_begin : 0);
+    for (int64_t q = warp; q < n_mine; q += kFinWarps) {
+        const int64_t w = e_begin + q < e_end ? e_begin + q : n_begin + (q - (e_end > e_begin ? e_end - e_begin : 0));
+        if (w < e_rows) {
             // one edge, both corruption sides at once: side 0 applies the relation to the source and compares with the
             // destination, side 1 the inverse relation to the destination and compares with the source, so each endpoint
             // receives one combined row instead of two
@@ -260,103 +248,115 @@ __global__ void __launch_bounds__(256) lp_finish_kernel(LpKernelArgs a, int rows
                 rid = d.rel_ids[(int64_t)i * d.rel_stride];
                 ok = ok && rid >= 0 && rid < d.R;
             }
-            if (ok) {  // bad rows were flagged by prep
-                const float* es = emb_row(d, sid);
-                const float* ed = emb_row(d, did);
-                const int slot_s = claim(sid), slot_d = claim(did);
-                int slot_r[2] = {-1, -1};
-                const float *r[2] = {nullptr, nullptr}, *dq[2];
-                float* rg[2] = {nullptr, nullptr};
-                float dpos[2];
+            if (!ok) continue;  // bad rows were flagged by prep
+            const float* es = emb_row(d, sid);
+            const float* ed = emb_row(d, did);
+            const float* r[2] = {nullptr, nullptr};
+            const float* dq[2] = {nullptr, nullptr};
+            float* rg[2] = {nullptr, nullptr};
+            int slot_r[2] = {-1, -1};
+            float dpos[2] = {0.f, 0.f};
+#pragma unroll
+            for (int s = 0; s < 2; s++) {
+                if (s >= L.S) break;
+                const int64_t qrow = (int64_t)s * L.Bp + i;
+                dq[s] = L.dQ + qrow * ld;
+                dpos[s] = __expf(L.pos[qrow] - L.lse[qrow]) - 1.0f;  // d loss / d pos_i = softmax prob of the positive - 1
+                if (d.has_relations) {
+                    r[s] = (s == 0 ? d.rel : d.inv_rel) + rid * D;
+                    rg[s] = (s == 0 ? d.rel_grad : d.inv_rel_grad) + rid * D;
+                    slot_r[s] = claim(((long long)(1 + s) << 40) | rid);
+                }
+            }
+            float* gsrc = d.node_grad + sid * D;
+            float* gdst = d.node_grad + did * D;
+            for (int c = lane; c < n_el; c += 32) {
+                // components 0 / 1 of coordinate c: (real, imaginary) for ComplEx, otherwise only component 0 is used
+                const int c2 = c + off2;
+                const float s0 = __ldg(es + c), d0 = __ldg(ed + c);
+                const float s1 = cplx ? __ldg(es + c2) : 0.f, d1 = cplx ? __ldg(ed + c2) : 0.f;
+                float gs0 = 0.f, gs1 = 0.f, gd0 = 0.f, gd1 = 0.f;  // gradient of the source / destination row at this coordinate
 #pragma unroll
                 for (int s = 0; s < 2; s++) {
                     if (s >= L.S) break;
-                    const int64_t qrow = (int64_t)s * L.Bp + i;
-                    dq[s] = L.dQ + qrow * ld;
-                    dpos[s] = __expf(L.pos[qrow] - L.lse[qrow]) - 1.0f;  // d loss / d pos_i = softmax prob of the positive - 1
-                    if (d.has_relations) {
-                        r[s] = (s == 0 ? d.rel : d.inv_rel) + rid * D;
-                        rg[s] = (s == 0 ? d.rel_grad : d.inv_rel_grad) + rid * D;
-                        slot_r[s] = claim(((long long)(1 + s) << 40) | rid);
+                    const float a0 = s == 0 ? s0 : d0, a1 = s == 0 ? s1 : d1;  // endpoint the relation is applied to
+                    const float b0 = s == 0 ? d0 : s0, b1 = s == 0 ? d1 : s1;  // endpoint it is compared with
+                    // gradient with respect to the relation-adjusted embedding q = op(a, r): from the negatives (dQ) and the positive
+                    const float g0 = dq[s][c] + dpos[s] * b0;
+                    const float g1 = cplx ? dq[s][c2] + dpos[s] * b1 : 0.f;
+                    float ga0, ga1 = 0.f, gb0, gb1 = 0.f, vr0 = 0.f, vr1 = 0.f;
+                    if (r[s] == nullptr) {            // Dot: q = a
+                        gb0 = dpos[s] * a0;
+                        ga0 = g0;
+                    } else if (!cplx) {               // DistMult: q = a * r
+                        const float r0 = __ldg(r[s] + c);
+                        gb0 = dpos[s] * (a0 * r0);
+                        ga0 = g0 * r0;
+                        vr0 = g0 * a0;
+                    } else {                          // ComplEx: q = a x r (complex product), backward through both factors
+                        const float r0 = __ldg(r[s] + c), r1 = __ldg(r[s] + c2);
+                        gb0 = dpos[s] * (a0 * r0 - a1 * r1);
+                        gb1 = dpos[s] * (a0 * r1 + a1 * r0);
+                        ga0 = g0 * r0 + g1 * r1;
+                        ga1 = -g0 * r1 + g1 * r0;
+                        vr0 = g0 * a0 + g1 * a1;
+                        vr1 = -g0 * a1 + g1 * a0;
+                    }
+                    if (s == 0) {
+                        gs0 += ga0; gs1 += ga1; gd0 += gb0; gd1 += gb1;
+                    } else {
+                        gd0 += ga0; gd1 += ga1; gs0 += gb0; gs1 += gb1;
+                    }
+                    if (rg[s] != nullptr) {
+                        if (slot_r[s] >= 0) {
+                            atomicAdd(&sm.acc[slot_r[s]][c], vr0);
+                            if (cplx) atomicAdd(&sm.acc[slot_r[s]][c2], vr1);
+                        } else {
+                            atomicAdd(rg[s] + c, vr0);
+                            if (cplx) atomicAdd(rg[s] + c2, vr1);
+                        }
                     }
                 }
-                for (int k = gl * 4; k < D; k += kFinLanes * 4) {
-                    const float4 s4 = load4(es, k, D, vec_e), d4 = load4(ed, k, D, vec_e);
-                    const float sv[4] = {s4.x, s4.y, s4.z, s4.w}, dv[4] = {d4.x, d4.y, d4.z, d4.w};
-                    float gs[4] = {0.f, 0.f, 0.f, 0.f}, gd[4] = {0.f, 0.f, 0.f, 0.f};  // gradient rows of the source / destination node
-#pragma unroll
-                    for (int s = 0; s < 2; s++) {
-                        if (s >= L.S) break;
-                        const float* ea = s == 0 ? es : ed;            // endpoint the relation is applied to
-                        const float* eb = s == 0 ? ed : es;            // endpoint it is compared with
-                        const float* eav = s == 0 ? sv : dv;
-                        const float* ebv = s == 0 ? dv : sv;
-                        float* ga = s == 0 ? gs : gd;
-                        float* gb = s == 0 ? gd : gs;
-                        // the relation-adjusted embedding q = op(ea, r) is recomputed from rows that are loaded anyway
-                        const float4 dq4 = *reinterpret_cast<const float4*>(dq[s] + k);
-                        const float dqv[4] = {dq4.x, dq4.y, dq4.z, dq4.w};
-                        float vr[4] = {0.f, 0.f, 0.f, 0.f};
-                        float rv[4] = {0.f, 0.f, 0.f, 0.f};
-                        if (r[s] != nullptr) {
-                            const float4 r4 = load4(r[s], k, D, vec_r);
-                            rv[0] = r4.x; rv[1] = r4.y; rv[2] = r4.z; rv[3] = r4.w;
-                        }
-#pragma unroll
-                        for (int e = 0; e < 4; e++) {
-                            const int c = k + e;
-                            const float g = dqv[e] + dpos[s] * ebv[e];  // d loss / d adjusted embedding
-                            if (r[s] == nullptr) {
-                                gb[e] += dpos[s] * eav[e];
-                                ga[e] += g;
-                            } else if (d.decoder == GE2_DECODER_DISTMULT) {
-                                gb[e] += dpos[s] * (eav[e] * rv[e]);
-                                ga[e] += g * rv[e];
-                                vr[e] = g * eav[e];
-                            } else if (c < D) {
-                                // complex Hadamard forward and backward: both need the partner component
-                                const int cp = c < h ? c + h : c - h;
-                                const float gp = dq[s][cp] + dpos[s] * __ldg(eb + cp);
-                                const float rp = __ldg(r[s] + cp), eap = __ldg(ea + cp);
-                                if (c < h) {  // real component: g = g_re, gp = g_im
-                                    gb[e] += dpos[s] * (eav[e] * rv[e] - eap * rp);
-                                    ga[e] += g * rv[e] + gp * rp;
-                                    vr[e] = g * eav[e] + gp * eap;
-                                } else {  // imaginary component: g = g_im, gp = g_re
-                                    gb[e] += dpos[s] * (eap * rv[e] + eav[e] * rp);
-                                    ga[e] += -gp * rv[e] + g * rp;
-                                    vr[e] = -gp * eav[e] + g * eap;
-                                }
-                            }
-                        }
-                        if (rg[s] != nullptr) add4(slot_r[s], rg[s], k, make_float4(vr[0], vr[1], vr[2], vr[3]));
-                    }
-                    add4(slot_s, d.node_grad + sid * D, k, make_float4(gs[0], gs[1], gs[2], gs[3]));
-                    add4(slot_d, d.node_grad + did * D, k, make_float4(gd[0], gd[1], gd[2], gd[3]));
+                atomicAdd(gsrc + c, gs0);
+                atomicAdd(gdst + c, gd0);
+                if (cplx) {
+                    atomicAdd(gsrc + c2, gs1);
+                    atomicAdd(gdst + c2, gd1);
                 }
             }
-        } else if (live) {
+        } else {
             const int64_t e = w - e_rows;
             const int s = (int)(e / L.CN);
             const int64_t j = e - (int64_t)s * L.CN;
             const int64_t id = (s == 0 ? d.dst_negs : d.src_negs)[j];
-            if (id >= 0 && id < d.U) {
-                const float* dk = L.dK + e * ld;
-                const int slot = claim(id);
-                for (int k = gl * 4; k < D; k += kFinLanes * 4) add4(slot, d.node_grad + id * D, k, *reinterpret_cast<const float4*>(dk + k));
+            if (id < 0 || id >= d.U) continue;
+            const float* dk = L.dK + e * ld;
+            float* grow = d.node_grad + id * D;
+            if (vec_g) {
+                for (int k = lane * 4; k < D; k += 128) {
+                    const float4 v = *reinterpret_cast<const float4*>(dk + k);
+                    if (v.x != 0.f || v.y != 0.f || v.z != 0.f || v.w != 0.f) atomicAdd(reinterpret_cast<float4*>(grow + k), v);
+                }
+            } else {
+                for (int k = lane; k < D; k += 32) {
+                    const float v = dk[k];
+                    if (v != 0.f) atomicAdd(grow + k, v);
+                }
             }
         }
     }
+    if (!d.has_relations) return;
     __syncthreads();
-    // flush: group g writes slot g
-    if (group < kFinSlots) {
-        const long long key = sm.tag[group];
-        if (key != kFinEmpty) {
-            const int kind = (int)(key >> 40);
-            const long long id = key & ((1ll << 40) - 1);
-            float* grow = kind == 0 ? d.node_grad + id * D : (kind == 1 ? d.rel_grad : d.inv_rel_grad) + id * D;
-            for (int k = gl * 4; k < D; k += kFinLanes * 4)
-                add4(-1, grow, k, make_float4(sm.acc[group][k], sm.acc[group][k + 1], sm.acc[group][k + 2], sm.acc[group][k + 3]));
+    // flush: warp w writes slots w, w + 8, ...
+    for (int slot = warp; slot < kFinSlots; slot += kFinWarps) {
+        const long long key = sm.tag[slot];
+        if (key == kFinEmpty) continue;
+        const int kind = (int)(key >> 40);
+        const long long id = key & ((1ll << 40) - 1);
+        float* grow = (kind == 1 ? d.rel_grad : d.inv_rel_grad) + id * D;
+        for (int k = lane; k < D; k += 32) {
+            const float v = sm.acc[slot][k];
+            if (v != 0.f) atomicAdd(grow + k, v);
         }
     }
 }
@@ -451,10 +451,12 @@ extern "C" int ge2_lp_step(const ge2_lp_desc* desc, ge2_stream_t stream_) {
     if (!(phases & 4)) return GE2_OK;
 
     const int64_t fin_rows = (int64_t)desc->B + (int64_t)L.S * L.CN;
-    // contiguous row ranges per CTA (so that repeated rows meet in a CTA's shared table), two CTAs per SM worth of ranges
-    const int fin_ctas = (int)(fin_rows < (int64_t)kNumSMs * 4 * 32 ? ceil_div<int64_t>(fin_rows, 32) : (int64_t)kNumSMs * 4);
-    const int rows_per_cta = (int)round_up<int64_t>(ceil_div<int64_t>(fin_rows, fin_ctas), 32);
-    lp_finish_kernel<<<(unsigned)ceil_div<int64_t>(fin_rows, rows_per_cta), 256, 0, stream>>>(a, rows_per_cta);
+    // about four CTAs per SM, each with a contiguous share of the edges (whose relation rows meet in its shared table) and of the negatives
+    const int64_t neg_rows = (int64_t)L.S * L.CN;
+    int fin_ctas = (int)std::min<int64_t>((int64_t)kNumSMs * 4, ceil_div<int64_t>(fin_rows, 8));
+    if (fin_ctas < 1) fin_ctas = 1;
+    const int edges_per_cta = (int)ceil_div<int64_t>(desc->B, fin_ctas), negs_per_cta = (int)ceil_div<int64_t>(neg_rows, fin_ctas);
+    lp_finish_kernel<<<(unsigned)fin_ctas, 256, 0, stream>>>(a, edges_per_cta, negs_per_cta);
     GE2_LAUNCH_CHECK();
     if (desc->pos_scores != nullptr || desc->inv_pos_scores != nullptr) {
         copy_pos_kernel<<<ceil_div(L.Bp, 256), 256, 0, stream>>>(L.pos, L.Bp, desc->pos_scores, desc->inv_pos_scores, L.S);
