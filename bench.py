@@ -346,11 +346,12 @@ def main():
         pbuf.swap(supersteps[0])  # initial load; also sets up the NCCL point-to-point connections before anything is timed
         pbuf.swap(supersteps[1 % len(supersteps)])
         table, state = pbuf.buf[0], pbuf.buf[1]
-    rel = torch.zeros((R, D), device=device)
-    rel[:, : D // 2] = 1  # ComplEx relation init (complex.cpp:18-20 of the reference project)
-    inv_rel = rel.clone()
+    rels = torch.zeros((2, R, D), device=device)  # relation and inverse-relation tables back to back: one optimizer launch for both
+    rels[:, :, : D // 2] = 1  # ComplEx relation init (complex.cpp:18-20 of the reference project)
+    rel, inv_rel = rels[0], rels[1]
+    rel_states = torch.zeros_like(rels)
     pcfg = pipeline.PipelineConfig(cfg["decoder"], B, C, N, cfg["degree_fraction"], D, R, nodes, lr=cfg["lr"], precision=args.precision)
-    pipe = pipeline.BatchPipeline(pcfg, table, state, rel, torch.zeros_like(rel), inv_rel, torch.zeros_like(inv_rel))
+    pipe = pipeline.BatchPipeline(pcfg, table, state, rel, rel_states[0], inv_rel, rel_states[1])
     rel_hook = None
     if world > 1:
         pipe.grad_scale = 1.0 / world
@@ -480,7 +481,7 @@ def main():
             e2e=dict(value=world * K * B / (ms_e2e * 1e-3), unit="edges/s", h2d_bytes_per_step=B * 3 * 8, d2h_bytes_per_step=4,
                      note="pinned host edges -> H2D, step, loss -> pinned host, all stream-ordered; one synchronize at the end"
                           + ("; the H2D copy issued in step i carries batch i+1 (drawn ahead while batch i trains) and runs on a copy stream, the loss read-back on another" if pipelined else "")),
-            gpu_launches=K * (pipe.launches_per_step() + 1),
+            gpu_launches=K * pipe.launches_per_step(),
             clocks=clock_info,
             roofline=dict(bound="tensor", kernel="lp_scores_%s" % args.precision, achieved=achieved, peak=pk["tf"], unit="TFLOP/s",
                           frac=achieved / pk["tf"], traffic=NCU_TRAFFIC.get(args.precision), peak_source=pk["src"] + " bf16 dense",

@@ -132,11 +132,11 @@ __device__ __forceinline__ unsigned long long global_ns() {
 }
 #define TR(role, it, k)                                                                              \
     do {                                                                                             \
-        if (blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0 && (it) < 64) g_trace[role][it][k] = clock64(); \
+        if (blockIdx.x == 0 && (it) < 64) g_trace[role][it][k] = clock64(); \
     } while (0)
 #define TRW(w, it, k)                                                                                \
     do {                                                                                             \
-        if (blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0 && (it) < 32 && (threadIdx.x & 31) == 0) g_wtrace[w][it][k] = clock64(); \
+        if (blockIdx.x == 0 && (it) < 32 && (threadIdx.x & 31) == 0) g_wtrace[w][it][k] = clock64(); \
     } while (0)
 #else
 #define TR(role, it, k)
@@ -146,7 +146,7 @@ __device__ __forceinline__ unsigned long long global_ns() {
 template <int DP>
 __global__ void __launch_bounds__(kThreads, 1)
     lp_scores_f16_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK, const __grid_constant__ CUtensorMap tmDK,
-                         const __grid_constant__ CUtensorMap tmDKt, LpKernelArgs a, int mode, int nsplit) {
+                         const __grid_constant__ CUtensorMap tmDKt, LpKernelArgs a, int mode, int nsplit, int item_begin) {
     using LY = Layout<DP>;
     extern __shared__ unsigned char smem_raw[];
     unsigned char* smem = (unsigned char*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
@@ -160,10 +160,14 @@ __global__ void __launch_bounds__(kThreads, 1)
     const ge2_lp_desc& d = a.d;
     const LpLayout& L = a.L;
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-    const int s = blockIdx.z, c = blockIdx.y;
-    // blockIdx.x = row block * nsplit + h: with nsplit > 1 the chunk's negative tiles are dealt round-robin to nsplit CTAs
+    // blockIdx.x = (item - item_begin) * nsplit + h, item = (side * C + chunk) * row_blocks + row block: with nsplit > 1 the
+    // chunk's negative tiles are dealt round-robin to nsplit CTAs
+    const int row_blocks = (L.npc + BM - 1) / BM;
+    const int item = item_begin + (int)blockIdx.x / nsplit;
     const int split_h = blockIdx.x % nsplit;
-    const int row0 = (blockIdx.x / nsplit) * BM;
+    const int rb = item % row_blocks;
+    const int c = (item / row_blocks) % d.C, s = item / (row_blocks * d.C);
+    const int row0 = rb * BM;
     const int valid_rows = min(BM, L.npc - row0);
     const int zc = s * d.C + c;  // third TMA coordinate: (side, chunk)
     const int64_t grow0 = (int64_t)s * L.Bp + (int64_t)c * L.npc + row0;
@@ -175,7 +179,7 @@ __global__ void __launch_bounds__(kThreads, 1)
     const int n_iter = nA + nB;
     // The row blocks of one chunk run side by side and all reduce into the same dK rows; each starts its sweeps at a
     // different tile so that at any moment they touch different rows instead of queueing on the same L2 lines.
-    const int rot = (blockIdx.x / nsplit) % T_loc;
+    const int rot = rb % T_loc;
     auto tile_n0 = [&](int i) {
         int lt = (i < nA ? i : i - nA) + rot;  // both terms are below T_loc: one conditional subtraction instead of a modulo
         lt = lt >= T_loc ? lt - T_loc : lt;
@@ -184,10 +188,13 @@ __global__ void __launch_bounds__(kThreads, 1)
     constexpr int NB = LY::NB;
 
 #ifdef GE2_TRACE
-    const int cta_lin = blockIdx.x + gridDim.x * (blockIdx.y + gridDim.y * blockIdx.z) + (mode == 2 ? 1024 : 0);
+    const int cta_lin = (item * nsplit + split_h) % 1024 + (mode == 2 ? 1024 : 0);
     if (tid == 0 && cta_lin < 2048) g_cta_times[cta_lin][0] = global_ns();
 #endif
-    if (tid == 0) {
+    // The TMA thread sets the barriers up and starts the first loads at once, so their latency overlaps the allocation of
+    // tensor memory and the block-wide barrier below (a fresh "empty" barrier needs no wait).
+    const int n_early = n_iter < kStagesK ? n_iter : kStagesK;
+    if (warp == kTmaWarp && lane == 0) {
         mbar_init(&bars[kBarQ], 1);
         for (int k = 0; k < kStagesK; k++) {
             mbar_init(&bars[kBarKFull + k], 1);
@@ -209,6 +216,17 @@ __global__ void __launch_bounds__(kThreads, 1)
         mbar_init(&bars[kBarXch], kSoftmaxWarps);  // the column groups of every row exchange their (max, sum) once, after sweep 1
         *s_abort = 0;
         mbar_init_fence();
+        prefetch_tensormap(&tmQ);
+        prefetch_tensormap(&tmK);
+        mbar_expect_tx(&bars[kBarQ], LY::kTileBytes);
+#pragma unroll
+        for (int b = 0; b < LY::NB; b++) tma_load_3d(sQ + b * kBlockBytes, &tmQ, b * 64, row0, zc, &bars[kBarQ]);
+        for (int i = 0; i < n_early; i++) {
+            mbar_expect_tx(&bars[kBarKFull + i], LY::kTileBytes);
+            const int n0 = tile_n0(i);
+#pragma unroll
+            for (int b = 0; b < LY::NB; b++) tma_load_3d(sK + i * LY::kTileBytes + b * kBlockBytes, &tmK, b * 64, n0, zc, &bars[kBarKFull + i]);
+        }
     }
     if (warp == kMmaWarp) {
         tmem_alloc(s_tmem, kTmemCols);
@@ -242,12 +260,7 @@ __global__ void __launch_bounds__(kThreads, 1)
     if (warp == kTmaWarp) {
         // ================================ TMA producer ================================
         if (lane == 0) {
-            prefetch_tensormap(&tmQ);
-            prefetch_tensormap(&tmK);
-            mbar_expect_tx(&bars[kBarQ], LY::kTileBytes);
-#pragma unroll
-            for (int b = 0; b < NB; b++) tma_load_3d(sQ + b * kBlockBytes, &tmQ, b * 64, row0, zc, &bars[kBarQ]);
-            for (int i = 0; i < n_iter; i++) {
+            for (int i = n_early; i < n_iter; i++) {  // the first loads went out before the block-wide barrier
                 const int st = i % kStagesK, use = i / kStagesK;
                 TR(0, i, 0);
                 if (!wait(kBarKEmpty + st, (use & 1) ^ 1)) break;
@@ -708,10 +721,9 @@ int make_map(CUtensorMap* map, __half* base, int ld, int rows, int mats) {
     return GE2_OK;
 }
 
-// How many CTAs share one (side, chunk, row block).  A small batch has fewer such blocks than the GPU has SMs; dealing
-// each block's tiles to 2 or 4 CTAs (sweep 1 and sweep 2 then run as two launches) fills the machine.  Once the grid
-// covers every SM, splitting only adds per-CTA set-up (Q load, barriers, tensor memory) and a second launch -- measured
-// on B200: 160 blocks take 85 us unsplit, 90 us split in two -- so the largest split that still fits one round is used.
+// How many CTAs share one (side, chunk, row block), for a set of `items` blocks that does not fill the GPU: dealing each
+// block's tiles to 2 or 4 CTAs (sweep 1 and sweep 2 then run as two launches) fills the machine.  Splitting adds per-CTA
+// set-up (Q load, barriers, tensor memory) and a second launch, so the largest split that still fits one round is used.
 int choose_nsplit(int items, int tiles) {
     if (const char* e = getenv("GE2_F16_NSPLIT")) {
         const int v = atoi(e);
@@ -762,18 +774,33 @@ int launch(const LpKernelArgs& a, cudaStream_t stream) {
     const int smem = Layout<DP>::kDynamic;
     GE2_CUDA_TRY(cudaFuncSetAttribute(lp_scores_f16_kernel<DP>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
     const int row_blocks = ceil_div(a.L.npc, BM);
-    const int nsplit = choose_nsplit(row_blocks * a.d.C * a.L.S, ceil_div(a.d.N, BN));
-    dim3 grid((unsigned)(row_blocks * nsplit), (unsigned)a.d.C, (unsigned)a.L.S);
-    if (nsplit == 1) {
-        lp_scores_f16_kernel<DP><<<grid, kThreads, smem, stream>>>(tmQ, tmK, tmDK, tmDKt, a, 0, 1);
+    const int items = row_blocks * a.d.C * a.L.S, tiles = ceil_div(a.d.N, BN);
+    // One CTA per item, one CTA per SM.  Whole rounds of kNumSMs items run unsplit in one launch; the items left over
+    // would occupy a few SMs for a full round of their own, so their tiles are dealt to 2 or 4 CTAs each (sweep 1 and sweep 2
+    // then run as two launches, meeting in the per-row partials) and the machine is filled once more for a fraction of a round.
+    int whole = (items / kNumSMs) * kNumSMs, rest = items - whole;
+    if (getenv("GE2_F16_NSPLIT") != nullptr) whole = 0, rest = items;  // development switch: one split factor for everything
+    if (whole > 0) {
+        lp_scores_f16_kernel<DP><<<(unsigned)whole, kThreads, smem, stream>>>(tmQ, tmK, tmDK, tmDKt, a, 0, 1, 0);
         GE2_LAUNCH_CHECK();
-    } else {
-        // dQ is reduced across the CTAs of a split: it starts from zero (dK next to it is zeroed by the caller already)
-        GE2_CUDA_TRY(cudaMemsetAsync(a.L.dQ, 0, (size_t)a.L.S * a.L.Bp * DP * sizeof(float), stream));
-        lp_scores_f16_kernel<DP><<<grid, kThreads, smem, stream>>>(tmQ, tmK, tmDK, tmDKt, a, 1, nsplit);
-        GE2_LAUNCH_CHECK();
-        lp_scores_f16_kernel<DP><<<grid, kThreads, smem, stream>>>(tmQ, tmK, tmDK, tmDKt, a, 2, nsplit);
-        GE2_LAUNCH_CHECK();
+    }
+    if (rest > 0) {
+        const int nsplit = choose_nsplit(rest, tiles);
+        if (nsplit == 1) {
+            lp_scores_f16_kernel<DP><<<(unsigned)rest, kThreads, smem, stream>>>(tmQ, tmK, tmDK, tmDKt, a, 0, 1, whole);
+            GE2_LAUNCH_CHECK();
+        } else {
+            // dQ of a split item is the sum over its CTAs: those rows start from zero (dK next to it is zeroed by the caller).
+            // Items are numbered in row order, so the rows of items [whole, items) are one contiguous range.
+            const int64_t first_row = (int64_t)(whole / (row_blocks * a.d.C)) * a.L.Bp + (int64_t)((whole / row_blocks) % a.d.C) * a.L.npc +
+                                      (int64_t)(whole % row_blocks) * BM;
+            const int64_t end_row = (int64_t)a.L.S * a.L.Bp;
+            GE2_CUDA_TRY(cudaMemsetAsync(a.L.dQ + first_row * DP, 0, (size_t)(end_row - first_row) * DP * sizeof(float), stream));
+            lp_scores_f16_kernel<DP><<<(unsigned)(rest * nsplit), kThreads, smem, stream>>>(tmQ, tmK, tmDK, tmDKt, a, 1, nsplit, whole);
+            GE2_LAUNCH_CHECK();
+            lp_scores_f16_kernel<DP><<<(unsigned)(rest * nsplit), kThreads, smem, stream>>>(tmQ, tmK, tmDK, tmDKt, a, 2, nsplit, whole);
+            GE2_LAUNCH_CHECK();
+        }
     }
     return GE2_OK;
 }

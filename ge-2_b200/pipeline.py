@@ -101,8 +101,20 @@ class BatchPipeline:
             self.rel_grads = torch.zeros((cfg.sides,) + tuple(rel.shape), dtype=rel.dtype, device=dev)
             self.rel_grad = self.rel_grads[0]
             self.inv_rel_grad = self.rel_grads[1] if cfg.sides == 2 else None
+            # when the caller keeps the two relation tables (and their states) back to back in one allocation, the dense
+            # optimizer step is one launch over both
+            self._rel_tables_adjacent = False
+            if cfg.sides == 2 and rel.is_contiguous() and inv_rel.is_contiguous() and rel_state.is_contiguous() and inv_rel_state.is_contiguous():
+                n = rel.numel()
+                adj = lambda a, b: (b.data_ptr() == a.data_ptr() + n * a.element_size()
+                                    and a.untyped_storage().data_ptr() == b.untyped_storage().data_ptr())
+                if adj(rel, inv_rel) and adj(rel_state, inv_rel_state):
+                    both = lambda a: torch.as_strided(a, (2,) + tuple(a.shape), (n,) + tuple(a.stride()))
+                    self._rel_both, self._rel_state_both = both(rel), both(rel_state)
+                    self._rel_tables_adjacent = True
         else:
             self.rel_grad = self.inv_rel_grad = None
+            self._rel_tables_adjacent = False
         # device-side batch counters of the graph-replay forms: {t, t + 1}
         self.step_dev = torch.tensor([0, 1], dtype=torch.int64, device=dev)
         self._graph = None
@@ -169,6 +181,10 @@ class BatchPipeline:
                              status=self.status)
         if cfg.has_relations:
             dl = cfg.lr if cfg.dense_lr is None else cfg.dense_lr
+            if cfg.sides == 2 and self._rel_tables_adjacent:
+                # relation and inverse-relation tables (and their states) sit back to back, as the gradients do: one launch
+                capi.dense_adagrad(self._rel_both, self._rel_state_both, self.rel_grads, dl, grad_scale=self.grad_scale, clear_grad=True)
+                return
             capi.dense_adagrad(self.rel, self.rel_state, self.rel_grad, dl, grad_scale=self.grad_scale, clear_grad=True)
             if cfg.sides == 2:
                 capi.dense_adagrad(self.inv_rel, self.inv_rel_state, self.inv_rel_grad, dl, grad_scale=self.grad_scale, clear_grad=True)
@@ -296,11 +312,26 @@ class BatchPipeline:
     def replay(self):
         self._graph.replay()
 
-    # kernels of libge2_b200.so launched per step (memsets not counted): sample, mark, scan, inverse, [mask], prep, scores,
-    # finish, loss, adagrad_scatter, dense adagrad per relation table
-    def launches_per_step(self) -> int:
+    def launches_per_step(self, resident: bool = True) -> int:
+        """Kernels of libge2_b200.so launched per step (memsets not counted)."""
         cfg = self.cfg
-        return 4 + (1 if cfg.n_deg > 0 else 0) + 4 + 1 + (cfg.sides if cfg.has_relations else 0)  # (+1 counter bump and up to +1 scores launch in the resident form)
+        n = 1 + 3                              # sampler; unique-map: mark, scan, inverse
+        n += 1 if cfg.n_deg > 0 else 0         # filter mask from the degree-sampled rows
+        n += 1                                 # prepare (gather + relation operator + positive scores)
+        if cfg.precision == "f16":             # scores: whole rounds of 148 blocks unsplit, the remainder split over two launches
+            npc = -(-cfg.B // cfg.C)
+            items, tiles = -(-npc // 128) * cfg.C * cfg.sides, -(-cfg.N // 128)
+            whole = items // 148 * 148
+            rest = items - whole
+            ns = max([k for k in (1, 2, 4) if k == 1 or (rest * k <= 148 and k <= tiles)]) if rest else 1
+            n += (1 if whole else 0) + (0 if rest == 0 else (1 if ns == 1 else 2))
+        else:
+            n += 1
+        n += 1                                 # finish (operator backward + scatter)
+        n += 1                                 # sparse Adagrad scatter
+        if cfg.has_relations:
+            n += 1 if (cfg.sides == 1 or self._rel_tables_adjacent) else 2
+        return n + (1 if resident else 0)      # device-side counter bump of the resident / graph forms
 
     def check_status(self):
         """Synchronises and raises if any kernel flagged bad data (call between epochs, not per batch)."""
