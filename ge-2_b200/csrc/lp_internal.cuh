@@ -30,7 +30,7 @@ struct LpLayout {
     __half* Qh;       // [S][Bp][ld]  fp16 copy of Q, operand of the tensor-core path (null on the fp32 path)
     __half* Kh;       // [S][CN][ld]  fp16 copy of K
     double* loss_acc; // [1] sum over rows of (lse - pos): zeroed by the prepare kernel, added to by the scores kernels
-    float* part;      // [S][Bp][4][2] per-row partial (max, sum) of sweep 1 when a chunk's tiles are split over CTAs
+    float* part;      // [S][Bp][8][2] per-row partial (max, sum) of sweep 1 when a chunk's tiles are split over CTAs
     size_t bytes;
     size_t zero_begin, zero_bytes;  // dK range
 };
@@ -69,7 +69,7 @@ inline LpLayout lp_make_layout(const ge2_lp_desc& d, void* base) {
     const bool half_copies = d.precision == GE2_PRECISION_F16;
     size_t oQh = half_copies ? take((size_t)L.S * L.Bp * L.ld * 2) : 0;
     size_t oKh = half_copies ? take((size_t)L.S * L.CN * L.ld * 2) : 0;
-    size_t opart = half_copies ? take((size_t)L.S * L.Bp * 8 * 4) : 0;
+    size_t opart = half_copies ? take((size_t)L.S * L.Bp * 16 * 4) : 0;
     L.Q = (float*)(p + oQ);
     L.K = (float*)(p + oK);
     L.dQ = (float*)(p + odQ);

@@ -50,6 +50,7 @@ constexpr int kDrainWarp0 = kSoftmaxWarps, kTmaWarp = kDrainWarp0 + 4, kMmaWarp 
 constexpr int kBlockBytes = 128 * 128;  // one 64-half column block of 128 rows
 constexpr int kMmaK = 16;               // k extent of one kind::f16 MMA (32 bytes)
 constexpr int kStagesK = 3;             // K ring depth
+constexpr int kMaxSplit = 8;            // most CTAs that share one (side, chunk, row block); size of a row's partial list
 constexpr uint32_t kTmemCols = 512;
 constexpr float kMasked = -1e9f;
 
@@ -365,7 +366,7 @@ __global__ void __launch_bounds__(kThreads, 1)
         };
         if (mode == 2 && row_live) {  // sweep 1 ran in an earlier launch: combine its partial (max, sum) pairs
             float m = -INFINITY, l = 0.f;
-            const float2* part = reinterpret_cast<const float2*>(L.part) + (grow0 + my_row) * 4;
+            const float2* part = reinterpret_cast<const float2*>(L.part) + (grow0 + my_row) * kMaxSplit;
             for (int k = 0; k < nsplit; k++) {
                 const float2 pk = part[k];
                 const float nm = fmaxf(m, pk.x);
@@ -506,7 +507,7 @@ __global__ void __launch_bounds__(kThreads, 1)
                 }
                 if (row_live) {
                     if (mode == 1) {  // hand the partial over to the sweep-2 launch
-                        if (slot == 0) reinterpret_cast<float2*>(L.part)[(grow0 + my_row) * 4 + split_h] = make_float2(nm, l);
+                        if (slot == 0) reinterpret_cast<float2*>(L.part)[(grow0 + my_row) * kMaxSplit + split_h] = make_float2(nm, l);
                     } else {
                         const float pos2 = pos_mine * kLog2e;
                         const float nm2 = fmaxf(nm, pos2);
@@ -722,15 +723,15 @@ int make_map(CUtensorMap* map, __half* base, int ld, int rows, int mats) {
 }
 
 // How many CTAs share one (side, chunk, row block), for a set of `items` blocks that does not fill the GPU: dealing each
-// block's tiles to 2 or 4 CTAs (sweep 1 and sweep 2 then run as two launches) fills the machine.  Splitting adds per-CTA
+// block's tiles to 2, 4 or 8 CTAs (sweep 1 and sweep 2 then run as two launches) fills the machine.  Splitting adds per-CTA
 // set-up (Q load, barriers, tensor memory) and a second launch, so the largest split that still fits one round is used.
 int choose_nsplit(int items, int tiles) {
     if (const char* e = getenv("GE2_F16_NSPLIT")) {
         const int v = atoi(e);
-        if ((v == 1 || v == 2 || v == 4) && v <= tiles) return v;
+        if ((v == 1 || v == 2 || v == 4 || v == 8) && v <= tiles) return v;
     }
     int best = 1;
-    for (int ns = 2; ns <= 4 && ns <= tiles; ns *= 2)
+    for (int ns = 2; ns <= kMaxSplit && ns <= tiles; ns *= 2)
         if (items * ns <= kNumSMs) best = ns;
     return best;
 }
@@ -776,26 +777,29 @@ int launch(const LpKernelArgs& a, cudaStream_t stream) {
     const int row_blocks = ceil_div(a.L.npc, BM);
     const int items = row_blocks * a.d.C * a.L.S, tiles = ceil_div(a.d.N, BN);
     // One CTA per item, one CTA per SM.  Whole rounds of kNumSMs items run unsplit in one launch; the items left over
-    // would occupy a few SMs for a full round of their own, so their tiles are dealt to 2 or 4 CTAs each (sweep 1 and sweep 2
+    // would occupy a few SMs for a full round of their own, so their tiles are dealt to 2, 4 or 8 CTAs each (sweep 1 and sweep 2
     // then run as two launches, meeting in the per-row partials) and the machine is filled once more for a fraction of a round.
     int whole = (items / kNumSMs) * kNumSMs, rest = items - whole;
     if (getenv("GE2_F16_NSPLIT") != nullptr) whole = 0, rest = items;  // development switch: one split factor for everything
+    const int nsplit = rest > 0 ? choose_nsplit(rest, tiles) : 1;
+    if (nsplit > 1) {
+        // dQ of a split item is the sum over its CTAs: those rows start from zero (dK next to it is zeroed by the caller).
+        // Items are numbered in row order, so the rows of items [whole, items) are one contiguous range.  Cleared first, so
+        // that nothing but the kernels themselves sits between the launches below.
+        const int64_t first_row = (int64_t)(whole / (row_blocks * a.d.C)) * a.L.Bp + (int64_t)((whole / row_blocks) % a.d.C) * a.L.npc +
+                                  (int64_t)(whole % row_blocks) * BM;
+        const int64_t end_row = (int64_t)a.L.S * a.L.Bp;
+        GE2_CUDA_TRY(cudaMemsetAsync(a.L.dQ + first_row * DP, 0, (size_t)(end_row - first_row) * DP * sizeof(float), stream));
+    }
     if (whole > 0) {
         lp_scores_f16_kernel<DP><<<(unsigned)whole, kThreads, smem, stream>>>(tmQ, tmK, tmDK, tmDKt, a, 0, 1, 0);
         GE2_LAUNCH_CHECK();
     }
     if (rest > 0) {
-        const int nsplit = choose_nsplit(rest, tiles);
         if (nsplit == 1) {
             lp_scores_f16_kernel<DP><<<(unsigned)rest, kThreads, smem, stream>>>(tmQ, tmK, tmDK, tmDKt, a, 0, 1, whole);
             GE2_LAUNCH_CHECK();
         } else {
-            // dQ of a split item is the sum over its CTAs: those rows start from zero (dK next to it is zeroed by the caller).
-            // Items are numbered in row order, so the rows of items [whole, items) are one contiguous range.
-            const int64_t first_row = (int64_t)(whole / (row_blocks * a.d.C)) * a.L.Bp + (int64_t)((whole / row_blocks) % a.d.C) * a.L.npc +
-                                      (int64_t)(whole % row_blocks) * BM;
-            const int64_t end_row = (int64_t)a.L.S * a.L.Bp;
-            GE2_CUDA_TRY(cudaMemsetAsync(a.L.dQ + first_row * DP, 0, (size_t)(end_row - first_row) * DP * sizeof(float), stream));
             lp_scores_f16_kernel<DP><<<(unsigned)(rest * nsplit), kThreads, smem, stream>>>(tmQ, tmK, tmDK, tmDKt, a, 1, nsplit, whole);
             GE2_LAUNCH_CHECK();
             lp_scores_f16_kernel<DP><<<(unsigned)(rest * nsplit), kThreads, smem, stream>>>(tmQ, tmK, tmDK, tmDKt, a, 2, nsplit, whole);

@@ -187,9 +187,16 @@ constexpr int kFinSlots = 32;     // relation rows cached per CTA
 constexpr int kFinWarps = 8;
 constexpr long long kFinEmpty = -1;
 
+constexpr int kFinEdgeBatch = 64;  // edges whose scalars (ids, table rows, d loss / d pos, table slots) are fetched together
+
 struct FinishSmem {
     float acc[kFinSlots][128];
     long long tag[kFinSlots];  // (1 + side) << 40 | relation id
+    // per edge of the current batch: filled by one thread per edge, so the chain id -> row index -> ... is walked for
+    // 64 edges at once instead of once per warp and edge
+    long long sid[kFinEdgeBatch], did[kFinEdgeBatch], srow[kFinEdgeBatch], drow[kFinEdgeBatch];
+    int rid[kFinEdgeBatch], slot[2][kFinEdgeBatch];  // rid < 0: skip the edge (bad ids, flagged by prep)
+    float dpos[2][kFinEdgeBatch];
 };
 
 __device__ __forceinline__ int fin_slot_of(long long key) { return (int)(((unsigned long long)key * 0x9E3779B97F4A7C15ull) >> 59); }  // top 5 bits
@@ -215,42 +222,84 @@ __global__ void __launch_bounds__(kFinWarps * 32) lp_finish_kernel(LpKernelArgs 
     }
     __syncthreads();
 
-    // claims (or finds) the shared slot of `key`; -1 when the slot belongs to another row.  Warp-uniform result.
-    auto claim = [&](long long key) -> int {
-        int slot = -1;
-        if (lane == 0) {
-            const int sidx = fin_slot_of(key);
-            const long long old = (long long)atomicCAS((unsigned long long*)&sm.tag[sidx], (unsigned long long)kFinEmpty, (unsigned long long)key);
-            slot = (old == kFinEmpty || old == key) ? sidx : -1;
-        }
-        return __shfl_sync(0xffffffffu, slot, 0);
-    };
-
     // Every CTA takes a contiguous share of the edges (heavy rows: six input rows, four output rows each) and a contiguous
     // share of the negatives (one row in, one out), so the heavy rows are spread over the whole grid.
     const int64_t e_begin = (int64_t)blockIdx.x * edges_per_cta;
     const int64_t e_end = e_begin + edges_per_cta < e_rows ? e_begin + edges_per_cta : e_rows;
     const int64_t n_begin = e_rows + (int64_t)blockIdx.x * negs_per_cta;
     const int64_t n_end = n_begin + negs_per_cta < total ? n_begin + negs_per_cta : total;
-    const int64_t n_mine = (e_end > e_begin ? e_end - e_begin : 0) + (n_end > n_begin ? n_end - n_begin : 0);
-    for (int64_t q = warp; q < n_mine; q += kFinWarps) {
-        const int64_t w = e_begin + q < e_end ? e_begin + q : n_begin + (q - (e_end > e_begin ? e_end - e_begin : 0));
-        if (w < e_rows) {
-            // one edge, both corruption sides at once: side 0 applies the relation to the source and compares with the
-            // destination, side 1 the inverse relation to the destination and compares with the source, so each endpoint
-            // receives one combined row instead of two
-            const int i = (int)w;
-            const int64_t sid = d.src_ids[(int64_t)i * d.edge_stride];
-            const int64_t did = d.dst_ids[(int64_t)i * d.edge_stride];
+
+    // the negatives of this CTA: one row of dK each, added to the gradient row of the node it was drawn as
+    auto scatter_negatives = [&]() {
+        for (int64_t w = n_begin + warp; w < n_end; w += kFinWarps) {
+            const int64_t e = w - e_rows;
+            const int s = (int)(e / L.CN);
+            const int64_t j = e - (int64_t)s * L.CN;
+            const int64_t id = (s == 0 ? d.dst_negs : d.src_negs)[j];
+            if (id < 0 || id >= d.U) continue;
+            const float* dk = L.dK + e * ld;
+            float* grow = d.node_grad + id * D;
+            if (vec_g) {
+                for (int k = lane * 4; k < D; k += 128) {
+                    const float4 v = *reinterpret_cast<const float4*>(dk + k);
+                    if (v.x != 0.f || v.y != 0.f || v.z != 0.f || v.w != 0.f) atomicAdd(reinterpret_cast<float4*>(grow + k), v);
+                }
+            } else {
+                for (int k = lane; k < D; k += 32) {
+                    const float v = dk[k];
+                    if (v != 0.f) atomicAdd(grow + k, v);
+                }
+            }
+        }
+    };
+    bool negs_done = false;
+    for (int64_t base = e_begin; base < e_end; base += kFinEdgeBatch) {
+        const int nb = (int)(e_end - base < kFinEdgeBatch ? e_end - base : kFinEdgeBatch);
+        if (tid < nb) {
+            const int64_t i = base + tid;
+            const int64_t sid = d.src_ids[i * d.edge_stride];
+            const int64_t did = d.dst_ids[i * d.edge_stride];
             bool ok = sid >= 0 && sid < d.U && did >= 0 && did < d.U;
             int64_t rid = 0;
             if (d.has_relations) {
-                rid = d.rel_ids[(int64_t)i * d.rel_stride];
+                rid = d.rel_ids[i * d.rel_stride];
                 ok = ok && rid >= 0 && rid < d.R;
             }
-            if (!ok) continue;  // bad rows were flagged by prep
-            const float* es = emb_row(d, sid);
-            const float* ed = emb_row(d, did);
+            sm.rid[tid] = ok ? (int)rid : -1;
+            if (ok) {
+                sm.sid[tid] = sid;
+                sm.did[tid] = did;
+                sm.srow[tid] = d.row_index != nullptr ? __ldg(&d.row_index[sid]) : sid;
+                sm.drow[tid] = d.row_index != nullptr ? __ldg(&d.row_index[did]) : did;
+                for (int s = 0; s < L.S; s++) {
+                    const int64_t qrow = (int64_t)s * L.Bp + i;
+                    sm.dpos[s][tid] = __expf(L.pos[qrow] - L.lse[qrow]) - 1.0f;  // d loss / d pos_i = softmax prob of the positive - 1
+                    int slot = -1;
+                    if (d.has_relations) {  // claim (or find) the shared slot of this relation row; -1 when it belongs to another row
+                        const long long key = ((long long)(1 + s) << 40) | rid;
+                        const int sidx = fin_slot_of(key);
+                        const long long old = (long long)atomicCAS((unsigned long long*)&sm.tag[sidx], (unsigned long long)kFinEmpty, (unsigned long long)key);
+                        slot = (old == kFinEmpty || old == key) ? sidx : -1;
+                    }
+                    sm.slot[s][tid] = slot;
+                }
+            }
+        }
+        if (!negs_done) {  // while the scalars of the first batch are on their way, the other warps start on the negatives
+            scatter_negatives();
+            negs_done = true;
+        }
+        __syncthreads();
+        for (int k = warp; k < nb; k += kFinWarps) {
+            // one edge, both corruption sides at once: side 0 applies the relation to the source and compares with the
+            // destination, side 1 the inverse relation to the destination and compares with the source, so each endpoint
+            // receives one combined row instead of two
+            const int64_t i = base + k;
+            const int rid = sm.rid[k];
+            if (rid < 0) continue;  // bad rows were flagged by prep
+            const int64_t sid = sm.sid[k], did = sm.did[k];
+            const float* es = d.node_emb + sm.srow[k] * d.emb_stride;
+            const float* ed = d.node_emb + sm.drow[k] * d.emb_stride;
             const float* r[2] = {nullptr, nullptr};
             const float* dq[2] = {nullptr, nullptr};
             float* rg[2] = {nullptr, nullptr};
@@ -259,13 +308,12 @@ __global__ void __launch_bounds__(kFinWarps * 32) lp_finish_kernel(LpKernelArgs 
 #pragma unroll
             for (int s = 0; s < 2; s++) {
                 if (s >= L.S) break;
-                const int64_t qrow = (int64_t)s * L.Bp + i;
-                dq[s] = L.dQ + qrow * ld;
-                dpos[s] = __expf(L.pos[qrow] - L.lse[qrow]) - 1.0f;  // d loss / d pos_i = softmax prob of the positive - 1
+                dq[s] = L.dQ + ((int64_t)s * L.Bp + i) * ld;
+                dpos[s] = sm.dpos[s][k];
                 if (d.has_relations) {
-                    r[s] = (s == 0 ? d.rel : d.inv_rel) + rid * D;
-                    rg[s] = (s == 0 ? d.rel_grad : d.inv_rel_grad) + rid * D;
-                    slot_r[s] = claim(((long long)(1 + s) << 40) | rid);
+                    r[s] = (s == 0 ? d.rel : d.inv_rel) + (int64_t)rid * D;
+                    rg[s] = (s == 0 ? d.rel_grad : d.inv_rel_grad) + (int64_t)rid * D;
+                    slot_r[s] = sm.slot[s][k];
                 }
             }
             float* gsrc = d.node_grad + sid * D;
@@ -324,27 +372,10 @@ __global__ void __launch_bounds__(kFinWarps * 32) lp_finish_kernel(LpKernelArgs 
                     atomicAdd(gdst + c2, gd1);
                 }
             }
-        } else {
-            const int64_t e = w - e_rows;
-            const int s = (int)(e / L.CN);
-            const int64_t j = e - (int64_t)s * L.CN;
-            const int64_t id = (s == 0 ? d.dst_negs : d.src_negs)[j];
-            if (id < 0 || id >= d.U) continue;
-            const float* dk = L.dK + e * ld;
-            float* grow = d.node_grad + id * D;
-            if (vec_g) {
-                for (int k = lane * 4; k < D; k += 128) {
-                    const float4 v = *reinterpret_cast<const float4*>(dk + k);
-                    if (v.x != 0.f || v.y != 0.f || v.z != 0.f || v.w != 0.f) atomicAdd(reinterpret_cast<float4*>(grow + k), v);
-                }
-            } else {
-                for (int k = lane; k < D; k += 32) {
-                    const float v = dk[k];
-                    if (v != 0.f) atomicAdd(grow + k, v);
-                }
-            }
         }
+        __syncthreads();  // the batch's scalars are overwritten by the next batch
     }
+    if (!negs_done) scatter_negatives();
     if (!d.has_relations) return;
     __syncthreads();
     // flush: warp w writes slots w, w + 8, ...

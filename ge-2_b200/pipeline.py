@@ -173,6 +173,27 @@ class BatchPipeline:
             desc.phases = 4
             capi.lp_step(desc)
 
+    def time_scores_phase(self, edges_all, reps: int = 20) -> float:
+        """Milliseconds per scores phase (the clearing of dK plus the scores launches) as it runs inside a replayed graph:
+        `reps` phases captured back to back on the operands the last step left in the workspace, bracketed by events.
+        Host-issued launches of the same phase carry a few microseconds of launch gaps that a graph replay does not have."""
+        desc = self._make_desc(edges_all, self.ids[0].rel_ids, 1)
+        desc.phases = 2
+        capi.lp_step(desc)
+        torch.cuda.synchronize(self.device)
+        g = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(g):
+            for _ in range(reps):
+                capi.lp_step(desc)
+        g.replay()
+        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        a.record()
+        g.replay()
+        b.record()
+        torch.cuda.synchronize(self.device)
+        desc.phases = 0
+        return a.elapsed_time(b) / reps
+
     def _update(self, ids: Optional[_IdSet] = None):
         cfg = self.cfg
         ids = ids or self.ids[0]
@@ -323,7 +344,7 @@ class BatchPipeline:
             items, tiles = -(-npc // 128) * cfg.C * cfg.sides, -(-cfg.N // 128)
             whole = items // 148 * 148
             rest = items - whole
-            ns = max([k for k in (1, 2, 4) if k == 1 or (rest * k <= 148 and k <= tiles)]) if rest else 1
+            ns = max([k for k in (1, 2, 4, 8) if k == 1 or (rest * k <= 148 and k <= tiles)]) if rest else 1
             n += (1 if whole else 0) + (0 if rest == 0 else (1 if ns == 1 else 2))
         else:
             n += 1
