@@ -146,3 +146,39 @@ def test_argument_validation(capi, cuda_device):
                           dst_negs=i, node_grad=t, loss=t)
     with pytest.raises(capi.Ge2Error):  # no workspace
         capi.lp_step(d)
+
+
+@pytest.mark.parametrize("precision", ["fp32", "f16"])
+def test_full_size_step_is_the_sum_of_its_chunks(capi, cuda_device, precision):
+    """Size-independent property at the benchmark's full batch (ComplEx d=100, B=10 000, 10 chunks x 1 000 shared negatives,
+    half of them degree-based, both corruption sides): chunks do not interact, so the loss and every gradient of the whole
+    step equal the sums over ten single-chunk steps.  The whole step runs 160 row blocks (one full round of unsplit blocks
+    plus split leftovers on the tensor path), a single chunk runs 16 blocks split over several CTAs each -- different
+    launch shapes of the same kernels."""
+    B, C, N, D, R, U = 10_000, 10, 1000, 100, 1000, 60_000
+    case = workloads.make_case("COMPLEX", B, C, N, D, R, U, 500, seed=77, relations=True, inverse=True, alpha=1.1)
+    whole = run_lp_step(capi, case, cuda_device, precision=precision, filter_mode="pairs", dump_scores=False)
+    assert whole["status"] == 0
+    npc = B // C
+    loss = 0.0
+    node_grad = np.zeros((U, D), np.float64)
+    rel_grad = np.zeros((R, D), np.float64)
+    inv_rel_grad = np.zeros((R, D), np.float64)
+    for c in range(C):
+        rows = slice(c * npc, (c + 1) * npc)
+        f = case.filt[(case.filt[:, 0] >= c * npc) & (case.filt[:, 0] < (c + 1) * npc)].copy()
+        f[:, 0] -= c * npc
+        part = workloads.BatchCase(case.kind, case.edges[rows], case.emb, case.state, case.rel, case.inv_rel, case.dst_negs[c:c + 1],
+                                   case.src_negs[c:c + 1], None, f)
+        res = run_lp_step(capi, part, cuda_device, precision=precision, filter_mode="pairs", dump_scores=False)
+        assert res["status"] == 0
+        loss += res["loss"]
+        node_grad += res["node_grad"]
+        rel_grad += res["rel_grad"]
+        inv_rel_grad += res["inv_rel_grad"]
+    tol = 2e-4 if precision == "fp32" else 2e-3  # both sides run the same arithmetic; only the order of fp32 additions differs
+    assert abs(whole["loss"] - loss) <= tol * abs(loss)
+    assert rel_err(whole["node_grad"], node_grad) < tol
+    assert rel_err(whole["rel_grad"], rel_grad) < tol
+    assert rel_err(whole["inv_rel_grad"], inv_rel_grad) < tol
+    assert np.abs(node_grad).max() > 0
