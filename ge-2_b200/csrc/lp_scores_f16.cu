@@ -147,7 +147,8 @@ __device__ __forceinline__ unsigned long long global_ns() {
 template <int DP>
 __global__ void __launch_bounds__(kThreads, 1)
     lp_scores_f16_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK, const __grid_constant__ CUtensorMap tmDK,
-                         const __grid_constant__ CUtensorMap tmDKt, LpKernelArgs a, int mode, int nsplit, int item_begin) {
+                         const __grid_constant__ CUtensorMap tmDKt, const __grid_constant__ CUtensorMap tmDQ,
+                         const __grid_constant__ CUtensorMap tmDQt, LpKernelArgs a, int mode, int nsplit, int item_begin) {
     using LY = Layout<DP>;
     extern __shared__ unsigned char smem_raw[];
     unsigned char* smem = (unsigned char*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
@@ -585,7 +586,6 @@ __global__ void __launch_bounds__(kThreads, 1)
         if (alive && mode != 1 && slot == 0 && (mode == 0 || split_h == 0)) add_row_loss(my_loss);
     } else {
         // ================================ drain warps (16-19) ================================
-        const int my_lane = tid - kDrainWarp0 * 32;  // TMEM lane: a negative of the tile for dK, a query row for dQ
         // columns of dK that are reduced into global memory: full 32-column slabs, then a narrow one
         int full_slabs = d.D / 32, tail = ((d.D % 32) + 3) & ~3;
         if (tail == 32) {
@@ -648,25 +648,41 @@ __global__ void __launch_bounds__(kThreads, 1)
         if (lane == 0) bulk_wait_group<0>();  // all of this warp's reductions have landed before the CTA can exit
         __syncwarp();
         if (ok && nB > 0 && warp_wait(kBarDqFull, 0)) {
+            // dQ leaves the same way as dK: 32 x 32 slabs through the staging buffers, one TMA operation per slab -- a plain
+            // store when this CTA owns the block's rows, a reduce-add when the block's tiles are shared (dQ is then the sum
+            // over the sharing CTAs and was cleared by the host side).  Rows past the chunk's last query are clipped by the
+            // tensor map, columns past D (rounded up to 4) are not written: nobody reads them.
             tc_fence_after();
+            unsigned char* scr0 = smem + LY::kDrain + (warp - kDrainWarp0) * 8192;
 #pragma unroll 1
-            for (int cb = 0; cb < DP / 32; cb++) {
+            for (int cb = 0; cb < n_slabs; cb++) {
                 float v[32];
                 tmem_ld_32x32(tdQ + lane_sel + cb * 32, v);
-                if (my_lane < valid_rows) {
-                    float* dst = L.dQ + (grow0 + my_lane) * DP + cb * 32;
-                    if (nsplit == 1) {
+                unsigned char* scr = scr0 + (cb & 1) * 4096;
+                if (lane == 0) bulk_wait_group_read<1>();
+                __syncwarp();
+                const bool narrow = cb == full_slabs;
+                if (!narrow) {
 #pragma unroll
-                        for (int q = 0; q < 8; q++)  // columns up to D rounded to the MMA step were computed; the rest of the row is never read
-                            if (cb * 32 + q * 4 < ((d.D + kMmaK - 1) / kMmaK) * kMmaK)
-                                *reinterpret_cast<float4*>(dst + q * 4) = make_float4(v[4 * q], v[4 * q + 1], v[4 * q + 2], v[4 * q + 3]);
-                    } else {  // the row's dQ is the sum over the CTAs that share the chunk's tiles (dQ was zeroed by the host side)
+                    for (int q = 0; q < 8; q++)
+                        *reinterpret_cast<float4*>(scr + lane * 128 + ((q ^ (lane & 7)) << 4)) = make_float4(v[4 * q], v[4 * q + 1], v[4 * q + 2], v[4 * q + 3]);
+                } else {
 #pragma unroll
-                        for (int q = 0; q < 8; q++)
-                            if (cb * 32 + q * 4 < d.D) atomicAdd(reinterpret_cast<float4*>(dst + q * 4), make_float4(v[4 * q], v[4 * q + 1], v[4 * q + 2], v[4 * q + 3]));
-                    }
+                    for (int q = 0; q < 8; q++)
+                        if (q * 4 < tail) *reinterpret_cast<float4*>(scr + lane * (tail * 4) + q * 16) = make_float4(v[4 * q], v[4 * q + 1], v[4 * q + 2], v[4 * q + 3]);
+                }
+                fence_proxy_async_smem();
+                __syncwarp();
+                if (lane == 0) {
+                    const CUtensorMap* map = narrow ? &tmDQt : &tmDQ;
+                    const int y = row0 + (warp - kDrainWarp0) * 32;
+                    if (nsplit == 1) tma_store_3d(map, cb * 32, y, zc, scr);
+                    else tma_reduce_add_3d(map, cb * 32, y, zc, scr);
+                    bulk_commit_group();
                 }
             }
+            if (lane == 0) bulk_wait_group<0>();
+            __syncwarp();
         }
     }
     // ---- common exit: every role ends here, normally or after an abort; then tensor memory is released ----------
@@ -772,6 +788,15 @@ int launch(const LpKernelArgs& a, cudaStream_t stream) {
         rc = make_map_f32_slab(&tmDKt, a.L.dK, DP, a.d.N, a.L.S * a.d.C, tail_cols);
         if (rc != GE2_OK) return rc;
     }
+    // dQ [S*C chunks][rows per chunk][ld floats]: the same slab shapes, for the stores / reductions of the query gradients
+    CUtensorMap tmDQ, tmDQt;
+    rc = make_map_f32_slab(&tmDQ, a.L.dQ, DP, a.L.npc, a.L.S * a.d.C);
+    if (rc != GE2_OK) return rc;
+    tmDQt = tmDQ;
+    if (tail_cols > 0 && tail_cols < 32) {
+        rc = make_map_f32_slab(&tmDQt, a.L.dQ, DP, a.L.npc, a.L.S * a.d.C, tail_cols);
+        if (rc != GE2_OK) return rc;
+    }
     const int smem = Layout<DP>::kDynamic;
     GE2_CUDA_TRY(cudaFuncSetAttribute(lp_scores_f16_kernel<DP>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
     const int row_blocks = ceil_div(a.L.npc, BM);
@@ -792,17 +817,17 @@ int launch(const LpKernelArgs& a, cudaStream_t stream) {
         GE2_CUDA_TRY(cudaMemsetAsync(a.L.dQ + first_row * DP, 0, (size_t)(end_row - first_row) * DP * sizeof(float), stream));
     }
     if (whole > 0) {
-        lp_scores_f16_kernel<DP><<<(unsigned)whole, kThreads, smem, stream>>>(tmQ, tmK, tmDK, tmDKt, a, 0, 1, 0);
+        lp_scores_f16_kernel<DP><<<(unsigned)whole, kThreads, smem, stream>>>(tmQ, tmK, tmDK, tmDKt, tmDQ, tmDQt, a, 0, 1, 0);
         GE2_LAUNCH_CHECK();
     }
     if (rest > 0) {
         if (nsplit == 1) {
-            lp_scores_f16_kernel<DP><<<(unsigned)rest, kThreads, smem, stream>>>(tmQ, tmK, tmDK, tmDKt, a, 0, 1, whole);
+            lp_scores_f16_kernel<DP><<<(unsigned)rest, kThreads, smem, stream>>>(tmQ, tmK, tmDK, tmDKt, tmDQ, tmDQt, a, 0, 1, whole);
             GE2_LAUNCH_CHECK();
         } else {
-            lp_scores_f16_kernel<DP><<<(unsigned)(rest * nsplit), kThreads, smem, stream>>>(tmQ, tmK, tmDK, tmDKt, a, 1, nsplit, whole);
+            lp_scores_f16_kernel<DP><<<(unsigned)(rest * nsplit), kThreads, smem, stream>>>(tmQ, tmK, tmDK, tmDKt, tmDQ, tmDQt, a, 1, nsplit, whole);
             GE2_LAUNCH_CHECK();
-            lp_scores_f16_kernel<DP><<<(unsigned)(rest * nsplit), kThreads, smem, stream>>>(tmQ, tmK, tmDK, tmDKt, a, 2, nsplit, whole);
+            lp_scores_f16_kernel<DP><<<(unsigned)(rest * nsplit), kThreads, smem, stream>>>(tmQ, tmK, tmDK, tmDKt, tmDQ, tmDQt, a, 2, nsplit, whole);
             GE2_LAUNCH_CHECK();
         }
     }

@@ -52,6 +52,12 @@ __device__ __forceinline__ void tma_reduce_add_3d(const CUtensorMap* map, int x,
                  "r"(smem_u32(smem_src)), "r"(x), "r"(y), "r"(z)
                  : "memory");
 }
+// TMA: tiled 3-D store shared -> global, tracked by bulk groups; parts of the box outside the tensor are dropped
+__device__ __forceinline__ void tma_store_3d(const CUtensorMap* map, int x, int y, int z, const void* smem_src) {
+    asm volatile("cp.async.bulk.tensor.3d.global.shared::cta.tile.bulk_group [%0, {%2, %3, %4}], [%1];" ::"l"(map), "r"(smem_u32(smem_src)),
+                 "r"(x), "r"(y), "r"(z)
+                 : "memory");
+}
 __device__ __forceinline__ void bulk_commit_group() { asm volatile("cp.async.bulk.commit_group;" ::: "memory"); }
 // waits until at most `kPending` of this thread's bulk groups still have to READ their shared-memory source
 template <int kPending>
