@@ -173,12 +173,13 @@ class BatchPipeline:
             desc.phases = 4
             capi.lp_step(desc)
 
-    def time_scores_phase(self, edges_all, reps: int = 20) -> float:
+    def time_scores_phase(self, edges_all, reps: int = 20, phases: int = 2) -> float:
         """Milliseconds per scores phase (the clearing of dK plus the scores launches) as it runs inside a replayed graph:
         `reps` phases captured back to back on the operands the last step left in the workspace, bracketed by events.
-        Host-issued launches of the same phase carry a few microseconds of launch gaps that a graph replay does not have."""
+        Host-issued launches of the same phase carry a few microseconds of launch gaps that a graph replay does not have.
+        (phases: 1 = prepare, 2 = scores, 4 = finish, as in ge2_lp_desc.)"""
         desc = self._make_desc(edges_all, self.ids[0].rel_ids, 1)
-        desc.phases = 2
+        desc.phases = phases
         capi.lp_step(desc)
         torch.cuda.synchronize(self.device)
         g = torch.cuda.CUDAGraph()

@@ -148,15 +148,18 @@ def test_argument_validation(capi, cuda_device):
         capi.lp_step(d)
 
 
-@pytest.mark.parametrize("precision", ["fp32", "f16"])
-def test_full_size_step_is_the_sum_of_its_chunks(capi, cuda_device, precision):
+@pytest.mark.parametrize("precision,B,C,N,D,R,U,n_deg", [
+    ("fp32", 10_000, 10, 1000, 100, 1000, 60_000, 500),   # the benchmark's batch
+    ("f16", 10_000, 10, 1000, 100, 1000, 60_000, 500),
+    ("f16", 12_800, 10, 2000, 128, 300, 90_000, 1000),    # d = 128, 2 000 negatives per chunk (ragged last tile), 200 row blocks
+])
+def test_full_size_step_is_the_sum_of_its_chunks(capi, cuda_device, precision, B, C, N, D, R, U, n_deg):
     """Size-independent property at the benchmark's full batch (ComplEx d=100, B=10 000, 10 chunks x 1 000 shared negatives,
     half of them degree-based, both corruption sides): chunks do not interact, so the loss and every gradient of the whole
     step equal the sums over ten single-chunk steps.  The whole step runs 160 row blocks (one full round of unsplit blocks
     plus split leftovers on the tensor path), a single chunk runs 16 blocks split over several CTAs each -- different
     launch shapes of the same kernels."""
-    B, C, N, D, R, U = 10_000, 10, 1000, 100, 1000, 60_000
-    case = workloads.make_case("COMPLEX", B, C, N, D, R, U, 500, seed=77, relations=True, inverse=True, alpha=1.1)
+    case = workloads.make_case("COMPLEX", B, C, N, D, R, U, n_deg, seed=77, relations=True, inverse=True, alpha=1.1)
     whole = run_lp_step(capi, case, cuda_device, precision=precision, filter_mode="pairs", dump_scores=False)
     assert whole["status"] == 0
     npc = B // C
