@@ -34,9 +34,10 @@ CFG = dict(name="kg-1M-entities/1k-relations/20M-triples ComplEx d=100 B=10000 n
            triples=20_000_000, decoder="COMPLEX", D=100, B=10_000, C=10, N=1000, degree_fraction=0.5, lr=0.1, alpha_nodes=1.1, alpha_rel=1.2)
 
 
-# dram__bytes_read.sum + dram__bytes_write.sum of one launch of the scores kernel on this workload, from the ncu capture
-# summarised in profiles/lp_scores_f16_config2.md (operands and partial gradients stay in the 126 MB L2)
-NCU_TRAFFIC = {"f16": 20_729_344, "fp32": None}
+# dram__bytes_read.sum + dram__bytes_write.sum of the scores launches of one step on this workload (whole round + the two
+# launches of the split leftover blocks), from the ncu capture summarised in profiles/lp_scores_f16_config2.md (operands and
+# partial gradients stay in the 126 MB L2)
+NCU_TRAFFIC = {"f16": 22_407_168, "fp32": None}
 
 
 def peaks():
@@ -342,6 +343,8 @@ def main():
     ap.add_argument("--no-aten-chain", action="store_true", help="skip the ATen restatement of the reference's GPU op chain (context figure)")
     ap.add_argument("--steps-per-state", type=int, default=50, help="N > 1: training steps between partition swaps")
     ap.add_argument("--no-graph", action="store_true", help="issue every launch from the host instead of replaying a CUDA graph")
+    ap.add_argument("--nccl-allreduce", action="store_true",
+                    help="N > 1: all-reduce the relation gradients with NCCL between two graphs instead of summing them over peer memory in the dense optimizer kernel")
     ap.add_argument("--no-pipeline", action="store_true", help="do not draw batch t+1 on a side stream while batch t trains")
     ap.add_argument("--cpu-budget", type=float, default=15.0)
     args = ap.parse_args()
@@ -401,10 +404,19 @@ def main():
     pcfg = pipeline.PipelineConfig(cfg["decoder"], B, C, N, cfg["degree_fraction"], D, R, nodes, lr=cfg["lr"], precision=args.precision)
     pipe = pipeline.BatchPipeline(pcfg, table, state, rel, rel_states[0], inv_rel, rel_states[1])
     rel_hook = None
-    if world > 1:
+    peer_reduce = world > 1 and not args.nccl_allreduce and not args.no_graph and not args.no_pipeline
+    if peer_reduce:
+        # Model::all_reduce of the reference (model.cpp:174-204) folded into the dense optimizer launch: every rank reads the
+        # other ranks' relation gradients over NVLink (peer memory), so the multi-GPU step stays one graph replay
+        try:
+            pipe.use_peer_gradients(pipeline.PeerGradients(dist, 2 * R * D, device))
+        except Exception as e:  # symmetric memory cannot be set up here: the NCCL form below does the same exchange
+            print(f"[bench] peer-memory gradient sum unavailable ({e!r}); using the NCCL all-reduce", file=sys.stderr)
+            peer_reduce = False
+    if world > 1 and not peer_reduce:
         pipe.grad_scale = 1.0 / world
 
-        def rel_hook(p):  # Model::all_reduce of the reference (model.cpp:174-204): sum of the replicas' relation gradients
+        def rel_hook(p):  # the same exchange as an NCCL collective between two graphs
             dist.all_reduce(p.rel_grads)  # both tables in one call
 
     def barrier():
@@ -524,10 +536,10 @@ def main():
             dtype="f32" if args.precision == "fp32" else "f16 tensor tiles, f32 accumulate and storage", data="synthetic",
             config=dict(workload=cfg["name"], per_gpu_batch=B, global_batch=B * world, precision=args.precision,
                         l2="tables (0.8 GB) and edge list larger than L2; rows touched per step are random", parallelism=f"dp{world}" if world > 1 else "single",
-                        launch=("one CUDA graph replay per step" if world == 1 else "two CUDA graph replays + one NCCL all-reduce per step") if use_graph else "host-issued launches",
+                        launch=("one CUDA graph replay per step" if (world == 1 or peer_reduce) else "two CUDA graph replays + one NCCL all-reduce per step") if use_graph else "host-issued launches",
                         pipelined="ids of batch t+1 are drawn and deduplicated on a side stream while batch t trains" if pipelined else None,
                         partitions=None if pbuf is None else dict(count=4 * world, rows=nodes // 4, steps_per_state=sps, swaps_in_timed_region=(K - 1) // sps,
-                                                                  exchange="NCCL send/recv of partition slabs + all-reduce of relation gradients every step")),
+                                                                  exchange="NCCL send/recv of partition slabs; relation gradients every step: " + ("summed over NVLink peer memory inside the dense optimizer kernel" if peer_reduce else "NCCL all-reduce"))),
             e2e=dict(value=world * K * B / (ms_e2e * 1e-3), unit="edges/s", h2d_bytes_per_step=B * 3 * 8, d2h_bytes_per_step=4,
                      note="pinned host edges -> H2D, step, loss -> pinned host, all stream-ordered; one synchronize at the end"
                           + ("; the H2D copy issued in step i carries batch i+1 (drawn ahead while batch i trains) and runs on a copy stream, the loss read-back on another" if pipelined else "")),

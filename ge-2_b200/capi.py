@@ -15,13 +15,14 @@ PKG = Path(__file__).resolve().parent
 GE2_OK = 0
 DECODER = {"DISTMULT": 0, "DOT": 0, "COMPLEX": 1}
 PRECISION = {"fp32": 0, "f16": 1}
-STATUS_BITS = {1: "id out of range", 2: "scan timeout", 4: "filter collision", 8: "bad index", 16: "pipeline timeout"}
+STATUS_BITS = {1: "id out of range", 2: "scan timeout", 4: "filter collision", 8: "bad index", 16: "pipeline timeout", 32: "peer timeout"}
 
 EXPORTS = [
     "ge2_version", "ge2_last_cuda_error", "ge2_status_string", "ge2_check_device", "ge2_unique_workspace_bytes",
     "ge2_unique_bitmap", "ge2_pack_ids", "ge2_lp_workspace_bytes", "ge2_lp_step", "ge2_sparse_adagrad", "ge2_index_read",
     "ge2_index_add", "ge2_adagrad_scatter", "ge2_dense_adagrad", "ge2_sample_negatives", "ge2_remap_edges_to_slots",
-    "ge2_copy_slabs", "ge2_unique_bitmap_static", "ge2_sample_batch", "ge2_advance_step",
+    "ge2_copy_slabs", "ge2_unique_bitmap_static", "ge2_sample_batch", "ge2_advance_step", "ge2_dense_adagrad_peers",
+    "ge2_enable_peer_access",
 ]
 
 
@@ -78,6 +79,9 @@ def load_library():
     lib.ge2_adagrad_scatter.argtypes = [C.c_void_p, C.c_void_p, C.c_int64, C.c_void_p, C.c_int64, C.c_void_p, C.c_void_p, C.c_int32, C.c_float,
                                         C.c_int32, C.c_void_p, C.c_void_p]
     lib.ge2_dense_adagrad.argtypes = [C.c_void_p, C.c_void_p, C.c_void_p, C.c_int64, C.c_float, C.c_float, C.c_float, C.c_int32, C.c_void_p]
+    lib.ge2_dense_adagrad_peers.argtypes = [C.c_void_p, C.c_void_p, C.POINTER(C.c_void_p), C.c_int32, C.c_int32, C.c_int64, C.c_void_p, C.c_float,
+                                            C.c_float, C.c_float, C.c_void_p, C.c_void_p]
+    lib.ge2_enable_peer_access.argtypes = [C.c_int32]
     lib.ge2_sample_negatives.argtypes = [C.c_void_p, C.c_void_p, C.c_int64, C.c_int32, C.c_int32, C.c_int32, C.c_int32, C.c_int64, C.c_int32,
                                          C.c_uint64, C.c_uint64, C.c_void_p, C.c_void_p, C.c_void_p]
     lib.ge2_sample_batch.argtypes = [C.c_void_p, C.c_int32, C.c_int64, C.c_void_p, C.c_int32, C.c_int32, C.c_int32, C.c_int32, C.c_int64, C.c_int32,
@@ -234,6 +238,18 @@ def adagrad_scatter(table, state, unique_ids, node_grad, lr: float, U=None, U_de
 def dense_adagrad(param, sum_state, grad, lr: float, eps: float = 1e-10, grad_scale: float = 1.0, clear_grad=False):
     check(load_library().ge2_dense_adagrad(ptr(param), ptr(sum_state), ptr(grad), param.numel(), lr, eps, grad_scale, 1 if clear_grad else 0,
                                            cur_stream()), "ge2_dense_adagrad")
+
+
+def dense_adagrad_peers(param, sum_state, peer_ptrs, rank: int, numel: int, step_dev, lr: float, status, eps: float = 1e-10,
+                        grad_scale: float = 1.0):
+    """peer_ptrs: list of device addresses (ints), one per rank, of the ranks' gradient buffers as mapped in this process."""
+    arr = (C.c_void_p * len(peer_ptrs))(*peer_ptrs)
+    check(load_library().ge2_dense_adagrad_peers(ptr(param), ptr(sum_state), arr, len(peer_ptrs), rank, numel, ptr(step_dev), lr, eps, grad_scale,
+                                                 ptr(status), cur_stream()), "ge2_dense_adagrad_peers")
+
+
+def enable_peer_access(peer_device: int):
+    check(load_library().ge2_enable_peer_access(peer_device), "ge2_enable_peer_access")
 
 
 def sample_negatives(src_ids, dst_ids, edge_stride, B, Cn, N, n_deg, domain, want_src, seed, batch_index, out_packed, out_deg_rows):

@@ -172,6 +172,70 @@ __global__ void __launch_bounds__(256) dense_adagrad_kernel(float* __restrict__ 
     }
 }
 
+// ---- dense Adagrad fused with the relation-gradient all-reduce over peer memory -------------------------------------
+// Every rank keeps its relation gradients in a buffer its peers can read (two halves used by alternate steps, then one
+// 8-byte flag per rank).  One launch per rank and step: announce "my gradients of step t are complete" by writing t + 1
+// into my slot of every peer's flag row, wait (bounded) until every peer has announced the same, then run the optimizer
+// step on the sum of all ranks' gradients, read straight from the peers over NVLink, and clear the half that the step
+// after next will accumulate into.  Why one barrier is enough: a rank announces step t + 1 only when its step-t launch
+// is over, so whoever gets past the wait of step t + 1 knows that nobody reads the half of step t any more.
+__device__ __forceinline__ void st_release_sys_u64(unsigned long long* p, unsigned long long v) {
+    asm volatile("st.release.sys.global.u64 [%0], %1;" ::"l"(p), "l"(v) : "memory");
+}
+__device__ __forceinline__ unsigned long long ld_acquire_sys_u64(const unsigned long long* p) {
+    unsigned long long v;
+    asm volatile("ld.acquire.sys.global.u64 %0, [%1];" : "=l"(v) : "l"(p) : "memory");
+    return v;
+}
+
+constexpr int kMaxPeers = 16;
+struct PeerBuffers {
+    float* buf[kMaxPeers];  // this process's mapping of every rank's gradient buffer, own rank included
+};
+
+__global__ void __launch_bounds__(256) dense_adagrad_peers_kernel(float* __restrict__ param, float* __restrict__ sum, PeerBuffers peers, int world,
+                                                                  int rank, int64_t numel, const unsigned long long* __restrict__ step_dev,
+                                                                  float neg_lr, float eps, float grad_scale, int32_t* status) {
+    const unsigned long long epoch = *step_dev + 1ull;
+    const int64_t cur = (int64_t)((epoch - 1ull) & 1ull) * numel;  // half holding this step's gradients
+    const int64_t other = numel - cur;                            // half to clear for the step after next
+    const int64_t flags_off = 2 * numel;                          // in floats; numel is even, so the flags are 8-byte aligned
+    __shared__ int s_ok;
+    if (blockIdx.x == 0 && threadIdx.x < world)
+        st_release_sys_u64(reinterpret_cast<unsigned long long*>(peers.buf[threadIdx.x] + flags_off) + rank, epoch);
+    if (threadIdx.x == 0) {
+        const unsigned long long* mine = reinterpret_cast<const unsigned long long*>(peers.buf[rank] + flags_off);
+        int ok = 1;
+        for (int p = 0; p < world && ok; p++) {
+            ok = 0;
+            for (uint32_t i = 0; i < (1u << 21); i++) {  // bounded: about a second; a peer that never arrives ends the step with a status bit
+                if (ld_acquire_sys_u64(mine + p) >= epoch) {
+                    ok = 1;
+                    break;
+                }
+                __nanosleep(i < 64 ? 20 : 400);
+            }
+        }
+        s_ok = ok;
+    }
+    __syncthreads();
+    if (!s_ok) {
+        if (threadIdx.x == 0) or_status(status, GE2_STATUS_PEER_TIMEOUT);
+        return;
+    }
+    const int64_t stride = (int64_t)gridDim.x * blockDim.x;
+    for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < numel; i += stride) {
+        float g = 0.f;
+        for (int p = 0; p < world; p++) g += __ldcv(peers.buf[p] + cur + i);  // volatile-style load: never a stale cached copy of peer memory
+        g = __fmul_rn(g, grad_scale);
+        const float sn = __fadd_rn(sum[i], __fmul_rn(g, g));
+        const float den = __fadd_rn(__fsqrt_rn(sn), eps);
+        sum[i] = sn;
+        param[i] = __fadd_rn(param[i], __fmul_rn(neg_lr, __fdiv_rn(g, den)));
+        peers.buf[rank][other + i] = 0.f;
+    }
+}
+
 __global__ void __launch_bounds__(256) remap_edges_kernel(const int64_t* __restrict__ edges, int64_t n, int cols,
                                                           const int64_t* __restrict__ part_to_slot, int num_partitions,
                                                           int64_t partition_size, int64_t* __restrict__ out, int32_t* status) {
@@ -338,6 +402,36 @@ extern "C" int ge2_dense_adagrad(float* param, float* sum_state, float* grad, in
     if (param == nullptr || sum_state == nullptr || grad == nullptr) return GE2_ERR_INVALID_ARGUMENT;
     dense_adagrad_kernel<<<stream_grid(numel, 256), 256, 0, as_stream(stream_)>>>(param, sum_state, grad, numel, -lr, eps, grad_scale, clear_grad);
     GE2_LAUNCH_CHECK();
+    return GE2_OK;
+}
+
+extern "C" int ge2_dense_adagrad_peers(float* param, float* sum_state, float* const* peer_bufs, int32_t world, int32_t rank, int64_t numel,
+                                       const uint64_t* step_dev, float lr, float eps, float grad_scale, int32_t* status, ge2_stream_t stream_) {
+    if (numel <= 0 || (numel & 1) || world < 1 || world > kMaxPeers || rank < 0 || rank >= world) return GE2_ERR_INVALID_ARGUMENT;
+    if (param == nullptr || sum_state == nullptr || peer_bufs == nullptr || step_dev == nullptr || status == nullptr) return GE2_ERR_INVALID_ARGUMENT;
+    PeerBuffers pb;
+    for (int p = 0; p < kMaxPeers; p++) pb.buf[p] = p < world ? peer_bufs[p] : nullptr;
+    for (int p = 0; p < world; p++)
+        if (pb.buf[p] == nullptr) return GE2_ERR_INVALID_ARGUMENT;
+    dense_adagrad_peers_kernel<<<stream_grid(numel, 256), 256, 0, as_stream(stream_)>>>(
+        param, sum_state, pb, world, rank, numel, reinterpret_cast<const unsigned long long*>(step_dev), -lr, eps, grad_scale, status);
+    GE2_LAUNCH_CHECK();
+    return GE2_OK;
+}
+
+extern "C" int ge2_enable_peer_access(int32_t peer_device) {
+    int dev = 0;
+    GE2_CUDA_TRY(cudaGetDevice(&dev));
+    if (peer_device == dev) return GE2_OK;
+    int can = 0;
+    GE2_CUDA_TRY(cudaDeviceCanAccessPeer(&can, dev, peer_device));
+    if (!can) return GE2_ERR_INVALID_ARGUMENT;
+    const cudaError_t e = cudaDeviceEnablePeerAccess(peer_device, 0);
+    if (e == cudaErrorPeerAccessAlreadyEnabled) {
+        (void)cudaGetLastError();
+        return GE2_OK;
+    }
+    GE2_CUDA_TRY(e);
     return GE2_OK;
 }
 

@@ -75,6 +75,40 @@ class _IdSet:
         self.dst_negs_local = self.inverse[off:off + CN]
 
 
+class PeerGradients:
+    """Relation-gradient buffers that every rank of a node can read over NVLink (one process per GPU): the sum over ranks
+    and the dense optimizer step then take one launch per rank (ge2_dense_adagrad_peers) instead of a collective call
+    between two halves of the step, and the whole multi-GPU step fits in one CUDA graph.  Replaces Model::all_reduce of
+    the reference (model.cpp:174-204).  Layout of each rank's buffer: two halves of `numel` floats (the step whose counter
+    is t accumulates into half t & 1), then one 8-byte flag per rank.
+
+    The buffers are torch symmetric memory: every rank's allocation is mapped into this process's address space with
+    access granted to this rank's GPU, which is what a kernel needs to load from it.  (A legacy CUDA IPC import of a
+    peer's tensor is mapped in the context of the peer's device and faulted when a kernel of this rank's device read it.)
+    No multicast object is bound to the buffers: the kernel uses plain peer loads and stores."""
+
+    def __init__(self, dist, numel: int, device):
+        import os
+
+        os.environ.setdefault("TORCH_SYMM_MEM_DISABLE_MULTICAST", "1")
+        import torch.distributed._symmetric_memory as symm_mem
+
+        assert numel % 2 == 0, "the flag row behind the two halves must be 8-byte aligned"
+        self.rank, self.world, self.numel = dist.get_rank(), dist.get_world_size(), numel
+        self.buf = symm_mem.empty(2 * numel + 2 * self.world + 32, dtype=torch.float32, device=device)
+        self.buf.zero_()
+        torch.cuda.synchronize(device)
+        self.handle = symm_mem.rendezvous(self.buf, dist.group.WORLD)  # collective; keeps the peers' mappings alive
+        self.ptrs = [int(p) for p in self.handle.buffer_ptrs]
+        if len(self.ptrs) != self.world or self.ptrs[self.rank] != self.buf.data_ptr():
+            raise RuntimeError("symmetric memory rendezvous returned an unexpected set of buffers")
+        dist.barrier()  # every rank has zeroed and mapped every buffer before anybody launches on them
+        torch.cuda.synchronize(device)
+
+    def half(self, parity: int):
+        return self.buf[parity * self.numel:(parity + 1) * self.numel]
+
+
 class BatchPipeline:
     """Owns the per-batch scratch (ids, unique map, gradients, workspaces); tables are owned by the caller."""
 
@@ -121,10 +155,28 @@ class BatchPipeline:
         self._desc = None
         self._ws = None
         self.grad_scale = 1.0  # 1 / #GPUs when relation gradients are all-reduced (model.cpp:188-192 of the reference project)
+        self.peer: Optional[PeerGradients] = None
+        self._t_host = 0       # host mirror of step_dev[0]; only the peer-gradient form needs it (which half a step writes)
 
-    def _make_desc(self, edges, rel_ids=None, rel_stride=None, ids: Optional[_IdSet] = None):
+    def use_peer_gradients(self, peer: PeerGradients):
+        """Multi-GPU: relation gradients go into `peer`'s buffer (alternating halves) and the dense optimizer step sums them
+        over the ranks itself.  Supported by enqueue_resident and capture_pipelined; needs the relation tables (and their
+        states) back to back when there are two."""
+        cfg = self.cfg
+        assert cfg.has_relations and (cfg.sides == 1 or self._rel_tables_adjacent)
+        assert peer.numel == cfg.sides * self.rel.numel()
+        self.peer = peer
+        self.grad_scale = 1.0 / peer.world
+        self._t_host = int(self.step_dev[0].item())
+        self._peer_views = [peer.half(h).view((cfg.sides,) + tuple(self.rel.shape)) for h in (0, 1)]
+
+    def _make_desc(self, edges, rel_ids=None, rel_stride=None, ids: Optional[_IdSet] = None, parity: Optional[int] = None):
         cfg = self.cfg
         ids = ids or self.ids[0]
+        rel_grad, inv_rel_grad = self.rel_grad, self.inv_rel_grad
+        if self.peer is not None:
+            view = self._peer_views[(self._t_host if parity is None else parity) & 1]
+            rel_grad, inv_rel_grad = view[0], (view[1] if cfg.sides == 2 else None)
         cols = edges.shape[1]
         if rel_ids is None and cfg.has_relations:
             rel_ids, rel_stride = edges[:, 1], cols
@@ -133,8 +185,8 @@ class BatchPipeline:
             U=self.cap, node_emb=self.table, row_index=ids.unique, emb_stride=cfg.D, src_ids=ids.src_local, dst_ids=ids.dst_local,
             rel_ids=rel_ids if cfg.has_relations else None, edge_stride=1, rel_stride=rel_stride or 1, dst_negs=ids.dst_negs_local,
             src_negs=ids.src_negs_local, deg_sample_rows=ids.deg_rows if cfg.n_deg > 0 else None, n_deg=cfg.n_deg,
-            rel=self.rel, inv_rel=self.inv_rel if cfg.sides == 2 else None, node_grad=self.node_grad, rel_grad=self.rel_grad,
-            inv_rel_grad=self.inv_rel_grad, loss=ids.loss, status=self.status, node_grad_is_zero=True)
+            rel=self.rel, inv_rel=self.inv_rel if cfg.sides == 2 else None, node_grad=self.node_grad, rel_grad=rel_grad,
+            inv_rel_grad=inv_rel_grad, loss=ids.loss, status=self.status, node_grad_is_zero=True)
         if self._ws is None:
             self._ws = torch.empty(capi.lp_workspace_bytes(d), dtype=torch.uint8, device=self.device)
         d.workspace, d.workspace_bytes = self._ws.data_ptr(), self._ws.numel()
@@ -203,6 +255,12 @@ class BatchPipeline:
                              status=self.status)
         if cfg.has_relations:
             dl = cfg.lr if cfg.dense_lr is None else cfg.dense_lr
+            if self.peer is not None:
+                # sum over the ranks' gradient buffers + Adagrad on both tables + clearing of the other half, one launch
+                both = cfg.sides == 2
+                capi.dense_adagrad_peers(self._rel_both if both else self.rel, self._rel_state_both if both else self.rel_state, self.peer.ptrs,
+                                         self.peer.rank, self.peer.numel, self.step_dev, dl, self.status, grad_scale=self.grad_scale)
+                return
             if cfg.sides == 2 and self._rel_tables_adjacent:
                 # relation and inverse-relation tables (and their states) sit back to back, as the gradients do: one launch
                 capi.dense_adagrad(self._rel_both, self._rel_state_both, self.rel_grads, dl, grad_scale=self.grad_scale, clear_grad=True)
@@ -222,10 +280,12 @@ class BatchPipeline:
         capi.unique_bitmap(self.packed, cfg.domain, workspace=self.uws, out_unique=self.unique, out_inverse=self.inverse, out_count=self.count)
         self._backward_and_update(self._make_desc(edges_all, self.rel_ids, 1), scores_events, rel_hook)
         capi.advance_step(self.step_dev, 2)
+        self._t_host += 1
 
     def capture_resident(self, edges_all, num_batches: int, rel_hook=None):
         """Captures one resident step into a CUDA graph (after one eager step, which also resolves driver entry points and
         function attributes outside the capture).  replay() then costs a single graph launch per step."""
+        assert self.peer is None, "the peer-gradient form needs the alternating graphs of capture_pipelined"
         self.enqueue_resident(edges_all, num_batches, rel_hook=rel_hook)
         torch.cuda.synchronize(self.device)
         self._graph_edges = edges_all  # keep the captured pointers alive
@@ -284,6 +344,9 @@ class BatchPipeline:
         self._front(self.ids[0], edges_all, num_batches, ctr_now)  # ids of the first pipelined batch
         torch.cuda.synchronize(self.device)
         graphs = []
+        t_first = self._t_host  # the step the first replay runs (graph p runs the steps t_first + p, t_first + p + 2, ...)
+        if self.peer is not None:
+            assert rel_hook is None and t_first == int(self.step_dev[0].item())
         for p in (0, 1):
             cur, nxt = self.ids[p], self.ids[1 - p]
             ga = torch.cuda.CUDAGraph()
@@ -293,7 +356,7 @@ class BatchPipeline:
                 side.wait_stream(main)
                 with torch.cuda.stream(side):
                     self._front(nxt, edges_all, num_batches, ctr_next)
-                self._backward(self._make_desc(edges_all, cur.rel_ids, 1, ids=cur))
+                self._backward(self._make_desc(edges_all, cur.rel_ids, 1, ids=cur, parity=t_first + p))
                 main.wait_stream(side)
                 if rel_hook is None:
                     self._update(cur)
@@ -317,6 +380,7 @@ class BatchPipeline:
                     rel_hook(pipe)
                     gb.replay()
                 _self.parity ^= 1
+                pipe._t_host += 1
 
             @property
             def loss(_self):

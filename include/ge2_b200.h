@@ -40,6 +40,7 @@ extern "C" {
 #define GE2_STATUS_FILTER_COLLISION 4 /* lp step: two filter pairs name the same (chunk, column)            */
 #define GE2_STATUS_BAD_INDEX 8        /* lp step / scatter: a local id or relation id out of bounds         */
 #define GE2_STATUS_PIPE_TIMEOUT 16    /* lp step (tensor path): a bounded mbarrier wait ran out             */
+#define GE2_STATUS_PEER_TIMEOUT 32    /* peer-reduced dense step: a rank did not announce its gradients in time */
 
 typedef void *ge2_stream_t; /* cudaStream_t */
 
@@ -202,6 +203,22 @@ GE2_API int ge2_adagrad_scatter(float *table, float *state, int64_t table_rows, 
  * Model::all_reduce, cpp/src/nn/model.cpp:188-192); clear_grad != 0 zeroes grad afterwards (clear_grad_all). */
 GE2_API int ge2_dense_adagrad(float *param, float *sum_state, float *grad, int64_t numel, float lr, float eps, float grad_scale,
                       int32_t clear_grad, ge2_stream_t stream);
+
+/* Model::all_reduce + the dense optimizer step of every replica (cpp/src/nn/model.cpp:174-204, cpp/src/nn/optim.cpp:109-143)
+ * as ONE launch per rank: the sum over ranks is read straight from the peers' gradient buffers over NVLink instead of
+ * going through a collective call.  peer_bufs[r] (host array of `world` device pointers) is this process's mapping of rank
+ * r's buffer, own rank included; every buffer holds 2 * numel floats (two halves, used by alternate steps: the step whose
+ * counter *step_dev is t accumulates its gradients into half t & 1) followed by `world` 8-byte flags, all zero at start;
+ * numel must be even.  The kernel announces step t to every peer, waits (bounded, about a second) for all peers'
+ * announcements, applies Adagrad to param / sum_state with g = grad_scale * sum over ranks, and clears half (t + 1) & 1 of
+ * its own buffer.  A peer that never arrives sets GE2_STATUS_PEER_TIMEOUT in *status and leaves the tables untouched.
+ * Every rank must launch it once per step, on devices that can access each other (ge2_enable_peer_access). */
+GE2_API int ge2_dense_adagrad_peers(float *param, float *sum_state, float *const *peer_bufs, int32_t world, int32_t rank, int64_t numel,
+                            const uint64_t *step_dev, float lr, float eps, float grad_scale, int32_t *status, ge2_stream_t stream);
+
+/* cudaDeviceEnablePeerAccess from the current device to peer_device (no-op when already enabled or the same device):
+ * what the relay path does before its peer copies (cpp/src/storage/storage.cpp:599-652 copies between device buffers). */
+GE2_API int ge2_enable_peer_access(int32_t peer_device);
 
 /* =====================================================================================================
  * producer side kept on the device so a training step needs no host round trip
