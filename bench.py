@@ -341,7 +341,9 @@ def main():
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-fp32-path", action="store_true", help="skip the side measurement of the fp32 CUDA-core path")
     ap.add_argument("--no-aten-chain", action="store_true", help="skip the ATen restatement of the reference's GPU op chain (context figure)")
-    ap.add_argument("--steps-per-state", type=int, default=50, help="N > 1: training steps between partition swaps")
+    ap.add_argument("--steps-per-state", type=int, default=0,
+                    help="N > 1: training steps between partition swaps; 0 = what the workload's schedule gives: its triples spread over "
+                         "(4N)^2 edge buckets, 16 buckets per state, one batch per step")
     ap.add_argument("--no-graph", action="store_true", help="issue every launch from the host instead of replaying a CUDA graph")
     ap.add_argument("--nccl-allreduce", action="store_true",
                     help="N > 1: all-reduce the relation gradients with NCCL between two graphs instead of summing them over peer memory in the dense optimizer kernel")
@@ -395,7 +397,13 @@ def main():
         pbuf = partition.PartitionBuffer([home_emb, home_state], psize, P, rank, world, dist)
         supersteps = partition.make_supersteps(P, world)
         pbuf.swap(supersteps[0])  # initial load; also sets up the NCCL point-to-point connections before anything is timed
-        pbuf.swap(supersteps[1 % len(supersteps)])
+        sw0, sw1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        dist.barrier()
+        sw0.record()
+        pbuf.swap(supersteps[1 % len(supersteps)])  # a full swap, timed on its own (reported beside the step time)
+        sw1.record()
+        torch.cuda.synchronize()
+        swap_ms = sw0.elapsed_time(sw1)
         table, state = pbuf.buf[0], pbuf.buf[1]
     rels = torch.zeros((2, R, D), device=device)  # relation and inverse-relation tables back to back: one optimizer launch for both
     rels[:, :, : D // 2] = 1  # ComplEx relation init (complex.cpp:18-20 of the reference project)
@@ -426,7 +434,8 @@ def main():
 
     num_batches = n_edges // B
     use_graph = not args.no_graph  # N > 1: two graphs per step with the host-issued NCCL all-reduce between them
-    sps = args.steps_per_state
+    # steps between swaps: a state holds 16 of the (4N)^2 edge buckets, i.e. triples * 16 / (4N)^2 edges = that many / B batches
+    sps = args.steps_per_state if args.steps_per_state > 0 else max(1, int(cfg["triples"] * 16 / (4 * world) ** 2 / B))
     swaps = [0]
 
     def maybe_swap(i, runner=None):
@@ -539,6 +548,8 @@ def main():
                         launch=("one CUDA graph replay per step" if (world == 1 or peer_reduce) else "two CUDA graph replays + one NCCL all-reduce per step") if use_graph else "host-issued launches",
                         pipelined="ids of batch t+1 are drawn and deduplicated on a side stream while batch t trains" if pipelined else None,
                         partitions=None if pbuf is None else dict(count=4 * world, rows=nodes // 4, steps_per_state=sps, swaps_in_timed_region=(K - 1) // sps,
+                                                                  swap_ms=swap_ms, swap_ms_per_step_amortized=swap_ms / sps,
+                                                                  value_with_amortized_swaps=world * K * B / ((ms + (K / sps - (K - 1) // sps) * swap_ms) * 1e-3),
                                                                   exchange="NCCL send/recv of partition slabs; relation gradients every step: " + ("summed over NVLink peer memory inside the dense optimizer kernel" if peer_reduce else "NCCL all-reduce"))),
             e2e=dict(value=world * K * B / (ms_e2e * 1e-3), unit="edges/s", h2d_bytes_per_step=B * 3 * 8, d2h_bytes_per_step=4,
                      note="pinned host edges -> H2D, step, loss -> pinned host, all stream-ordered; one synchronize at the end"

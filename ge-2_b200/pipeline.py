@@ -248,11 +248,18 @@ class BatchPipeline:
         return a.elapsed_time(b) / reps
 
     def _update(self, ids: Optional[_IdSet] = None):
+        self._update_nodes(ids)
+        self._update_relations()
+
+    def _update_nodes(self, ids: Optional[_IdSet] = None):
         cfg = self.cfg
         ids = ids or self.ids[0]
         # clear_grad: the rows just consumed are zeroed in the same pass, so the next step needs no memset of the gradient buffer
         capi.adagrad_scatter(self.table, self.state, ids.unique, self.node_grad, cfg.lr, U=self.cap, U_dev=ids.count, clear_grad=True,
                              status=self.status)
+
+    def _update_relations(self):
+        cfg = self.cfg
         if cfg.has_relations:
             dl = cfg.lr if cfg.dense_lr is None else cfg.dense_lr
             if self.peer is not None:
@@ -359,7 +366,13 @@ class BatchPipeline:
                 self._backward(self._make_desc(edges_all, cur.rel_ids, 1, ids=cur, parity=t_first + p))
                 main.wait_stream(side)
                 if rel_hook is None:
-                    self._update(cur)
+                    # the two optimizer updates touch different tables: the dense one (with its wait for the other ranks'
+                    # gradients in the multi-GPU form) runs beside the sparse scatter
+                    side.wait_stream(main)
+                    with torch.cuda.stream(side):
+                        self._update_relations()
+                    self._update_nodes(cur)
+                    main.wait_stream(side)
                     capi.advance_step(self.step_dev, 2)
             gb = None
             if rel_hook is not None:

@@ -30,9 +30,9 @@ def _worker(rank, world, port, mode, out_dir):
     nodes, B, C, N, D, R, nb = 6000, 512, 2, 256, 100, 16, 6
     rng = np.random.default_rng(100 + rank)  # every rank trains its own edges on its own node table (disjoint partitions)
     table = torch.from_numpy((0.3 * rng.standard_normal((nodes, D))).astype(np.float32)).to(dev)
-    state = torch.zeros_like(table)
+    state = torch.full_like(table, 0.05)  # a state floor: the first Adagrad step from a zero state is +-lr whatever the gradient's size
     rels = torch.from_numpy(np.tile((1 + 0.2 * np.random.default_rng(5).standard_normal((1, R, D))).astype(np.float32), (2, 1, 1))).to(dev)
-    rel_states = torch.zeros_like(rels)
+    rel_states = torch.full_like(rels, 0.05)
     edges = np.stack([workloads.zipf_ids(rng, nb * B, nodes, 1.0), workloads.zipf_ids(rng, nb * B, R, 1.2),
                       workloads.zipf_ids(rng, nb * B, nodes, 1.0)], axis=1).astype(np.int64)
     d_edges = torch.from_numpy(edges).to(dev)
@@ -74,9 +74,9 @@ def test_peer_reduce_matches_nccl_all_reduce(tmp_path):
     for rank in range(world):
         a, b = np.load(tmp_path / f"nccl_{rank}.npz"), np.load(tmp_path / f"peer_{rank}.npz")
         for key in ("rels", "rel_states", "table"):
-            assert np.abs(a[key] - b[key]).max() <= 1e-6 * np.abs(a[key]).max(), key
+            assert np.abs(a[key] - b[key]).max() <= 1e-5 * np.abs(a[key]).max(), key
         assert abs(float(a["loss"]) - float(b["loss"])) <= 1e-5 * abs(float(a["loss"]))
     # every replica ends with the same relation tables (they start equal and apply the same summed gradient)
     r0, r1 = np.load(tmp_path / "peer_0.npz")["rels"], np.load(tmp_path / "peer_1.npz")["rels"]
-    assert np.array_equal(r0, r1)
+    assert np.abs(r0 - r1).max() == 0.0  # same start, same summed gradient, same arithmetic on every rank
     assert np.abs(r0 - np.tile((1 + 0.2 * np.random.default_rng(5).standard_normal((1, 16, 100))).astype(np.float32), (2, 1, 1))).max() > 0
