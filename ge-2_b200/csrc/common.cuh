@@ -2,6 +2,8 @@
 #pragma once
 #include <cuda_runtime.h>
 #include <stdint.h>
+#include <stdio.h>
+#include <stdlib.h>
 
 #include "../../include/ge2_b200.h"
 
@@ -11,21 +13,24 @@ constexpr int kNumSMs = 148;  // B200: 2 dies x 74 SMs; grids of streaming kerne
 
 extern thread_local int g_last_cuda_error;
 
-inline int cuda_fail(cudaError_t e) {
+inline int cuda_fail(cudaError_t e, const char* what = nullptr, const char* file = nullptr, int line = 0) {
     g_last_cuda_error = (int)e;
+    if (what != nullptr && getenv("GE2_DEBUG_ERRORS") != nullptr)
+        fprintf(stderr, "[ge2] %s failed with cudaError %d (%s) at %s:%d\n", what, (int)e, cudaGetErrorString(e), file, line);
     return GE2_ERR_CUDA;
 }
 
-#define GE2_CUDA_TRY(expr)                                  \
-    do {                                                    \
-        cudaError_t _e = (expr);                            \
-        if (_e != cudaSuccess) return ::ge2::cuda_fail(_e); \
+// GE2_DEBUG_ERRORS=1 in the environment: the failing call site is printed to stderr before the status is returned
+#define GE2_CUDA_TRY(expr)                                                          \
+    do {                                                                            \
+        cudaError_t _e = (expr);                                                    \
+        if (_e != cudaSuccess) return ::ge2::cuda_fail(_e, #expr, __FILE__, __LINE__); \
     } while (0)
 
-#define GE2_LAUNCH_CHECK()                                  \
-    do {                                                    \
-        cudaError_t _e = cudaGetLastError();                \
-        if (_e != cudaSuccess) return ::ge2::cuda_fail(_e); \
+#define GE2_LAUNCH_CHECK()                                                                  \
+    do {                                                                                    \
+        cudaError_t _e = cudaGetLastError();                                                \
+        if (_e != cudaSuccess) return ::ge2::cuda_fail(_e, "kernel launch", __FILE__, __LINE__); \
     } while (0)
 
 inline cudaStream_t as_stream(ge2_stream_t s) { return reinterpret_cast<cudaStream_t>(s); }

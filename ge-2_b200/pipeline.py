@@ -337,7 +337,7 @@ class BatchPipeline:
                           ids.packed, ids.deg_rows if cfg.n_deg > 0 else None, ids.rel_ids if cfg.has_relations else None)
         capi.unique_bitmap(ids.packed, cfg.domain, workspace=ids.uws, out_unique=ids.unique, out_inverse=ids.inverse, out_count=ids.count)
 
-    def capture_pipelined(self, edges_all, num_batches: int, rel_hook=None):
+    def capture_pipelined(self, edges_all, num_batches: int, rel_hook=None, front_after_scores: bool = True):
         """Software-pipelined steps: while the decoder step of batch t runs (its scores kernel leaves most SMs idle in its
         second round), the ids of batch t+1 are drawn and deduplicated on a side stream into the other id set; the optimizer
         updates of batch t follow the join, so batch t+1 gathers the updated rows.  Two graphs alternate (one per id set);
@@ -350,37 +350,68 @@ class BatchPipeline:
         ctr_now, ctr_next = self.step_dev[0:1], self.step_dev[1:2]
         self._front(self.ids[0], edges_all, num_batches, ctr_now)  # ids of the first pipelined batch
         torch.cuda.synchronize(self.device)
-        graphs = []
-        t_first = self._t_host  # the step the first replay runs (graph p runs the steps t_first + p, t_first + p + 2, ...)
-        if self.peer is not None:
-            assert rel_hook is None and t_first == int(self.step_dev[0].item())
-        for p in (0, 1):
-            cur, nxt = self.ids[p], self.ids[1 - p]
-            ga = torch.cuda.CUDAGraph()
-            with torch.cuda.graph(ga):
-                main = torch.cuda.current_stream()
-                side = torch.cuda.Stream(device=self.device)
-                side.wait_stream(main)
-                with torch.cuda.stream(side):
-                    self._front(nxt, edges_all, num_batches, ctr_next)
-                self._backward(self._make_desc(edges_all, cur.rel_ids, 1, ids=cur, parity=t_first + p))
-                main.wait_stream(side)
-                if rel_hook is None:
-                    # the two optimizer updates touch different tables: the dense one (with its wait for the other ranks'
-                    # gradients in the multi-GPU form) runs beside the sparse scatter
-                    side.wait_stream(main)
-                    with torch.cuda.stream(side):
-                        self._update_relations()
-                    self._update_nodes(cur)
-                    main.wait_stream(side)
-                    capi.advance_step(self.step_dev, 2)
-            gb = None
-            if rel_hook is not None:
-                gb = torch.cuda.CUDAGraph()
-                with torch.cuda.graph(gb):
-                    self._update(cur)
-                    capi.advance_step(self.step_dev, 2)
-            graphs.append((ga, gb))
+        # Side streams are made once, outside any capture, and nothing is destroyed while a capture is open (a stream,
+        # graph or tensor of an earlier capture dying inside a later one invalidates it): no garbage collection meanwhile.
+        import gc
+
+        if getattr(self, "_side_streams", None) is None:
+            self._side_streams = (torch.cuda.Stream(device=self.device), torch.cuda.Stream(device=self.device))
+        self._make_desc(edges_all, self.ids[0].rel_ids, 1)  # sizes the workspace before the capture
+        gc.collect()
+        gc_was_on = gc.isenabled()
+        gc.disable()
+        try:
+            graphs = []
+            t_first = self._t_host  # the step the first replay runs (graph p runs the steps t_first + p, t_first + p + 2, ...)
+            if self.peer is not None:
+                assert rel_hook is None and t_first == int(self.step_dev[0].item())
+            for p in (0, 1):
+                cur, nxt = self.ids[p], self.ids[1 - p]
+                ga = torch.cuda.CUDAGraph()
+                with torch.cuda.graph(ga):
+                    main = torch.cuda.current_stream()
+                    side, side2 = self._side_streams
+                    desc = self._make_desc(edges_all, cur.rel_ids, 1, ids=cur, parity=t_first + p)
+                    if front_after_scores:
+                        # The scores kernel owns whole SMs (one CTA with all of its shared memory); the small kernels of the next
+                        # batch's sampler and unique-map would delay its CTAs, so they are forked after it and run beside the
+                        # scatter and the optimizer updates, which leave room on every SM.
+                        desc.phases = 3
+                        capi.lp_step(desc)
+                        side.wait_stream(main)
+                        with torch.cuda.stream(side):
+                            self._front(nxt, edges_all, num_batches, ctr_next)
+                        desc.phases = 4
+                        capi.lp_step(desc)
+                        desc.phases = 0
+                    else:
+                        side.wait_stream(main)
+                        with torch.cuda.stream(side):
+                            self._front(nxt, edges_all, num_batches, ctr_next)
+                        self._backward(desc)
+                        main.wait_stream(side)
+                    if rel_hook is None:
+                        # the two optimizer updates touch different tables: the dense one (with its wait for the other ranks'
+                        # gradients in the multi-GPU form) runs beside the sparse scatter
+                        side2.wait_stream(main)
+                        with torch.cuda.stream(side2):
+                            self._update_relations()
+                        self._update_nodes(cur)
+                        main.wait_stream(side2)
+                        main.wait_stream(side)
+                        capi.advance_step(self.step_dev, 2)
+                    if rel_hook is not None and front_after_scores:
+                        main.wait_stream(side)
+                gb = None
+                if rel_hook is not None:
+                    gb = torch.cuda.CUDAGraph()
+                    with torch.cuda.graph(gb):
+                        self._update(cur)
+                        capi.advance_step(self.step_dev, 2)
+                graphs.append((ga, gb))
+        finally:
+            if gc_was_on:
+                gc.enable()
         pipe = self
 
         class _Pipelined:
