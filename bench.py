@@ -466,6 +466,7 @@ def main():
     elif use_graph:
         graph = pipe.capture_resident(edges, num_batches) if world == 1 else pipe.capture_resident_split(edges, num_batches, rel_hook)
     if use_graph:
+        barrier()  # captures take different times on different ranks; start replaying together
         for _ in range(W):
             graph.replay()
     start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
@@ -513,6 +514,7 @@ def main():
                 pipe.enqueue_resident(stage, 1, rel_hook=rel_hook)
         host_loss[i:i + 1].copy_(pipe.loss, non_blocking=True)
 
+    barrier()
     for i in range(min(W, K)):
         e2e_step(i)
     s2, e2 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)

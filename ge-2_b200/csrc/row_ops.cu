@@ -208,7 +208,8 @@ __global__ void __launch_bounds__(256) dense_adagrad_peers_kernel(float* __restr
         int ok = 1;
         for (int p = 0; p < world && ok; p++) {
             ok = 0;
-            for (uint32_t i = 0; i < (1u << 21); i++) {  // bounded: about a second; a peer that never arrives ends the step with a status bit
+            for (uint32_t i = 0; i < (1u << 23); i++) {  // bounded: a few seconds (ranks drift apart while one of them captures a graph or
+                                                          // swaps partitions); a peer that never arrives ends the step with a status bit
                 if (ld_acquire_sys_u64(mine + p) >= epoch) {
                     ok = 1;
                     break;

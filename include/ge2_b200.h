@@ -209,7 +209,7 @@ GE2_API int ge2_dense_adagrad(float *param, float *sum_state, float *grad, int64
  * going through a collective call.  peer_bufs[r] (host array of `world` device pointers) is this process's mapping of rank
  * r's buffer, own rank included; every buffer holds 2 * numel floats (two halves, used by alternate steps: the step whose
  * counter *step_dev is t accumulates its gradients into half t & 1) followed by `world` 8-byte flags, all zero at start;
- * numel must be even.  The kernel announces step t to every peer, waits (bounded, about a second) for all peers'
+ * numel must be even.  The kernel announces step t to every peer, waits (bounded, a few seconds) for all peers'
  * announcements, applies Adagrad to param / sum_state with g = grad_scale * sum over ranks, and clears half (t + 1) & 1 of
  * its own buffer.  A peer that never arrives sets GE2_STATUS_PEER_TIMEOUT in *status and leaves the tables untouched.
  * Every rank must launch it once per step, on devices that can access each other (ge2_enable_peer_access). */
