@@ -87,7 +87,7 @@ def _worker(rank, world, P, rows, D, port, out):
         dist.destroy_process_group()
 
 
-@pytest.mark.parametrize("P,world", [(8, 2), (16, 2)])
+@pytest.mark.parametrize("P,world", [(8, 2), (16, 2), (16, 4)])
 def test_swap_protocol_two_gloo_ranks(P, world):
     rows, D = 3, 2
     ctx = mp.get_context("spawn")
