@@ -19,10 +19,12 @@
 // cpp/src/nn/loss.cpp:46-63 of the reference project).
 //
 // Warp roles, connected by mbarrier pipelines (no block-wide barrier inside the loops):
-//   warps 0-15  softmax, two groups of 8 that take alternate tiles: thread = accumulator row (TMEM lane), 64 columns per warp;
-//               S -> registers (then the S accumulator is handed back) -> running max/sum in the exp2 domain, later -> P
+//   warps 0-15  softmax: thread = accumulator row (TMEM lane).  Sweep 1: two groups of 8 warps take alternate tiles (64
+//               columns per warp), S -> registers -> running max/sum in the exp2 domain.  Sweep 2: all 16 warps on every tile
+//               (32 columns per warp), S -> registers (the accumulator is handed back at once) -> P in shared memory
 //   warps 16-19 drain: dK accumulator -> swizzled staging in shared memory -> one TMA reduce-add per 32 x 32 slab into
-//               global dK (row blocks of a chunk add up there); at the end dQ accumulator -> global dQ
+//               global dK (row blocks of a chunk add up there); at the end dQ accumulator -> global dQ the same way (TMA
+//               stores, or reduce-adds when the block's tiles are shared between CTAs)
 //   warp  20    lane 0: TMA producer for the K ring (and the one-off Q load)
 //   warp  21    lane 0: issues the score contractions; the warp also allocates and frees tensor memory
 //   warp  22    lane 0: issues the gradient contractions of sweep 2
