@@ -345,6 +345,7 @@ def main():
                     help="N > 1: training steps between partition swaps; 0 = what the workload's schedule gives: its triples spread over "
                          "(4N)^2 edge buckets, 16 buckets per state, one batch per step")
     ap.add_argument("--no-graph", action="store_true", help="issue every launch from the host instead of replaying a CUDA graph")
+    ap.add_argument("--nccl-swaps", action="store_true", help="N > 1: move partitions between ranks with NCCL send/recv instead of peer-memory copies")
     ap.add_argument("--nccl-allreduce", action="store_true",
                     help="N > 1: all-reduce the relation gradients with NCCL between two graphs instead of summing them over peer memory in the dense optimizer kernel")
     ap.add_argument("--no-pipeline", action="store_true", help="do not draw batch t+1 on a side stream while batch t trains")
@@ -394,9 +395,15 @@ def main():
         P, psize = 4 * world, nodes // 4
         home_emb = (torch.rand((4 * psize, D), device=device, generator=gen) - 0.5) * 0.2
         home_state = torch.zeros((4 * psize, D), device=device)
-        pbuf = partition.PartitionBuffer([home_emb, home_state], psize, P, rank, world, dist)
+        try:  # partitions that change hands are pulled by the receiver over NVLink peer memory; NCCL send/recv as fall-back
+            pbuf = partition.PartitionBuffer([home_emb, home_state], psize, P, rank, world, dist, peer_copies=not args.nccl_swaps)
+        except Exception as e:
+            print(f"[bench] peer-memory partition copies unavailable ({e!r}); using NCCL send/recv", file=sys.stderr)
+            pbuf = partition.PartitionBuffer([home_emb, home_state], psize, P, rank, world, dist)
         supersteps = partition.make_supersteps(P, world)
-        pbuf.swap(supersteps[0])  # initial load; also sets up the NCCL point-to-point connections before anything is timed
+        for st in supersteps:  # initial load and one pass over the schedule: every connection a swap needs exists before anything is timed
+            pbuf.swap(st)
+        pbuf.swap(supersteps[0])
         sw0, sw1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         dist.barrier()
         sw0.record()
@@ -552,7 +559,7 @@ def main():
                         partitions=None if pbuf is None else dict(count=4 * world, rows=nodes // 4, steps_per_state=sps, swaps_in_timed_region=(K - 1) // sps,
                                                                   swap_ms=swap_ms, swap_ms_per_step_amortized=swap_ms / sps,
                                                                   value_with_amortized_swaps=world * K * B / ((ms + (K / sps - (K - 1) // sps) * swap_ms) * 1e-3),
-                                                                  exchange="NCCL send/recv of partition slabs; relation gradients every step: " + ("summed over NVLink peer memory inside the dense optimizer kernel" if peer_reduce else "NCCL all-reduce"))),
+                                                                  exchange=("partition slabs pulled over NVLink peer memory" if pbuf.peer_buf is not None else "NCCL send/recv of partition slabs") + "; relation gradients every step: " + ("summed over NVLink peer memory inside the dense optimizer kernel" if peer_reduce else "NCCL all-reduce"))),
             e2e=dict(value=world * K * B / (ms_e2e * 1e-3), unit="edges/s", h2d_bytes_per_step=B * 3 * 8, d2h_bytes_per_step=4,
                      note="pinned host edges -> H2D, step, loss -> pinned host, all stream-ordered; one synchronize at the end"
                           + ("; the H2D copy issued in step i carries batch i+1 (drawn ahead while batch i trains) and runs on a copy stream, the loss read-back on another" if pipelined else "")),

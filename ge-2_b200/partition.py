@@ -165,16 +165,37 @@ class PartitionBuffer:
     """Active buffer [4 * partition_rows, D] plus home slabs for the partitions this rank is home of, for one or more
     tables moved together (embeddings and Adagrad state, graph_storage.h:247-281 of the reference moves both)."""
 
-    def __init__(self, tables_home: Sequence, partition_rows: int, num_partitions: int, rank: int, world: int, dist=None):
+    def __init__(self, tables_home: Sequence, partition_rows: int, num_partitions: int, rank: int, world: int, dist=None,
+                 peer_copies: bool = False):
         """tables_home[t]: tensor [n_home * partition_rows, D] with this rank's home partitions (p % world == rank, ascending).
-        dist: torch.distributed module (None for a single process)."""
+        dist: torch.distributed module (None for a single process).
+        peer_copies (GPUs of one node, one process each): the active buffers are symmetric memory, and a partition that moves
+        from one rank's buffer to another's is PULLED by the receiver with a copy kernel that reads the holder's buffer over
+        NVLink (the reference's relay copy, storage.cpp:626-652, as a load instead of a peer memcpy), between two host
+        barriers; NCCL send/recv then only serves moves from or to home slabs."""
         import torch
 
         self.rank, self.world, self.dist = rank, world, dist
         self.rows = partition_rows
         self.num_partitions = num_partitions
         self.home = list(tables_home)
-        self.buf = [torch.empty((CAPACITY * partition_rows, t.shape[1]), dtype=t.dtype, device=t.device) for t in self.home]
+        self.peer_buf = None
+        if peer_copies and world > 1:
+            import os
+
+            os.environ.setdefault("TORCH_SYMM_MEM_DISABLE_MULTICAST", "1")  # plain peer loads only
+            import torch.distributed._symmetric_memory as symm_mem
+
+            self.buf, self.peer_buf, self._handles = [], [], []
+            for t in self.home:
+                shape = (CAPACITY * partition_rows, t.shape[1])
+                b = symm_mem.empty(shape, dtype=t.dtype, device=t.device)
+                h = symm_mem.rendezvous(b, dist.group.WORLD)
+                self.buf.append(b)
+                self._handles.append(h)
+                self.peer_buf.append([b if r == rank else h.get_buffer(r, shape, t.dtype) for r in range(world)])
+        else:
+            self.buf = [torch.empty((CAPACITY * partition_rows, t.shape[1]), dtype=t.dtype, device=t.device) for t in self.home]
         self.staging = [torch.empty_like(b) for b in self.buf]
         self.place = Placement.initial(world, num_partitions)
 
@@ -191,7 +212,15 @@ class PartitionBuffer:
 
         moves, new_slots = plan_swap(self.place, next_states)
         ops, reqs, local, staged_in = [], [], [], []
+        pulls: Dict[int, List[Tuple[int, int]]] = {}
+        pull_any = False  # the same on every rank: all ranks see the same plan
         for m in moves:  # same order on every rank: sends and receives pair up per peer in that order
+            if self.peer_buf is not None and m.src_kind == "buf" and m.dst_kind == "buf" and m.src_rank != m.dst_rank:
+                pull_any = True
+                if m.dst_rank == self.rank:  # the receiver fetches it from the holder's buffer
+                    pulls.setdefault(m.src_rank, []).append((m.src_index, m.dst_index))
+                    staged_in.extend((m, t) for t in range(len(self.home)))
+                continue
             for t in range(len(self.home)):
                 if m.src_rank == self.rank and m.dst_rank == self.rank:
                     local.append((m, t))
@@ -207,12 +236,26 @@ class PartitionBuffer:
             if m.dst_kind == "buf":
                 self._slab("buf", m.dst_index, t, staged=True).copy_(self._slab(m.src_kind, m.src_index, t))
                 staged_in.append((m, t))
+        if pull_any:
+            import importlib
+
+            capi = importlib.import_module(__package__ + ".capi")
+            # every rank's last training step is complete, so the holders' slabs are final
+            torch.cuda.current_stream().synchronize()
+            self.dist.barrier()
+            for src_rank, pairs in pulls.items():
+                for t in range(len(self.home)):
+                    capi.copy_slabs(self.peer_buf[t][src_rank], self.staging[t], pairs, self.rows * self.home[t].shape[1])
         if ops:
             d = self.dist
             p2p = [d.P2POp(d.isend if kind == "send" else d.irecv, ten, peer) for kind, ten, peer in ops]
             reqs = d.batch_isend_irecv(p2p)
             for r in reqs:
                 r.wait()
+        if pull_any:
+            # nobody overwrites a slot of its buffer before every rank has fetched what it needs from it
+            torch.cuda.current_stream().synchronize()
+            self.dist.barrier()
         for m, t in local:
             if m.dst_kind == "home":
                 self._slab("home", m.dst_index, t).copy_(self._slab("buf", m.src_index, t))
