@@ -8,11 +8,18 @@
 // (batch.cpp:229); plus map_tensors (util.cpp:311) and deg_negative_local_filter (negative.cpp:215).
 // Used to pin the numpy restatement (oracle/ge2_oracle.py), to generate tests/golden fixtures and as the
 // timed CPU reference arm of bench.py.  Nothing here is a copy of reference code: it only calls it.
+//
+// The same file builds twice: CPU-only as gege_ref, and with -DGEGE_CUDA beside the reference's CUDA sources as
+// gege_ref_cuda, where RefModel takes a device string, its tensors live on that GPU, and the reference's
+// map_tensors_unique_inverse_cuda (unique_map_cuda.cu:1002-1023) is exported for the bit-exact unique-map tests.
 #include <torch/extension.h>
 
 #include <cstdlib>
 
 #include "common/util.h"
+#ifdef GEGE_CUDA
+#include "common/unique_map_cuda.h"
+#endif
 #include "data/batch.h"
 #include "data/samplers/negative.h"
 #include "nn/decoders/edge/complex.h"
@@ -29,11 +36,12 @@ struct RefModel {
     std::shared_ptr<AdagradOptimizer> dense_opt;
     float sparse_lr;
 
-    RefModel(const std::string &decoder_type, int64_t num_relations, int64_t dim, bool inverse, double dense_lr, double sparse_lr_) {
+    RefModel(const std::string &decoder_type, int64_t num_relations, int64_t dim, bool inverse, double dense_lr, double sparse_lr_,
+             const std::string &device = "cpu") {
         setenv("GEGE_CSR_DEBUG", "0", 1);
         setenv("GEGE_STAGE_DEBUG", "0", 1);
         setenv("GEGE_CSR_GATHER", "0", 1);
-        auto opts = torch::TensorOptions().dtype(torch::kFloat32);
+        auto opts = torch::TensorOptions().dtype(torch::kFloat32).device(torch::Device(device));
         if (decoder_type == "DISTMULT") {
             decoder = std::make_shared<DistMult>((int)num_relations, (int)dim, opts, inverse, EdgeDecoderMethod::CORRUPT_NODE);
         } else if (decoder_type == "COMPLEX") {
@@ -95,7 +103,7 @@ struct RefModel {
         batch->src_neg_indices_mapping_ = src_negs;
         batch->dst_neg_filter_ = dst_filter;
         batch->src_neg_filter_ = src_filter;
-        batch->unique_node_indices_ = torch::arange(node_embeddings.size(0), torch::kInt64);
+        batch->unique_node_indices_ = torch::arange(node_embeddings.size(0), torch::TensorOptions().dtype(torch::kInt64).device(node_embeddings.device()));
 
         if (call_step) dense_opt->clear_grad();              // model.cpp:363-365
         batch->node_embeddings_.requires_grad_();            // model.cpp:367-369
@@ -152,11 +160,21 @@ torch::Tensor ref_deg_filter(torch::Tensor sample_edge_ids, torch::Tensor edges)
 // translation unit drags in the whole storage layer; index_add_ on CPU is the same arithmetic for unique ids.
 void ref_index_add(torch::Tensor table, torch::Tensor ids, torch::Tensor values) { table.index_add_(0, ids, values); }
 
+#ifdef GEGE_CUDA
+// The reference's GPU unique-map; the backend is chosen by GEGE_UNIQUE_BACKEND in the environment (read once per process).
+std::tuple<torch::Tensor, torch::Tensor, std::string> ref_unique_inverse_cuda(torch::Tensor ids, bool sorted, int64_t domain) {
+    UniqueMapCudaDebugInfo info;
+    auto tup = map_tensors_unique_inverse_cuda(ids, sorted, &info, domain);
+    return {std::get<0>(tup).clone(), std::get<1>(tup).clone(), info.executed_backend};
+}
+#endif
+
 }  // namespace
 
-PYBIND11_MODULE(gege_ref, m) {
+PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
     py::class_<RefModel>(m, "RefModel")
-        .def(py::init<const std::string &, int64_t, int64_t, bool, double, double>())
+        .def(py::init<const std::string &, int64_t, int64_t, bool, double, double, const std::string &>(), py::arg("decoder_type"),
+             py::arg("num_relations"), py::arg("dim"), py::arg("inverse"), py::arg("dense_lr"), py::arg("sparse_lr"), py::arg("device") = "cpu")
         .def("set_relations", &RefModel::set_relations)
         .def("set_relation_state", &RefModel::set_relation_state)
         .def("get_relations", &RefModel::get_relations)
@@ -164,4 +182,7 @@ PYBIND11_MODULE(gege_ref, m) {
     m.def("map_tensors", &ref_map_tensors);
     m.def("deg_negative_local_filter", &ref_deg_filter);
     m.def("index_add", &ref_index_add);
+#ifdef GEGE_CUDA
+    m.def("unique_inverse_cuda", &ref_unique_inverse_cuda, py::call_guard<py::gil_scoped_release>());
+#endif
 }
