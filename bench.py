@@ -34,10 +34,10 @@ CFG = dict(name="kg-1M-entities/1k-relations/20M-triples ComplEx d=100 B=10000 n
            triples=20_000_000, decoder="COMPLEX", D=100, B=10_000, C=10, N=1000, degree_fraction=0.5, lr=0.1, alpha_nodes=1.1, alpha_rel=1.2)
 
 
-# dram__bytes_read.sum + dram__bytes_write.sum of the scores launches of one step on this workload (whole round + the two
-# launches of the split leftover blocks), from the ncu capture summarised in profiles/lp_scores_f16_config2.md (operands and
-# partial gradients stay in the 126 MB L2)
+# dram__bytes_read.sum + dram__bytes_write.sum of the scores launches of one step on this workload, taken from one ncu
+# capture of those launches (operands and partial gradients stay in the 126 MB L2, so it is far below the operand bytes)
 NCU_TRAFFIC = {"f16": 22_407_168, "fp32": None}
+REPEATS = 9  # the K-step timed region is run this many times; `value` is total steps over total time, the spread is reported
 
 
 def peaks():
@@ -266,56 +266,37 @@ def reference_arm(args):
     print(json.dumps(line), flush=True)
 
 
-def aten_chain_ms(cfg, table, state, rel, inv_rel, edges, steps, device):
-    """For context only (never the product path): the reference's per-batch op chain restated with the same ATen calls it makes
-    on the GPU -- randint negatives, unique, index_select gathers, bmm scores, logsumexp + cross_entropy, autograd backward,
-    Adagrad element-wise ops, index_add_ (decoder_methods.cpp:724-946, loss.cpp:46-63, batch.cpp:264-266, storage.cpp:1216 of the
-    reference project) -- timed on this GPU.  It is what the reference's build would launch, minus its host-side bookkeeping, so
-    it flatters the reference; the reference itself needs its CMake build and an omegaconf-based config loader and is not run."""
-    B, C, N, D, n = cfg["B"], cfg["C"], cfg["N"], cfg["D"], cfg["nodes"]
-    nd = int(N * cfg["degree_fraction"])
-    h = D // 2
-    rel_p = rel.clone().requires_grad_(True)
-    inv_p = inv_rel.clone().requires_grad_(True)
-    rs, irs = torch.zeros_like(rel), torch.zeros_like(rel)
-    tab, st = table.clone(), state.clone()
+def reference_gpu_ms(cfg, table, state, edges, steps, device):
+    """The reference project's OWN GPU code on this GPU and workload (test infrastructure, never the product path):
+    oracle/_ref/gege_ref_cuda.so is its sources compiled with -DGEGE_CUDA for sm_100 -- its bitmap unique-map
+    (unique_map_cuda.cu:771-882), its DEG filter (negative.cpp:215-263), its decoder / loss / autograd / optimizer steps in the
+    order of Model::train_batch (model.cpp:362-404) -- around the ATen calls its dataloader and storage make per batch
+    (randint negatives negative.cpp:104-169, index_select storage.cpp:1173-1184, index_add_ storage.cpp:1186-1259).
+    Its trainer loop, config system and batch queue are not run, so host-side overheads of the reference are missing
+    here: the figure flatters the reference."""
+    os.environ.setdefault("GEGE_UNIQUE_BACKEND", "bitmap")
+    for k in ("GEGE_CSR_GATHER", "GEGE_CSR_DEBUG", "GEGE_STAGE_DEBUG"):
+        os.environ.setdefault(k, "0")
+    import gege_ref_cuda as G
 
-    def cmul(e, r):
-        out = torch.zeros_like(e)
-        out[:, :h] = e[:, :h] * r[:, :h] - e[:, h:] * r[:, h:]
-        out[:, h:] = e[:, :h] * r[:, h:] + e[:, h:] * r[:, :h]
-        return out
+    B, C, N, D, n, R = cfg["B"], cfg["C"], cfg["N"], cfg["D"], cfg["nodes"], cfg["relations"]
+    nd = int(N * cfg["degree_fraction"])
+    model = G.RefModel(cfg["decoder"], R, D, True, cfg["lr"], cfg["lr"], str(device))
+    tab, st = table.clone(), state.clone()
 
     def one(i):
         e = edges[i * B:(i + 1) * B]
         uni = torch.randint(n, (C, N - nd), device=device)
         rows = torch.randint(0, B, (C, nd), device=device)
         dneg, sneg = torch.cat([e[:, 2][rows], uni], 1), torch.cat([e[:, 0][rows], uni], 1)
+        filt = G.deg_negative_local_filter(rows, e)
         ids = torch.cat([e[:, 0], e[:, 2], sneg.reshape(-1), dneg.reshape(-1)])
-        uniq, inv = torch.unique(ids, sorted=True, return_inverse=True)
-        emb = tab.index_select(0, uniq).requires_grad_(True)
-        s_l, d_l = inv[:B], inv[B:2 * B]
-        src, dst = emb.index_select(0, s_l), emb.index_select(0, d_l)
-        loss = 0
-        for q_e, o_e, r_tab, negs in ((src, dst, rel_p, inv[2 * B + C * N:]), (dst, src, inv_p, inv[2 * B:2 * B + C * N])):
-            q = cmul(q_e, r_tab.index_select(0, e[:, 1]))
-            pos = (q * o_e).sum(-1)
-            ne = emb.index_select(0, negs).reshape(C, N, D)
-            neg = q.view(C, B // C, D).bmm(ne.transpose(-1, -2)).flatten(0, 1)
-            y = torch.cat([pos.unsqueeze(1), neg.logsumexp(1, True)], -1)
-            loss = loss + torch.nn.functional.cross_entropy(y, torch.zeros(B, dtype=torch.int64, device=device), reduction="sum")
-        loss.backward()
-        with torch.no_grad():
-            for p_, s_ in ((rel_p, rs), (inv_p, irs)):
-                s_.addcmul_(p_.grad, p_.grad, value=1.0)
-                p_.addcdiv_(p_.grad, s_.sqrt().add_(1e-10), value=-cfg["lr"])
-                p_.grad = None
-            g = emb.grad
-            upd = g.pow(2)
-            stl = st.index_select(0, uniq).add_(upd)
-            delta = -cfg["lr"] * (g / stl.sqrt().add_(1e-10))
-            tab.index_add_(0, uniq, delta)
-            st.index_add_(0, uniq, upd)
+        uniq, inv, _ = G.unique_inverse_cuda(ids, False, n)
+        local = torch.stack([inv[:B], e[:, 1], inv[B:2 * B]], 1)
+        sl, dl = inv[2 * B:2 * B + C * N].reshape(C, N), inv[2 * B + C * N:].reshape(C, N)
+        out = model.train_batch(local, tab.index_select(0, uniq), st.index_select(0, uniq), dl, sl, filt, filt, True, False)
+        tab.index_add_(0, uniq, out["node_update"])
+        st.index_add_(0, uniq, out["node_state_update"])
 
     for i in range(3):
         one(i)
@@ -340,10 +321,11 @@ def main():
                     help="f16: tcgen05 fp16-operand tiles with fp32 accumulation (1e-2 parity, the designed path); fp32: CUDA-core path (1e-4 parity)")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-fp32-path", action="store_true", help="skip the side measurement of the fp32 CUDA-core path")
-    ap.add_argument("--no-aten-chain", action="store_true", help="skip the ATen restatement of the reference's GPU op chain (context figure)")
+    ap.add_argument("--no-reference-gpu", action="store_true", help="skip timing the reference's own GPU code (oracle/_ref/gege_ref_cuda.so) on this GPU")
     ap.add_argument("--steps-per-state", type=int, default=0,
                     help="N > 1: training steps between partition swaps; 0 = what the workload's schedule gives: its triples spread over "
                          "(4N)^2 edge buckets, 16 buckets per state, one batch per step")
+    ap.add_argument("--no-epoch", action="store_true", help="N = 1: skip the one-epoch (triples / B steps) timed region")
     ap.add_argument("--no-graph", action="store_true", help="issue every launch from the host instead of replaying a CUDA graph")
     ap.add_argument("--nccl-swaps", action="store_true", help="N > 1: move partitions between ranks with NCCL send/recv instead of peer-memory copies")
     ap.add_argument("--nccl-allreduce", action="store_true",
@@ -476,20 +458,29 @@ def main():
         barrier()  # captures take different times on different ranks; start replaying together
         for _ in range(W):
             graph.replay()
-    start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    # The clock sampler starts before the barrier (its start-up takes milliseconds and differs between ranks); the barrier and
+    # the first event sit back to back.  The K-step region runs REPEATS times, each repeat bracketed by barrier + synchronize
+    # on both sides and timed with CUDA events; the step counter runs on across repeats, so at N > 1 partition swaps fall
+    # into the timed regions at the rate the workload's schedule gives them.
     clocks = ClockSampler(local_rank)
-    barrier()
     clocks.start()
-    start.record()
-    for i in range(K):
-        maybe_swap(i, graph if use_graph else None)
-        if use_graph:
-            graph.replay()
-        else:
-            pipe.enqueue_resident(edges, num_batches, rel_hook=rel_hook)
-    end.record()
-    barrier()
-    ms = start.elapsed_time(end)
+    time.sleep(0.02)
+    rep_ms, gstep = [], 0
+    for r in range(REPEATS):
+        start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        barrier()
+        start.record()
+        for i in range(K):
+            maybe_swap(gstep, graph if use_graph else None)
+            gstep += 1
+            if use_graph:
+                graph.replay()
+            else:
+                pipe.enqueue_resident(edges, num_batches, rel_hook=rel_hook)
+        end.record()
+        barrier()
+        rep_ms.append(start.elapsed_time(end))
+    swaps_timed = swaps[0]
     pipe.check_status()
 
     # ---- end-to-end timing (`e2e`): host edges in, loss out, through the same public step call -----------------
@@ -507,13 +498,17 @@ def main():
     elif use_graph:
         graph_e2e = pipe.capture_resident(stage, 1) if world == 1 else pipe.capture_resident_split(stage, 1, rel_hook)
 
+    e2e_count = [0]
+
     def e2e_step(i):
+        g = e2e_count[0]  # steps since the e2e pass began: partition swaps keep their rhythm across repeats
+        e2e_count[0] += 1
         if pipelined:
-            maybe_swap(i, graph_e2e)
+            maybe_swap(g, graph_e2e)
             graph_e2e.step(host_edges[(i + 1) % K], host_loss[i:i + 1])  # trains batch i, copies and draws batch i+1
             return
         else:
-            maybe_swap(i)
+            maybe_swap(g)
             stage.copy_(host_edges[i], non_blocking=True)
             if use_graph:
                 graph_e2e.replay()
@@ -524,24 +519,49 @@ def main():
     barrier()
     for i in range(min(W, K)):
         e2e_step(i)
-    s2, e2 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    barrier()
-    s2.record()
-    for i in range(K):
-        e2e_step(i)
-    if pipelined:
-        graph_e2e.drain()
-    e2.record()
-    barrier()
-    ms_e2e = s2.elapsed_time(e2)
+    rep_e2e = []
+    for r in range(REPEATS):
+        s2, e2 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        barrier()
+        s2.record()
+        for i in range(K):
+            e2e_step(i)
+        if pipelined:
+            graph_e2e.drain()
+        e2.record()
+        barrier()
+        rep_e2e.append(s2.elapsed_time(e2))
     clock_info = clocks.stop()
     pipe.check_status()
     assert bool(torch.isfinite(host_loss).all()) and float(host_loss[-1]) > 0
 
+    t = torch.tensor(rep_ms + rep_e2e + [scores_ms], device=device, dtype=torch.float64)
     if dist is not None:
-        t = torch.tensor([ms, ms_e2e, scores_ms], device=device, dtype=torch.float64)
-        dist.all_reduce(t, op=dist.ReduceOp.MAX)
-        ms, ms_e2e, scores_ms = (float(x) for x in t.cpu())
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)  # every repeat: the slowest rank's device time
+    t = t.cpu().tolist()
+    rep_ms, rep_e2e, scores_ms = t[:REPEATS], t[REPEATS:2 * REPEATS], t[-1]
+    ms, ms_e2e = sum(rep_ms) / REPEATS, sum(rep_e2e) / REPEATS  # mean K-step region = total steps over total time
+
+    # ---- N = 1: one epoch of the workload (its triples / B steps) as a single timed region, clocks sampled across it -----
+    epoch_info = None
+    if world == 1 and use_graph and not args.no_epoch:
+        ep_steps = cfg["triples"] // B
+        ck = ClockSampler(local_rank)
+        ck.start()
+        time.sleep(0.02)
+        a_ep, b_ep = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        torch.cuda.synchronize()
+        a_ep.record()
+        for _ in range(ep_steps):
+            graph.replay()
+        b_ep.record()
+        torch.cuda.synchronize()
+        ep_ms = a_ep.elapsed_time(b_ep)
+        ci = ck.stop()
+        pipe.check_status()
+        epoch_info = dict(steps=ep_steps, seconds=ep_ms * 1e-3, value=ep_steps * B / (ep_ms * 1e-3), unit="edges/s", sm_mhz=ci.get("sm_mhz"),
+                          reasons=ci.get("reasons"), ms_x_mhz_per_step=(ep_ms / ep_steps) * (ci.get("sm_mhz") or 0.0),
+                          note="train edges / epoch seconds, the reference's Edges per Second line (trainer.cpp:229-232), device-resident edges")
 
     if rank == 0:
         pk = peaks()
@@ -550,20 +570,23 @@ def main():
         achieved = flops / (scores_ms * 1e-3) / 1e12
         line = dict(
             metric="train edges/sec/box", value=world * K * B / (ms * 1e-3), unit="edges/s", n_gpus=world, steps=K, warmup=W,
-            ms_per_step=ms / K, higher_is_better=True, scaling="weak", vs_baseline=None,
+            ms_per_step=ms / K, higher_is_better=True, scaling="weak", vs_baseline=None, repeats=REPEATS,
+            ms_per_step_repeats=dict(min=min(rep_ms) / K, median=float(np.median(rep_ms)) / K, max=max(rep_ms) / K,
+                                     note="each repeat = K steps between barrier + synchronize, CUDA events, max over ranks; value = mean"),
             dtype="f32" if args.precision == "fp32" else "f16 tensor tiles, f32 accumulate and storage", data="synthetic",
             config=dict(workload=cfg["name"], per_gpu_batch=B, global_batch=B * world, precision=args.precision,
                         l2="tables (0.8 GB) and edge list larger than L2; rows touched per step are random", parallelism=f"dp{world}" if world > 1 else "single",
                         launch=("one CUDA graph replay per step" if (world == 1 or peer_reduce) else "two CUDA graph replays + one NCCL all-reduce per step") if use_graph else "host-issued launches",
                         pipelined="ids of batch t+1 are drawn and deduplicated on a side stream while batch t trains" if pipelined else None,
-                        partitions=None if pbuf is None else dict(count=4 * world, rows=nodes // 4, steps_per_state=sps, swaps_in_timed_region=(K - 1) // sps,
+                        partitions=None if pbuf is None else dict(count=4 * world, rows=nodes // 4, steps_per_state=sps, swaps_in_timed_region=swaps_timed, steps_in_timed_region=K * REPEATS,
                                                                   swap_ms=swap_ms, swap_ms_per_step_amortized=swap_ms / sps,
-                                                                  value_with_amortized_swaps=world * K * B / ((ms + (K / sps - (K - 1) // sps) * swap_ms) * 1e-3),
+                                                                  
                                                                   exchange=("partition slabs pulled over NVLink peer memory" if pbuf.peer_buf is not None else "NCCL send/recv of partition slabs") + "; relation gradients every step: " + ("summed over NVLink peer memory inside the dense optimizer kernel" if peer_reduce else "NCCL all-reduce"))),
             e2e=dict(value=world * K * B / (ms_e2e * 1e-3), unit="edges/s", h2d_bytes_per_step=B * 3 * 8, d2h_bytes_per_step=4,
-                     note="pinned host edges -> H2D, step, loss -> pinned host, all stream-ordered; one synchronize at the end"
+                     ms_per_step=ms_e2e / K, ms_per_step_median=float(np.median(rep_e2e)) / K,
+                     note="pinned host edges -> H2D, step, loss -> pinned host, all stream-ordered; one synchronize at the end of each repeat"
                           + ("; the H2D copy issued in step i carries batch i+1 (drawn ahead while batch i trains) and runs on a copy stream, the loss read-back on another" if pipelined else "")),
-            gpu_launches=K * pipe.launches_per_step(),
+            gpu_launches=K * pipe.launches_per_step(), epoch=epoch_info,
             clocks=clock_info,
             roofline=dict(bound="tensor", kernel="lp_scores_%s" % args.precision, achieved=achieved, peak=pk["tf"], unit="TFLOP/s",
                           frac=achieved / pk["tf"], traffic=NCU_TRAFFIC.get(args.precision), peak_source=pk["src"] + " bf16 dense",
@@ -588,14 +611,15 @@ def main():
             b32.record()
             torch.cuda.synchronize()
             line["fp32_path"] = dict(value=k32 * B / (a32.elapsed_time(b32) * 1e-3), unit="edges/s", ms_per_step=a32.elapsed_time(b32) / k32, steps=k32)
-        if world == 1 and not args.no_aten_chain:
+        if world == 1 and not args.no_reference_gpu:
             try:
-                ms_chain = aten_chain_ms(cfg, table, state, rel, inv_rel, edges, min(K, 20), device)
-                line["aten_chain"] = dict(value=B / (ms_chain * 1e-3), unit="edges/s", ms_per_step=ms_chain,
-                                          note="the reference's GPU op chain restated with the same ATen calls (torch library kernels), same workload, "
-                                               "same GPU; context for the speed-up, not the reference build and not part of the product path")
+                ms_ref = reference_gpu_ms(cfg, table, state, edges, min(K, 20), device)
+                line["reference_gpu"] = dict(value=B / (ms_ref * 1e-3), unit="edges/s", ms_per_step=ms_ref, speedup_e2e=line["e2e"]["value"] / (B / (ms_ref * 1e-3)),
+                                             note="the reference project's own GPU code (its CUDA unique-map, bitmap backend, and its decoder/loss/autograd/"
+                                                  "Adagrad translation units compiled for sm_100) on the same GPU and workload, without its trainer loop's "
+                                                  "host overheads; test infrastructure, not part of the product path")
             except Exception as ex:  # context only: never let it break the bench line
-                line["aten_chain"] = dict(unavailable=str(ex)[:120])
+                line["reference_gpu"] = dict(unavailable=str(ex)[:160])
         if world == 1 and not args.no_cpu_baseline:
             cpu = CpuReference(cfg, 20262)
             v, k, dt = cpu.timed(args.cpu_budget)

@@ -52,7 +52,7 @@ def build_kernels(force: bool = False, verbose: bool = False) -> Path:
     objs = [OBJ / (s.stem + ".o") for s in sources]
     if force or jobs or _stale(LIB, objs):
         _run([NVCC, "-shared", "-o", str(LIB), *map(str, objs), "-gencode", "arch=compute_100a,code=sm_100a",
-              "-Xcompiler", "-fPIC", "-lcuda"])
+              "-Xcompiler", "-fPIC"])  # static cudart; libcuda is not linked (driver entry points are looked up at run time)
     return LIB
 
 

@@ -80,7 +80,7 @@ def load_library():
                                         C.c_int32, C.c_void_p, C.c_void_p]
     lib.ge2_dense_adagrad.argtypes = [C.c_void_p, C.c_void_p, C.c_void_p, C.c_int64, C.c_float, C.c_float, C.c_float, C.c_int32, C.c_void_p]
     lib.ge2_dense_adagrad_peers.argtypes = [C.c_void_p, C.c_void_p, C.POINTER(C.c_void_p), C.c_int32, C.c_int32, C.c_int64, C.c_void_p, C.c_float,
-                                            C.c_float, C.c_float, C.c_void_p, C.c_void_p]
+                                            C.c_float, C.c_float, C.c_uint32, C.c_void_p, C.c_void_p]
     lib.ge2_enable_peer_access.argtypes = [C.c_int32]
     lib.ge2_sample_negatives.argtypes = [C.c_void_p, C.c_void_p, C.c_int64, C.c_int32, C.c_int32, C.c_int32, C.c_int32, C.c_int64, C.c_int32,
                                          C.c_uint64, C.c_uint64, C.c_void_p, C.c_void_p, C.c_void_p]
@@ -241,11 +241,12 @@ def dense_adagrad(param, sum_state, grad, lr: float, eps: float = 1e-10, grad_sc
 
 
 def dense_adagrad_peers(param, sum_state, peer_ptrs, rank: int, numel: int, step_dev, lr: float, status, eps: float = 1e-10,
-                        grad_scale: float = 1.0):
-    """peer_ptrs: list of device addresses (ints), one per rank, of the ranks' gradient buffers as mapped in this process."""
+                        grad_scale: float = 1.0, wait_budget_us: int = 0):
+    """peer_ptrs: list of device addresses (ints), one per rank, of the ranks' gradient buffers as mapped in this process.
+    wait_budget_us: how long to wait for the other ranks' announcements (0 = the library's default of 4 s)."""
     arr = (C.c_void_p * len(peer_ptrs))(*peer_ptrs)
     check(load_library().ge2_dense_adagrad_peers(ptr(param), ptr(sum_state), arr, len(peer_ptrs), rank, numel, ptr(step_dev), lr, eps, grad_scale,
-                                                 ptr(status), cur_stream()), "ge2_dense_adagrad_peers")
+                                                 wait_budget_us, ptr(status), cur_stream()), "ge2_dense_adagrad_peers")
 
 
 def enable_peer_access(peer_device: int):

@@ -123,28 +123,6 @@ __device__ __forceinline__ bool pipe_wait(uint64_t* bar, uint32_t parity, volati
     return false;
 }
 
-#ifdef GE2_TRACE
-// development aid (not compiled into the shipped library): clock stamps of CTA (0,0,0), read back by a debug export
-__device__ long long g_trace[4][64][8];
-__device__ unsigned long long g_cta_times[2048][2];
-__device__ long long g_wtrace[20][32][4];  // per softmax / drain warp of CTA (0,0,0): clock stamps per iteration
-__device__ __forceinline__ unsigned long long global_ns() {
-    unsigned long long t;
-    asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t));
-    return t;
-}
-#define TR(role, it, k)                                                                              \
-    do {                                                                                             \
-        if (blockIdx.x == 0 && (it) < 64) g_trace[role][it][k] = clock64(); \
-    } while (0)
-#define TRW(w, it, k)                                                                                \
-    do {                                                                                             \
-        if (blockIdx.x == 0 && (it) < 32 && (threadIdx.x & 31) == 0) g_wtrace[w][it][k] = clock64(); \
-    } while (0)
-#else
-#define TR(role, it, k)
-#define TRW(w, it, k)
-#endif
 
 template <int DP>
 __global__ void __launch_bounds__(kThreads, 1)
@@ -191,10 +169,6 @@ __global__ void __launch_bounds__(kThreads, 1)
     };
     constexpr int NB = LY::NB;
 
-#ifdef GE2_TRACE
-    const int cta_lin = (item * nsplit + split_h) % 1024 + (mode == 2 ? 1024 : 0);
-    if (tid == 0 && cta_lin < 2048) g_cta_times[cta_lin][0] = global_ns();
-#endif
     // The TMA thread sets the barriers up and starts the first loads at once, so their latency overlaps the allocation of
     // tensor memory and the block-wide barrier below (a fresh "empty" barrier needs no wait).
     const int n_early = n_iter < kStagesK ? n_iter : kStagesK;
@@ -266,9 +240,7 @@ __global__ void __launch_bounds__(kThreads, 1)
         if (lane == 0) {
             for (int i = n_early; i < n_iter; i++) {  // the first loads went out before the block-wide barrier
                 const int st = i % kStagesK, use = i / kStagesK;
-                TR(0, i, 0);
                 if (!wait(kBarKEmpty + st, (use & 1) ^ 1)) break;
-                TR(0, i, 1);
                 mbar_expect_tx(&bars[kBarKFull + st], LY::kTileBytes);
                 const int n0 = tile_n0(i);
 #pragma unroll
@@ -285,9 +257,7 @@ __global__ void __launch_bounds__(kThreads, 1)
             for (int i = 0; ok && i < n_iter; i++) {
                 const int st = i % kStagesK, use = i / kStagesK;
                 const int sb = s_buf(i), su = s_use(i);
-                TR(1, i, 0);
                 if (!wait(kBarKFull + st, use & 1)) break;
-                TR(1, i, 1);
                 if (i < nA) {
                     if (!wait(kBarSEmpty + sb, (su & 1) ^ 1)) break;
                 } else {
@@ -295,14 +265,12 @@ __global__ void __launch_bounds__(kThreads, 1)
                     if (i == nA && nA > 0 && !wait(kBarSEmpty + 0, (s_uses1 - 1) & 1)) break;
                     if (!wait(kBarSEmpty + 2, ((i - nA) & 1) ^ 1)) break;
                 }
-                TR(1, i, 2);
                 tc_fence_after();
                 const uint64_t dKk = desc_kmajor_base(aK0 + st * LY::kTileBytes);
 #pragma unroll
                 for (int ks = 0; ks < DP / kMmaK; ks++) mma_f16_ss(tS + sb * 128, dQk + koff_kmajor(ks), dKk + koff_kmajor(ks), kIdescS, ks > 0);
                 mma_commit(&bars[i < nA ? kBarSFull + (i & 1) : kBarSFull + 2]);
                 if (i < nA) mma_commit(&bars[kBarKEmpty + st]);  // sweep 1 needs the tile for nothing else
-                TR(1, i, 3);
             }
         }
     } else if (warp == kGradWarp) {
@@ -321,9 +289,7 @@ __global__ void __launch_bounds__(kThreads, 1)
                 const int j = nA + t, pb = t & 1, st = j % kStagesK;
                 // (no wait on the K stage: the probabilities were made from scores that were made from it)
                 if (!wait(kBarPFull + pb, (t >> 1) & 1)) break;
-                TR(1, j, 4);
                 if (!wait(kBarDkEmpty + (t & 1), ((t >> 1) & 1) ^ 1)) break;
-                TR(1, j, 5);
                 tc_fence_after();
                 const uint32_t aK = aK0 + st * LY::kTileBytes, aP = aP0 + pb * LY::kPBytes;
                 const uint64_t dPk = desc_kmajor_base(aP), dPm = desc_mnmajor_base(aP), dKm = desc_mnmajor_base(aK);
@@ -337,7 +303,6 @@ __global__ void __launch_bounds__(kThreads, 1)
                 mma_commit(&bars[kBarPEmpty + pb]);
                 mma_commit(&bars[kBarDkFull + (t & 1)]);
                 if (t == nB - 1) mma_commit(&bars[kBarDqFull]);
-                TR(1, j, 6);
             }
         }
     } else if (warp < kDrainWarp0) {
@@ -428,10 +393,7 @@ __global__ void __launch_bounds__(kThreads, 1)
             const int n0 = tile_n0(i);
             mask_bits(i + 2 < nA ? i + 2 : n_iter);
             const int sb = s_buf(i);
-            if (tid == 0) TR(2, i, 0);
             if (!warp_wait(kBarSFull + grp, (i >> 1) & 1)) { alive = false; break; }  // warp-uniform: tcgen05.ld is collective
-            if (tid == 0) TR(2, i, 1);
-            TRW(warp, i, 0);
             tc_fence_after();
 #pragma unroll
             for (int k = 0; k < 2; k++) {
@@ -442,7 +404,6 @@ __global__ void __launch_bounds__(kThreads, 1)
                     tc_fence_before();
                     __syncwarp();
                     if (lane == 0) mbar_arrive(&bars[kBarSEmpty + sb]);  // the tile is in registers: this S accumulator is free again
-                    TRW(warp, i, 1);
                 }
                 if (nv <= 0) continue;
                 if (nv < 32 || dump != nullptr) {  // ragged last tile, or the score dump of the tests
@@ -474,8 +435,6 @@ __global__ void __launch_bounds__(kThreads, 1)
                 run_l = fmaf(run_l, exp2f_fast(run_m - nm), (add[0] + add[1]) + (add[2] + add[3]));
                 run_m = nm;
             }
-            if (tid == 0) TR(2, i, 3);
-            TRW(warp, i, 3);
         }
         const int cg = warp >> 2;  // sweep 2: this warp's 32 columns of every tile
         auto load_mask2 = [&](int i) -> int32_t {
@@ -492,9 +451,7 @@ __global__ void __launch_bounds__(kThreads, 1)
             xch[slot * 128 + my_row] = make_float2(run_m, run_l);
             __syncwarp();
             if (lane == 0) mbar_arrive(&bars[kBarXch]);  // used once per launch: one arrival per softmax warp
-            TRW(warp, 31, 0);
             alive = warp_wait(kBarXch, 0);
-            TRW(warp, 31, 1);
             if (alive) {
                 float2 pr[kColGroups];
                 float nm = -INFINITY;
@@ -519,7 +476,6 @@ __global__ void __launch_bounds__(kThreads, 1)
                         my_loss = (lse2 - pos2) * 0.6931471805599453f;
                     }
                 }
-                TRW(warp, 31, 2);
             }
         }
         // ---------------- sweep 2: probabilities, all 16 warps on every tile ----------------
@@ -540,17 +496,13 @@ __global__ void __launch_bounds__(kThreads, 1)
                 }
             }
             const uint32_t wbits = __reduce_or_sync(0xffffffffu, mbits);
-            if (tid == 0) TR(2, i, 0);
             if (!warp_wait(kBarSFull + 2, t & 1)) break;
-            if (tid == 0) TR(2, i, 1);
-            TRW(warp, i, 0);
             tc_fence_after();
             float v[32];
             tmem_ld_32x32(tS + cg * 32 + lane_sel, v);
             tc_fence_before();
             __syncwarp();
             if (lane == 0) mbar_arrive(&bars[kBarSEmpty + 2]);  // the tile is in registers: the S accumulator is free again
-            TRW(warp, i, 1);
 #pragma unroll
             for (int j = 0; j < 32; j++) v[j] = exp2f_fast(fmaf(v[j], kLog2e, -lse2));
             // Masked entries were overwritten in place by the reference: no gradient reaches them.  Nothing else needs
@@ -566,8 +518,6 @@ __global__ void __launch_bounds__(kThreads, 1)
             }
             // the gradient MMAs that read this P buffer two tiles ago must be done
             if (!warp_wait(kBarPEmpty + pb, ((t >> 1) & 1) ^ 1)) break;
-            if (tid == 0) TR(2, i, 2);
-            TRW(warp, i, 2);
             unsigned char* sPb = sP + pb * LY::kPBytes;
 #pragma unroll
             for (int q = 0; q < 4; q++) {  // 8 halves = one 16-byte chunk
@@ -581,8 +531,6 @@ __global__ void __launch_bounds__(kThreads, 1)
             fence_proxy_async_smem();  // P was written with ordinary stores; the MMA reads it through the async proxy
             __syncwarp();
             if (lane == 0) mbar_arrive(&bars[kBarPFull + pb]);
-            if (tid == 0) TR(2, i, 3);
-            TRW(warp, i, 3);
         }
         // the loss of this block's rows, off the path between the sweeps
         if (alive && mode != 1 && slot == 0 && (mode == 0 || split_h == 0)) add_row_loss(my_loss);
@@ -598,9 +546,7 @@ __global__ void __launch_bounds__(kThreads, 1)
         bool ok = true;
         for (int t = 0; t < nB; t++) {
             const int n0 = tile_n0(nA + t);
-            if (tid == kDrainWarp0 * 32) TR(3, t, 0);
             if (!warp_wait(kBarDkFull + (t & 1), (t >> 1) & 1)) { ok = false; break; }
-            if (tid == kDrainWarp0 * 32) TR(3, t, 1);
             tc_fence_after();
             // Each 32 x 32 slab of the accumulator goes through a per-warp staging buffer in shared memory (128-byte rows,
             // 16-byte chunks XOR-swizzled by row: conflict-free stores, and the layout a SWIZZLE_128B tensor map expects) and
@@ -615,14 +561,11 @@ __global__ void __launch_bounds__(kThreads, 1)
 #pragma unroll 1
             for (int cb = 0; cb < n_slabs; cb++) {
                 float v[32];
-                if (tid == kDrainWarp0 * 32 && t == 1) TR(3, 32 + cb, 0);
                 tmem_ld_32x32(tdK + (t & 1) * 128 + lane_sel + cb * 32, v);  // warp-collective
-                if (tid == kDrainWarp0 * 32 && t == 1) TR(3, 32 + cb, 1);
                 if (cb == n_slabs - 1) {
                     tc_fence_before();
                     __syncwarp();
                     if (lane == 0) mbar_arrive(&bars[kBarDkEmpty + (t & 1)]);
-                    if (tid == kDrainWarp0 * 32) TR(3, t, 2);
                 }
                 unsigned char* scr = scr0 + (cb & 1) * 4096;
                 if (lane == 0) bulk_wait_group_read<1>();  // the reduction that last used this buffer (two slabs ago) has read it
@@ -639,12 +582,10 @@ __global__ void __launch_bounds__(kThreads, 1)
                 }
                 fence_proxy_async_smem();
                 __syncwarp();
-                if (tid == kDrainWarp0 * 32 && t == 1) TR(3, 32 + cb, 2);
                 if (lane == 0) {
                     tma_reduce_add_3d(narrow ? &tmDKt : &tmDK, cb * 32, n0 + (warp - kDrainWarp0) * 32, zc, scr);
                     bulk_commit_group();
                 }
-                if (tid == kDrainWarp0 * 32 && t == 1) TR(3, 32 + cb, 3);
             }
         }
         if (lane == 0) bulk_wait_group<0>();  // all of this warp's reductions have landed before the CTA can exit
@@ -701,9 +642,6 @@ __global__ void __launch_bounds__(kThreads, 1)
         tc_fence_after();
         tmem_dealloc(tmem, kTmemCols);
     }
-#ifdef GE2_TRACE
-    if (tid == 0 && cta_lin < 2048) g_cta_times[cta_lin][1] = global_ns();
-#endif
 }
 
 typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*, const cuuint32_t*,
@@ -838,17 +776,6 @@ int launch(const LpKernelArgs& a, cudaStream_t stream) {
 
 }  // namespace
 
-#ifdef GE2_TRACE
-extern "C" __attribute__((visibility("default"))) int ge2_debug_read_trace(long long* host_out) {
-    return (int)cudaMemcpyFromSymbol(host_out, g_trace, sizeof(long long) * 4 * 64 * 8);
-}
-extern "C" __attribute__((visibility("default"))) int ge2_debug_read_wtrace(long long* host_out) {
-    return (int)cudaMemcpyFromSymbol(host_out, g_wtrace, sizeof(long long) * 20 * 32 * 4);
-}
-extern "C" __attribute__((visibility("default"))) int ge2_debug_read_cta_times(unsigned long long* host_out) {
-    return (int)cudaMemcpyFromSymbol(host_out, g_cta_times, sizeof(unsigned long long) * 2048 * 2);
-}
-#endif
 
 int lp_scores_f16(const LpKernelArgs& a, cudaStream_t stream) {
     if (a.L.ld == 64) return launch<64>(a, stream);

@@ -173,12 +173,16 @@ __global__ void __launch_bounds__(256) dense_adagrad_kernel(float* __restrict__ 
 }
 
 // ---- dense Adagrad fused with the relation-gradient all-reduce over peer memory -------------------------------------
-// Every rank keeps its relation gradients in a buffer its peers can read (two halves used by alternate steps, then one
-// 8-byte flag per rank).  One launch per rank and step: announce "my gradients of step t are complete" by writing t + 1
-// into my slot of every peer's flag row, wait (bounded) until every peer has announced the same, then run the optimizer
-// step on the sum of all ranks' gradients, read straight from the peers over NVLink, and clear the half that the step
-// after next will accumulate into.  Why one barrier is enough: a rank announces step t + 1 only when its step-t launch
-// is over, so whoever gets past the wait of step t + 1 knows that nobody reads the half of step t any more.
+// Every rank keeps its relation gradients in a buffer its peers can read: two halves used by alternate steps, then one
+// 8-byte arrival flag per rank, then one 8-byte verdict word.  Two launches per rank and step:
+//   peer_arrive_kernel (one warp): announce "my gradients of step t are complete" by writing t + 1 into my slot of every
+//     peer's flag row, then wait -- lane p polls peer p, bounded by a time budget -- until every peer has announced the
+//     same, and publish ONE verdict for the step in this rank's verdict word (t + 1 = go, 0 = a peer never arrived);
+//   dense_adagrad_peers_kernel: every block reads that verdict, so all of them either run the optimizer step on the sum
+//     of the ranks' gradients (read straight from the peers over NVLink, 16 bytes at a time) and clear the half the step
+//     after next will accumulate into, or all of them leave the tables and the buffer untouched.
+// Why one barrier is enough: a rank announces step t + 1 only when its step-t launches are over, so whoever gets past
+// the wait of step t + 1 knows that nobody reads the half of step t any more.
 __device__ __forceinline__ void st_release_sys_u64(unsigned long long* p, unsigned long long v) {
     asm volatile("st.release.sys.global.u64 [%0], %1;" ::"l"(p), "l"(v) : "memory");
 }
@@ -187,53 +191,81 @@ __device__ __forceinline__ unsigned long long ld_acquire_sys_u64(const unsigned 
     asm volatile("ld.acquire.sys.global.u64 %0, [%1];" : "=l"(v) : "l"(p) : "memory");
     return v;
 }
+__device__ __forceinline__ unsigned long long global_timer_ns() {
+    unsigned long long t;
+    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+    return t;
+}
 
 constexpr int kMaxPeers = 16;
 struct PeerBuffers {
     float* buf[kMaxPeers];  // this process's mapping of every rank's gradient buffer, own rank included
 };
 
+__global__ void __launch_bounds__(32) peer_arrive_kernel(PeerBuffers peers, int world, int rank, int64_t numel,
+                                                         const unsigned long long* __restrict__ step_dev, unsigned long long budget_ns,
+                                                         int32_t* status) {
+    const unsigned long long epoch = *step_dev + 1ull;
+    const int64_t flags_off = 2 * numel;  // in floats; numel is even, so the flags are 8-byte aligned
+    const int lane = threadIdx.x;
+    int ok = 1;
+    if (lane < world) {
+        st_release_sys_u64(reinterpret_cast<unsigned long long*>(peers.buf[lane] + flags_off) + rank, epoch);
+        const unsigned long long* mine = reinterpret_cast<const unsigned long long*>(peers.buf[rank] + flags_off) + lane;
+        const unsigned long long t0 = global_timer_ns();
+        ok = 0;
+        // bounded twice: by the time budget and by an iteration count (should the timer not advance)
+        for (uint32_t i = 0; i < (1u << 26); i++) {
+            if (ld_acquire_sys_u64(mine) >= epoch) {
+                ok = 1;
+                break;
+            }
+            if ((i & 15u) == 15u && global_timer_ns() - t0 > budget_ns) break;
+            __nanosleep(i < 64 ? 20 : 400);
+        }
+    }
+    const bool all_ok = __all_sync(0xffffffffu, ok);
+    if (lane == 0) {
+        unsigned long long* verdict = reinterpret_cast<unsigned long long*>(peers.buf[rank] + flags_off) + world;
+        *verdict = all_ok ? epoch : 0ull;
+        if (!all_ok) or_status(status, GE2_STATUS_PEER_TIMEOUT);
+    }
+}
+
+template <int V>
 __global__ void __launch_bounds__(256) dense_adagrad_peers_kernel(float* __restrict__ param, float* __restrict__ sum, PeerBuffers peers, int world,
                                                                   int rank, int64_t numel, const unsigned long long* __restrict__ step_dev,
-                                                                  float neg_lr, float eps, float grad_scale, int32_t* status) {
+                                                                  float neg_lr, float eps, float grad_scale) {
+    using VT = typename Vec<V>::type;
     const unsigned long long epoch = *step_dev + 1ull;
+    const int64_t flags_off = 2 * numel;
+    // the one verdict of this step, written by the launch before this one on the same stream
+    if (*(reinterpret_cast<const unsigned long long*>(peers.buf[rank] + flags_off) + world) != epoch) return;
     const int64_t cur = (int64_t)((epoch - 1ull) & 1ull) * numel;  // half holding this step's gradients
     const int64_t other = numel - cur;                            // half to clear for the step after next
-    const int64_t flags_off = 2 * numel;                          // in floats; numel is even, so the flags are 8-byte aligned
-    __shared__ int s_ok;
-    if (blockIdx.x == 0 && threadIdx.x < world)
-        st_release_sys_u64(reinterpret_cast<unsigned long long*>(peers.buf[threadIdx.x] + flags_off) + rank, epoch);
-    if (threadIdx.x == 0) {
-        const unsigned long long* mine = reinterpret_cast<const unsigned long long*>(peers.buf[rank] + flags_off);
-        int ok = 1;
-        for (int p = 0; p < world && ok; p++) {
-            ok = 0;
-            for (uint32_t i = 0; i < (1u << 23); i++) {  // bounded: a few seconds (ranks drift apart while one of them captures a graph or
-                                                          // swaps partitions); a peer that never arrives ends the step with a status bit
-                if (ld_acquire_sys_u64(mine + p) >= epoch) {
-                    ok = 1;
-                    break;
-                }
-                __nanosleep(i < 64 ? 20 : 400);
-            }
-        }
-        s_ok = ok;
-    }
-    __syncthreads();
-    if (!s_ok) {
-        if (threadIdx.x == 0) or_status(status, GE2_STATUS_PEER_TIMEOUT);
-        return;
-    }
+    const int64_t nv = numel / V;
     const int64_t stride = (int64_t)gridDim.x * blockDim.x;
-    for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < numel; i += stride) {
-        float g = 0.f;
-        for (int p = 0; p < world; p++) g += __ldcv(peers.buf[p] + cur + i);  // volatile-style load: never a stale cached copy of peer memory
-        g = __fmul_rn(g, grad_scale);
-        const float sn = __fadd_rn(sum[i], __fmul_rn(g, g));
-        const float den = __fadd_rn(__fsqrt_rn(sn), eps);
-        sum[i] = sn;
-        param[i] = __fadd_rn(param[i], __fmul_rn(neg_lr, __fdiv_rn(g, den)));
-        peers.buf[rank][other + i] = 0.f;
+    for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < nv; i += stride) {
+        float g[V], t[V], sm[V], pr[V], z[V];
+#pragma unroll
+        for (int k = 0; k < V; k++) g[k] = 0.f, z[k] = 0.f;
+        for (int p = 0; p < world; p++) {  // volatile-style load: never a stale cached copy of peer memory
+            to_arr<V>(__ldcv(reinterpret_cast<const VT*>(peers.buf[p] + cur) + i), t);
+#pragma unroll
+            for (int k = 0; k < V; k++) g[k] += t[k];
+        }
+        to_arr<V>(reinterpret_cast<const VT*>(sum)[i], sm);
+        to_arr<V>(reinterpret_cast<const VT*>(param)[i], pr);
+#pragma unroll
+        for (int k = 0; k < V; k++) {
+            const float gk = __fmul_rn(g[k], grad_scale);
+            sm[k] = __fadd_rn(sm[k], __fmul_rn(gk, gk));
+            const float den = __fadd_rn(__fsqrt_rn(sm[k]), eps);
+            pr[k] = __fadd_rn(pr[k], __fmul_rn(neg_lr, __fdiv_rn(gk, den)));
+        }
+        reinterpret_cast<VT*>(sum)[i] = from_arr<V>(sm);
+        reinterpret_cast<VT*>(param)[i] = from_arr<V>(pr);
+        reinterpret_cast<VT*>(peers.buf[rank] + other)[i] = from_arr<V>(z);
     }
 }
 
@@ -407,15 +439,25 @@ extern "C" int ge2_dense_adagrad(float* param, float* sum_state, float* grad, in
 }
 
 extern "C" int ge2_dense_adagrad_peers(float* param, float* sum_state, float* const* peer_bufs, int32_t world, int32_t rank, int64_t numel,
-                                       const uint64_t* step_dev, float lr, float eps, float grad_scale, int32_t* status, ge2_stream_t stream_) {
+                                       const uint64_t* step_dev, float lr, float eps, float grad_scale, uint32_t wait_budget_us, int32_t* status,
+                                       ge2_stream_t stream_) {
     if (numel <= 0 || (numel & 1) || world < 1 || world > kMaxPeers || rank < 0 || rank >= world) return GE2_ERR_INVALID_ARGUMENT;
     if (param == nullptr || sum_state == nullptr || peer_bufs == nullptr || step_dev == nullptr || status == nullptr) return GE2_ERR_INVALID_ARGUMENT;
     PeerBuffers pb;
     for (int p = 0; p < kMaxPeers; p++) pb.buf[p] = p < world ? peer_bufs[p] : nullptr;
     for (int p = 0; p < world; p++)
         if (pb.buf[p] == nullptr) return GE2_ERR_INVALID_ARGUMENT;
-    dense_adagrad_peers_kernel<<<stream_grid(numel, 256), 256, 0, as_stream(stream_)>>>(
-        param, sum_state, pb, world, rank, numel, reinterpret_cast<const unsigned long long*>(step_dev), -lr, eps, grad_scale, status);
+    const unsigned long long budget_ns = (wait_budget_us == 0 ? 4000000ull : (unsigned long long)wait_budget_us) * 1000ull;
+    cudaStream_t stream = as_stream(stream_);
+    const unsigned long long* step = reinterpret_cast<const unsigned long long*>(step_dev);
+    peer_arrive_kernel<<<1, 32, 0, stream>>>(pb, world, rank, numel, step, budget_ns, status);
+    GE2_LAUNCH_CHECK();
+    uintptr_t bits = (uintptr_t)param | (uintptr_t)sum_state;
+    for (int p = 0; p < world; p++) bits |= (uintptr_t)pb.buf[p];
+    if (numel % 4 == 0 && (bits & 15) == 0)
+        dense_adagrad_peers_kernel<4><<<stream_grid(numel / 4, 256), 256, 0, stream>>>(param, sum_state, pb, world, rank, numel, step, -lr, eps, grad_scale);
+    else
+        dense_adagrad_peers_kernel<1><<<stream_grid(numel, 256), 256, 0, stream>>>(param, sum_state, pb, world, rank, numel, step, -lr, eps, grad_scale);
     GE2_LAUNCH_CHECK();
     return GE2_OK;
 }

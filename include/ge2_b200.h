@@ -204,17 +204,23 @@ GE2_API int ge2_adagrad_scatter(float *table, float *state, int64_t table_rows, 
 GE2_API int ge2_dense_adagrad(float *param, float *sum_state, float *grad, int64_t numel, float lr, float eps, float grad_scale,
                       int32_t clear_grad, ge2_stream_t stream);
 
-/* Model::all_reduce + the dense optimizer step of every replica (cpp/src/nn/model.cpp:174-204, cpp/src/nn/optim.cpp:109-143)
- * as ONE launch per rank: the sum over ranks is read straight from the peers' gradient buffers over NVLink instead of
- * going through a collective call.  peer_bufs[r] (host array of `world` device pointers) is this process's mapping of rank
- * r's buffer, own rank included; every buffer holds 2 * numel floats (two halves, used by alternate steps: the step whose
- * counter *step_dev is t accumulates its gradients into half t & 1) followed by `world` 8-byte flags, all zero at start;
- * numel must be even.  The kernel announces step t to every peer, waits (bounded, a few seconds) for all peers'
- * announcements, applies Adagrad to param / sum_state with g = grad_scale * sum over ranks, and clears half (t + 1) & 1 of
- * its own buffer.  A peer that never arrives sets GE2_STATUS_PEER_TIMEOUT in *status and leaves the tables untouched.
- * Every rank must launch it once per step, on devices that can access each other (ge2_enable_peer_access). */
+/* Model::all_reduce + the dense optimizer step of every replica (cpp/src/nn/model.cpp:174-204, cpp/src/nn/optim.cpp:109-143):
+ * the sum over ranks is read straight from the peers' gradient buffers over NVLink instead of going through a collective
+ * call.  peer_bufs[r] (host array of `world` device pointers) is this process's mapping of rank r's buffer, own rank
+ * included; every buffer holds 2 * numel floats (two halves, used by alternate steps: the step whose counter *step_dev is
+ * t accumulates its gradients into half t & 1) followed by `world` 8-byte arrival flags and one 8-byte verdict word, all
+ * zero at start; numel must be even.  Two launches: a one-warp kernel announces step t to every peer, waits for all
+ * peers' announcements -- at most wait_budget_us microseconds (0 = 4 s) -- and writes one verdict for the step; the update
+ * kernel then either applies Adagrad to param / sum_state with g = grad_scale * sum over ranks and clears half (t + 1) & 1
+ * of its own buffer, or -- a peer never arrived -- changes nothing at all: GE2_STATUS_PEER_TIMEOUT is set in *status and
+ * param, sum_state and the buffer are left bit for bit as they were.  After a timeout the replicas can no longer be
+ * assumed equal (the peers may have gone on with this rank's gradients): treat it as fatal for the run.
+ * Every rank launches it once per step, on devices that can access each other (ge2_enable_peer_access); a rank that has
+ * no batch in a step (lanes of a superstep have unequal batch counts; the reference zero-fills their gradients,
+ * model.cpp:182-187) launches only this: its half is still zero, so it contributes zeros and keeps its replica in step. */
 GE2_API int ge2_dense_adagrad_peers(float *param, float *sum_state, float *const *peer_bufs, int32_t world, int32_t rank, int64_t numel,
-                            const uint64_t *step_dev, float lr, float eps, float grad_scale, int32_t *status, ge2_stream_t stream);
+                            const uint64_t *step_dev, float lr, float eps, float grad_scale, uint32_t wait_budget_us, int32_t *status,
+                            ge2_stream_t stream);
 
 /* cudaDeviceEnablePeerAccess from the current device to peer_device (no-op when already enabled or the same device):
  * what the relay path does before its peer copies (cpp/src/storage/storage.cpp:599-652 copies between device buffers). */

@@ -141,3 +141,76 @@ def test_sample_negatives_structure(capi, cuda_device, want_src):
     uni = dst_negs[:, n_deg:].reshape(-1)
     assert abs(uni.mean() / domain - 0.5) < 0.05 and np.unique(uni).size > 0.9 * uni.size * (1 - uni.size / domain)
     assert not np.array_equal(p, packed2.cpu().numpy())  # another batch index, other draws
+
+
+def _peer_buffers(world, numel, device, rng):
+    """`world` gradient buffers on ONE device laid out as ge2_dense_adagrad_peers expects (two halves, `world` 8-byte arrival
+    flags, one 8-byte verdict word); half 0 holds random gradients, half 1 a sentinel the step has to clear."""
+    bufs, grads = [], []
+    for _ in range(world):
+        g = (0.1 * rng.standard_normal(numel)).astype(np.float32)
+        b = torch.zeros(2 * numel + 2 * world + 2, dtype=torch.float32, device=device)
+        b[:numel] = torch.from_numpy(g).to(device)
+        b[numel:2 * numel] = 7.0
+        bufs.append(b)
+        grads.append(g)
+    return bufs, grads
+
+
+def _set_arrival(buf, numel, world, slot, epoch):
+    """what a peer's announcement writes: `epoch` into arrival flag `slot` of this rank's buffer"""
+    flags = buf[2 * numel:2 * numel + 2 * world].view(torch.int64)
+    flags[slot] = epoch
+
+
+@pytest.mark.parametrize("world", [2, 4])
+def test_peer_reduced_dense_adagrad_matches_oracle(capi, cuda_device, world):
+    """Model::all_reduce + the dense step against the oracle (gradients divided by the device count, summed in device
+    order, then Adagrad), with the ranks' buffers emulated on one GPU: the peers' announcements are written by the host, so
+    no kernel waits for another launch."""
+    rng = np.random.default_rng(world)
+    numel = 2 * 37 * 100
+    bufs, grads = _peer_buffers(world, numel, cuda_device, rng)
+    p = rng.standard_normal(numel).astype(np.float32)
+    s = rng.random(numel).astype(np.float32)
+    t_p, t_s = torch.from_numpy(p.copy()).to(cuda_device), torch.from_numpy(s.copy()).to(cuda_device)
+    step = torch.zeros(2, dtype=torch.int64, device=cuda_device)
+    status = torch.zeros(1, dtype=torch.int32, device=cuda_device)
+    for peer in range(1, world):
+        _set_arrival(bufs[0], numel, world, peer, 1)
+    capi.dense_adagrad_peers(t_p, t_s, [b.data_ptr() for b in bufs], 0, numel, step, 0.1, status, grad_scale=1.0 / world, wait_budget_us=2000)
+    torch.cuda.synchronize()
+    assert int(status) == 0
+    g = O.allreduce_relation_grads(grads)
+    ep, es = O.dense_adagrad(p.copy(), g, s.copy(), 0.1)
+    assert np.array_equal(t_p.cpu().numpy(), ep) and np.array_equal(t_s.cpu().numpy(), es)
+    assert float(bufs[0][numel:2 * numel].abs().max()) == 0.0           # the other half is cleared for the step after next
+    assert np.array_equal(bufs[0][:numel].cpu().numpy(), grads[0])      # this step's half is left for the peers to read
+    flags = bufs[0][2 * numel:].view(torch.int64).cpu().tolist()
+    assert flags[0] == 1 and flags[world] == 1                          # own announcement, and the verdict of step 0
+
+
+def test_peer_wait_runs_out_and_leaves_everything_untouched(capi, cuda_device):
+    """A peer that never announces: the bounded wait (5 ms here) ends, GE2_STATUS_PEER_TIMEOUT is set, and neither the
+    tables nor the gradient buffer change by a single bit -- every block acts on the one verdict of the launch."""
+    rng = np.random.default_rng(9)
+    world, numel = 2, 2 * 1000 * 100
+    bufs, _ = _peer_buffers(world, numel, cuda_device, rng)
+    p = rng.standard_normal(numel).astype(np.float32)
+    s = rng.random(numel).astype(np.float32)
+    t_p, t_s = torch.from_numpy(p.copy()).to(cuda_device), torch.from_numpy(s.copy()).to(cuda_device)
+    before = bufs[0][:2 * numel].clone()
+    step = torch.zeros(2, dtype=torch.int64, device=cuda_device)
+    status = torch.zeros(1, dtype=torch.int32, device=cuda_device)
+    capi.dense_adagrad_peers(t_p, t_s, [b.data_ptr() for b in bufs], 0, numel, step, 0.1, status, grad_scale=0.5, wait_budget_us=5000)
+    torch.cuda.synchronize()
+    assert int(status) & 32
+    assert np.array_equal(t_p.cpu().numpy(), p) and np.array_equal(t_s.cpu().numpy(), s)
+    assert torch.equal(bufs[0][:2 * numel], before)
+    assert bufs[0][2 * numel:].view(torch.int64).cpu().tolist()[world] == 0  # verdict: no go
+    # the context is still usable and a later, complete step goes through
+    status.zero_()
+    _set_arrival(bufs[0], numel, world, 1, 1)
+    capi.dense_adagrad_peers(t_p, t_s, [b.data_ptr() for b in bufs], 0, numel, step, 0.1, status, grad_scale=0.5, wait_budget_us=5000)
+    torch.cuda.synchronize()
+    assert int(status) == 0 and not np.array_equal(t_p.cpu().numpy(), p)

@@ -20,11 +20,17 @@ def test_static_scratch_matches_workspace_entry_twice(capi, cuda_device):
         u = torch.full((n,), -7, dtype=torch.int64, device=cuda_device)
         inv = torch.full((n,), -7, dtype=torch.int64, device=cuda_device)
         cnt = torch.full((2,), -7, dtype=torch.int32, device=cuda_device)
+        if call == 0:  # warm-up: the first call on a device looks up the scratch array's address (and loads the kernels)
+            capi.unique_bitmap_static(ids, domain, u, inv, cnt)
         torch.cuda.synchronize()
+        # free bytes as the driver counts them: a cudaMalloc inside the library (which links its own static runtime and is
+        # invisible to torch's allocator statistics) would lower it
+        free_before = torch.cuda.mem_get_info(cuda_device)[0]
         before = torch.cuda.memory_allocated(cuda_device)
         capi.unique_bitmap_static(ids, domain, u, inv, cnt)
         torch.cuda.synchronize()
         assert torch.cuda.memory_allocated(cuda_device) == before
+        assert torch.cuda.mem_get_info(cuda_device)[0] == free_before
         c = int(ref_cnt[0])
         assert cnt.cpu().tolist() == [c, 0] and ref_cnt.cpu().tolist() == [c, 0]
         assert torch.equal(u[:c], ref_u[:c]) and torch.equal(inv, ref_inv)  # integers: exact
