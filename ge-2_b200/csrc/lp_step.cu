@@ -96,6 +96,8 @@ __global__ void __launch_bounds__(256) lp_prep_kernel(LpKernelArgs a) {
     const bool vec_r = D % 4 == 0 && ((((uintptr_t)d.rel) | ((uintptr_t)d.inv_rel)) & 15) == 0;
     const bool write_k32 = d.precision != GE2_PRECISION_F16;  // the tensor path reads only the fp16 copy of the negatives
     if (blockIdx.x == 0 && tid == 0) *L.loss_acc = 0.0;        // the scores kernel of this step adds every row's loss term to it
+    if (blockIdx.x == 0 && L.item_ctr != nullptr)               // arrival counters of the tensor path's logsumexp pass start at zero
+        for (int k = tid; k < L.n_items + 2; k += blockDim.x) L.item_ctr[k] = 0;
     for (int64_t w = ((int64_t)blockIdx.x * blockDim.x + tid) >> 3; w < total_pad; w += groups) {
         if (w >= total) continue;
         if (w < q_rows) {
@@ -213,6 +215,7 @@ __global__ void __launch_bounds__(kFinWarps * 32) lp_finish_kernel(LpKernelArgs 
     const int n_el = cplx ? h : D;       // coordinates a lane loop runs over: complex pairs, or plain columns
     const int off2 = cplx ? h : 0;       // where the second component of a coordinate lives
     const bool vec_g = (D % 4 == 0) && (((uintptr_t)d.node_grad) & 15) == 0;
+    const float gs = L.grad_unscale;  // the tensor path leaves dQ / dK scaled by a power of two
 
     // loss = sum over sides and padded rows of (lse - pos), accumulated in double by the scores kernel that ran before
     if (blockIdx.x == 0 && tid == 0) *d.loss = (float)*L.loss_acc;
@@ -241,12 +244,13 @@ __global__ void __launch_bounds__(kFinWarps * 32) lp_finish_kernel(LpKernelArgs 
             float* grow = d.node_grad + id * D;
             if (vec_g) {
                 for (int k = lane * 4; k < D; k += 128) {
-                    const float4 v = *reinterpret_cast<const float4*>(dk + k);
+                    float4 v = *reinterpret_cast<const float4*>(dk + k);
+                    v.x *= gs, v.y *= gs, v.z *= gs, v.w *= gs;
                     if (v.x != 0.f || v.y != 0.f || v.z != 0.f || v.w != 0.f) atomicAdd(reinterpret_cast<float4*>(grow + k), v);
                 }
             } else {
                 for (int k = lane; k < D; k += 32) {
-                    const float v = dk[k];
+                    const float v = dk[k] * gs;
                     if (v != 0.f) atomicAdd(grow + k, v);
                 }
             }
@@ -330,8 +334,8 @@ __global__ void __launch_bounds__(kFinWarps * 32) lp_finish_kernel(LpKernelArgs 
                     const float a0 = s == 0 ? s0 : d0, a1 = s == 0 ? s1 : d1;  // endpoint the relation is applied to
                     const float b0 = s == 0 ? d0 : s0, b1 = s == 0 ? d1 : s1;  // endpoint it is compared with
                     // gradient with respect to the relation-adjusted embedding q = op(a, r): from the negatives (dQ) and the positive
-                    const float g0 = dq[s][c] + dpos[s] * b0;
-                    const float g1 = cplx ? dq[s][c2] + dpos[s] * b1 : 0.f;
+                    const float g0 = dq[s][c] * gs + dpos[s] * b0;
+                    const float g1 = cplx ? dq[s][c2] * gs + dpos[s] * b1 : 0.f;
                     float ga0, ga1 = 0.f, gb0, gb1 = 0.f, vr0 = 0.f, vr1 = 0.f;
                     if (r[s] == nullptr) {            // Dot: q = a
                         gb0 = dpos[s] * a0;
@@ -448,7 +452,8 @@ extern "C" int ge2_lp_step(const ge2_lp_desc* desc, ge2_stream_t stream_) {
     cudaStream_t stream = as_stream(stream_);
 
     const int phases = desc->phases == 0 ? 7 : desc->phases;
-    if (phases & 2) GE2_CUDA_TRY(cudaMemsetAsync(L.dK, 0, L.zero_bytes, stream));
+    // fp32 path: dK is reduced with atomics and starts from zero; the tensor path stores whole tiles and clears nothing
+    if ((phases & 2) && desc->precision == GE2_PRECISION_FP32) GE2_CUDA_TRY(cudaMemsetAsync(L.dK, 0, L.zero_bytes, stream));
     if ((phases & 4) && !(desc->flags & GE2_LP_NODE_GRAD_IS_ZERO))
         GE2_CUDA_TRY(cudaMemsetAsync(desc->node_grad, 0, (size_t)desc->U * desc->D * 4, stream));
     if (phases & 1) {

@@ -45,6 +45,12 @@ __device__ __forceinline__ void tma_load_3d(void* smem_dst, const CUtensorMap* m
         "l"(map), "r"(smem_u32(bar)), "r"(x), "r"(y), "r"(z)
         : "memory");
 }
+// Untiled bulk copy global -> shared (both addresses 16-byte aligned, size a multiple of 16), counted on the same kind of mbarrier
+__device__ __forceinline__ void bulk_load_1d(void* smem_dst, const void* gsrc, uint32_t bytes, uint64_t* bar) {
+    asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(smem_u32(smem_dst)), "l"(gsrc),
+                 "r"(bytes), "r"(smem_u32(bar))
+                 : "memory");
+}
 // TMA: tiled 3-D reduction shared -> global (element-wise fp32 add into global memory), tracked by bulk groups.
 // Rows / columns of the box that fall outside the tensor are dropped.
 __device__ __forceinline__ void tma_reduce_add_3d(const CUtensorMap* map, int x, int y, int z, const void* smem_src) {

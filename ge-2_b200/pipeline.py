@@ -448,15 +448,7 @@ class BatchPipeline:
         n = 1 + 3                              # sampler; unique-map: mark, scan, inverse
         n += 1 if cfg.n_deg > 0 else 0         # filter mask from the degree-sampled rows
         n += 1                                 # prepare (gather + relation operator + positive scores)
-        if cfg.precision == "f16":             # scores: whole rounds of 148 blocks unsplit, the remainder split over two launches
-            npc = -(-cfg.B // cfg.C)
-            items, tiles = -(-npc // 128) * cfg.C * cfg.sides, -(-cfg.N // 128)
-            whole = items // 148 * 148
-            rest = items - whole
-            ns = max([k for k in (1, 2, 4, 8) if k == 1 or (rest * k <= 148 and k <= tiles)]) if rest else 1
-            n += (1 if whole else 0) + (0 if rest == 0 else (1 if ns == 1 else 2))
-        else:
-            n += 1
+        n += 2 if cfg.precision == "f16" else 1  # scores: logsumexp pass + gradient pass (persistent launches), or the fp32 kernel
         n += 1                                 # finish (operator backward + scatter)
         n += 1                                 # sparse Adagrad scatter
         if cfg.has_relations:
