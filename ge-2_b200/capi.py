@@ -22,7 +22,7 @@ EXPORTS = [
     "ge2_unique_bitmap", "ge2_pack_ids", "ge2_lp_workspace_bytes", "ge2_lp_step", "ge2_sparse_adagrad", "ge2_index_read",
     "ge2_index_add", "ge2_adagrad_scatter", "ge2_dense_adagrad", "ge2_sample_negatives", "ge2_remap_edges_to_slots",
     "ge2_copy_slabs", "ge2_unique_bitmap_static", "ge2_sample_batch", "ge2_advance_step", "ge2_dense_adagrad_peers",
-    "ge2_enable_peer_access",
+    "ge2_enable_peer_access", "ge2_build_state_edges", "ge2_swap_begin", "ge2_swap_wait", "ge2_sample_batch_dev",
 ]
 
 
@@ -45,6 +45,12 @@ class LpDesc(C.Structure):
         ("pos_scores", C.c_void_p), ("neg_scores", C.c_void_p), ("inv_pos_scores", C.c_void_p), ("inv_neg_scores", C.c_void_p),
         ("status", C.c_void_p), ("workspace", C.c_void_p), ("workspace_bytes", C.c_size_t),
     ]
+
+
+class SwapDesc(C.Structure):
+    _fields_ = [("world", C.c_int32), ("rank", C.c_int32), ("flag_rows", C.POINTER(C.c_void_p)), ("epoch", C.c_uint64),
+                ("wait_budget_us", C.c_uint32), ("num_pulls", C.c_int32), ("pull_src", C.POINTER(C.c_void_p)), ("pull_dst", C.POINTER(C.c_void_p)),
+                ("slab_bytes", C.c_int64), ("status", C.c_void_p)]
 
 
 _lib = None
@@ -86,6 +92,12 @@ def load_library():
                                          C.c_uint64, C.c_uint64, C.c_void_p, C.c_void_p, C.c_void_p]
     lib.ge2_sample_batch.argtypes = [C.c_void_p, C.c_int32, C.c_int64, C.c_void_p, C.c_int32, C.c_int32, C.c_int32, C.c_int32, C.c_int64, C.c_int32,
                                      C.c_uint64, C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p]
+    lib.ge2_sample_batch_dev.argtypes = [C.c_void_p, C.c_int32, C.c_void_p, C.c_void_p, C.c_int32, C.c_int32, C.c_int32, C.c_int32, C.c_int64, C.c_int32,
+                                         C.c_uint64, C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p]
+    lib.ge2_build_state_edges.argtypes = [C.c_void_p, C.c_int32, C.POINTER(C.c_int64), C.POINTER(C.c_int64), C.c_int32, C.c_void_p, C.c_int32, C.c_int64,
+                                          C.c_uint64, C.c_void_p, C.POINTER(C.c_int64), C.c_void_p, C.c_void_p]
+    lib.ge2_swap_begin.argtypes = [C.POINTER(SwapDesc), C.c_void_p]
+    lib.ge2_swap_wait.argtypes = [C.c_void_p, C.c_void_p]
     lib.ge2_advance_step.argtypes = [C.c_void_p, C.c_int32, C.c_void_p]
     lib.ge2_remap_edges_to_slots.argtypes = [C.c_void_p, C.c_int64, C.c_int32, C.c_void_p, C.c_int32, C.c_int64, C.c_void_p, C.c_void_p, C.c_void_p]
     lib.ge2_copy_slabs.argtypes = [C.c_void_p, C.c_void_p, C.POINTER(C.c_int32), C.c_int32, C.c_int64, C.c_void_p]
@@ -261,6 +273,44 @@ def sample_negatives(src_ids, dst_ids, edge_stride, B, Cn, N, n_deg, domain, wan
 def sample_batch(edges, num_batches, step_dev, B, Cn, N, n_deg, domain, want_src, seed, out_packed, out_deg_rows, out_rel):
     check(load_library().ge2_sample_batch(ptr(edges), edges.shape[1], num_batches, ptr(step_dev), B, Cn, N, n_deg, domain, 1 if want_src else 0,
                                           seed, ptr(out_packed), ptr(out_deg_rows), ptr(out_rel), cur_stream()), "ge2_sample_batch")
+
+
+def sample_batch_dev(edges, num_batches_dev, step_dev, B, Cn, N, n_deg, domain, want_src, seed, out_packed, out_deg_rows, out_rel):
+    """sample_batch with the number of batches of the resident edge list read from device memory (int64 scalar tensor)."""
+    check(load_library().ge2_sample_batch_dev(ptr(edges), edges.shape[1], ptr(num_batches_dev), ptr(step_dev), B, Cn, N, n_deg, domain,
+                                              1 if want_src else 0, seed, ptr(out_packed), ptr(out_deg_rows), ptr(out_rel), cur_stream()),
+          "ge2_sample_batch_dev")
+
+
+def build_state_edges(edges_sorted, bucket_begin, bucket_len, partition_to_slot, partition_size: int, seed: int, out_edges, status=None) -> int:
+    """Edge list of one partition-buffer state: the named buckets of the bucket-sorted list, concatenated, remapped to buffer
+    slots and shuffled, in one launch.  bucket_begin / bucket_len: Python lists.  Returns the number of rows written."""
+    nb = len(bucket_begin)
+    beg = (C.c_int64 * max(nb, 1))(*bucket_begin)
+    ln = (C.c_int64 * max(nb, 1))(*bucket_len)
+    total = C.c_int64(0)
+    assert sum(bucket_len) <= out_edges.shape[0]
+    check(load_library().ge2_build_state_edges(ptr(edges_sorted), edges_sorted.shape[1], beg, ln, nb, ptr(partition_to_slot), partition_to_slot.numel(),
+                                               partition_size, seed, ptr(out_edges), C.byref(total), ptr(status), cur_stream()), "ge2_build_state_edges")
+    return total.value
+
+
+def swap_begin(world: int, rank: int, flag_row_ptrs, epoch: int, pulls, slab_bytes: int, status, wait_budget_us: int = 0, stream=None):
+    """pulls: list of (src address, dst address) ints.  flag_row_ptrs: list of `world` addresses (None when world == 1)."""
+    d = SwapDesc()
+    d.world, d.rank, d.epoch, d.wait_budget_us = world, rank, epoch, wait_budget_us
+    rows = (C.c_void_p * max(world, 1))(*(flag_row_ptrs or [None]))
+    d.flag_rows = C.cast(rows, C.POINTER(C.c_void_p))
+    n = len(pulls)
+    src = (C.c_void_p * max(n, 1))(*[p[0] for p in pulls])
+    dst = (C.c_void_p * max(n, 1))(*[p[1] for p in pulls])
+    d.num_pulls, d.pull_src, d.pull_dst = n, C.cast(src, C.POINTER(C.c_void_p)), C.cast(dst, C.POINTER(C.c_void_p))
+    d.slab_bytes, d.status = slab_bytes, ptr(status)
+    check(load_library().ge2_swap_begin(C.byref(d), cur_stream() if stream is None else stream), "ge2_swap_begin")
+
+
+def swap_wait(swap_stream: int, compute_stream: int):
+    check(load_library().ge2_swap_wait(swap_stream, compute_stream), "ge2_swap_wait")
 
 
 def advance_step(step_dev, n=1):

@@ -319,10 +319,14 @@ __global__ void __launch_bounds__(256) sample_negatives_kernel(const int64_t* __
                                                                int want_src, uint64_t key, int64_t* __restrict__ packed,
                                                                int64_t* __restrict__ deg_rows, const uint64_t* __restrict__ step_dev,
                                                                int64_t num_batches, const int64_t* __restrict__ rel_ids,
-                                                               int64_t* __restrict__ out_rel) {
+                                                               int64_t* __restrict__ out_rel, const int64_t* __restrict__ num_batches_dev) {
     // graph-replay form: the batch index lives on the device, so the same launch serves every batch of the epoch
     if (step_dev != nullptr) {
         const uint64_t step = *step_dev;
+        if (num_batches_dev != nullptr) {  // ... and so does the length of the resident edge list
+            num_batches = *num_batches_dev;
+            if (num_batches < 1) num_batches = 1;
+        }
         const int64_t off = (int64_t)(step % (uint64_t)num_batches) * B * edge_stride;
         src_ids += off;
         dst_ids += off;
@@ -488,14 +492,14 @@ extern "C" int ge2_sample_negatives(const int64_t* src_ids, const int64_t* dst_i
     const uint64_t key = seed * 0xD1342543DE82EF95ull + batch_index * 0x9E3779B97F4A7C15ull + 0x632BE59BD9B4E019ull;
     sample_negatives_kernel<<<stream_grid(total, 256), 256, 0, as_stream(stream_)>>>(src_ids, dst_ids, edge_stride, B, C, N, n_deg, domain,
                                                                                    want_src_negs, key, out_packed_ids, out_deg_rows, nullptr, 1,
-                                                                                   nullptr, nullptr);
+                                                                                   nullptr, nullptr, nullptr);
     GE2_LAUNCH_CHECK();
     return GE2_OK;
 }
 
-extern "C" int ge2_sample_batch(const int64_t* edges, int32_t cols, int64_t num_batches, const uint64_t* step_dev, int32_t B, int32_t C,
-                                int32_t N, int32_t n_deg, int64_t domain, int32_t want_src_negs, uint64_t seed, int64_t* out_packed_ids,
-                                int64_t* out_deg_rows, int64_t* out_rel_ids, ge2_stream_t stream_) {
+static int sample_batch_impl(const int64_t* edges, int32_t cols, int64_t num_batches, const int64_t* num_batches_dev, const uint64_t* step_dev,
+                             int32_t B, int32_t C, int32_t N, int32_t n_deg, int64_t domain, int32_t want_src_negs, uint64_t seed,
+                             int64_t* out_packed_ids, int64_t* out_deg_rows, int64_t* out_rel_ids, ge2_stream_t stream_) {
     if (B <= 0 || C <= 0 || N <= 0 || n_deg < 0 || n_deg > N || domain <= 0 || num_batches <= 0 || (cols != 2 && cols != 3))
         return GE2_ERR_INVALID_ARGUMENT;
     if (edges == nullptr || step_dev == nullptr || out_packed_ids == nullptr) return GE2_ERR_INVALID_ARGUMENT;
@@ -504,9 +508,24 @@ extern "C" int ge2_sample_batch(const int64_t* edges, int32_t cols, int64_t num_
     const uint64_t key = seed * 0xD1342543DE82EF95ull + 0x632BE59BD9B4E019ull;
     sample_negatives_kernel<<<stream_grid(total, 256), 256, 0, as_stream(stream_)>>>(
         edges, edges + cols - 1, cols, B, C, N, n_deg, domain, want_src_negs, key, out_packed_ids, out_deg_rows, step_dev, num_batches,
-        cols == 3 ? edges + 1 : nullptr, cols == 3 ? out_rel_ids : nullptr);
+        cols == 3 ? edges + 1 : nullptr, cols == 3 ? out_rel_ids : nullptr, num_batches_dev);
     GE2_LAUNCH_CHECK();
     return GE2_OK;
+}
+
+extern "C" int ge2_sample_batch(const int64_t* edges, int32_t cols, int64_t num_batches, const uint64_t* step_dev, int32_t B, int32_t C,
+                                int32_t N, int32_t n_deg, int64_t domain, int32_t want_src_negs, uint64_t seed, int64_t* out_packed_ids,
+                                int64_t* out_deg_rows, int64_t* out_rel_ids, ge2_stream_t stream) {
+    return sample_batch_impl(edges, cols, num_batches, nullptr, step_dev, B, C, N, n_deg, domain, want_src_negs, seed, out_packed_ids,
+                             out_deg_rows, out_rel_ids, stream);
+}
+
+extern "C" int ge2_sample_batch_dev(const int64_t* edges, int32_t cols, const int64_t* num_batches_dev, const uint64_t* step_dev, int32_t B,
+                                    int32_t C, int32_t N, int32_t n_deg, int64_t domain, int32_t want_src_negs, uint64_t seed,
+                                    int64_t* out_packed_ids, int64_t* out_deg_rows, int64_t* out_rel_ids, ge2_stream_t stream) {
+    if (num_batches_dev == nullptr) return GE2_ERR_INVALID_ARGUMENT;
+    return sample_batch_impl(edges, cols, 1, num_batches_dev, step_dev, B, C, N, n_deg, domain, want_src_negs, seed, out_packed_ids,
+                             out_deg_rows, out_rel_ids, stream);
 }
 
 __global__ void advance_step_kernel(uint64_t* step, int n) {

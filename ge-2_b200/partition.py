@@ -122,6 +122,11 @@ def plan_swap(place: Placement, next_states: Sequence[Optional[Sequence[int]]]) 
             if p in claimed:
                 raise ValueError(f"partition {p} claimed by ranks {claimed[p]} and {r}: states of a superstep must be disjoint")
             claimed[p] = r
+    for r, st in enumerate(next_states):
+        if st is None:  # an idle rank keeps its partitions: nobody else may claim one of them
+            for p in place.slots[r]:
+                if p >= 0 and p in claimed:
+                    raise ValueError(f"partition {p} stays on idle rank {r} but rank {claimed[p]} claims it")
     new_slots = [list(s) for s in place.slots]
     moves: List[Move] = []
     # 1. evictions: resident partitions that their rank does not keep
@@ -277,3 +282,240 @@ class PartitionBuffer:
             if p >= 0:
                 tab[p] = slot
         return tab
+
+
+# ----------------------------------------------------------------------------------------------------------------
+# the buffer with device-side swaps: two active buffers per table, receiver-side pulls behind a device-side barrier
+# ----------------------------------------------------------------------------------------------------------------
+def plan_relay(place: Placement, next_states: Sequence[Optional[Sequence[int]]]):
+    """Slot tables and pulls of a swap of RelayBuffer: every rank's next buffer is filled slot by slot (the state's
+    partitions in ascending order) from wherever each partition is now -- a slot of some rank's current buffer (the
+    reference's relay copy, storage.cpp:626-652) or its home slab -- and a resident partition that nobody keeps is pulled
+    by its home rank.  A rank whose next state is None keeps its partitions (they still move to its other buffer).
+    Returns (new_slots, pulls) with pulls[rank] = list of (src_kind, src_rank, src_index, dst_kind, dst_index)."""
+    world = place.world
+    states = []
+    claimed = {}
+    for r in range(world):
+        st = next_states[r]
+        st = sorted(p for p in place.slots[r] if p >= 0) if st is None else sorted(st)
+        if len(st) > CAPACITY or len(set(st)) != len(st):
+            raise ValueError("a state holds at most 4 distinct partitions")
+        for p in st:
+            if p in claimed:
+                raise ValueError(f"partition {p} claimed by ranks {claimed[p]} and {r}: states of a superstep must be disjoint")
+            claimed[p] = r
+        states.append(st)
+    new_slots = [st + [-1] * (CAPACITY - len(st)) for st in states]
+    pulls = [[] for _ in range(world)]
+    for r in range(world):
+        for slot, p in enumerate(states[r]):
+            if p in place.in_buffer:
+                sr, ss = place.in_buffer[p]
+                pulls[r].append(("buf", sr, ss, "buf", slot))
+            else:
+                pulls[r].append(("home", place.home_rank(p), place.home_index(p), "buf", slot))
+    for p, (sr, ss) in sorted(place.in_buffer.items()):
+        if p not in claimed:  # nobody needs it next: its home rank fetches it
+            pulls[place.home_rank(p)].append(("buf", sr, ss, "home", place.home_index(p)))
+    return new_slots, pulls
+
+
+class RelayBuffer:
+    """Partition buffer whose swaps run on the device (ge2_swap_begin): two active buffers [4 * partition_rows, D] per table
+    that alternate from superstep to superstep, home slabs for the partitions this rank is home of (p % world == rank), all
+    of it symmetric memory when world > 1 so that every rank can read every other rank's slabs over NVLink.  A swap reads
+    the buffers of the superstep that ended and writes the buffers of the one that begins: no staging copy, no host barrier.
+
+    The counterpart of MemPartitionBufferStorage (storage.cpp:359-757 of the reference) with its peer relay, except that every
+    partition also has a home on some GPU, so nothing is staged through the host when world * 4 < num_partitions."""
+
+    def __init__(self, tables_home: Sequence, partition_rows: int, num_partitions: int, rank: int, world: int, dist=None):
+        import torch
+
+        from . import capi
+
+        self.capi = capi
+        self.rank, self.world, self.dist = rank, world, dist
+        self.rows, self.num_partitions = partition_rows, num_partitions
+        self.parity = 0
+        self.epoch = 0
+        self.place = Placement.initial(world, num_partitions)
+        dev = tables_home[0].device
+        self.status = torch.zeros(1, dtype=torch.int32, device=dev)
+        self.slab_bytes = [partition_rows * t.shape[1] * t.element_size() for t in tables_home]
+        shape = lambda t: (CAPACITY * partition_rows, t.shape[1])
+        if world > 1:
+            import os
+
+            os.environ.setdefault("TORCH_SYMM_MEM_DISABLE_MULTICAST", "1")  # plain peer loads only
+            import torch.distributed._symmetric_memory as symm_mem
+
+            self._keep = []
+
+            def shared(sh, dtype, init=None):
+                b = symm_mem.empty(sh, dtype=dtype, device=dev)
+                if init is None:
+                    b.zero_()
+                else:
+                    b.copy_(init)
+                torch.cuda.synchronize(dev)
+                h = symm_mem.rendezvous(b, dist.group.WORLD)
+                self._keep.append(h)
+                return b, [int(x) for x in h.buffer_ptrs]
+
+            self.home, self.home_ptrs, self.bufs, self.buf_ptrs = [], [], [[], []], [[], []]
+            for t in tables_home:
+                b, ptrs = shared(tuple(t.shape), t.dtype, t)
+                self.home.append(b)
+                self.home_ptrs.append(ptrs)
+                for k in (0, 1):
+                    b, ptrs = shared(shape(t), t.dtype)
+                    self.bufs[k].append(b)
+                    self.buf_ptrs[k].append(ptrs)
+            self.flags, self.flag_ptrs = shared((world + 1,), torch.int64)
+            dist.barrier()
+            torch.cuda.synchronize(dev)
+        else:
+            self.home = list(tables_home)
+            self.home_ptrs = [[t.data_ptr()] for t in self.home]
+            self.bufs = [[torch.zeros(shape(t), dtype=t.dtype, device=dev) for t in self.home] for _ in (0, 1)]
+            self.buf_ptrs = [[[b.data_ptr()] for b in self.bufs[k]] for k in (0, 1)]
+            self.flags, self.flag_ptrs = None, None
+
+    def buf(self, t: int, parity: Optional[int] = None):
+        return self.bufs[self.parity if parity is None else parity][t]
+
+    def swap(self, next_states: Sequence[Optional[Sequence[int]]], wait_budget_us: int = 0):
+        """Enqueues the swap on the current stream (all ranks call this with the same argument): the barrier kernel, then one
+        pull kernel per table.  Afterwards `parity` names the buffers that hold the new state."""
+        new_slots, pulls = plan_relay(self.place, next_states)
+        self.epoch += 1
+        old, new = self.parity, self.parity ^ 1
+        for t in range(len(self.home)):
+            sb = self.slab_bytes[t]
+            lst = []
+            for src_kind, sr, si, dst_kind, di in pulls[self.rank]:
+                src = (self.buf_ptrs[old][t][sr] if src_kind == "buf" else self.home_ptrs[t][sr]) + si * sb
+                dst = (self.bufs[new][t].data_ptr() if dst_kind == "buf" else self.home[t].data_ptr()) + di * sb
+                lst.append((src, dst))
+            # the barrier goes with the first table's pulls; the others follow it on the same stream
+            if t == 0:
+                self.capi.swap_begin(self.world, self.rank, self.flag_ptrs, self.epoch, lst, sb, self.status, wait_budget_us)
+            elif lst:
+                self.capi.swap_begin(1, 0, None, self.epoch, lst, sb, self.status)
+        self.parity = new
+        self.place = apply_plan(self.place, new_slots)
+        return pulls[self.rank]
+
+    def flush(self):
+        """Every resident partition goes to its home slab (end of training / before evaluation)."""
+        return self.swap([[] for _ in range(self.world)])
+
+    def slot_table(self):
+        tab = [-1] * self.num_partitions
+        for slot, p in enumerate(self.place.slots[self.rank]):
+            if p >= 0:
+                tab[p] = slot
+        return tab
+
+    def check_status(self):
+        import torch
+
+        torch.cuda.synchronize(self.status.device)
+        word = int(self.status.item())
+        if word:
+            raise self.capi.Ge2Error("partition swap: " + self.capi.decode_status(word))
+
+
+def state_buckets(supersteps, num_partitions: int):
+    """buckets[k][rank] = list of bucket ids (src partition * P + dst partition) trained by `rank` in superstep k: every
+    ordered bucket goes to the first state that holds both of its partitions (ordering.cpp:1350-1370 of the reference)."""
+    owner = assign_buckets(supersteps, num_partitions)
+    out = [[[] for _ in lanes] for lanes in supersteps]
+    for (a, b), (k, r) in sorted(owner.items()):
+        out[k][r].append(a * num_partitions + b)
+    return out
+
+
+class PartitionedTrainer:
+    """One epoch over a partitioned graph on this rank: for every superstep swap partitions (RelayBuffer), rebuild the state's
+    edge list on the device (ge2_build_state_edges), train its batches through the pipelined step graphs, and -- with several
+    ranks -- keep taking part in the relation-gradient exchange until the longest lane of the superstep is done.
+    The loop of the reference's multi-GPU trainer (engine/trainer.cpp:779-898) for one lane."""
+
+    def __init__(self, pipe, relay: RelayBuffer, edges_sorted, bucket_sizes, seed: int = 1):
+        import numpy as np
+        import torch
+
+        self.pipe, self.relay = pipe, relay
+        self.edges_sorted = edges_sorted
+        self.sizes = np.asarray(bucket_sizes, np.int64)
+        self.begin = np.concatenate([[0], np.cumsum(self.sizes)])[:-1]
+        P, world = relay.num_partitions, relay.world
+        self.supersteps = make_supersteps(P, world)
+        self.buckets = state_buckets(self.supersteps, P)
+        self.seed = seed
+        B = pipe.cfg.B
+        self.state_edges_count = [[int(self.sizes[b].sum()) if len(b) else 0 for b in lanes] for lanes in self.buckets]
+        cap = max(max(c) for c in self.state_edges_count)
+        cap = max(cap, 2 * B)
+        dev = edges_sorted.device
+        self.state_edges = torch.zeros((cap, edges_sorted.shape[1]), dtype=torch.int64, device=dev)
+        self.slot_dev = torch.full((P,), -1, dtype=torch.int64, device=dev)
+        self.runners = [None, None]
+        self.states_done = 0
+
+    def _runner(self, parity: int):
+        """The pipelined step graphs for the tables of buffer `parity` (captured on first use).  Returns (runner, warmed):
+        the very first capture of a pipeline runs one host-issued training step (it resolves driver entry points and function
+        attributes outside the capture); that step trains a batch of the current state and counts as one of its steps."""
+        warmed = False
+        if self.runners[parity] is None:
+            r = self.relay
+            warmed = self.runners[0] is None and self.runners[1] is None
+            self.runners[parity] = self.pipe.capture_pipelined(self.state_edges, 1, tables=(r.buf(0, parity), r.buf(1, parity)), warm=warmed)
+        return self.runners[parity], warmed
+
+    def run_epoch(self, epoch: int = 0, on_step=None, on_state=None):
+        """on_state(k, total): optional callable after the edge list of superstep k is built; on_step(k, i, ids): optional
+        callable after step i of superstep k, `ids` being the id set the step trained from (tests replay the step there)."""
+        import torch
+
+        from . import capi
+
+        pipe, relay = self.pipe, self.relay
+        B = pipe.cfg.B
+        for k, lanes in enumerate(self.supersteps):
+            relay.swap(lanes)
+            mine = self.buckets[k][relay.rank]
+            nb = 0
+            if lanes[relay.rank] is not None and mine:
+                self.slot_dev.copy_(torch.tensor(relay.slot_table(), dtype=torch.int64))
+                total = capi.build_state_edges(self.edges_sorted, [int(self.begin[b]) for b in mine], [int(self.sizes[b]) for b in mine],
+                                               self.slot_dev, relay.rows, self.state_seed(epoch, k), self.state_edges, pipe.status)
+                nb = total // B  # a tail shorter than a batch is left out of this epoch (another tail next epoch: the shuffle differs)
+                if on_state is not None:
+                    on_state(k, total)
+            nb_max = max(c // B for c in self.state_edges_count[k])
+            if nb > 0:
+                pipe.set_num_batches(nb)
+                runner, warmed = self._runner(relay.parity)
+                done = 0
+                if warmed:
+                    done = 1
+                    if on_step is not None:
+                        on_step(k, 0, pipe.ids[0])
+                runner.refill()
+                for i in range(done, nb):
+                    runner.replay()
+                    if on_step is not None:
+                        on_step(k, i, pipe.ids[pipe._ids_parity ^ 1])
+            if relay.world > 1 and pipe.peer is not None:
+                for _ in range(nb_max - nb):
+                    pipe.idle_step()
+            self.states_done += 1
+        relay.flush()
+
+    def state_seed(self, epoch: int, k: int) -> int:
+        return self.seed + 7919 * (epoch * len(self.supersteps) + k)

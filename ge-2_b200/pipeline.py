@@ -157,6 +157,25 @@ class BatchPipeline:
         self.grad_scale = 1.0  # 1 / #GPUs when relation gradients are all-reduced (model.cpp:188-192 of the reference project)
         self.peer: Optional[PeerGradients] = None
         self._t_host = 0       # host mirror of step_dev[0]; only the peer-gradient form needs it (which half a step writes)
+        # number of batches of the resident edge list, on the device: a partition-buffer state replaces the list by one of
+        # another length without the captured launches changing (set_num_batches); None = the host-side count is used
+        self.nb_dev = None
+        self._ids_parity = 0   # which id set holds the batch drawn ahead (shared by every pipelined runner of this pipeline)
+
+    def set_num_batches(self, num_batches: int):
+        """Stream-ordered update of the device-side batch count used by the resident / pipelined forms."""
+        if self.nb_dev is None:
+            self.nb_dev = torch.zeros(1, dtype=torch.int64, device=self.device)
+        self.nb_dev.fill_(max(1, int(num_batches)))
+
+    def _sample(self, ids: "_IdSet", edges_all, num_batches: int, counter):
+        cfg = self.cfg
+        args = (cfg.B, cfg.C, cfg.N, cfg.n_deg, cfg.domain, cfg.sides == 2, cfg.seed, ids.packed, ids.deg_rows if cfg.n_deg > 0 else None,
+                ids.rel_ids if cfg.has_relations else None)
+        if self.nb_dev is not None:
+            capi.sample_batch_dev(edges_all, self.nb_dev, counter, *args)
+        else:
+            capi.sample_batch(edges_all, num_batches, counter, *args)
 
     def use_peer_gradients(self, peer: PeerGradients):
         """Multi-GPU: relation gradients go into `peer`'s buffer (alternating halves) and the dense optimizer step sums them
@@ -282,12 +301,12 @@ class BatchPipeline:
         advances the device-side counter at the end.  No argument changes from step to step, so the launch list can be
         captured once into a CUDA graph (capture_resident) and replayed."""
         cfg = self.cfg
-        capi.sample_batch(edges_all, num_batches, self.step_dev, cfg.B, cfg.C, cfg.N, cfg.n_deg, cfg.domain, cfg.sides == 2, cfg.seed,
-                          self.packed, self.deg_rows if cfg.n_deg > 0 else None, self.rel_ids if cfg.has_relations else None)
+        self._sample(self.ids[0], edges_all, num_batches, self.step_dev)
         capi.unique_bitmap(self.packed, cfg.domain, workspace=self.uws, out_unique=self.unique, out_inverse=self.inverse, out_count=self.count)
         self._backward_and_update(self._make_desc(edges_all, self.rel_ids, 1), scores_events, rel_hook)
         capi.advance_step(self.step_dev, 2)
         self._t_host += 1
+        self._ids_parity = self._t_host & 1  # (a pipelined runner used after this needs refill(): nothing is drawn ahead)
 
     def capture_resident(self, edges_all, num_batches: int, rel_hook=None):
         """Captures one resident step into a CUDA graph (after one eager step, which also resolves driver entry points and
@@ -333,22 +352,41 @@ class BatchPipeline:
     def _front(self, ids: _IdSet, edges_all, num_batches: int, counter):
         """sampler + unique-map into one id set; `counter` is the device counter holding the batch number to use"""
         cfg = self.cfg
-        capi.sample_batch(edges_all, num_batches, counter, cfg.B, cfg.C, cfg.N, cfg.n_deg, cfg.domain, cfg.sides == 2, cfg.seed,
-                          ids.packed, ids.deg_rows if cfg.n_deg > 0 else None, ids.rel_ids if cfg.has_relations else None)
+        self._sample(ids, edges_all, num_batches, counter)
         capi.unique_bitmap(ids.packed, cfg.domain, workspace=ids.uws, out_unique=ids.unique, out_inverse=ids.inverse, out_count=ids.count)
 
-    def capture_pipelined(self, edges_all, num_batches: int, rel_hook=None, front_after_scores: bool = True):
-        """Software-pipelined steps: while the decoder step of batch t runs (its scores kernel leaves most SMs idle in its
+    def idle_step(self):
+        """A step of a lane that has no batch (lanes of a superstep have unequal batch counts): the relation-gradient
+        exchange alone -- this rank's half of the gradient buffer is zero, so it contributes zeros, as the reference's
+        zero-filled gradients do (model.cpp:182-187) -- and the counter bump, so that the replicas of the relation tables
+        stay in step with the ranks that train."""
+        self._update_relations()
+        capi.advance_step(self.step_dev, 2)
+        self._t_host += 1
+        self._ids_parity = self._t_host & 1
+
+    def capture_pipelined(self, edges_all, num_batches: int, rel_hook=None, front_after_scores: bool = True, tables=None, warm: bool = True):
+        """tables: (table, state) to capture the graphs for, when not the pipeline's own -- a partition buffer that alternates
+        between two active buffers keeps one runner per buffer; runners of one pipeline are interchangeable from step to
+        step (they share the id sets, the counters and the rule "the step whose counter is t uses id set t & 1").
+        warm = False skips the host-issued warm-up step (a later capture of a pipeline that has run already).
+
+        Software-pipelined steps: while the decoder step of batch t runs (its scores kernel leaves most SMs idle in its
         second round), the ids of batch t+1 are drawn and deduplicated on a side stream into the other id set; the optimizer
         updates of batch t follow the join, so batch t+1 gathers the updated rows.  Two graphs alternate (one per id set);
         with rel_hook (the multi-GPU all-reduce, host-issued) each step is two graph launches around the hook.
         Returns an object with replay().  The same batches, negatives and arithmetic as the plain resident form."""
-        self.enqueue_resident(edges_all, num_batches, rel_hook=rel_hook)  # warm-up: driver entry points, function attributes
+        own_tables = (self.table, self.state)
+        if tables is not None:
+            self.table, self.state = tables
+        if warm:
+            self.enqueue_resident(edges_all, num_batches, rel_hook=rel_hook)  # warm-up: driver entry points, function attributes
         torch.cuda.synchronize(self.device)
         self._graph_edges = edges_all
         cfg = self.cfg
         ctr_now, ctr_next = self.step_dev[0:1], self.step_dev[1:2]
-        self._front(self.ids[0], edges_all, num_batches, ctr_now)  # ids of the first pipelined batch
+        self._ids_parity = self._t_host & 1
+        self._front(self.ids[self._ids_parity], edges_all, num_batches, ctr_now)  # ids of the first pipelined batch
         torch.cuda.synchronize(self.device)
         # Side streams are made once, outside any capture, and nothing is destroyed while a capture is open (a stream,
         # graph or tensor of an earlier capture dying inside a later one invalidates it): no garbage collection meanwhile.
@@ -362,16 +400,16 @@ class BatchPipeline:
         gc.disable()
         try:
             graphs = []
-            t_first = self._t_host  # the step the first replay runs (graph p runs the steps t_first + p, t_first + p + 2, ...)
             if self.peer is not None:
-                assert rel_hook is None and t_first == int(self.step_dev[0].item())
+                assert rel_hook is None and self._t_host == int(self.step_dev[0].item())
             for p in (0, 1):
                 cur, nxt = self.ids[p], self.ids[1 - p]
                 ga = torch.cuda.CUDAGraph()
                 with torch.cuda.graph(ga):
                     main = torch.cuda.current_stream()
                     side, side2 = self._side_streams
-                    desc = self._make_desc(edges_all, cur.rel_ids, 1, ids=cur, parity=t_first + p)
+                    # graph p trains the steps whose counter has parity p: id set p, half p of the peer gradient buffer
+                    desc = self._make_desc(edges_all, cur.rel_ids, 1, ids=cur, parity=p)
                     if front_after_scores:
                         # The scores kernel owns whole SMs (one CTA with all of its shared memory); the small kernels of the next
                         # batch's sampler and unique-map would delay its CTAs, so they are forked after it and run beside the
@@ -412,29 +450,28 @@ class BatchPipeline:
         finally:
             if gc_was_on:
                 gc.enable()
+            self.table, self.state = own_tables
         pipe = self
 
         class _Pipelined:
-            parity = 0
-
             def replay(_self):
-                ga, gb = graphs[_self.parity]
+                ga, gb = graphs[pipe._ids_parity]
                 ga.replay()
                 if gb is not None:
                     rel_hook(pipe)
                     gb.replay()
-                _self.parity ^= 1
+                pipe._ids_parity ^= 1
                 pipe._t_host += 1
 
             @property
             def loss(_self):
                 """device scalar holding the loss of the batch trained by the last replay"""
-                return pipe.ids[_self.parity ^ 1].loss
+                return pipe.ids[pipe._ids_parity ^ 1].loss
 
             def refill(_self):
                 """Draws the ids of the coming batch again (host-issued): call after the resident edge list was replaced,
                 e.g. at a partition swap, since the batch sampled ahead came from the old list."""
-                pipe._front(pipe.ids[_self.parity], edges_all, num_batches, ctr_now)
+                pipe._front(pipe.ids[pipe._ids_parity], edges_all, num_batches, ctr_now)
 
         self._pipelined = graphs
         return _Pipelined()

@@ -248,6 +248,11 @@ GE2_API int ge2_sample_negatives(const int64_t *src_ids, const int64_t *dst_ids,
 GE2_API int ge2_sample_batch(const int64_t *edges, int32_t cols, int64_t num_batches, const uint64_t *step_dev, int32_t B, int32_t C,
                              int32_t N, int32_t n_deg, int64_t domain, int32_t want_src_negs, uint64_t seed, int64_t *out_packed_ids,
                              int64_t *out_deg_rows, int64_t *out_rel_ids, ge2_stream_t stream);
+/* The same with the number of batches read from device memory (*num_batches_dev >= 1): a partition-buffer state replaces the
+ * resident edge list by one of another length (ge2_build_state_edges) without the captured launch changing. */
+GE2_API int ge2_sample_batch_dev(const int64_t *edges, int32_t cols, const int64_t *num_batches_dev, const uint64_t *step_dev, int32_t B,
+                                 int32_t C, int32_t N, int32_t n_deg, int64_t domain, int32_t want_src_negs, uint64_t seed,
+                                 int64_t *out_packed_ids, int64_t *out_deg_rows, int64_t *out_rel_ids, ge2_stream_t stream);
 GE2_API int ge2_advance_step(uint64_t *step_dev, int32_t n, ge2_stream_t stream);
 
 /* GraphModelStorage::mapEdgesWithPartitionSlots_ (cpp/src/storage/graph_storage.cpp:270-303):
@@ -256,6 +261,56 @@ GE2_API int ge2_advance_step(uint64_t *step_dev, int32_t n, ge2_stream_t stream)
 GE2_API int ge2_remap_edges_to_slots(const int64_t *edges, int64_t n, int32_t cols, const int64_t *partition_to_slot,
                              int32_t num_partitions, int64_t partition_size, int64_t *out, int32_t *status,
                              ge2_stream_t stream);
+
+/* The edge list of one partition-buffer state, ready to train on, in ONE pass over the state's edges:
+ * GraphModelStorage::updateInMemorySubGraph_ (cpp/src/storage/graph_storage.cpp:938-1240: copy of the resident buckets' edges,
+ * arithmetic remap :270-303) + DataLoader::setActiveEdges (cpp/src/data/dataloader.cpp:524-633: concatenation, randperm,
+ * index_select) -- CPU loops, OpenMP and an upload of the whole state in the reference.
+ * edges_sorted[E, cols] int64 (device) is the training edge list sorted by bucket (src partition * P + dst partition), global
+ * node ids, as the preprocessor writes it (python/tools/preprocess/converters/partitioners/torch_partitioner.py:12-31);
+ * bucket_begin_host / bucket_len_host[num_buckets] (HOST arrays, <= 64 entries) name the buckets of the state in the order they
+ * are concatenated; partition_to_slot[num_partitions] (device) is the buffer slot of every resident partition (-1 otherwise).
+ * out_edges[total, cols] receives row perm(j) of the concatenation at position j, first and last column remapped to
+ * slot * partition_size + id % partition_size; perm is a fixed function of (seed, total): four Feistel rounds with cycle
+ * walking (a uniform shuffle is all the reference asks of its randperm; this one needs no sort and no scratch).
+ * *out_total_host = total (host, written before the launch).  An endpoint whose partition is not resident sets
+ * GE2_STATUS_BAD_INDEX and becomes -1. */
+GE2_API int ge2_build_state_edges(const int64_t *edges_sorted, int32_t cols, const int64_t *bucket_begin_host,
+                                  const int64_t *bucket_len_host, int32_t num_buckets, const int64_t *partition_to_slot,
+                                  int32_t num_partitions, int64_t partition_size, uint64_t seed, int64_t *out_edges,
+                                  int64_t *out_total_host, int32_t *status, ge2_stream_t stream);
+
+/* MemPartitionBufferStorage::performNextSwap(int32_t device_idx) (cpp/include/storage/storage.h:157-187,
+ * cpp/src/storage/storage.cpp:576-689), peer-relay branch :599-652, as receiver-side pulls behind a device-side barrier:
+ * no host synchronisation, no cudaDeviceSynchronize, no staging through the host.
+ * Every rank keeps TWO active buffers and alternates between them from superstep to superstep, so a swap only reads the
+ * buffers of the superstep that ended and only writes the buffers of the one that begins: one barrier per swap is enough
+ * (everybody has finished training before anybody pulls; by the time these source buffers are written again, in the swap
+ * after next, every rank has announced the end of another superstep, which it does after its own pulls).
+ *   flag_rows[r]  (host array of `world` device pointers) this process's mapping of rank r's flag row: world + 1 8-byte words,
+ *                 all zero at start; needed when world > 1
+ *   epoch         1, 2, 3, ... the number of this swap (the same on every rank)
+ *   pull_src/dst  (host arrays of num_pulls <= 32 device pointers) slabs of slab_bytes bytes (a multiple of 16): sources are
+ *                 peer mappings or local memory (a partition's slot in its holder's current buffer, or its home slab),
+ *                 destinations this rank's memory (a slot of its next buffer, or a home slab for a partition nobody keeps)
+ * ge2_swap_begin enqueues on `stream`: a one-warp kernel that announces `epoch` to every rank and waits for all of them, at
+ * most wait_budget_us microseconds (0 = 4 s), then one copy kernel for all slabs (plain 16-byte peer loads) that does nothing
+ * when the wait ran out (GE2_STATUS_PEER_TIMEOUT in *status; buffers untouched).  ge2_swap_wait makes compute_stream wait for
+ * what ge2_swap_begin enqueued on swap_stream (an event; nothing blocks the host), so the pulls can run beside the tail of the
+ * superstep's other work. */
+typedef struct ge2_swap_desc {
+    int32_t world, rank;
+    void *const *flag_rows;
+    uint64_t epoch;
+    uint32_t wait_budget_us;
+    int32_t num_pulls;
+    const void *const *pull_src;
+    void *const *pull_dst;
+    int64_t slab_bytes;
+    int32_t *status;
+} ge2_swap_desc;
+GE2_API int ge2_swap_begin(const ge2_swap_desc *desc, ge2_stream_t stream);
+GE2_API int ge2_swap_wait(ge2_stream_t swap_stream, ge2_stream_t compute_stream);
 
 /* Slab copies of MemPartitionBufferStorage::performNextSwap's relay branch that stay on one device
  * (cpp/src/storage/storage.cpp:626-652, src_dev == device_idx): moves[k] = {src_slot, dst_slot}; copies whole

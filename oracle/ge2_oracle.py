@@ -302,6 +302,67 @@ def map_edges_with_partition_slots(edges, partition_to_slot, partition_size: int
     return out
 
 
+_M64 = (1 << 64) - 1
+
+
+def _mix64(x: np.ndarray) -> np.ndarray:
+    """splitmix64 finaliser on uint64 arrays (wrap-around arithmetic)."""
+    with np.errstate(over="ignore"):
+        x = x + np.uint64(0x9E3779B97F4A7C15)
+        x = (x ^ (x >> np.uint64(30))) * np.uint64(0xBF58476D1CE4E5B9)
+        x = (x ^ (x >> np.uint64(27))) * np.uint64(0x94D049BB133111EB)
+        return x ^ (x >> np.uint64(31))
+
+
+def state_shuffle_permutation(n: int, seed: int) -> np.ndarray:
+    """The permutation DataLoader::setActiveEdges draws with randperm (cpp/src/data/dataloader.cpp:613-616), restated as the
+    fixed bijection the device path uses so that both sides can be compared bit for bit: four Feistel rounds over the
+    smallest even number of bits covering n, walked until the value falls below n.  perm[j] = source row of output row j."""
+    if n == 0:
+        return np.empty(0, np.int64)
+    bits = 2
+    while bits < 62 and (1 << bits) < n:
+        bits += 1
+    if bits & 1:
+        bits += 1
+    half = np.uint64(bits // 2)
+    mask = np.uint64((1 << (bits // 2)) - 1)
+    key = np.uint64((seed * 0x9E3779B97F4A7C15 + 0x632BE59BD9B4E019) & _M64)
+    x = np.arange(n, dtype=np.uint64)
+    todo = np.ones(n, bool)
+    with np.errstate(over="ignore"):
+        while todo.any():
+            v = x[todo]
+            l, r = v >> half, v & mask
+            for rnd in range(4):
+                f = _mix64(key + np.uint64((rnd * 0xD1342543DE82EF95) & _M64) + r) & mask
+                l, r = r, l ^ f
+            v = (l << half) | r
+            x[todo] = v
+            todo[todo] = v >= np.uint64(n)
+    return x.astype(np.int64)
+
+
+def build_state_edges(edges_sorted, bucket_begin, bucket_len, partition_to_slot, partition_size: int, seed: int):
+    """GraphModelStorage::updateInMemorySubGraph_ + DataLoader::setActiveEdges for one state
+    (cpp/src/storage/graph_storage.cpp:938-1240, cpp/src/data/dataloader.cpp:524-633): the state's buckets of the bucket-sorted
+    edge list concatenated in the given order, endpoints remapped to buffer slots (:270-303), rows shuffled."""
+    parts = [np.asarray(edges_sorted[b:b + l]) for b, l in zip(bucket_begin, bucket_len)]
+    cat = np.concatenate(parts, axis=0) if parts else np.empty((0, edges_sorted.shape[1]), np.int64)
+    perm = state_shuffle_permutation(cat.shape[0], seed)
+    return map_edges_with_partition_slots(cat[perm], partition_to_slot, partition_size)
+
+
+def bucket_sort_edges(edges, num_partitions: int, partition_size: int):
+    """The preprocessor's partitioned edge order (python/tools/preprocess/converters/partitioners/torch_partitioner.py:12-31):
+    edges sorted (stably) by bucket id = src partition * P + dst partition, plus the P*P bucket sizes."""
+    edges = np.asarray(edges, np.int64)
+    b = (edges[:, 0] // partition_size) * num_partitions + edges[:, -1] // partition_size
+    order = np.argsort(b, kind="stable")
+    sizes = np.bincount(b, minlength=num_partitions * num_partitions).astype(np.int64)
+    return edges[order], sizes
+
+
 def relay_swap_plan(current_states, next_states):
     """Owner lookup of MemPartitionBufferStorage::performNextSwap, peer-relay branch (cpp/src/storage/storage.cpp:599-652).
 

@@ -1,0 +1,147 @@
+"""Partition-buffer training on ONE GPU (world = 1, 8 partitions, 4 resident): swaps between home slabs and the two active
+buffers (ge2_swap_begin), the per-state edge list built on the device (ge2_build_state_edges), pipelined training steps on
+the resident partitions -- against the oracle running the same schedule step by step on global tables.
+What is checked: the state edge lists bit for bit, every step's loss, and after the final flush every partition's
+embeddings and Adagrad state in its home slab."""
+from importlib import import_module
+
+import numpy as np
+import pytest
+import torch
+
+import ge2_oracle as O
+import workloads
+
+pytestmark = pytest.mark.gpu
+
+
+def test_state_edge_list_bit_exact(capi, cuda_device):
+    """bucket gather + slot remap + shuffle in one launch against the oracle's restatement, 2- and 3-column edges."""
+    rng = np.random.default_rng(3)
+    P, psize = 8, 1000
+    for cols in (3, 2):
+        e = rng.integers(0, P * psize, (50_000, cols))
+        if cols == 3:
+            e[:, 1] = rng.integers(0, 17, 50_000)
+        es, sizes = O.bucket_sort_edges(e, P, psize)
+        begin = np.concatenate([[0], np.cumsum(sizes)])[:-1]
+        state = [1, 3, 4, 6]
+        slots = np.full(P, -1, np.int64)
+        slots[state] = [2, 0, 3, 1]
+        buckets = [a * P + b for a in state for b in state][3:]  # any subset, any order
+        d_es = torch.from_numpy(es).to(cuda_device)
+        out = torch.full((int(sizes.sum()), cols), -5, dtype=torch.int64, device=cuda_device)
+        status = torch.zeros(1, dtype=torch.int32, device=cuda_device)
+        total = capi.build_state_edges(d_es, [int(begin[b]) for b in buckets], [int(sizes[b]) for b in buckets],
+                                       torch.from_numpy(slots).to(cuda_device), psize, 99, out, status)
+        torch.cuda.synchronize()
+        exp = O.build_state_edges(es, [int(begin[b]) for b in buckets], [int(sizes[b]) for b in buckets], slots, psize, 99)
+        assert total == exp.shape[0] and int(status) == 0
+        assert np.array_equal(out[:total].cpu().numpy(), exp)
+        assert int(out[total:].max()) == -5 if total < out.shape[0] else True
+        # every endpoint is a buffer-local id of a resident partition; the rows are a permutation of the buckets' rows
+        assert exp[:, [0, -1]].min() >= 0 and exp[:, [0, -1]].max() < 4 * psize
+    # an endpoint outside the resident partitions is flagged, not dereferenced
+    slots[6] = -1
+    status.zero_()
+    capi.build_state_edges(d_es, [int(begin[6 * P + 6])], [int(sizes[6 * P + 6])], torch.from_numpy(slots).to(cuda_device), psize, 1, out, status)
+    torch.cuda.synchronize()
+    assert int(status) & 8
+
+
+@pytest.mark.parametrize("decoder,D,R", [("DISTMULT", 50, 12), ("COMPLEX", 100, 9)])
+def test_partitioned_epoch_matches_oracle(ge2, capi, cuda_device, decoder, D, R):
+    pipeline = import_module("ge-2_b200.pipeline")
+    partition = import_module("ge-2_b200.partition")
+    rng = np.random.default_rng(5)
+    P, psize, B, C, N = 8, 400, 300, 3, 120
+    nodes = P * psize
+    n_edges = 9000
+    edges = np.stack([workloads.zipf_ids(rng, n_edges, nodes, 0.8), workloads.zipf_ids(rng, n_edges, R, 1.2),
+                      workloads.zipf_ids(rng, n_edges, nodes, 0.8)], axis=1).astype(np.int64)
+    es, sizes = O.bucket_sort_edges(edges, P, psize)
+    begin = np.concatenate([[0], np.cumsum(sizes)])[:-1]
+    table = (0.3 * rng.standard_normal((nodes, D))).astype(np.float32)
+    state = (0.01 + 0.05 * rng.random((nodes, D))).astype(np.float32)
+    rel = (1 + 0.2 * rng.standard_normal((R, D))).astype(np.float32)
+    inv = (1 + 0.2 * rng.standard_normal((R, D))).astype(np.float32)
+    rel_state, inv_state = np.zeros_like(rel), np.zeros_like(inv)
+    t = lambda a: torch.from_numpy(a.copy()).to(cuda_device)
+    relay = partition.RelayBuffer([t(table), t(state)], psize, P, 0, 1)
+    rels = torch.stack([t(rel), t(inv)])
+    rel_states = torch.zeros_like(rels)
+    cfg = pipeline.PipelineConfig(decoder, B, C, N, 0.5, D, R, 4 * psize, lr=0.1, precision="fp32")
+    pipe = pipeline.BatchPipeline(cfg, relay.buf(0, 0), relay.buf(1, 0), rels[0], rel_states[0], rels[1], rel_states[1])
+    trainer = partition.PartitionedTrainer(pipe, relay, t(es), sizes, seed=11)
+    seen = dict(steps=0, states=0)
+
+    def on_state(k, total):
+        mine = trainer.buckets[k][0]
+        slots = np.array(relay.slot_table())
+        exp = O.build_state_edges(es, [int(begin[b]) for b in mine], [int(sizes[b]) for b in mine], slots, psize, trainer.state_seed(0, k))
+        torch.cuda.synchronize()
+        assert total == exp.shape[0]
+        assert np.array_equal(trainer.state_edges[:total].cpu().numpy(), exp)
+        seen["states"] += 1
+        seen["slots"] = np.array(relay.place.slots[0])
+        seen["edges"] = exp
+        seen["nb"] = total // B
+
+    def to_global(local):
+        return seen["slots"][local // psize] * psize + local % psize
+
+    def on_step(k, i, ids):
+        torch.cuda.synchronize()
+        packed = ids.packed.cpu().numpy()
+        CN = C * N
+        e_local = np.stack([packed[:B], ids.rel_ids.cpu().numpy(), packed[B:2 * B]], axis=1)
+        # the batch is one of the state's batches (consecutive rows of the shuffled list)
+        step = int(pipe.step_dev[0].item()) - 1
+        b0 = (step % seen["nb"]) * B
+        assert np.array_equal(e_local, seen["edges"][b0:b0 + B])
+        e_glob = e_local.copy()
+        e_glob[:, 0], e_glob[:, 2] = to_global(e_local[:, 0]), to_global(e_local[:, 2])
+        src_negs = to_global(packed[2 * B:2 * B + CN]).reshape(C, N)
+        dst_negs = to_global(packed[2 * B + CN:]).reshape(C, N)
+        filt = O.deg_negative_local_filter(ids.deg_rows.cpu().numpy(), B)
+        loss, U = O.train_step(decoder, table, state, rel, rel_state, inv, inv_state, e_glob, dst_negs, src_negs, filt, filt, 0.1, nodes)
+        assert int(ids.count[0]) == U and int(ids.count[1]) == 0
+        assert abs(float(ids.loss) - loss) <= 2e-4 * abs(loss)
+        seen["steps"] += 1
+
+    trainer.run_epoch(0, on_step=on_step, on_state=on_state)
+    pipe.check_status()
+    relay.check_status()
+    assert seen["states"] == len(trainer.supersteps) and seen["steps"] == sum(c[0] // B for c in trainer.state_edges_count)
+    # after the flush every partition is back in its home slab, trained exactly as the oracle trained the global tables
+    got_table, got_state = relay.home[0].cpu().numpy(), relay.home[1].cpu().numpy()
+    assert np.abs(got_table - table).max() <= 5e-4 * np.abs(table).max()
+    assert np.abs(got_state - state).max() <= 5e-4 * np.abs(state).max()
+    assert np.abs(rels[0].cpu().numpy() - rel).max() <= 5e-4 * np.abs(rel).max()
+    assert np.abs(rels[1].cpu().numpy() - inv).max() <= 5e-4 * np.abs(inv).max()
+
+
+def test_swap_plan_device_pulls_round_trip(capi, cuda_device):
+    """Two epochs of the schedule without training: after the flush every home slab holds what it held (bit for bit), and in
+    between every slot of the current buffer holds the partition the placement table names."""
+    partition = import_module("ge-2_b200.partition")
+    P, rows, D = 12, 257, 52
+    mk = lambda off: torch.cat([torch.full((rows, D), float(p) + off, device=cuda_device) + torch.arange(rows, device=cuda_device)[:, None] * 1e-3
+                               for p in range(P)])
+    home = [mk(0.0), mk(0.5)]
+    ref = [h.clone() for h in home]
+    relay = partition.RelayBuffer(home, rows, P, 0, 1)
+    steps = partition.make_supersteps(P, 1)
+    for st in steps + steps:
+        relay.swap(st)
+        torch.cuda.synchronize()
+        for slot, p in enumerate(relay.place.slots[0]):
+            assert p >= 0 and float(relay.buf(0)[slot * rows, 0]) == float(p)
+            assert abs(float(relay.buf(1)[slot * rows + 7, 3]) - (p + 0.5 + 7e-3)) < 1e-5
+    # change something while resident: it must arrive in the home slab
+    p0 = relay.place.slots[0][2]
+    relay.buf(0)[2 * rows + 5, 1] = -123.0
+    relay.flush()
+    relay.check_status()
+    ref[0][p0 * rows + 5, 1] = -123.0
+    assert torch.equal(relay.home[0], ref[0]) and torch.equal(relay.home[1], ref[1])

@@ -118,3 +118,69 @@ def test_swap_protocol_two_gloo_ranks(P, world):
         parts = [p for p in range(P) if p % world == r]
         assert np.array_equal(got[r][0], np.concatenate([exp_e[p] for p in parts]))
         assert np.array_equal(got[r][1], np.concatenate([exp_s[p] for p in parts]))
+
+
+def test_plan_swap_rejects_claiming_an_idle_ranks_partition():
+    place = partition.apply_plan(partition.Placement.initial(2, 8), [[0, 1, 2, 3], [4, 5, 6, 7]])
+    with pytest.raises(ValueError, match="idle rank"):
+        partition.plan_swap(place, [None, [2, 5, 6, 7]])  # rank 0 idles and keeps partition 2
+
+
+@pytest.mark.parametrize("P,world", [(8, 1), (8, 2), (16, 2), (32, 8)])
+def test_relay_plan_moves_every_partition_exactly_once(P, world):
+    """The device-side swap's plan: simulated with numpy slabs it must give every rank exactly its state, leave nothing
+    stranded, and agree with the reference's owner lookup (oracle.relay_swap_plan) when everything is resident."""
+    rows = 3
+    home = {p: np.full((rows, 2), float(p)) for p in range(P)}  # home slab contents = partition id
+    bufs = [np.full((partition.CAPACITY * rows, 2), -1.0) for _ in range(world)]
+    place = partition.Placement.initial(world, P)
+    steps = partition.make_supersteps(P, world)
+    for lanes in steps + steps:
+        new_slots, pulls = partition.plan_relay(place, lanes)
+        if world * partition.CAPACITY == P and place.in_buffer:
+            ref = O.relay_swap_plan([list(s) for s in place.slots], [list(s) for s in new_slots])
+            ref_src = {p: (sd, ss) for moves in ref for (_slot, p, sd, ss) in moves}
+        else:
+            ref_src = None
+        new_bufs = [b.copy() for b in bufs]
+        for r in range(world):
+            for src_kind, sr, si, dst_kind, di in pulls[r]:
+                slab = bufs[sr][si * rows:(si + 1) * rows] if src_kind == "buf" else home[[p for p in range(P) if p % world == sr and p // world == si][0]]
+                if dst_kind == "buf":
+                    new_bufs[r][di * rows:(di + 1) * rows] = slab
+                    if ref_src is not None and src_kind == "buf":
+                        assert ref_src[int(slab[0, 0])] == (sr, si)
+                else:
+                    home[[p for p in range(P) if p % world == r and p // world == di][0]] = slab.copy()
+        bufs = new_bufs
+        place = partition.apply_plan(place, new_slots)
+        for r, st in enumerate(lanes):
+            want = sorted(st) if st is not None else sorted(p for p in place.slots[r] if p >= 0)
+            got = [int(bufs[r][k * rows, 0]) for k in range(len(want))]
+            assert got == want
+    _, pulls = partition.plan_relay(place, [[] for _ in range(world)])  # flush: every resident partition is fetched by its home rank
+    assert sorted(p for r in range(world) for p in [(di * world + r) for (_k, _sr, _si, dk, di) in pulls[r] if dk == "home"]) == sorted(place.in_buffer)
+
+
+def test_state_shuffle_is_a_permutation_and_edge_list_restatement():
+    for n in (0, 1, 2, 3, 17, 256, 1000, 65537):
+        perm = O.state_shuffle_permutation(n, 5)
+        assert sorted(perm.tolist()) == list(range(n))
+    assert not np.array_equal(O.state_shuffle_permutation(1000, 5), O.state_shuffle_permutation(1000, 6))
+    rng = np.random.default_rng(0)
+    P, psize = 4, 50
+    e = np.stack([rng.integers(0, P * psize, 2000), rng.integers(0, 5, 2000), rng.integers(0, P * psize, 2000)], 1)
+    es, sizes = O.bucket_sort_edges(e, P, psize)
+    assert sizes.sum() == 2000 and np.all(np.diff((es[:, 0] // psize) * P + es[:, 2] // psize) >= 0)
+    begin = np.concatenate([[0], np.cumsum(sizes)])[:-1]
+    slots = np.array([1, -1, 0, -1])
+    bk = [0 * P + 2, 2 * P + 0, 2 * P + 2]
+    out = O.build_state_edges(es, [int(begin[b]) for b in bk], [int(sizes[b]) for b in bk], slots, psize, 3)
+    assert out.shape[0] == sizes[bk].sum() and out[:, [0, 2]].max() < 2 * psize
+    # undo the remap: the multiset of rows equals the buckets' rows
+    back = out.copy()
+    inv = {1: 0, 0: 2}
+    for col in (0, 2):
+        back[:, col] = np.array([inv[s] for s in out[:, col] // psize]) * psize + out[:, col] % psize
+    exp = np.concatenate([es[begin[b]:begin[b] + sizes[b]] for b in bk])
+    assert sorted(map(tuple, back.tolist())) == sorted(map(tuple, exp.tolist()))
