@@ -424,9 +424,11 @@ def mrr(ranks: np.ndarray) -> float:
 # one full reference training step on global tables (the shape bench.py's CPU "port" leg times)
 # --------------------------------------------------------------------------------------------------
 def train_step(kind, table, state, rel, rel_state, inv_rel, inv_rel_state, edges_global, dst_neg_global, src_neg_global,
-               dst_filter, src_filter, lr, domain, dense_lr=None):
+               dst_filter, src_filter, lr, domain, dense_lr=None, rel_grads_out=None):
     """SynchronousTrainer's loop body (cpp/src/engine/trainer.cpp:170-211) on CPU: map_tensors -> indexRead ->
-    train_batch -> accumulateGradients -> indexAdd.  Updates table/state/rel tables in place; returns (loss, U)."""
+    train_batch -> accumulateGradients -> indexAdd.  Updates table/state/rel tables in place; returns (loss, U).
+    rel_grads_out: a list; when given, the relation gradients are appended to it as (rel_grad, inv_rel_grad) and the dense
+    optimizer step is left to the caller (the multi-GPU trainer averages them over the devices first, multi_gpu_dense_step)."""
     has_rel = edges_global.shape[1] == 3
     lists = [edges_global[:, 0], edges_global[:, -1]]
     if src_neg_global is not None:
@@ -446,7 +448,9 @@ def train_step(kind, table, state, rel, rel_state, inv_rel, inv_rel_state, edges
     emb = table[uniq]
     st = state[uniq]
     res = lp_train_forward_backward(kind, e_local, emb, rel, inv_rel, dst_neg_l, src_neg_l, dst_filter, src_filter)
-    if has_rel:
+    if has_rel and rel_grads_out is not None:
+        rel_grads_out.append((res.rel_grad, res.inv_rel_grad))
+    elif has_rel:
         dl = lr if dense_lr is None else dense_lr
         dense_adagrad(rel, res.rel_grad, rel_state, dl)
         if inv_rel is not None:
@@ -455,3 +459,15 @@ def train_step(kind, table, state, rel, rel_state, inv_rel, inv_rel_state, edges
     index_add(table, uniq, delta)
     index_add(state, uniq, upd)
     return res.loss, uniq.shape[0]
+
+
+def multi_gpu_dense_step(rel, rel_state, inv_rel, inv_rel_state, grads_per_device, lr):
+    """Model::all_reduce + step_all (cpp/src/nn/model.cpp:174-204; barrier cpp/src/engine/trainer.cpp:846-883) for one batch
+    round: grads_per_device[j] = (rel_grad, inv_rel_grad) of device j, or None for a device without a batch (its gradients are
+    zero-filled, :182-187).  Every gradient is divided by the number of devices, summed, and every replica takes the same
+    Adagrad step: one table stands for all replicas."""
+    g = allreduce_relation_grads([None if x is None else x[0] for x in grads_per_device])
+    dense_adagrad(rel, g, rel_state, lr)
+    if inv_rel is not None:
+        gi = allreduce_relation_grads([None if x is None else x[1] for x in grads_per_device])
+        dense_adagrad(inv_rel, gi, inv_rel_state, lr)
