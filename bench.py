@@ -33,6 +33,20 @@ import torch  # noqa: E402
 CFG = dict(name="kg-1M-entities/1k-relations/20M-triples ComplEx d=100 B=10000 neg=10x1000 (50% degree)", nodes=1_000_000, relations=1000,
            triples=20_000_000, decoder="COMPLEX", D=100, B=10_000, C=10, N=1000, degree_fraction=0.5, lr=0.1, alpha_nodes=1.1, alpha_rel=1.2)
 
+# The partitioned configurations (--config 3|4|5, run with --gpus 2|4|8).  Node ids are drawn from a Zipf law over a random
+# relabelling; the rank-frequency exponent alpha stands for the stated degree law (degree exponent g <-> alpha = 1 / (g - 1):
+# preferential attachment g = 3 -> 0.5, g = 2.2 -> 0.83).  Seeded synthetic stand-ins with the stated sizes.
+PARTITIONED = {
+    3: dict(name="social-4.85M-nodes/69M-edges Dot d=100 B=50000 neg=50x1000, 16 partitions", nodes=4_847_571, relations=1, triples=68_993_773,
+            decoder="DISTMULT", D=100, B=50_000, C=50, N=1000, degree_fraction=0.0, lr=0.1, alpha_nodes=0.5, alpha_rel=1.2, P=16, gpus=2),
+    4: dict(name="follower-41.65M-nodes/1.468B-edges Dot d=100 B=50000 neg=50x1000, 16 partitions", nodes=41_652_230, relations=1,
+            triples=1_468_365_182, decoder="DISTMULT", D=100, B=50_000, C=50, N=1000, degree_fraction=0.0, lr=0.1, alpha_nodes=0.83, alpha_rel=1.2,
+            P=16, gpus=4),
+    5: dict(name="kg-100M-entities/10k-relations/3B-triples DistMult d=128 B=100000 neg=100x2000, 32 partitions", nodes=100_000_000, relations=10_000,
+            triples=3_000_000_000, decoder="DISTMULT", D=128, B=100_000, C=100, N=2000, degree_fraction=0.0, lr=0.1, alpha_nodes=1.1, alpha_rel=1.2,
+            P=32, gpus=8),
+}
+
 
 # dram__bytes_read.sum + dram__bytes_write.sum of the scores launches of one step on this workload, taken from one ncu
 # capture of those launches (operands and partial gradients stay in the 126 MB L2, so it is far below the operand bytes)
@@ -310,6 +324,314 @@ def reference_gpu_ms(cfg, table, state, edges, steps, device):
     return a.elapsed_time(b) / steps
 
 
+def make_partitioned_edges(cfg, P, psize, keep_buckets, seed, device, chunk=40_000_000):
+    """The graph's training edges, generated chunk by chunk with the same seed on every rank; a rank keeps the edges of
+    the buckets it will train (keep_buckets) sorted by bucket -- the preprocessor's order
+    (torch_partitioner.py:12-31 of the reference project) -- and the sizes of ALL P*P buckets.
+    Returns (edges_sorted [n_kept, cols] int64, sizes [P*P] int64 numpy, begin [P*P] int64 numpy, -1 for buckets not kept)."""
+    gen = torch.Generator(device=device)
+    gen.manual_seed(seed)
+    nodes, R = cfg["nodes"], cfg["relations"]
+    has_rel = R > 1
+
+    def sampler(domain, alpha):
+        w = torch.arange(1, domain + 1, dtype=torch.float64, device=device).pow_(-alpha)
+        cdf = torch.cumsum(w, 0)
+        cdf /= cdf[-1].clone()
+        cdf = cdf.to(torch.float32) if domain > 50_000_000 else cdf  # 100 M entries: keep the table at 0.4 GB
+        perm = torch.randperm(domain, device=device, generator=gen)
+        return lambda n: perm[torch.searchsorted(cdf, torch.rand(n, dtype=cdf.dtype, device=device, generator=gen)).clamp_(max=domain - 1)]
+
+    draw_node = sampler(nodes, cfg["alpha_nodes"])
+    draw_rel = sampler(R, cfg["alpha_rel"]) if has_rel else None
+    keep = torch.zeros(P * P, dtype=torch.bool, device=device)
+    keep[torch.tensor(sorted(keep_buckets), dtype=torch.int64, device=device)] = True
+    sizes = torch.zeros(P * P, dtype=torch.int64, device=device)
+    kept, kept_b = [], []
+    left = cfg["triples"]
+    while left > 0:
+        n = min(chunk, left)
+        left -= n
+        src, dst = draw_node(n), draw_node(n)
+        b = (src // psize) * P + dst // psize
+        sizes += torch.bincount(b, minlength=P * P)
+        m = keep[b]
+        cols = [src[m]] + ([draw_rel(n)[m]] if has_rel else []) + [dst[m]]
+        kept.append(torch.stack(cols, dim=1))
+        kept_b.append(b[m])
+        del src, dst, b, m
+    e = torch.cat(kept)
+    bk = torch.cat(kept_b)
+    del kept, kept_b
+    order = torch.sort(bk, stable=True).indices
+    e = e[order].contiguous()
+    sizes_np = sizes.cpu().numpy()
+    begin = np.full(P * P, -1, np.int64)
+    off = 0
+    for bkt in sorted(keep_buckets):
+        begin[bkt] = off
+        off += int(sizes_np[bkt])
+    assert off == e.shape[0]
+    return e, sizes_np, begin
+
+
+def per_kernel_rooflines(pipe, pcfg, capi, edges, num_batches, reps=20):
+    """The HBM-bound kernels of the step, each replayed `reps` times as a graph of its own on the buffers a full step left
+    behind and bracketed by CUDA events: achieved = algorithmic bytes / time, against the measured copy bandwidth.  The
+    working set of one step (ids, fp16 operands, gradient rows) stays in the 126 MB L2 between replays; the embedding rows a
+    batch touches are a random 1-2 % of a 0.8 GB table."""
+    pk = peaks()
+    B, C, N, D, S = pcfg.B, pcfg.C, pcfg.N, pcfg.D, pcfg.sides
+    CN, n_ids = C * N, pcfg.n_ids
+    U = int(pipe.count[0].item())
+
+    def tg(fn):
+        fn()
+        torch.cuda.synchronize()
+        g = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(g):
+            for _ in range(reps):
+                fn()
+        g.replay()
+        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        a.record()
+        g.replay()
+        b.record()
+        torch.cuda.synchronize()
+        return a.elapsed_time(b) / reps
+
+    ids = pipe.ids[0]  # the id set of the batch trained last
+    out = {}
+
+    def add(name, ms, nbytes, what):
+        gbs = nbytes / (ms * 1e-3) / 1e9
+        out[name] = dict(ms=ms, bytes=nbytes, achieved=gbs, unit="GB/s", peak=pk["hbm"], frac=gbs / pk["hbm"], bound="hbm", bytes_are=what)
+
+    add("unique_map", tg(lambda: capi.unique_bitmap(ids.packed, pcfg.domain, workspace=ids.uws, out_unique=ids.unique, out_inverse=ids.inverse,
+                                                      out_count=ids.count)),
+        16 * n_ids + 8 * U, "16 B per id (read id, write rank) + 8 B per distinct id; the domain-sized bitset passes (0.19 B per node) not counted")
+    add("gather_prepare", pipe.time_scores_phase(edges, reps, 1),
+        ((2 + S) * B + S * CN) * D * 4 + (S * pcfg.B + S * CN) * 128 * 2, "embedding / relation rows read (fp32) + fp16 operand rows written")
+    add("scatter_finish", pipe.time_scores_phase(edges, reps, 4),
+        (B * (6 + 4) + S * CN * 2) * D * 4, "per edge 6 rows in + 4 gradient rows out, per negative 1 row in + 1 out (fp32)")
+    t2, s2 = pipe.table.clone(), pipe.state.clone()  # scratch copies: the timing must not train the real tables
+    pipe.node_grad.normal_()
+    add("adagrad_scatter", tg(lambda: capi.adagrad_scatter(t2, s2, ids.unique, pipe.node_grad, 0.1, U=pipe.cap, U_dev=ids.count,
+                                                            clear_grad=False, status=pipe.status)),
+        20 * U * D, "per touched row: embedding + state read and written (16 B per float) + gradient read (4 B)")
+    pipe.node_grad.zero_()
+    del t2, s2
+    return out
+
+
+def scores_roofline(precision, sides, B, N, D, scores_ms, scores_host_ms):
+    """roofline object of the dominant kernel (the scores launches): algorithmic flops 6 * S * B * N * D per step (forward
+    contraction + the two backward contractions, per side) over the launches' device time, against the measured bf16 peak"""
+    pk = peaks()
+    flops = 6.0 * sides * B * N * D
+    achieved = flops / (scores_ms * 1e-3) / 1e12
+    return dict(bound="tensor", kernel="lp_scores_%s" % precision, achieved=achieved, peak=pk["tf"], unit="TFLOP/s", frac=achieved / pk["tf"],
+                traffic=NCU_TRAFFIC.get(precision) if (B, N, D, sides) == (CFG["B"], CFG["N"], CFG["D"], 2) else None,
+                peak_source=pk["src"] + " bf16 dense", ms_per_launch=scores_ms, flops_per_launch=flops, ms_host_issued=scores_host_ms,
+                timing="CUDA events around 20 scores phases (the logsumexp launch + the gradient launch) replayed as one CUDA graph, as in the "
+                       "timed region; ms_host_issued = the same phase bracketed by events in a host-issued pass (includes launch gaps)")
+
+
+def multi_gpu_main(args, rank, world, local_rank, device, dist):
+    """N > 1: the partitioned workload.  The graph's nodes are cut into P partitions, four of which are resident per GPU; a
+    superstep trains, on every GPU, the edge buckets of its four resident partitions (pairwise disjoint between GPUs: no
+    exchange for node embeddings), then the partitions change hands (device-side pulls over NVLink peer memory) and every GPU
+    builds its next edge list on the device.  Relation gradients are summed over peer memory inside every step.
+    Default: configuration 2 weak-scaled (per-GPU domain, batch and triples as at N = 1, P = 4 N partitions)."""
+    pkg = importlib.import_module("ge-2_b200")
+    pkg.load_library()
+    pipeline = importlib.import_module("ge-2_b200.pipeline")
+    partition = importlib.import_module("ge-2_b200.partition")
+    capi = pkg.capi
+    K, W = args.steps, args.warmup
+    if args.config in PARTITIONED:
+        cfg = dict(PARTITIONED[args.config])
+        if cfg["gpus"] != world:
+            raise SystemExit(f"configuration {args.config} is stated for {cfg['gpus']} GPUs (got --gpus {world})")
+        P = cfg["P"]
+        scaling = "strong"  # a fixed graph; listed for completeness, the driver's scaling run uses the default workload
+    else:
+        cfg = dict(CFG)
+        P = 4 * world
+        cfg["nodes"], cfg["triples"] = CFG["nodes"] * world, CFG["triples"] * world
+        cfg["name"] = CFG["name"] + f", weak-scaled: {world} x nodes and triples, {P} partitions"
+        scaling = "weak"
+    B, C, N, D, R = cfg["B"], cfg["C"], cfg["N"], cfg["D"], cfg["relations"]
+    has_rel = R > 1
+    psize = -(-cfg["nodes"] // P)  # ceil, as the reference sizes its partitions (storage.cpp:368)
+    domain = partition.CAPACITY * psize
+    supersteps = partition.make_supersteps(P, world)
+    buckets = partition.state_buckets(supersteps, P)
+    mine = sorted(b for lanes in buckets for b in lanes[rank])
+
+    def barrier():
+        dist.barrier()
+        torch.cuda.synchronize()
+
+    t_setup = time.perf_counter()
+    edges_sorted, sizes, begin = make_partitioned_edges(cfg, P, psize, mine, 20262, device)
+    gen = torch.Generator(device=device).manual_seed(7 + rank)
+    n_home = len([p for p in range(P) if p % world == rank])
+    home_emb = (torch.rand((n_home * psize, D), device=device, generator=gen) - 0.5) * 0.2
+    home_state = torch.zeros((n_home * psize, D), device=device)
+    relay = partition.RelayBuffer([home_emb, home_state], psize, P, rank, world, dist)
+    del home_emb, home_state
+    rels = torch.zeros((2, max(R, 1), D), device=device)
+    rels[:, :, : D // 2] = 1
+    if cfg["decoder"] == "DISTMULT":
+        rels[:] = 1  # distmult.cpp:18 of the reference project
+    rel_states = torch.zeros_like(rels)
+    pcfg = pipeline.PipelineConfig(cfg["decoder"], B, C, N, cfg["degree_fraction"], D, R, domain, lr=cfg["lr"], precision=args.precision)
+    pipe = pipeline.BatchPipeline(pcfg, relay.buf(0, 0), relay.buf(1, 0), rels[0] if has_rel else None, rel_states[0] if has_rel else None,
+                                  rels[1] if has_rel else None, rel_states[1] if has_rel else None)
+    if has_rel:
+        pipe.use_peer_gradients(pipeline.PeerGradients(dist, 2 * R * D, device))
+    trainer = partition.PartitionedTrainer(pipe, relay, edges_sorted, sizes, seed=31, bucket_begin=begin)
+    setup_s = time.perf_counter() - t_setup
+
+    # ---- the schedule's arithmetic: batches per lane and superstep, from the bucket sizes -----------------------------------
+    nb = [[c // B for c in lanes] for lanes in trainer.state_edges_count]
+    nb_max = [max(x) for x in nb]
+    epoch_edges = sum(sum(x) for x in nb) * B
+    epoch_steps = sum(nb_max)  # every lane takes part in that many relation-gradient exchanges
+
+    # ---- superstep 0: swap in, build the edge list, capture the step graphs (outside every timed region) ---------------------
+    state_no = [0]
+    sw_ms = []
+
+    def next_state(timed: bool):
+        """partition swap + rebuild of this rank's edge list + redraw of the batch sampled ahead, as one device-timed region"""
+        k = state_no[0] % len(supersteps)
+        state_no[0] += 1
+        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        if timed:
+            barrier()
+        a.record()
+        relay.swap(supersteps[k])
+        lane = buckets[k][rank]
+        total = 0
+        if supersteps[k][rank] is not None and lane:
+            trainer.slot_dev.copy_(torch.tensor(relay.slot_table(), dtype=torch.int64))
+            total = capi.build_state_edges(edges_sorted, [int(begin[x]) for x in lane], [int(sizes[x]) for x in lane], trainer.slot_dev, psize,
+                                           trainer.state_seed(0, k), trainer.state_edges, pipe.status)
+        pipe.set_num_batches(max(1, total // B))
+        runner, _ = trainer._runner(relay.parity)
+        runner.refill()
+        b.record()
+        if timed:
+            barrier()
+            sw_ms.append(a.elapsed_time(b))
+        return runner, total
+
+    runner, total0 = next_state(False)
+    while total0 // B < 1:  # a lane without a batch in this superstep: move on until this rank has one (all ranks move together)
+        runner, total0 = next_state(False)
+    barrier()
+    for _ in range(W):
+        runner.replay()
+    pipe.check_status()
+    relay.check_status()
+
+    # ---- timed steps: REPEATS regions of K steps inside one state ----------------------------------------------------------------
+    clocks = ClockSampler(local_rank)
+    clocks.start()
+    time.sleep(0.02)
+    rep_ms = []
+    for r in range(REPEATS):
+        start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        barrier()
+        start.record()
+        for i in range(K):
+            runner.replay()
+        end.record()
+        barrier()
+        rep_ms.append(start.elapsed_time(end))
+    pipe.check_status()
+
+    # ---- timed swaps: the next three supersteps' swap + rebuild, each as its own region ---------------------------------------------
+    for _ in range(3):
+        runner, total = next_state(True)
+        for _ in range(2):
+            runner.replay()  # the new state trains: graphs of the other buffer, new edge list
+    pipe.check_status()
+    relay.check_status()
+
+    # ---- end to end: the state's batches from pinned host memory through HostFeed, loss read back every step ----------------------
+    cols = edges_sorted.shape[1]
+    nb_here = max(1, total // B)
+    kk = min(K, nb_here)
+    host_edges = torch.empty((kk, B, cols), dtype=torch.int64).pin_memory()
+    host_edges.copy_(trainer.state_edges[: kk * B].reshape(kk, B, cols).cpu())
+    host_loss = torch.zeros(K, dtype=torch.float32).pin_memory()
+    pipe.set_num_batches(2)  # HostFeed trains from a two-slot staging list
+    feed = pipeline.HostFeed(pipe, cols)
+    feed.start(host_edges[kk - 1], host_edges[0], tables=(relay.buf(0), relay.buf(1)))
+    barrier()
+    for i in range(min(W, K)):
+        feed.step(host_edges[(i + 1) % kk], host_loss[i:i + 1])
+    rep_e2e = []
+    for r in range(REPEATS):
+        s2, e2 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        barrier()
+        s2.record()
+        for i in range(K):
+            feed.step(host_edges[(i + 1) % kk], host_loss[i:i + 1])
+        feed.drain()
+        e2.record()
+        barrier()
+        rep_e2e.append(s2.elapsed_time(e2))
+    clock_info = clocks.stop()
+    pipe.check_status()
+    assert bool(torch.isfinite(host_loss).all()) and float(host_loss[-1]) > 0
+
+    scores_ms = pipe.time_scores_phase(trainer.state_edges)  # the scores launches of one step, replayed as a graph of their own
+    t = torch.tensor(rep_ms + rep_e2e + sw_ms + [scores_ms], device=device, dtype=torch.float64)
+    dist.all_reduce(t, op=dist.ReduceOp.MAX)  # every region: the slowest rank's device time
+    t = t.cpu().tolist()
+    rep_ms, rep_e2e, sw_ms, scores_ms = t[:REPEATS], t[REPEATS:2 * REPEATS], t[2 * REPEATS:-1], t[-1]
+    ms_step = sum(rep_ms) / REPEATS / K
+    ms_step_e2e = sum(rep_e2e) / REPEATS / K
+    swap_ms = float(np.median(sw_ms))
+    n_sw = len(supersteps)
+    # one epoch of the schedule: every superstep runs max-over-lanes steps (short lanes idle in the gradient exchange) and ends
+    # with a swap + rebuild; value = the epoch's train edges over that time, from the step and swap times measured above
+    epoch_ms = epoch_steps * ms_step + n_sw * swap_ms
+    epoch_ms_e2e = epoch_steps * ms_step_e2e + n_sw * swap_ms
+    if rank == 0:
+        line = dict(
+            metric="train edges/sec/box", value=epoch_edges / (epoch_ms * 1e-3), unit="edges/s", n_gpus=world, steps=K, warmup=W,
+            ms_per_step=ms_step, higher_is_better=True, scaling=scaling, vs_baseline=None, repeats=REPEATS,
+            ms_per_step_repeats=dict(min=min(rep_ms) / K, median=float(np.median(rep_ms)) / K, max=max(rep_ms) / K),
+            dtype="f32" if args.precision == "fp32" else "f16 tensor tiles, f32 accumulate and storage", data="synthetic",
+            config=dict(workload=cfg["name"], per_gpu_batch=B, global_batch=B * world, precision=args.precision, parallelism=f"dp{world}",
+                        l2="tables and edge lists larger than L2; rows touched per step are random",
+                        launch="one CUDA graph replay per step (relation gradients summed over NVLink peer memory inside it)",
+                        value_is="one epoch of the partition schedule: its train edges / (its steps x the measured step time + its swaps x "
+                                 "the measured swap + edge-list rebuild time); steps and swaps are timed in this run on the device, max over ranks",
+                        partitions=dict(count=P, rows=psize, resident_per_gpu=partition.CAPACITY, supersteps=n_sw, epoch_steps_per_lane=epoch_steps,
+                                        epoch_train_edges=epoch_edges, steps_per_superstep_mean=epoch_steps / n_sw,
+                                        lane_balance=epoch_edges / (epoch_steps * B * world), swap_ms=swap_ms, swap_ms_all=sw_ms,
+                                        swap_share_of_epoch=n_sw * swap_ms / epoch_ms, slab_mb=psize * D * 4 / 1e6,
+                                        exchange_us_per_step=None, step_only_value=world * B / (ms_step * 1e-3),
+                                        swap="receiver-side pulls over NVLink peer memory behind a device-side barrier, two alternating active "
+                                             "buffers, edge list of the new state built on the device (bucket gather + slot remap + shuffle)"),
+                        setup_seconds=setup_s),
+            e2e=dict(value=epoch_edges / (epoch_ms_e2e * 1e-3), unit="edges/s", h2d_bytes_per_step=B * cols * 8, d2h_bytes_per_step=4,
+                     ms_per_step=ms_step_e2e, note="the same epoch arithmetic with the step time measured through HostFeed: the batch arrives in "
+                                                    "pinned host memory (already in buffer-local ids), H2D copy, step, loss read back, every step"),
+            gpu_launches=K * pipe.launches_per_step(), clocks=clock_info,
+            roofline=scores_roofline(args.precision, pcfg.sides, B, N, D, scores_ms, None),
+        )
+        print(json.dumps(line), flush=True)
+    dist.barrier()
+    dist.destroy_process_group()
+
+
 # ----------------------------------------------------------------------------------------------------------------
 def main():
     ap = argparse.ArgumentParser()
@@ -317,20 +639,18 @@ def main():
     ap.add_argument("--steps", type=int, default=100)
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--config", type=int, default=2, choices=[2, 3, 4, 5],
+                    help="2: the single-GPU configuration (weak-scaled over partitions at N > 1); 3, 4, 5: the stated partitioned configurations "
+                         "(need --gpus 2, 4, 8)")
     ap.add_argument("--precision", default=os.environ.get("GE2_PRECISION", "f16"), choices=["fp32", "f16"],
                     help="f16: tcgen05 fp16-operand tiles with fp32 accumulation (1e-2 parity, the designed path); fp32: CUDA-core path (1e-4 parity)")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-fp32-path", action="store_true", help="skip the side measurement of the fp32 CUDA-core path")
     ap.add_argument("--no-reference-gpu", action="store_true", help="skip timing the reference's own GPU code (oracle/_ref/gege_ref_cuda.so) on this GPU")
-    ap.add_argument("--steps-per-state", type=int, default=0,
-                    help="N > 1: training steps between partition swaps; 0 = what the workload's schedule gives: its triples spread over "
-                         "(4N)^2 edge buckets, 16 buckets per state, one batch per step")
     ap.add_argument("--no-epoch", action="store_true", help="N = 1: skip the one-epoch (triples / B steps) timed region")
-    ap.add_argument("--no-graph", action="store_true", help="issue every launch from the host instead of replaying a CUDA graph")
-    ap.add_argument("--nccl-swaps", action="store_true", help="N > 1: move partitions between ranks with NCCL send/recv instead of peer-memory copies")
-    ap.add_argument("--nccl-allreduce", action="store_true",
-                    help="N > 1: all-reduce the relation gradients with NCCL between two graphs instead of summing them over peer memory in the dense optimizer kernel")
-    ap.add_argument("--no-pipeline", action="store_true", help="do not draw batch t+1 on a side stream while batch t trains")
+    ap.add_argument("--no-kernel-rooflines", action="store_true", help="N = 1: skip the per-kernel timings behind roofline_kernels")
+    ap.add_argument("--no-graph", action="store_true", help="N = 1: issue every launch from the host instead of replaying a CUDA graph")
+    ap.add_argument("--no-pipeline", action="store_true", help="N = 1: do not draw batch t+1 on a side stream while batch t trains")
     ap.add_argument("--cpu-budget", type=float, default=15.0)
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3)
@@ -346,141 +666,84 @@ def main():
         raise SystemExit("bench.py needs a CUDA device: the hot path has no CPU fallback")
     torch.cuda.set_device(local_rank)
     device = torch.device("cuda", local_rank)
-    dist = None
     if world > 1:
-        import torch.distributed as dist_mod
+        import torch.distributed as dist
 
-        dist = dist_mod
         dist.init_process_group("nccl", device_id=device)
+        multi_gpu_main(args, rank, world, local_rank, device, dist)
+        return
+    if args.config != 2:
+        raise SystemExit(f"configuration {args.config} is stated for {PARTITIONED[args.config]['gpus']} GPUs: run it with --gpus {PARTITIONED[args.config]['gpus']}")
 
     pkg = importlib.import_module("ge-2_b200")
     pkg.load_library()
     pipeline = importlib.import_module("ge-2_b200.pipeline")
+    capi = pkg.capi
     cfg = CFG
     B, C, N, D, R, nodes = cfg["B"], cfg["C"], cfg["N"], cfg["D"], cfg["relations"], cfg["nodes"]
     K, W = args.steps, args.warmup
 
     # ---- synthetic data, resident in HBM before the timed region -------------------------------------------
     n_edges = cfg["triples"] if (K + W) * B <= cfg["triples"] else (K + W) * B
-    edges = make_graph(cfg, n_edges, 20262 + rank, device)  # each rank: its own edge share (weak scaling)
+    edges = make_graph(cfg, n_edges, 20262, device)
     edges = edges[torch.randperm(n_edges, device=device)]    # epoch shuffle (dataloader.cpp:613-616 of the reference project)
-    gen = torch.Generator(device=device).manual_seed(7 + rank)
-    pbuf, supersteps = None, None
-    if world == 1:
-        table = (torch.rand((nodes, D), device=device, generator=gen) - 0.5) * 0.2
-        state = torch.zeros((nodes, D), device=device)
-    else:
-        # Partition buffer (the reference's multi-GPU layout): 4 * world node partitions, every rank trains on the 4 that are
-        # resident in its buffer (same per-GPU domain and batch as the single-GPU run: weak scaling); between supersteps the
-        # partitions change hands over NCCL.  Edge endpoints are buffer-local ids, as after the reference's slot remap.
-        partition = importlib.import_module("ge-2_b200.partition")
-        P, psize = 4 * world, nodes // 4
-        home_emb = (torch.rand((4 * psize, D), device=device, generator=gen) - 0.5) * 0.2
-        home_state = torch.zeros((4 * psize, D), device=device)
-        try:  # partitions that change hands are pulled by the receiver over NVLink peer memory; NCCL send/recv as fall-back
-            pbuf = partition.PartitionBuffer([home_emb, home_state], psize, P, rank, world, dist, peer_copies=not args.nccl_swaps)
-        except Exception as e:
-            print(f"[bench] peer-memory partition copies unavailable ({e!r}); using NCCL send/recv", file=sys.stderr)
-            pbuf = partition.PartitionBuffer([home_emb, home_state], psize, P, rank, world, dist)
-        supersteps = partition.make_supersteps(P, world)
-        for st in supersteps:  # initial load and one pass over the schedule: every connection a swap needs exists before anything is timed
-            pbuf.swap(st)
-        pbuf.swap(supersteps[0])
-        sw0, sw1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-        dist.barrier()
-        sw0.record()
-        pbuf.swap(supersteps[1 % len(supersteps)])  # a full swap, timed on its own (reported beside the step time)
-        sw1.record()
-        torch.cuda.synchronize()
-        swap_ms = sw0.elapsed_time(sw1)
-        table, state = pbuf.buf[0], pbuf.buf[1]
+    gen = torch.Generator(device=device).manual_seed(7)
+    table = (torch.rand((nodes, D), device=device, generator=gen) - 0.5) * 0.2
+    state = torch.zeros((nodes, D), device=device)
     rels = torch.zeros((2, R, D), device=device)  # relation and inverse-relation tables back to back: one optimizer launch for both
     rels[:, :, : D // 2] = 1  # ComplEx relation init (complex.cpp:18-20 of the reference project)
     rel, inv_rel = rels[0], rels[1]
     rel_states = torch.zeros_like(rels)
     pcfg = pipeline.PipelineConfig(cfg["decoder"], B, C, N, cfg["degree_fraction"], D, R, nodes, lr=cfg["lr"], precision=args.precision)
     pipe = pipeline.BatchPipeline(pcfg, table, state, rel, rel_states[0], inv_rel, rel_states[1])
-    rel_hook = None
-    peer_reduce = world > 1 and not args.nccl_allreduce and not args.no_graph and not args.no_pipeline
-    if peer_reduce:
-        # Model::all_reduce of the reference (model.cpp:174-204) folded into the dense optimizer launch: every rank reads the
-        # other ranks' relation gradients over NVLink (peer memory), so the multi-GPU step stays one graph replay
-        try:
-            pipe.use_peer_gradients(pipeline.PeerGradients(dist, 2 * R * D, device))
-        except Exception as e:  # symmetric memory cannot be set up here: the NCCL form below does the same exchange
-            print(f"[bench] peer-memory gradient sum unavailable ({e!r}); using the NCCL all-reduce", file=sys.stderr)
-            peer_reduce = False
-    if world > 1 and not peer_reduce:
-        pipe.grad_scale = 1.0 / world
-
-        def rel_hook(p):  # the same exchange as an NCCL collective between two graphs
-            dist.all_reduce(p.rel_grads)  # both tables in one call
 
     def barrier():
-        if dist is not None:
-            dist.barrier()
         torch.cuda.synchronize()
 
     num_batches = n_edges // B
-    use_graph = not args.no_graph  # N > 1: two graphs per step with the host-issued NCCL all-reduce between them
-    # steps between swaps: a state holds 16 of the (4N)^2 edge buckets, i.e. triples * 16 / (4N)^2 edges = that many / B batches
-    sps = args.steps_per_state if args.steps_per_state > 0 else max(1, int(cfg["triples"] * 16 / (4 * world) ** 2 / B))
-    swaps = [0]
-
-    def maybe_swap(i, runner=None):
-        """superstep boundary: every `sps` steps the ranks exchange partitions (performNextSwap of the reference)"""
-        if pbuf is not None and i > 0 and i % sps == 0:
-            swaps[0] += 1
-            pbuf.swap(supersteps[(1 + swaps[0]) % len(supersteps)])
-            if runner is not None and hasattr(runner, "refill"):
-                runner.refill()  # a new state brings a new edge bucket: the batch drawn ahead is drawn again
+    use_graph = not args.no_graph
 
     # ---- warm-up, then an event-bracketed pass that times the scores kernel alone (roofline) ---------------------
     for i in range(W):
-        pipe.enqueue_resident(edges, num_batches, rel_hook=rel_hook)
+        pipe.enqueue_resident(edges, num_batches)
     pipe.check_status()
     ev_pairs = [(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)) for _ in range(K)]
     barrier()
     for i in range(K):
-        pipe.enqueue_resident(edges, num_batches, scores_events=ev_pairs[i], rel_hook=rel_hook)
+        pipe.enqueue_resident(edges, num_batches, scores_events=ev_pairs[i])
     barrier()
     scores_host_ms = float(np.mean([a.elapsed_time(b) for a, b in ev_pairs]))
     # the same phase as it runs in the timed region: inside a replayed graph, without the host's launch gaps
     scores_ms = pipe.time_scores_phase(edges) if use_graph else scores_host_ms
+    kernel_rooflines = None if (args.no_kernel_rooflines or not use_graph) else per_kernel_rooflines(pipe, pcfg, capi, edges, num_batches)
 
     # ---- device-resident timing (`value`): K steps, one CUDA-graph launch per step -----------------------------------
     pipelined = use_graph and not args.no_pipeline
     if pipelined:
-        graph = pipe.capture_pipelined(edges, num_batches, rel_hook=rel_hook)
+        graph = pipe.capture_pipelined(edges, num_batches)
     elif use_graph:
-        graph = pipe.capture_resident(edges, num_batches) if world == 1 else pipe.capture_resident_split(edges, num_batches, rel_hook)
+        graph = pipe.capture_resident(edges, num_batches)
     if use_graph:
-        barrier()  # captures take different times on different ranks; start replaying together
         for _ in range(W):
             graph.replay()
-    # The clock sampler starts before the barrier (its start-up takes milliseconds and differs between ranks); the barrier and
-    # the first event sit back to back.  The K-step region runs REPEATS times, each repeat bracketed by barrier + synchronize
-    # on both sides and timed with CUDA events; the step counter runs on across repeats, so at N > 1 partition swaps fall
-    # into the timed regions at the rate the workload's schedule gives them.
+    # The clock sampler starts before the first timed region (its start-up takes milliseconds).  The K-step region runs
+    # REPEATS times, each repeat bracketed by a synchronize on both sides and timed with CUDA events.
     clocks = ClockSampler(local_rank)
     clocks.start()
     time.sleep(0.02)
-    rep_ms, gstep = [], 0
+    rep_ms = []
     for r in range(REPEATS):
         start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         barrier()
         start.record()
         for i in range(K):
-            maybe_swap(gstep, graph if use_graph else None)
-            gstep += 1
             if use_graph:
                 graph.replay()
             else:
-                pipe.enqueue_resident(edges, num_batches, rel_hook=rel_hook)
+                pipe.enqueue_resident(edges, num_batches)
         end.record()
         barrier()
         rep_ms.append(start.elapsed_time(end))
-    swaps_timed = swaps[0]
     pipe.check_status()
 
     # ---- end-to-end timing (`e2e`): host edges in, loss out, through the same public step call -----------------
@@ -493,27 +756,20 @@ def main():
     stage.copy_(host_edges[0])
     if pipelined:
         # two staging slots: while batch i trains, the ids of batch i+1 are drawn from the slot copied during step i-1
-        graph_e2e = pipeline.HostFeed(pipe, 3, rel_hook=rel_hook)
+        graph_e2e = pipeline.HostFeed(pipe, 3)
         graph_e2e.start(host_edges[K - 1], host_edges[0])
     elif use_graph:
-        graph_e2e = pipe.capture_resident(stage, 1) if world == 1 else pipe.capture_resident_split(stage, 1, rel_hook)
-
-    e2e_count = [0]
+        graph_e2e = pipe.capture_resident(stage, 1)
 
     def e2e_step(i):
-        g = e2e_count[0]  # steps since the e2e pass began: partition swaps keep their rhythm across repeats
-        e2e_count[0] += 1
         if pipelined:
-            maybe_swap(g, graph_e2e)
             graph_e2e.step(host_edges[(i + 1) % K], host_loss[i:i + 1])  # trains batch i, copies and draws batch i+1
             return
+        stage.copy_(host_edges[i], non_blocking=True)
+        if use_graph:
+            graph_e2e.replay()
         else:
-            maybe_swap(g)
-            stage.copy_(host_edges[i], non_blocking=True)
-            if use_graph:
-                graph_e2e.replay()
-            else:
-                pipe.enqueue_resident(stage, 1, rel_hook=rel_hook)
+            pipe.enqueue_resident(stage, 1)
         host_loss[i:i + 1].copy_(pipe.loss, non_blocking=True)
 
     barrier()
@@ -534,17 +790,11 @@ def main():
     clock_info = clocks.stop()
     pipe.check_status()
     assert bool(torch.isfinite(host_loss).all()) and float(host_loss[-1]) > 0
-
-    t = torch.tensor(rep_ms + rep_e2e + [scores_ms], device=device, dtype=torch.float64)
-    if dist is not None:
-        dist.all_reduce(t, op=dist.ReduceOp.MAX)  # every repeat: the slowest rank's device time
-    t = t.cpu().tolist()
-    rep_ms, rep_e2e, scores_ms = t[:REPEATS], t[REPEATS:2 * REPEATS], t[-1]
     ms, ms_e2e = sum(rep_ms) / REPEATS, sum(rep_e2e) / REPEATS  # mean K-step region = total steps over total time
 
-    # ---- N = 1: one epoch of the workload (its triples / B steps) as a single timed region, clocks sampled across it -----
+    # ---- one epoch of the workload (its triples / B steps) as a single timed region, clocks sampled across it -----
     epoch_info = None
-    if world == 1 and use_graph and not args.no_epoch:
+    if use_graph and not args.no_epoch:
         ep_steps = cfg["triples"] // B
         ck = ClockSampler(local_rank)
         ck.start()
@@ -563,37 +813,27 @@ def main():
                           reasons=ci.get("reasons"), ms_x_mhz_per_step=(ep_ms / ep_steps) * (ci.get("sm_mhz") or 0.0),
                           note="train edges / epoch seconds, the reference's Edges per Second line (trainer.cpp:229-232), device-resident edges")
 
+    world = 1
     if rank == 0:
-        pk = peaks()
         S = pcfg.sides
-        flops = 6.0 * S * B * N * D  # forward contraction + the two backward contractions, per side
-        achieved = flops / (scores_ms * 1e-3) / 1e12
         line = dict(
-            metric="train edges/sec/box", value=world * K * B / (ms * 1e-3), unit="edges/s", n_gpus=world, steps=K, warmup=W,
+            metric="train edges/sec/box", value=K * B / (ms * 1e-3), unit="edges/s", n_gpus=1, steps=K, warmup=W,
             ms_per_step=ms / K, higher_is_better=True, scaling="weak", vs_baseline=None, repeats=REPEATS,
             ms_per_step_repeats=dict(min=min(rep_ms) / K, median=float(np.median(rep_ms)) / K, max=max(rep_ms) / K,
-                                     note="each repeat = K steps between barrier + synchronize, CUDA events, max over ranks; value = mean"),
+                                     note="each repeat = K steps between synchronizes, CUDA events; value = mean"),
             dtype="f32" if args.precision == "fp32" else "f16 tensor tiles, f32 accumulate and storage", data="synthetic",
-            config=dict(workload=cfg["name"], per_gpu_batch=B, global_batch=B * world, precision=args.precision,
-                        l2="tables (0.8 GB) and edge list larger than L2; rows touched per step are random", parallelism=f"dp{world}" if world > 1 else "single",
-                        launch=("one CUDA graph replay per step" if (world == 1 or peer_reduce) else "two CUDA graph replays + one NCCL all-reduce per step") if use_graph else "host-issued launches",
-                        pipelined="ids of batch t+1 are drawn and deduplicated on a side stream while batch t trains" if pipelined else None,
-                        partitions=None if pbuf is None else dict(count=4 * world, rows=nodes // 4, steps_per_state=sps, swaps_in_timed_region=swaps_timed, steps_in_timed_region=K * REPEATS,
-                                                                  swap_ms=swap_ms, swap_ms_per_step_amortized=swap_ms / sps,
-                                                                  
-                                                                  exchange=("partition slabs pulled over NVLink peer memory" if pbuf.peer_buf is not None else "NCCL send/recv of partition slabs") + "; relation gradients every step: " + ("summed over NVLink peer memory inside the dense optimizer kernel" if peer_reduce else "NCCL all-reduce"))),
-            e2e=dict(value=world * K * B / (ms_e2e * 1e-3), unit="edges/s", h2d_bytes_per_step=B * 3 * 8, d2h_bytes_per_step=4,
+            config=dict(workload=cfg["name"], per_gpu_batch=B, global_batch=B, precision=args.precision,
+                        l2="tables (0.8 GB) and edge list larger than L2; rows touched per step are random", parallelism="single",
+                        launch="one CUDA graph replay per step" if use_graph else "host-issued launches",
+                        pipelined="ids of batch t+1 are drawn and deduplicated on a side stream while batch t trains" if pipelined else None),
+            e2e=dict(value=K * B / (ms_e2e * 1e-3), unit="edges/s", h2d_bytes_per_step=B * 3 * 8, d2h_bytes_per_step=4,
                      ms_per_step=ms_e2e / K, ms_per_step_median=float(np.median(rep_e2e)) / K,
                      note="pinned host edges -> H2D, step, loss -> pinned host, all stream-ordered; one synchronize at the end of each repeat"
                           + ("; the H2D copy issued in step i carries batch i+1 (drawn ahead while batch i trains) and runs on a copy stream, the loss read-back on another" if pipelined else "")),
             gpu_launches=K * pipe.launches_per_step(), epoch=epoch_info,
             clocks=clock_info,
-            roofline=dict(bound="tensor", kernel="lp_scores_%s" % args.precision, achieved=achieved, peak=pk["tf"], unit="TFLOP/s",
-                          frac=achieved / pk["tf"], traffic=NCU_TRAFFIC.get(args.precision), peak_source=pk["src"] + " bf16 dense",
-                          ms_per_launch=scores_ms, flops_per_launch=flops, ms_host_issued=scores_host_ms,
-                          timing="CUDA events around 20 scores phases (dK clear + the scores launches: whole rounds unsplit, leftover blocks as "
-                                 "two split launches) replayed as one CUDA graph, as in the timed region; ms_host_issued = the same phase "
-                                 "bracketed by events in a host-issued pass of the same K steps (includes launch gaps)"),
+            roofline=scores_roofline(args.precision, S, B, N, D, scores_ms, scores_host_ms),
+            roofline_kernels=kernel_rooflines,
         )
         if world == 1 and args.precision == "f16" and not args.no_fp32_path:
             # the same step on the fp32 CUDA-core path (1e-4 parity), for reference next to the headline
@@ -626,8 +866,6 @@ def main():
             line["cpu_baseline"] = dict(value=v, unit="edges/s", cores=cpu.cores, kind=cpu.kind,
                                         sample=f"{k} batches of {B} edges of the same workload in {dt:.1f} s on the host cores")
         print(json.dumps(line), flush=True)
-    if dist is not None:
-        dist.destroy_process_group()
 
 
 if __name__ == "__main__":

@@ -444,14 +444,17 @@ class PartitionedTrainer:
     ranks -- keep taking part in the relation-gradient exchange until the longest lane of the superstep is done.
     The loop of the reference's multi-GPU trainer (engine/trainer.cpp:779-898) for one lane."""
 
-    def __init__(self, pipe, relay: RelayBuffer, edges_sorted, bucket_sizes, seed: int = 1):
+    def __init__(self, pipe, relay: RelayBuffer, edges_sorted, bucket_sizes, seed: int = 1, bucket_begin=None):
+        """edges_sorted: the bucket-sorted training edges on this device (global node ids); bucket_sizes[P * P]: rows of every
+        bucket of the graph; bucket_begin[P * P]: first row of each bucket in edges_sorted when the rank holds only the buckets
+        it trains (default: the list holds all buckets back to back)."""
         import numpy as np
         import torch
 
         self.pipe, self.relay = pipe, relay
         self.edges_sorted = edges_sorted
         self.sizes = np.asarray(bucket_sizes, np.int64)
-        self.begin = np.concatenate([[0], np.cumsum(self.sizes)])[:-1]
+        self.begin = np.concatenate([[0], np.cumsum(self.sizes)])[:-1] if bucket_begin is None else np.asarray(bucket_begin, np.int64)
         P, world = relay.num_partitions, relay.world
         self.supersteps = make_supersteps(P, world)
         self.buckets = state_buckets(self.supersteps, P)

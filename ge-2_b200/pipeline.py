@@ -519,13 +519,14 @@ class HostFeed:
         self.read = [torch.cuda.Event() for _ in range(2)]
         self.runner, self.j = None, 0
 
-    def start(self, batch0, batch1):
+    def start(self, batch0, batch1, tables=None):
+        """tables: (table, state) to train, when not the pipeline's own (a partition buffer's current pair)"""
         pipe = self.pipe
         c = int(pipe.step_dev[0].item())
         self.stage[c % 2].copy_(batch0)
         self.stage[(c + 1) % 2].copy_(batch1)
         self.slot0 = c + 2
-        self.runner = pipe.capture_pipelined(self.stage.view(2 * pipe.cfg.B, -1), 2, rel_hook=self.rel_hook)
+        self.runner = pipe.capture_pipelined(self.stage.view(2 * pipe.cfg.B, -1), 2, rel_hook=self.rel_hook, tables=tables)
         torch.cuda.synchronize(pipe.device)
         self.j = 0
 
