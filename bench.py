@@ -324,7 +324,12 @@ def reference_gpu_ms(cfg, table, state, edges, steps, device):
     return a.elapsed_time(b) / steps
 
 
-def make_partitioned_edges(cfg, P, psize, keep_buckets, seed, device, chunk=40_000_000):
+def bucket_sizes_of(cfg, P, psize, seed, device):
+    """sizes of all P * P buckets of the graph make_partitioned_edges generates (a counting pass over the same draws)"""
+    return make_partitioned_edges(cfg, P, psize, [], seed, device, count_only=True)[1]
+
+
+def make_partitioned_edges(cfg, P, psize, keep_buckets, seed, device, chunk=40_000_000, count_only=False):
     """The graph's training edges, generated chunk by chunk with the same seed on every rank; a rank keeps the edges of
     the buckets it will train (keep_buckets) sorted by bucket -- the preprocessor's order
     (torch_partitioner.py:12-31 of the reference project) -- and the sizes of ALL P*P buckets.
@@ -338,14 +343,14 @@ def make_partitioned_edges(cfg, P, psize, keep_buckets, seed, device, chunk=40_0
         w = torch.arange(1, domain + 1, dtype=torch.float64, device=device).pow_(-alpha)
         cdf = torch.cumsum(w, 0)
         cdf /= cdf[-1].clone()
-        cdf = cdf.to(torch.float32) if domain > 50_000_000 else cdf  # 100 M entries: keep the table at 0.4 GB
         perm = torch.randperm(domain, device=device, generator=gen)
         return lambda n: perm[torch.searchsorted(cdf, torch.rand(n, dtype=cdf.dtype, device=device, generator=gen)).clamp_(max=domain - 1)]
 
     draw_node = sampler(nodes, cfg["alpha_nodes"])
     draw_rel = sampler(R, cfg["alpha_rel"]) if has_rel else None
     keep = torch.zeros(P * P, dtype=torch.bool, device=device)
-    keep[torch.tensor(sorted(keep_buckets), dtype=torch.int64, device=device)] = True
+    if len(keep_buckets):
+        keep[torch.tensor(sorted(keep_buckets), dtype=torch.int64, device=device)] = True
     sizes = torch.zeros(P * P, dtype=torch.int64, device=device)
     kept, kept_b = [], []
     left = cfg["triples"]
@@ -356,10 +361,14 @@ def make_partitioned_edges(cfg, P, psize, keep_buckets, seed, device, chunk=40_0
         b = (src // psize) * P + dst // psize
         sizes += torch.bincount(b, minlength=P * P)
         m = keep[b]
-        cols = [src[m]] + ([draw_rel(n)[m]] if has_rel else []) + [dst[m]]
-        kept.append(torch.stack(cols, dim=1))
-        kept_b.append(b[m])
-        del src, dst, b, m
+        rel_col = draw_rel(n) if has_rel else None  # drawn in both passes: the generator's stream stays the same
+        if not count_only:
+            cols = [src[m]] + ([rel_col[m]] if has_rel else []) + [dst[m]]
+            kept.append(torch.stack(cols, dim=1))
+            kept_b.append(b[m])
+        del src, dst, b, m, rel_col
+    if count_only:
+        return None, sizes.cpu().numpy(), None
     e = torch.cat(kept)
     bk = torch.cat(kept_b)
     del kept, kept_b
@@ -466,15 +475,17 @@ def multi_gpu_main(args, rank, world, local_rank, device, dist):
     psize = -(-cfg["nodes"] // P)  # ceil, as the reference sizes its partitions (storage.cpp:368)
     domain = partition.CAPACITY * psize
     supersteps = partition.make_supersteps(P, world)
-    buckets = partition.state_buckets(supersteps, P)
-    mine = sorted(b for lanes in buckets for b in lanes[rank])
 
     def barrier():
         dist.barrier()
         torch.cuda.synchronize()
 
     t_setup = time.perf_counter()
-    edges_sorted, sizes, begin = make_partitioned_edges(cfg, P, psize, mine, 20262, device)
+    sizes = bucket_sizes_of(cfg, P, psize, 20262, device)   # first pass: the sizes of all buckets (the schedule balances lanes with them)
+    buckets = partition.state_buckets(supersteps, P, sizes)
+    mine = sorted(b for lanes in buckets for b in lanes[rank])
+    edges_sorted, sizes2, begin = make_partitioned_edges(cfg, P, psize, mine, 20262, device)
+    assert np.array_equal(sizes, sizes2)
     gen = torch.Generator(device=device).manual_seed(7 + rank)
     n_home = len([p for p in range(P) if p % world == rank])
     home_emb = (torch.rand((n_home * psize, D), device=device, generator=gen) - 0.5) * 0.2
@@ -590,6 +601,25 @@ def multi_gpu_main(args, rank, world, local_rank, device, dist):
     assert bool(torch.isfinite(host_loss).all()) and float(host_loss[-1]) > 0
 
     scores_ms = pipe.time_scores_phase(trainer.state_edges)  # the scores launches of one step, replayed as a graph of their own
+    # The relation-gradient exchange on its own: the announce/wait kernel + the peer-summing optimizer kernel, 20 times back to
+    # back (the step counter stands still, so nobody waits: this is the kernels' own time, without the skew between ranks that
+    # a real step adds; the half they read was cleared by the last step, so the tables do not move).
+    exchange_us = None
+    if has_rel:
+        barrier()
+        g = torch.cuda.CUDAGraph()
+        pipe._update_relations()
+        torch.cuda.synchronize()
+        with torch.cuda.graph(g):
+            for _ in range(20):
+                pipe._update_relations()
+        barrier()
+        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        a.record()
+        g.replay()
+        b.record()
+        barrier()
+        exchange_us = 1e3 * a.elapsed_time(b) / 20
     t = torch.tensor(rep_ms + rep_e2e + sw_ms + [scores_ms], device=device, dtype=torch.float64)
     dist.all_reduce(t, op=dist.ReduceOp.MAX)  # every region: the slowest rank's device time
     t = t.cpu().tolist()
@@ -617,7 +647,7 @@ def multi_gpu_main(args, rank, world, local_rank, device, dist):
                                         epoch_train_edges=epoch_edges, steps_per_superstep_mean=epoch_steps / n_sw,
                                         lane_balance=epoch_edges / (epoch_steps * B * world), swap_ms=swap_ms, swap_ms_all=sw_ms,
                                         swap_share_of_epoch=n_sw * swap_ms / epoch_ms, slab_mb=psize * D * 4 / 1e6,
-                                        exchange_us_per_step=None, step_only_value=world * B / (ms_step * 1e-3),
+                                        exchange_us_per_step=exchange_us, step_only_value=world * B / (ms_step * 1e-3),
                                         swap="receiver-side pulls over NVLink peer memory behind a device-side barrier, two alternating active "
                                              "buffers, edge list of the new state built on the device (bucket gather + slot remap + shuffle)"),
                         setup_seconds=setup_s),

@@ -428,13 +428,54 @@ class RelayBuffer:
             raise self.capi.Ge2Error("partition swap: " + self.capi.decode_status(word))
 
 
-def state_buckets(supersteps, num_partitions: int):
-    """buckets[k][rank] = list of bucket ids (src partition * P + dst partition) trained by `rank` in superstep k: every
-    ordered bucket goes to the first state that holds both of its partitions (ordering.cpp:1350-1370 of the reference)."""
-    owner = assign_buckets(supersteps, num_partitions)
+def state_buckets(supersteps, num_partitions: int, bucket_sizes=None):
+    """buckets[k][rank] = list of bucket ids (src partition * P + dst partition) trained by `rank` in superstep k.
+    Without sizes every ordered bucket goes to the first state that holds both of its partitions (the reference's greedy
+    assignment, ordering.cpp:1350-1370).  With bucket_sizes[P * P] the buckets that several states could train (both
+    partitions in one unit of the round-robin design: they meet in every round) are dealt out largest first to where they
+    lengthen the epoch least -- the epoch's length is the sum over supersteps of the longest lane, the quantity the
+    reference's schedule optimizer balances (ordering.cpp:659-728)."""
+    P = num_partitions
+    where: Dict[Tuple[int, int], List[Tuple[int, int]]] = {}
+    for k, lanes in enumerate(supersteps):
+        for r, st in enumerate(lanes):
+            if st is None:
+                continue
+            for a in st:
+                for b in st:
+                    where.setdefault((a, b), []).append((k, r))
+    missing = [(a, b) for a in range(P) for b in range(P) if (a, b) not in where]
+    if missing:
+        raise ValueError(f"schedule does not cover buckets {missing[:4]}...")
     out = [[[] for _ in lanes] for lanes in supersteps]
-    for (a, b), (k, r) in sorted(owner.items()):
-        out[k][r].append(a * num_partitions + b)
+    if bucket_sizes is None:
+        for (a, b), places in sorted(where.items()):
+            k, r = places[0]
+            out[k][r].append(a * P + b)
+        return out
+    size = lambda ab: int(bucket_sizes[ab[0] * P + ab[1]])
+    load = [[0] * len(lanes) for lanes in supersteps]
+    flexible = []
+    for ab, places in sorted(where.items()):
+        if len(places) == 1:
+            k, r = places[0]
+            out[k][r].append(ab[0] * P + ab[1])
+            load[k][r] += size(ab)
+        else:
+            flexible.append(ab)
+    for ab in sorted(flexible, key=lambda x: (-size(x), x)):
+        best = None
+        for k, r in where[ab]:
+            longest = max(load[k])
+            cost = (max(longest, load[k][r] + size(ab)) - longest, load[k][r], k, r)
+            if best is None or cost < best:
+                best = cost
+        _, _, k, r = best
+        out[k][r].append(ab[0] * P + ab[1])
+        load[k][r] += size(ab)
+    for lanes in out:
+        for lst in lanes:
+            lst.sort()
     return out
 
 
@@ -457,7 +498,7 @@ class PartitionedTrainer:
         self.begin = np.concatenate([[0], np.cumsum(self.sizes)])[:-1] if bucket_begin is None else np.asarray(bucket_begin, np.int64)
         P, world = relay.num_partitions, relay.world
         self.supersteps = make_supersteps(P, world)
-        self.buckets = state_buckets(self.supersteps, P)
+        self.buckets = state_buckets(self.supersteps, P, self.sizes)
         self.seed = seed
         B = pipe.cfg.B
         self.state_edges_count = [[int(self.sizes[b].sum()) if len(b) else 0 for b in lanes] for lanes in self.buckets]
