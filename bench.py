@@ -513,7 +513,7 @@ def multi_gpu_main(args, rank, world, local_rank, device, dist):
 
     # ---- superstep 0: swap in, build the edge list, capture the step graphs (outside every timed region) ---------------------
     state_no = [0]
-    sw_ms = []
+    sw_ms, sw_parts = [], []
 
     def next_state(timed: bool):
         """partition swap + rebuild of this rank's edge list + redraw of the batch sampled ahead, as one device-timed region"""
@@ -524,12 +524,16 @@ def multi_gpu_main(args, rank, world, local_rank, device, dist):
             barrier()
         a.record()
         relay.swap(supersteps[k])
+        mid1 = torch.cuda.Event(enable_timing=True)
+        mid1.record()
         lane = buckets[k][rank]
         total = 0
         if supersteps[k][rank] is not None and lane:
             trainer.slot_dev.copy_(torch.tensor(relay.slot_table(), dtype=torch.int64))
             total = capi.build_state_edges(edges_sorted, [int(begin[x]) for x in lane], [int(sizes[x]) for x in lane], trainer.slot_dev, psize,
                                            trainer.state_seed(0, k), trainer.state_edges, pipe.status)
+        mid2 = torch.cuda.Event(enable_timing=True)
+        mid2.record()
         pipe.set_num_batches(max(1, total // B))
         runner, _ = trainer._runner(relay.parity)
         runner.refill()
@@ -537,6 +541,7 @@ def multi_gpu_main(args, rank, world, local_rank, device, dist):
         if timed:
             barrier()
             sw_ms.append(a.elapsed_time(b))
+            sw_parts.append((a.elapsed_time(mid1), mid1.elapsed_time(mid2), mid2.elapsed_time(b)))
         return runner, total
 
     runner, total0 = next_state(False)
@@ -645,7 +650,7 @@ def multi_gpu_main(args, rank, world, local_rank, device, dist):
                                  "the measured swap + edge-list rebuild time); steps and swaps are timed in this run on the device, max over ranks",
                         partitions=dict(count=P, rows=psize, resident_per_gpu=partition.CAPACITY, supersteps=n_sw, epoch_steps_per_lane=epoch_steps,
                                         epoch_train_edges=epoch_edges, steps_per_superstep_mean=epoch_steps / n_sw,
-                                        lane_balance=epoch_edges / (epoch_steps * B * world), swap_ms=swap_ms, swap_ms_all=sw_ms,
+                                        lane_balance=epoch_edges / (epoch_steps * B * world), swap_ms=swap_ms, swap_ms_all=sw_ms, swap_parts_ms_rank0=[dict(pulls=x, edge_list=y, refill=z) for x, y, z in sw_parts],
                                         swap_share_of_epoch=n_sw * swap_ms / epoch_ms, slab_mb=psize * D * 4 / 1e6,
                                         exchange_us_per_step=exchange_us, step_only_value=world * B / (ms_step * 1e-3),
                                         swap="receiver-side pulls over NVLink peer memory behind a device-side barrier, two alternating active "

@@ -7,6 +7,8 @@
 //                   buckets, randperm, index_select) -- host loops, OpenMP and a full upload there, one kernel here;
 //   swap            storage/storage.cpp:576-689 (MemPartitionBufferStorage::performNextSwap, peer-relay branch :599-652: every slot
 //                   of the next state is copied from the device and slot that hold the partition now, between thread barriers).
+#include <algorithm>
+
 #include "common.cuh"
 
 namespace ge2 {
@@ -133,23 +135,29 @@ struct PullList {
     int32_t count;
 };
 
-// Copies every slab of the list (blockIdx.y = slab) -- unless the verdict of the barrier before it says that a rank never
-// arrived, in which case nothing is touched.  Plain 16-byte peer loads; no multicast object is involved.
-__global__ void __launch_bounds__(256) swap_pull_kernel(PullList pulls, int64_t slab_vec4, const unsigned long long* __restrict__ verdict,
-                                                        unsigned long long epoch) {
+// Copies every slab of the list -- unless the verdict of the barrier before it says that a rank never arrived, in which
+// case nothing is touched.  Plain 16-byte peer loads; no multicast object is involved.  The list is cut into pieces of
+// kPullPiece bytes dealt round-robin over slabs and CTAs, so every CTA works on local and remote slabs alike; a warp
+// instruction covers 512 contiguous bytes and every thread keeps eight loads in flight.
+constexpr int kPullThreads = 256, kPullInFlight = 8;
+constexpr int64_t kPullPieceVec4 = (int64_t)kPullThreads * kPullInFlight;  // 32 KB
+__global__ void __launch_bounds__(kPullThreads) swap_pull_kernel(PullList pulls, int64_t slab_vec4, const unsigned long long* __restrict__ verdict,
+                                                                 unsigned long long epoch) {
     if (verdict != nullptr && *verdict != epoch) return;
-    const float4* __restrict__ s = pulls.src[blockIdx.y];
-    float4* __restrict__ d = pulls.dst[blockIdx.y];
-    const int64_t stride = (int64_t)gridDim.x * blockDim.x * 4;
-    for (int64_t i = ((int64_t)blockIdx.x * blockDim.x + threadIdx.x) * 4; i < slab_vec4; i += stride) {
-        // four independent 16-byte loads in flight per thread: NVLink latency is several microseconds
-        float4 v[4];
+    const int64_t per_slab = (slab_vec4 + kPullPieceVec4 - 1) / kPullPieceVec4;
+    const int64_t total = per_slab * pulls.count;
+    for (int64_t q = blockIdx.x; q < total; q += gridDim.x) {
+        const int slab = (int)(q % pulls.count);
+        const int64_t base = (q / pulls.count) * kPullPieceVec4 + threadIdx.x;
+        const float4* __restrict__ s = pulls.src[slab];
+        float4* __restrict__ d = pulls.dst[slab];
+        float4 v[kPullInFlight];
 #pragma unroll
-        for (int k = 0; k < 4; k++)
-            if (i + k < slab_vec4) v[k] = __ldcv(s + i + k);
+        for (int k = 0; k < kPullInFlight; k++)
+            if (base + k * kPullThreads < slab_vec4) v[k] = __ldcv(s + base + k * kPullThreads);
 #pragma unroll
-        for (int k = 0; k < 4; k++)
-            if (i + k < slab_vec4) d[i + k] = v[k];
+        for (int k = 0; k < kPullInFlight; k++)
+            if (base + k * kPullThreads < slab_vec4) d[base + k * kPullThreads] = v[k];
     }
 }
 
@@ -220,13 +228,10 @@ extern "C" int ge2_swap_begin(const ge2_swap_desc* desc, ge2_stream_t stream_) {
     for (int k = 0; k < desc->num_pulls; k++)
         if (pl.src[k] == nullptr || pl.dst[k] == nullptr || (((uintptr_t)pl.src[k] | (uintptr_t)pl.dst[k]) & 15) != 0) return GE2_ERR_INVALID_ARGUMENT;
     const int64_t v4 = desc->slab_bytes / 16;
-    // the copy engine of this GPU is its SMs: enough CTAs per slab to keep NVLink / HBM busy, all slabs side by side
-    int per_slab = (kNumSMs * 4) / desc->num_pulls;
-    if (per_slab < 8) per_slab = 8;
-    const int64_t need = ceil_div<int64_t>(v4, 256 * 4);
-    if (per_slab > need) per_slab = (int)(need < 1 ? 1 : need);
-    dim3 grid((unsigned)per_slab, (unsigned)desc->num_pulls);
-    swap_pull_kernel<<<grid, 256, 0, stream>>>(pl, v4, verdict, desc->epoch);
+    // the copy engine of this GPU is its SMs: every SM full of copy warps, pieces of all slabs dealt over them
+    const int64_t pieces = ceil_div<int64_t>(v4, kPullPieceVec4) * desc->num_pulls;
+    const int grid = (int)std::min<int64_t>(pieces, (int64_t)kNumSMs * 6);
+    swap_pull_kernel<<<grid, kPullThreads, 0, stream>>>(pl, v4, verdict, desc->epoch);
     GE2_LAUNCH_CHECK();
     return GE2_OK;
 }

@@ -51,6 +51,10 @@ __device__ __forceinline__ void bulk_load_1d(void* smem_dst, const void* gsrc, u
                  "r"(bytes), "r"(smem_u32(bar))
                  : "memory");
 }
+// Untiled bulk copy shared -> global (same alignment rules), tracked by bulk groups
+__device__ __forceinline__ void bulk_store_1d(void* gdst, const void* smem_src, uint32_t bytes) {
+    asm volatile("cp.async.bulk.global.shared::cta.bulk_group [%0], [%1], %2;" ::"l"(gdst), "r"(smem_u32(smem_src)), "r"(bytes) : "memory");
+}
 // TMA: tiled 3-D reduction shared -> global (element-wise fp32 add into global memory), tracked by bulk groups.
 // Rows / columns of the box that fall outside the tensor are dropped.
 __device__ __forceinline__ void tma_reduce_add_3d(const CUtensorMap* map, int x, int y, int z, const void* smem_src) {
