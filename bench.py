@@ -329,6 +329,9 @@ def bucket_sizes_of(cfg, P, psize, seed, device):
     return make_partitioned_edges(cfg, P, psize, [], seed, device, count_only=True)[1]
 
 
+_CDF_CACHE = {}
+
+
 def make_partitioned_edges(cfg, P, psize, keep_buckets, seed, device, chunk=40_000_000, count_only=False):
     """The graph's training edges, generated chunk by chunk with the same seed on every rank; a rank keeps the edges of
     the buckets it will train (keep_buckets) sorted by bucket -- the preprocessor's order
@@ -340,9 +343,15 @@ def make_partitioned_edges(cfg, P, psize, keep_buckets, seed, device, chunk=40_0
     has_rel = R > 1
 
     def sampler(domain, alpha):
-        w = torch.arange(1, domain + 1, dtype=torch.float64, device=device).pow_(-alpha)
-        cdf = torch.cumsum(w, 0)
-        cdf /= cdf[-1].clone()
+        key = (domain, alpha, str(device))
+        if key not in _CDF_CACHE:
+            # powers on the device (element-wise: the same on every rank), the running sum on the host: a device scan adds
+            # its tiles in an order that varies from run to run, and every rank and both passes must draw exactly the same graph
+            w = torch.arange(1, domain + 1, dtype=torch.float64, device=device).pow_(-alpha).cpu().numpy()
+            np.cumsum(w, out=w)
+            w /= w[-1]
+            _CDF_CACHE[key] = torch.from_numpy(w).to(device)
+        cdf = _CDF_CACHE[key]
         perm = torch.randperm(domain, device=device, generator=gen)
         return lambda n: perm[torch.searchsorted(cdf, torch.rand(n, dtype=cdf.dtype, device=device, generator=gen)).clamp_(max=domain - 1)]
 
@@ -482,6 +491,10 @@ def multi_gpu_main(args, rank, world, local_rank, device, dist):
 
     t_setup = time.perf_counter()
     sizes = bucket_sizes_of(cfg, P, psize, 20262, device)   # first pass: the sizes of all buckets (the schedule balances lanes with them)
+    chk = torch.from_numpy(sizes).to(device)
+    dist.broadcast(chk, 0)
+    if not np.array_equal(chk.cpu().numpy(), sizes):
+        raise SystemExit("the ranks generated different graphs")
     buckets = partition.state_buckets(supersteps, P, sizes)
     mine = sorted(b for lanes in buckets for b in lanes[rank])
     edges_sorted, sizes2, begin = make_partitioned_edges(cfg, P, psize, mine, 20262, device)
@@ -558,6 +571,7 @@ def multi_gpu_main(args, rank, world, local_rank, device, dist):
     clocks.start()
     time.sleep(0.02)
     rep_ms = []
+    waited0 = pipe.peer.waited_ns() if has_rel else 0
     for r in range(REPEATS):
         start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         barrier()
@@ -568,6 +582,12 @@ def multi_gpu_main(args, rank, world, local_rank, device, dist):
         barrier()
         rep_ms.append(start.elapsed_time(end))
     pipe.check_status()
+    # how long this rank's announce kernel sat waiting for the slowest rank, per step (the first step of each region also
+    # absorbs the host barrier's skew)
+    waited_us = torch.tensor([(pipe.peer.waited_ns() - waited0) / (1e3 * REPEATS * K) if has_rel else 0.0], device=device, dtype=torch.float64)
+    waited_all = [torch.zeros_like(waited_us) for _ in range(world)]
+    dist.all_gather(waited_all, waited_us)
+    waited_all = [float(x) for x in waited_all]
 
     # ---- timed swaps: the next three supersteps' swap + rebuild, each as its own region ---------------------------------------------
     for _ in range(3):
@@ -625,6 +645,23 @@ def multi_gpu_main(args, rank, world, local_rank, device, dist):
         b.record()
         barrier()
         exchange_us = 1e3 * a.elapsed_time(b) / 20
+    # the step's kernels on this rank's own state, each timed alone: lanes differ (the buckets of a hub partition repeat a few
+    # rows thousands of times), and the exchange makes every step as long as the slowest lane's
+    kernel_ms_by_rank = None
+    if not args.no_kernel_rooflines:
+        barrier()
+        mine_ms = per_kernel_rooflines(pipe, pcfg, capi, trainer.state_edges, max(1, total // B))
+        names = sorted(mine_ms)
+        row = torch.tensor([mine_ms[n]["ms"] for n in names] + [float(pipe.ids[0].count[0].item())], device=device, dtype=torch.float64)
+        rows = [torch.zeros_like(row) for _ in range(world)]
+        dist.all_gather(rows, row)
+        kernel_ms_by_rank = {n: [round(float(r[i]), 5) for r in rows] for i, n in enumerate(names + ["distinct_rows"])}
+        kernel_ms_by_rank["scores"] = None  # filled below
+    sc_row = torch.tensor([scores_ms], device=device, dtype=torch.float64)
+    sc_rows = [torch.zeros_like(sc_row) for _ in range(world)]
+    dist.all_gather(sc_rows, sc_row)
+    if kernel_ms_by_rank is not None:
+        kernel_ms_by_rank["scores"] = [round(float(x), 5) for x in sc_rows]
     t = torch.tensor(rep_ms + rep_e2e + sw_ms + [scores_ms], device=device, dtype=torch.float64)
     dist.all_reduce(t, op=dist.ReduceOp.MAX)  # every region: the slowest rank's device time
     t = t.cpu().tolist()
@@ -650,7 +687,7 @@ def multi_gpu_main(args, rank, world, local_rank, device, dist):
                                  "the measured swap + edge-list rebuild time); steps and swaps are timed in this run on the device, max over ranks",
                         partitions=dict(count=P, rows=psize, resident_per_gpu=partition.CAPACITY, supersteps=n_sw, epoch_steps_per_lane=epoch_steps,
                                         epoch_train_edges=epoch_edges, steps_per_superstep_mean=epoch_steps / n_sw,
-                                        lane_balance=epoch_edges / (epoch_steps * B * world), swap_ms=swap_ms, swap_ms_all=sw_ms, swap_parts_ms_rank0=[dict(pulls=x, edge_list=y, refill=z) for x, y, z in sw_parts],
+                                        lane_balance=epoch_edges / (epoch_steps * B * world), exchange_wait_us_per_step_by_rank=waited_all if has_rel else None, kernel_ms_by_rank=kernel_ms_by_rank, swap_ms=swap_ms, swap_ms_all=sw_ms, swap_parts_ms_rank0=[dict(pulls=x, edge_list=y, refill=z) for x, y, z in sw_parts],
                                         swap_share_of_epoch=n_sw * swap_ms / epoch_ms, slab_mb=psize * D * 4 / 1e6,
                                         exchange_us_per_step=exchange_us, step_only_value=world * B / (ms_step * 1e-3),
                                         swap="receiver-side pulls over NVLink peer memory behind a device-side barrier, two alternating active "

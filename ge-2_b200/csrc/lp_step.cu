@@ -190,6 +190,7 @@ constexpr int kFinWarps = 8;
 constexpr long long kFinEmpty = -1;
 
 constexpr int kFinEdgeBatch = 64;  // edges whose scalars (ids, table rows, d loss / d pos, table slots) are fetched together
+constexpr int kFinHotSlots = 8;    // node rows cached per CTA: rows that occur more than once among a batch's endpoints
 
 struct FinishSmem {
     float acc[kFinSlots][128];
@@ -199,6 +200,12 @@ struct FinishSmem {
     long long sid[kFinEdgeBatch], did[kFinEdgeBatch], srow[kFinEdgeBatch], drow[kFinEdgeBatch];
     int rid[kFinEdgeBatch], slot[2][kFinEdgeBatch];  // rid < 0: skip the edge (bad ids, flagged by prep)
     float dpos[2][kFinEdgeBatch];
+    // Hub rows: in a skewed graph one node can be an endpoint of a tenth of the batch, and thousands of atomics on the same
+    // 128 bytes of its gradient row serialise in L2.  A row seen twice among the 128 endpoints of an edge batch gets a
+    // shared-memory row (first come, kept until the end of the CTA) and reaches global memory once per CTA.
+    float hot[kFinHotSlots][128];
+    long long hot_tag[kFinHotSlots];      // batch-local node id, or kFinEmpty
+    int hot_slot[2][kFinEdgeBatch];      // per edge: slot of its source / destination row, or -1
 };
 
 __device__ __forceinline__ int fin_slot_of(long long key) { return (int)(((unsigned long long)key * 0x9E3779B97F4A7C15ull) >> 59); }  // top 5 bits
@@ -223,6 +230,8 @@ __global__ void __launch_bounds__(kFinWarps * 32) lp_finish_kernel(LpKernelArgs 
         for (int k = tid; k < kFinSlots * 128; k += kFinWarps * 32) (&sm.acc[0][0])[k] = 0.f;
         if (tid < kFinSlots) sm.tag[tid] = kFinEmpty;
     }
+    for (int k = tid; k < kFinHotSlots * 128; k += kFinWarps * 32) (&sm.hot[0][0])[k] = 0.f;
+    if (tid < kFinHotSlots) sm.hot_tag[tid] = kFinEmpty;
     __syncthreads();
 
     // Every CTA takes a contiguous share of the edges (heavy rows: six input rows, four output rows each) and a contiguous
@@ -294,6 +303,27 @@ __global__ void __launch_bounds__(kFinWarps * 32) lp_finish_kernel(LpKernelArgs 
             negs_done = true;
         }
         __syncthreads();
+        if (tid < 2 * kFinEdgeBatch) {  // thread (side, k): does the row of this endpoint occur again in the batch, or hold a slot already?
+            const int side = tid / kFinEdgeBatch, k = tid % kFinEdgeBatch;
+            int hs = -1;
+            if (k < nb && sm.rid[k] >= 0) {
+                const long long id = side == 0 ? sm.sid[k] : sm.did[k];
+                const int sidx = (int)(((unsigned long long)id * 0x9E3779B97F4A7C15ull) >> 61);  // top 3 bits
+                if (sm.hot_tag[sidx] == id) {
+                    hs = sidx;
+                } else if (sm.hot_tag[sidx] == kFinEmpty) {
+                    int seen = 0;
+                    for (int j = 0; j < nb; j++)
+                        if (sm.rid[j] >= 0) seen += (sm.sid[j] == id) + (sm.did[j] == id);
+                    if (seen > 1) {
+                        const long long old = (long long)atomicCAS((unsigned long long*)&sm.hot_tag[sidx], (unsigned long long)kFinEmpty, (unsigned long long)id);
+                        if (old == kFinEmpty || old == id) hs = sidx;
+                    }
+                }
+            }
+            sm.hot_slot[side][k] = hs;
+        }
+        __syncthreads();
         for (int k = warp; k < nb; k += kFinWarps) {
             // one edge, both corruption sides at once: side 0 applies the relation to the source and compares with the
             // destination, side 1 the inverse relation to the destination and compares with the source, so each endpoint
@@ -320,8 +350,10 @@ __global__ void __launch_bounds__(kFinWarps * 32) lp_finish_kernel(LpKernelArgs 
                     slot_r[s] = sm.slot[s][k];
                 }
             }
-            float* gsrc = d.node_grad + sid * D;
-            float* gdst = d.node_grad + did * D;
+            // generic pointers: a shared-memory row for a hub, the global gradient row otherwise (the atomics below take either)
+            const int hs_s = sm.hot_slot[0][k], hs_d = sm.hot_slot[1][k];
+            float* gsrc = hs_s >= 0 ? sm.hot[hs_s] : d.node_grad + sid * D;
+            float* gdst = hs_d >= 0 ? sm.hot[hs_d] : d.node_grad + did * D;
             for (int c = lane; c < n_el; c += 32) {
                 // components 0 / 1 of coordinate c: (real, imaginary) for ComplEx, otherwise only component 0 is used
                 const int c2 = c + off2;
@@ -380,8 +412,17 @@ __global__ void __launch_bounds__(kFinWarps * 32) lp_finish_kernel(LpKernelArgs 
         __syncthreads();  // the batch's scalars are overwritten by the next batch
     }
     if (!negs_done) scatter_negatives();
-    if (!d.has_relations) return;
     __syncthreads();
+    for (int slot = warp; slot < kFinHotSlots; slot += kFinWarps) {  // hub rows: one pass over global memory per CTA
+        const long long id = sm.hot_tag[slot];
+        if (id == kFinEmpty) continue;
+        float* grow = d.node_grad + id * D;
+        for (int k = lane; k < D; k += 32) {
+            const float v = sm.hot[slot][k];
+            if (v != 0.f) atomicAdd(grow + k, v);
+        }
+    }
+    if (!d.has_relations) return;
     // flush: warp w writes slots w, w + 8, ...
     for (int slot = warp; slot < kFinSlots; slot += kFinWarps) {
         const long long key = sm.tag[slot];

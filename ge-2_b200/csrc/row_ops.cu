@@ -174,7 +174,7 @@ __global__ void __launch_bounds__(256) dense_adagrad_kernel(float* __restrict__ 
 
 // ---- dense Adagrad fused with the relation-gradient all-reduce over peer memory -------------------------------------
 // Every rank keeps its relation gradients in a buffer its peers can read: two halves used by alternate steps, then one
-// 8-byte arrival flag per rank, then one 8-byte verdict word.  Two launches per rank and step:
+// 8-byte arrival flag per rank, one 8-byte verdict word and one 8-byte wait-time counter.  Two launches per rank and step:
 //   peer_arrive_kernel (one warp): announce "my gradients of step t are complete" by writing t + 1 into my slot of every
 //     peer's flag row, then wait -- lane p polls peer p, bounded by a time budget -- until every peer has announced the
 //     same, and publish ONE verdict for the step in this rank's verdict word (t + 1 = go, 0 = a peer never arrived);
@@ -209,6 +209,7 @@ __global__ void __launch_bounds__(32) peer_arrive_kernel(PeerBuffers peers, int 
     const int64_t flags_off = 2 * numel;  // in floats; numel is even, so the flags are 8-byte aligned
     const int lane = threadIdx.x;
     int ok = 1;
+    const unsigned long long t_enter = global_timer_ns();
     if (lane < world) {
         st_release_sys_u64(reinterpret_cast<unsigned long long*>(peers.buf[lane] + flags_off) + rank, epoch);
         const unsigned long long* mine = reinterpret_cast<const unsigned long long*>(peers.buf[rank] + flags_off) + lane;
@@ -225,9 +226,11 @@ __global__ void __launch_bounds__(32) peer_arrive_kernel(PeerBuffers peers, int 
         }
     }
     const bool all_ok = __all_sync(0xffffffffu, ok);
+    const unsigned waited = __reduce_max_sync(0xffffffffu, lane < world ? (unsigned)min(global_timer_ns() - t_enter, 0xffffffffull) : 0u);
     if (lane == 0) {
         unsigned long long* verdict = reinterpret_cast<unsigned long long*>(peers.buf[rank] + flags_off) + world;
         *verdict = all_ok ? epoch : 0ull;
+        verdict[1] += waited;  // diagnostic: nanoseconds this rank has spent in this kernel waiting for the slowest rank
         if (!all_ok) or_status(status, GE2_STATUS_PEER_TIMEOUT);
     }
 }

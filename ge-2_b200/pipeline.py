@@ -80,7 +80,7 @@ class PeerGradients:
     and the dense optimizer step then take one launch per rank (ge2_dense_adagrad_peers) instead of a collective call
     between two halves of the step, and the whole multi-GPU step fits in one CUDA graph.  Replaces Model::all_reduce of
     the reference (model.cpp:174-204).  Layout of each rank's buffer: two halves of `numel` floats (the step whose counter
-    is t accumulates into half t & 1), then one 8-byte flag per rank.
+    is t accumulates into half t & 1), then one 8-byte flag per rank, the verdict word and the wait-time counter.
 
     The buffers are torch symmetric memory: every rank's allocation is mapped into this process's address space with
     access granted to this rank's GPU, which is what a kernel needs to load from it.  (A legacy CUDA IPC import of a
@@ -107,6 +107,10 @@ class PeerGradients:
 
     def half(self, parity: int):
         return self.buf[parity * self.numel:(parity + 1) * self.numel]
+
+    def waited_ns(self) -> int:
+        """nanoseconds this rank's announcing kernels have spent waiting for the slowest rank so far (synchronises)"""
+        return int(self.buf[2 * self.numel:2 * self.numel + 2 * self.world + 4].view(torch.int64)[self.world + 1].item())
 
 
 class BatchPipeline:

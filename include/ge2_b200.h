@@ -208,7 +208,8 @@ GE2_API int ge2_dense_adagrad(float *param, float *sum_state, float *grad, int64
  * the sum over ranks is read straight from the peers' gradient buffers over NVLink instead of going through a collective
  * call.  peer_bufs[r] (host array of `world` device pointers) is this process's mapping of rank r's buffer, own rank
  * included; every buffer holds 2 * numel floats (two halves, used by alternate steps: the step whose counter *step_dev is
- * t accumulates its gradients into half t & 1) followed by `world` 8-byte arrival flags and one 8-byte verdict word, all
+ * t accumulates its gradients into half t & 1) followed by `world` 8-byte arrival flags, one 8-byte verdict word and one 8-byte counter (the nanoseconds the
+ * announcing kernel has spent waiting for the slowest rank, summed over the steps: a diagnostic), all
  * zero at start; numel must be even.  Two launches: a one-warp kernel announces step t to every peer, waits for all
  * peers' announcements -- at most wait_budget_us microseconds (0 = 4 s) -- and writes one verdict for the step; the update
  * kernel then either applies Adagrad to param / sum_state with g = grad_scale * sum over ranks and clears half (t + 1) & 1

@@ -145,11 +145,11 @@ def test_sample_negatives_structure(capi, cuda_device, want_src):
 
 def _peer_buffers(world, numel, device, rng):
     """`world` gradient buffers on ONE device laid out as ge2_dense_adagrad_peers expects (two halves, `world` 8-byte arrival
-    flags, one 8-byte verdict word); half 0 holds random gradients, half 1 a sentinel the step has to clear."""
+    flags, one 8-byte verdict word, one 8-byte wait-time counter); half 0 holds random gradients, half 1 a sentinel the step has to clear."""
     bufs, grads = [], []
     for _ in range(world):
         g = (0.1 * rng.standard_normal(numel)).astype(np.float32)
-        b = torch.zeros(2 * numel + 2 * world + 2, dtype=torch.float32, device=device)
+        b = torch.zeros(2 * numel + 2 * world + 4, dtype=torch.float32, device=device)
         b[:numel] = torch.from_numpy(g).to(device)
         b[numel:2 * numel] = 7.0
         bufs.append(b)
@@ -207,7 +207,9 @@ def test_peer_wait_runs_out_and_leaves_everything_untouched(capi, cuda_device):
     assert int(status) & 32
     assert np.array_equal(t_p.cpu().numpy(), p) and np.array_equal(t_s.cpu().numpy(), s)
     assert torch.equal(bufs[0][:2 * numel], before)
-    assert bufs[0][2 * numel:].view(torch.int64).cpu().tolist()[world] == 0  # verdict: no go
+    words = bufs[0][2 * numel:].view(torch.int64).cpu().tolist()
+    assert words[world] == 0              # verdict: no go
+    assert words[world + 1] >= 5_000_000  # the wait-time counter saw the whole budget go by
     # the context is still usable and a later, complete step goes through
     status.zero_()
     _set_arrival(bufs[0], numel, world, 1, 1)
