@@ -23,6 +23,7 @@ EXPORTS = [
     "ge2_index_add", "ge2_adagrad_scatter", "ge2_dense_adagrad", "ge2_sample_negatives", "ge2_remap_edges_to_slots",
     "ge2_copy_slabs", "ge2_unique_bitmap_static", "ge2_sample_batch", "ge2_advance_step", "ge2_dense_adagrad_peers",
     "ge2_enable_peer_access", "ge2_build_state_edges", "ge2_swap_begin", "ge2_swap_wait", "ge2_sample_batch_dev",
+    "ge2_eval_workspace_bytes", "ge2_eval_ranks",
 ]
 
 
@@ -43,6 +44,19 @@ class LpDesc(C.Structure):
         ("rel", C.c_void_p), ("inv_rel", C.c_void_p),
         ("node_grad", C.c_void_p), ("rel_grad", C.c_void_p), ("inv_rel_grad", C.c_void_p), ("loss", C.c_void_p),
         ("pos_scores", C.c_void_p), ("neg_scores", C.c_void_p), ("inv_pos_scores", C.c_void_p), ("inv_neg_scores", C.c_void_p),
+        ("status", C.c_void_p), ("workspace", C.c_void_p), ("workspace_bytes", C.c_size_t),
+    ]
+
+
+class EvalDesc(C.Structure):
+    _fields_ = [
+        ("decoder", C.c_int32), ("has_relations", C.c_int32), ("use_inverse", C.c_int32), ("D", C.c_int32),
+        ("B", C.c_int64), ("num_nodes", C.c_int64), ("R", C.c_int64),
+        ("node_emb", C.c_void_p), ("emb_stride", C.c_int64),
+        ("src_ids", C.c_void_p), ("rel_ids", C.c_void_p), ("dst_ids", C.c_void_p), ("edge_stride", C.c_int64), ("rel_stride", C.c_int64),
+        ("rel", C.c_void_p), ("inv_rel", C.c_void_p), ("neg_ids", C.c_void_p), ("num_negs", C.c_int64),
+        ("dst_filter", C.c_void_p), ("dst_filter_n", C.c_int64), ("src_filter", C.c_void_p), ("src_filter_n", C.c_int64),
+        ("dst_ranks", C.c_void_p), ("src_ranks", C.c_void_p), ("pos_scores", C.c_void_p), ("inv_pos_scores", C.c_void_p),
         ("status", C.c_void_p), ("workspace", C.c_void_p), ("workspace_bytes", C.c_size_t),
     ]
 
@@ -307,6 +321,41 @@ def swap_begin(world: int, rank: int, flag_row_ptrs, epoch: int, pulls, slab_byt
     d.num_pulls, d.pull_src, d.pull_dst = n, C.cast(src, C.POINTER(C.c_void_p)), C.cast(dst, C.POINTER(C.c_void_p))
     d.slab_bytes, d.status = slab_bytes, ptr(status)
     check(load_library().ge2_swap_begin(C.byref(d), cur_stream() if stream is None else stream), "ge2_swap_begin")
+
+
+def eval_ranks(decoder, node_emb, edges, rel=None, inv_rel=None, dst_filter=None, src_filter=None, neg_ids=None, status=None):
+    """Ranks of edges[B, 2|3] (rows of node_emb) against every node (or the rows neg_ids lists): (dst_ranks, src_ranks or None).
+    Filter pairs are [F, 2] int64 (edge row, candidate column)."""
+    import torch
+
+    lib = load_library()
+    lib.ge2_eval_workspace_bytes.restype = C.c_size_t
+    lib.ge2_eval_workspace_bytes.argtypes = [C.POINTER(EvalDesc)]
+    lib.ge2_eval_ranks.argtypes = [C.POINTER(EvalDesc), C.c_void_p]
+    B, cols = edges.shape
+    dev = node_emb.device
+    d = EvalDesc()
+    d.decoder = {"DISTMULT": 0, "DOT": 0, "COMPLEX": 1}[decoder]
+    d.has_relations = int(cols == 3 and rel is not None)
+    d.use_inverse = int(d.has_relations and inv_rel is not None)
+    d.D, d.B, d.num_nodes = node_emb.shape[1], B, node_emb.shape[0]
+    d.R = rel.shape[0] if rel is not None else 0
+    d.node_emb, d.emb_stride = ptr(node_emb), node_emb.stride(0)
+    d.src_ids, d.dst_ids = ptr(edges), edges.data_ptr() + 8 * (cols - 1)
+    d.rel_ids = edges.data_ptr() + 8 if d.has_relations else None
+    d.edge_stride = d.rel_stride = cols
+    d.rel, d.inv_rel = ptr(rel), ptr(inv_rel) if d.use_inverse else None
+    d.neg_ids, d.num_negs = ptr(neg_ids), (neg_ids.numel() if neg_ids is not None else 0)
+    d.dst_filter, d.dst_filter_n = ptr(dst_filter), (dst_filter.shape[0] if dst_filter is not None else 0)
+    d.src_filter, d.src_filter_n = ptr(src_filter), (src_filter.shape[0] if src_filter is not None else 0)
+    dst_ranks = torch.zeros(B, dtype=torch.int64, device=dev)
+    src_ranks = torch.zeros(B, dtype=torch.int64, device=dev) if d.use_inverse else None
+    d.dst_ranks, d.src_ranks = ptr(dst_ranks), ptr(src_ranks)
+    d.status = ptr(status)
+    ws = torch.empty(int(lib.ge2_eval_workspace_bytes(C.byref(d))), dtype=torch.uint8, device=dev)
+    d.workspace, d.workspace_bytes = ws.data_ptr(), ws.numel()
+    check(lib.ge2_eval_ranks(C.byref(d), cur_stream()), "ge2_eval_ranks")
+    return dst_ranks, src_ranks
 
 
 def swap_wait(swap_stream: int, compute_stream: int):

@@ -320,6 +320,48 @@ GE2_API int ge2_swap_wait(ge2_stream_t swap_stream, ge2_stream_t compute_stream)
 GE2_API int ge2_copy_slabs(const float *src, float *dst, const int32_t *moves_host, int32_t num_moves, int64_t slab_floats,
                    ge2_stream_t stream);
 
+/* =====================================================================================================
+ * Link-prediction evaluation: ranks of a batch of test edges against candidate nodes, both corruption sides.
+ * Reference: node_corrupt_forward (cpp/src/nn/decoders/edge/decoder_methods.cpp:597-659) -> apply_score_filter
+ * (cpp/src/data/samplers/negative.cpp:570-575; filter pairs from compute_filter_corruption, :421-568) ->
+ * LinkPredictionReporter::computeRanks (cpp/src/reporting/reporting.cpp:52-54): rank = #(negative score >= positive score) + 1,
+ * a filtered score counting as -1e9.  Candidates are all rows [0, num_nodes) of node_emb (the filtered evaluation of the
+ * reference: one chunk with every node, negative.cpp:585-589) or, with neg_ids != NULL, the num_negs rows it lists (one shared
+ * chunk); filter pairs are (edge row, candidate column), duplicates allowed.  Edge ids are rows of node_emb.  fp32 throughout;
+ * every score is the chain acc = fma(q[d], e[d], acc) with d ascending.  The [B, candidates] score matrix is never stored.
+ * src_ranks / src_filter are used when has_relations && use_inverse (the inverse relation applied to the destination,
+ * compared with candidate sources).  A row with an id out of range sets GE2_STATUS_BAD_INDEX and gets rank 0.
+ * ===================================================================================================== */
+typedef struct ge2_eval_desc {
+    int32_t decoder;       /* GE2_DECODER_* */
+    int32_t has_relations;
+    int32_t use_inverse;
+    int32_t D;             /* <= 128 */
+    int64_t B;             /* test edges */
+    int64_t num_nodes;     /* rows of node_emb */
+    int64_t R;
+    const float *node_emb; /* [num_nodes, D], row stride emb_stride floats */
+    int64_t emb_stride;
+    const int64_t *src_ids, *rel_ids, *dst_ids; /* element i at ptr[i * edge_stride] (rel_ids: i * rel_stride) */
+    int64_t edge_stride, rel_stride;
+    const float *rel, *inv_rel;                 /* [R, D] */
+    const int64_t *neg_ids;                     /* NULL: every node is a candidate; else [num_negs] rows of node_emb */
+    int64_t num_negs;
+    const int64_t *dst_filter; /* [F, 2] (edge row, candidate column) */
+    int64_t dst_filter_n;
+    const int64_t *src_filter;
+    int64_t src_filter_n;
+    int64_t *dst_ranks;    /* [B] out */
+    int64_t *src_ranks;    /* [B] out (two-sided evaluation) */
+    float *pos_scores;     /* [B] out, optional */
+    float *inv_pos_scores; /* [B] out, optional */
+    int32_t *status;       /* device int32, GE2_STATUS_* bits OR-ed in; may be NULL */
+    void *workspace;       /* 256-byte aligned, ge2_eval_workspace_bytes(desc) bytes */
+    size_t workspace_bytes;
+} ge2_eval_desc;
+GE2_API size_t ge2_eval_workspace_bytes(const ge2_eval_desc *desc);
+GE2_API int ge2_eval_ranks(const ge2_eval_desc *desc, ge2_stream_t stream);
+
 #ifdef __cplusplus
 }
 #endif

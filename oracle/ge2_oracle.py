@@ -420,6 +420,70 @@ def mrr(ranks: np.ndarray) -> float:
     return float((np.float32(1.0) / ranks.astype(np.float32)).mean())
 
 
+def _fma_chain_scores(q: np.ndarray, e: np.ndarray) -> np.ndarray:
+    """scores[i, n] = the float32 chain acc = fma(q[i, d], e[n, d], acc), d ascending.  Emulated through float64: the product
+    of two float32 values is exact there, and rounding the float64 sum to float32 differs from a fused multiply-add only
+    when that sum sits within 2^-29 of a float32 midpoint."""
+    acc = np.zeros((q.shape[0], e.shape[0]), np.float32)
+    q64, e64 = q.astype(np.float64), e.astype(np.float64)
+    for d in range(q.shape[1]):
+        acc = (acc.astype(np.float64) + q64[:, d, None] * e64[None, :, d]).astype(np.float32)
+    return acc
+
+
+def _fma_chain_rows(q: np.ndarray, e: np.ndarray) -> np.ndarray:
+    acc = np.zeros(q.shape[0], np.float32)
+    q64, e64 = q.astype(np.float64), e.astype(np.float64)
+    for d in range(q.shape[1]):
+        acc = (acc.astype(np.float64) + q64[:, d] * e64[:, d]).astype(np.float32)
+    return acc
+
+
+def eval_ranks(kind, table, rel, inv_rel, edges, dst_filter=None, src_filter=None, neg_ids=None):
+    """Filtered link-prediction ranks of `edges` (global ids) against all nodes or the rows `neg_ids` lists.
+    node_corrupt_forward (cpp/src/nn/decoders/edge/decoder_methods.cpp:597-659) -> apply_score_filter
+    (cpp/src/data/samplers/negative.cpp:570-575: filtered scores become -1e9) -> computeRanks
+    (cpp/src/reporting/reporting.cpp:52-54).  The reference contracts through its BLAS (order unspecified); here every score
+    is a float32 chain in ascending column order, which is what the device kernel evaluates.
+    Returns (dst_ranks, src_ranks or None)."""
+    has_rel = edges.shape[1] == 3 and rel is not None
+    src, dst = table[edges[:, 0]], table[edges[:, -1]]
+    cand = table if neg_ids is None else table[neg_ids]
+    out = []
+    for side, filt in ((0, dst_filter), (1, src_filter)):
+        if side == 1 and not (has_rel and inv_rel is not None):
+            out.append(None)
+            continue
+        a, b = (src, dst) if side == 0 else (dst, src)
+        r = (rel if side == 0 else inv_rel)[edges[:, 1]] if has_rel else None
+        q = _apply_relation(kind, a, r).astype(np.float32)
+        pos = _fma_chain_rows(q, b)
+        neg = _fma_chain_scores(q, cand)
+        if filt is not None and len(filt):
+            neg[filt[:, 0], filt[:, 1]] = np.float32(-1e9)
+        out.append(ranks_from_scores(pos, neg).astype(np.int64))
+    return out[0], out[1]
+
+
+def global_filter(all_edges: np.ndarray, edges: np.ndarray, inverse: bool) -> np.ndarray:
+    """compute_filter_corruption with global = true (cpp/src/data/samplers/negative.cpp:421-568): for evaluation edge i all
+    (i, n) such that replacing its destination (inverse: its source) by n gives an edge of `all_edges` (same relation when the
+    edges carry one).  Rows in the reference's order: by edge, neighbours in the order of the sorted edge list."""
+    has_rel = edges.shape[1] == 3
+    keep, corrupt = (edges.shape[1] - 1, 0) if inverse else (0, edges.shape[1] - 1)
+    order = np.argsort(all_edges[:, keep], kind="stable")
+    sorted_edges = all_edges[order]
+    starts = np.searchsorted(sorted_edges[:, keep], edges[:, keep], side="left")
+    ends = np.searchsorted(sorted_edges[:, keep], edges[:, keep], side="right")
+    rows = []
+    for i in range(len(edges)):
+        nb = sorted_edges[starts[i]:ends[i]]
+        if has_rel:
+            nb = nb[nb[:, 1] == edges[i, 1]]
+        rows.append(np.stack([np.full(len(nb), i, np.int64), nb[:, corrupt].astype(np.int64)], 1))
+    return np.concatenate(rows) if rows else np.zeros((0, 2), np.int64)
+
+
 # --------------------------------------------------------------------------------------------------
 # one full reference training step on global tables (the shape bench.py's CPU "port" leg times)
 # --------------------------------------------------------------------------------------------------
