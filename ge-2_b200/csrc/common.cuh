@@ -52,6 +52,37 @@ inline int stream_grid(int64_t work, int per_cta, int ctas_per_sm = 8) {
     return (int)(need < cap ? need : cap);
 }
 
+// Programmatic dependent launch: a kernel launched with launch_after() may start while the kernel before it on the stream is
+// still running (its CTAs become resident as SMs free up, and its prologue -- shared-memory set-up, barrier initialisation,
+// tensor-memory allocation -- overlaps the predecessor's tail).  griddep_wait() returns once the predecessor grid has completed
+// and its memory is visible; every thread calls it before its first access to global memory.  Without the launch attribute
+// (or with a predecessor that is not a kernel) it returns at once.
+__device__ __forceinline__ void griddep_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+
+// GE2_PDL=0 in the environment turns the attribute off (plain stream order)
+inline bool pdl_enabled() {
+    static const bool on = [] {
+        const char* e = getenv("GE2_PDL");
+        return e == nullptr || atoi(e) != 0;
+    }();
+    return on;
+}
+
+template <typename... KArgs, typename... Args>
+inline cudaError_t launch_after(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream, Args&&... args) {
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = grid;
+    cfg.blockDim = block;
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = pdl_enabled() ? 1 : 0;
+    return cudaLaunchKernelEx(&cfg, kernel, static_cast<KArgs>(args)...);
+}
+
 __device__ __forceinline__ void or_status(int32_t* status, int32_t bit) {
     if (status != nullptr) atomicOr(status, bit);
 }

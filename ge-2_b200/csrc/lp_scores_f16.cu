@@ -292,6 +292,7 @@ __global__ void __launch_bounds__(kThreads, 1)
         mbar_init_fence();
         prefetch_tensormap(&tmQ);
         prefetch_tensormap(&tmK);
+        griddep_wait();  // the operands come from the kernel before this one
         // early loads: the first two tiles, and only while no wait can depend on another role (first block)
         while (tma_it < n_iter && tma_it < 2 && (tma_it == 0 || tma_un.tile != 0)) {
             produce(tma_it);
@@ -305,6 +306,7 @@ __global__ void __launch_bounds__(kThreads, 1)
     tc_fence_before();
     __syncthreads();
     tc_fence_after();
+    griddep_wait();  // set-up done; from here on global memory written by the preceding kernel is read and its buffers rewritten
     const uint32_t tmem = *s_tmem;
     const uint32_t lane_sel = (uint32_t)((warp & 3) * 32) << 16;  // this warp's quarter of the 128 tensor-memory lanes
 
@@ -646,6 +648,7 @@ __global__ void __launch_bounds__(kThreads, 1)
         mbar_init_fence();
         prefetch_tensormap(&tmQ);
         prefetch_tensormap(&tmK);
+        griddep_wait();  // the operands come from the kernel before this one
         // early loads: the first two tiles, and only while no wait can depend on another role (first block)
         while (tma_it < n_iter && tma_it < 2 && (tma_it == 0 || tma_un.tile != 0)) {
             produce(tma_it);
@@ -659,6 +662,7 @@ __global__ void __launch_bounds__(kThreads, 1)
     tc_fence_before();
     __syncthreads();
     tc_fence_after();
+    griddep_wait();  // set-up done; from here on global memory written by the preceding kernel is read and its buffers rewritten
     const uint32_t tmem = *s_tmem;
     // tensor memory: two score accumulators at 0 and 128 (one per softmax group), dQ at 256 (accumulated over the block's
     // whole stream), dK of the current tile at 384
@@ -1072,12 +1076,11 @@ int launch(const LpKernelArgs& a, cudaStream_t stream) {
     GE2_CUDA_TRY(cudaFuncSetAttribute(lp_grad_kernel<DP>, cudaFuncAttributeMaxDynamicSharedMemorySize, Layout<DP>::kDynamicB));
     const int only = env_int("GE2_F16_ONLY", 0);  // development switch: 1 = logsumexp pass alone, 2 = gradient pass alone (on a workspace a full step left behind)
     if (only != 2) {
-        lp_lse_kernel<DP><<<(unsigned)sc.gridA, kThreads, Layout<DP>::kDynamicA, stream>>>(tmQ, tmK, a, sc);
-        GE2_LAUNCH_CHECK();
+        GE2_CUDA_TRY(launch_after(lp_lse_kernel<DP>, dim3((unsigned)sc.gridA), dim3(kThreads), Layout<DP>::kDynamicA, stream, tmQ, tmK, a, sc));
     }
     if (only != 1) {
-        lp_grad_kernel<DP><<<(unsigned)sc.gridB, kThreads, Layout<DP>::kDynamicB, stream>>>(tmQ, tmK, tmDK, tmDKt, tmDQ, tmDQt, a, sc);
-        GE2_LAUNCH_CHECK();
+        GE2_CUDA_TRY(launch_after(lp_grad_kernel<DP>, dim3((unsigned)sc.gridB), dim3(kThreads), Layout<DP>::kDynamicB, stream, tmQ, tmK, tmDK, tmDKt, tmDQ,
+                                  tmDQt, a, sc));
     }
     return GE2_OK;
 }

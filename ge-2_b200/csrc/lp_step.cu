@@ -95,6 +95,7 @@ __global__ void __launch_bounds__(256) lp_prep_kernel(LpKernelArgs a) {
     const bool vec_e = (d.emb_stride % 4 == 0) && (((uintptr_t)d.node_emb) & 15) == 0 && D % 4 == 0;
     const bool vec_r = D % 4 == 0 && ((((uintptr_t)d.rel) | ((uintptr_t)d.inv_rel)) & 15) == 0;
     const bool write_k32 = d.precision != GE2_PRECISION_F16;  // the tensor path reads only the fp16 copy of the negatives
+    griddep_wait();
     if (blockIdx.x == 0 && tid == 0) *L.loss_acc = 0.0;        // the scores kernel of this step adds every row's loss term to it
     if (blockIdx.x == 0 && L.item_ctr != nullptr)               // arrival counters of the tensor path's logsumexp pass start at zero
         for (int k = tid; k < L.n_items + 2; k += blockDim.x) L.item_ctr[k] = 0;
@@ -224,14 +225,15 @@ __global__ void __launch_bounds__(kFinWarps * 32) lp_finish_kernel(LpKernelArgs 
     const bool vec_g = (D % 4 == 0) && (((uintptr_t)d.node_grad) & 15) == 0;
     const float gs = L.grad_unscale;  // the tensor path leaves dQ / dK scaled by a power of two
 
-    // loss = sum over sides and padded rows of (lse - pos), accumulated in double by the scores kernel that ran before
-    if (blockIdx.x == 0 && tid == 0) *d.loss = (float)*L.loss_acc;
     if (d.has_relations) {
         for (int k = tid; k < kFinSlots * 128; k += kFinWarps * 32) (&sm.acc[0][0])[k] = 0.f;
         if (tid < kFinSlots) sm.tag[tid] = kFinEmpty;
     }
     for (int k = tid; k < kFinHotSlots * 128; k += kFinWarps * 32) (&sm.hot[0][0])[k] = 0.f;
     if (tid < kFinHotSlots) sm.hot_tag[tid] = kFinEmpty;
+    griddep_wait();  // the shared-memory set-up above overlaps the tail of the scores kernel
+    // loss = sum over sides and padded rows of (lse - pos), accumulated in double by the scores kernel that ran before
+    if (blockIdx.x == 0 && tid == 0) *d.loss = (float)*L.loss_acc;
     __syncthreads();
 
     // Every CTA takes a contiguous share of the edges (heavy rows: six input rows, four output rows each) and a contiguous
@@ -517,8 +519,7 @@ extern "C" int ge2_lp_step(const ge2_lp_desc* desc, ge2_stream_t stream_) {
     }
 
     const int64_t prep_rows = (int64_t)L.S * L.Bp + (int64_t)L.S * L.CN;
-    lp_prep_kernel<<<stream_grid(prep_rows, 32, 8), 256, 0, stream>>>(a);
-    GE2_LAUNCH_CHECK();
+    GE2_CUDA_TRY(launch_after(lp_prep_kernel, dim3((unsigned)stream_grid(prep_rows, 32, 8)), dim3(256), 0, stream, a));
     }
 
     if (phases & 2) {
@@ -533,8 +534,7 @@ extern "C" int ge2_lp_step(const ge2_lp_desc* desc, ge2_stream_t stream_) {
     int fin_ctas = (int)std::min<int64_t>((int64_t)kNumSMs * 4, ceil_div<int64_t>(fin_rows, 8));
     if (fin_ctas < 1) fin_ctas = 1;
     const int edges_per_cta = (int)ceil_div<int64_t>(desc->B, fin_ctas), negs_per_cta = (int)ceil_div<int64_t>(neg_rows, fin_ctas);
-    lp_finish_kernel<<<(unsigned)fin_ctas, 256, 0, stream>>>(a, edges_per_cta, negs_per_cta);
-    GE2_LAUNCH_CHECK();
+    GE2_CUDA_TRY(launch_after(lp_finish_kernel, dim3((unsigned)fin_ctas), dim3(256), 0, stream, a, edges_per_cta, negs_per_cta));
     if (desc->pos_scores != nullptr || desc->inv_pos_scores != nullptr) {
         copy_pos_kernel<<<ceil_div(L.Bp, 256), 256, 0, stream>>>(L.pos, L.Bp, desc->pos_scores, desc->inv_pos_scores, L.S);
         GE2_LAUNCH_CHECK();

@@ -127,6 +127,7 @@ __global__ void __launch_bounds__(256) adagrad_scatter_kernel(float* __restrict_
                                                               float* __restrict__ node_grad, int vec_per_row, float neg_lr, int clear_grad,
                                                               int32_t* status) {
     using VT = typename Vec<V>::type;
+    griddep_wait();  // the gradient rows come from the kernel before this one
     const int64_t total = live_rows(U, U_dev) * vec_per_row;
     const int64_t stride = (int64_t)gridDim.x * blockDim.x;
     for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += stride) {
@@ -428,10 +429,10 @@ extern "C" int ge2_adagrad_scatter(float* table, float* state, int64_t table_row
     cudaStream_t stream = as_stream(stream_);
     const int V = vec_width(D, table, state, node_grad);
     const int grid = stream_grid(U * (D / V), 256);
-    if (V == 4) adagrad_scatter_kernel<4><<<grid, 256, 0, stream>>>(table, state, table_rows, unique_ids, U, U_dev, node_grad, D / 4, -lr, clear_grad, status);
-    else if (V == 2) adagrad_scatter_kernel<2><<<grid, 256, 0, stream>>>(table, state, table_rows, unique_ids, U, U_dev, node_grad, D / 2, -lr, clear_grad, status);
-    else adagrad_scatter_kernel<1><<<grid, 256, 0, stream>>>(table, state, table_rows, unique_ids, U, U_dev, node_grad, D, -lr, clear_grad, status);
-    GE2_LAUNCH_CHECK();
+    const dim3 g((unsigned)grid), b(256);
+    if (V == 4) GE2_CUDA_TRY(launch_after(adagrad_scatter_kernel<4>, g, b, 0, stream, table, state, table_rows, unique_ids, U, U_dev, node_grad, D / 4, -lr, clear_grad, status));
+    else if (V == 2) GE2_CUDA_TRY(launch_after(adagrad_scatter_kernel<2>, g, b, 0, stream, table, state, table_rows, unique_ids, U, U_dev, node_grad, D / 2, -lr, clear_grad, status));
+    else GE2_CUDA_TRY(launch_after(adagrad_scatter_kernel<1>, g, b, 0, stream, table, state, table_rows, unique_ids, U, U_dev, node_grad, D, -lr, clear_grad, status));
     return GE2_OK;
 }
 
