@@ -23,6 +23,7 @@ PYBIND11_MODULE(ge2_host, m) {
         .def_readwrite("edges", &Batch::edges_)
         .def_readwrite("src_neg_filter", &Batch::src_neg_filter_)
         .def_readwrite("dst_neg_filter", &Batch::dst_neg_filter_)
+        .def_readwrite("deg_sample_rows", &Batch::deg_sample_rows_)
         .def_readwrite("loss", &Batch::loss_)
         .def("accumulateGradients", &Batch::accumulateGradients)
         .def("clear", &Batch::clear);
@@ -35,12 +36,42 @@ PYBIND11_MODULE(ge2_host, m) {
         .def("step", &Model::step)
         .def("clear_grad", &Model::clear_grad)
         .def("step_after_all_reduce", &Model::step_after_all_reduce)
-        .def_readwrite("relations", &Model::relations_)
-        .def_readwrite("inverse_relations", &Model::inverse_relations_)
-        .def_readwrite("relations_grad", &Model::relations_grad_)
-        .def_readwrite("inverse_relations_grad", &Model::inverse_relations_grad_)
-        .def_readwrite("relations_state", &Model::relations_state_)
-        .def_readwrite("inverse_relations_state", &Model::inverse_relations_state_);
+        .def("broadcast", &Model::broadcast)
+        .def("all_reduce", &Model::all_reduce)
+        .def("check_status", &Model::check_status)
+        .def_readonly("device_models", &Model::device_models_)
+        // the tables are views of one allocation (both tables back to back): assignment copies into them
+        .def_property("relations", [](Model& m) { return m.relations_; }, [](Model& m, torch::Tensor v) { m.relations_.copy_(v); })
+        .def_property("inverse_relations", [](Model& m) { return m.inverse_relations_; }, [](Model& m, torch::Tensor v) { m.inverse_relations_.copy_(v); })
+        .def_property("relations_state", [](Model& m) { return m.relations_state_; }, [](Model& m, torch::Tensor v) { m.relations_state_.copy_(v); })
+        .def_property("inverse_relations_state", [](Model& m) { return m.inverse_relations_state_; },
+                      [](Model& m, torch::Tensor v) { m.inverse_relations_state_.copy_(v); })
+        .def_readonly("relations_grad", &Model::relations_grad_)
+        .def_readonly("inverse_relations_grad", &Model::inverse_relations_grad_);
+    py::class_<MemPartitionBufferStorage, std::shared_ptr<MemPartitionBufferStorage>>(m, "MemPartitionBufferStorage")
+        .def(py::init<int64_t, int64_t, int32_t, std::vector<torch::Device>>(), py::arg("dim0_size"), py::arg("dim1_size"), py::arg("num_partitions"),
+             py::arg("devices"))
+        .def("load", &MemPartitionBufferStorage::load)
+        .def("unload", &MemPartitionBufferStorage::unload)
+        .def("setBufferOrdering", &MemPartitionBufferStorage::setBufferOrdering)
+        .def("hasSwap", &MemPartitionBufferStorage::hasSwap, py::arg("device_idx") = 0)
+        .def("performNextSwap", &MemPartitionBufferStorage::performNextSwap)
+        .def("getNextAdmit", &MemPartitionBufferStorage::getNextAdmit, py::arg("device_idx") = 0)
+        .def("getNextEvict", &MemPartitionBufferStorage::getNextEvict, py::arg("device_idx") = 0)
+        .def("getPartitionToBufferSlotMap", &MemPartitionBufferStorage::getPartitionToBufferSlotMap, py::arg("device_idx") = 0)
+        .def("indexRead", &MemPartitionBufferStorage::indexRead)
+        .def("indexAdd", &MemPartitionBufferStorage::indexAdd)
+        .def("activeBuffer", &MemPartitionBufferStorage::activeBuffer)
+        .def("getPartitionSize", &MemPartitionBufferStorage::getPartitionSize, py::arg("device_idx") = 0)
+        .def("getNumInMemory", &MemPartitionBufferStorage::getNumInMemory, py::arg("device_idx") = 0)
+        .def("checkStatus", &MemPartitionBufferStorage::checkStatus);
+    py::class_<DataLoader, std::shared_ptr<DataLoader>>(m, "DataLoader")
+        .def(py::init<torch::Tensor, std::shared_ptr<InMemory>, std::shared_ptr<InMemory>, int64_t, int32_t, int32_t, float, bool, uint64_t>(),
+             py::arg("edges"), py::arg("node_embeddings"), py::arg("node_embeddings_state"), py::arg("batch_size"), py::arg("num_chunks"),
+             py::arg("negatives_per_chunk"), py::arg("degree_fraction"), py::arg("inverse_edges"), py::arg("seed"))
+        .def("getBatch", &DataLoader::getBatch)
+        .def("updateEmbeddings", &DataLoader::updateEmbeddings)
+        .def_readwrite("batch_id", &DataLoader::batch_id_);
     py::class_<InMemory, std::shared_ptr<InMemory>>(m, "InMemory")
         .def(py::init<torch::Tensor>())
         .def("indexRead", &InMemory::indexRead)

@@ -2,6 +2,10 @@
 
 #include <ATen/cuda/CUDAContext.h>
 #include <c10/cuda/CUDAGuard.h>
+#include <cuda_runtime_api.h>
+
+#include <algorithm>
+#include <map>
 
 #include "ge2_b200.h"
 
@@ -124,18 +128,103 @@ Model::Model(DecoderType type, int64_t num_relations, int64_t dim, bool use_inve
         if (type == DecoderType::COMPLEX) t.narrow(1, 0, dim / 2).fill_(1);
         return t;
     };
-    relations_ = init();
-    relations_grad_ = torch::zeros_like(relations_);
-    relations_state_ = torch::zeros_like(relations_);
+    // both tables (and their states, and their gradients) back to back: one launch serves them, and the replicated form
+    // exchanges them as one buffer
+    const int64_t S = use_inverse_relations ? 2 : 1;
+    rel_both_ = torch::empty({S, num_relations, dim}, opts);
+    state_both_ = torch::zeros({S, num_relations, dim}, opts);
+    grad_buf_ = torch::zeros({S * num_relations * dim}, opts);
+    for (int64_t k = 0; k < S; k++) rel_both_[k].copy_(init());
+    relations_ = rel_both_[0];
+    relations_state_ = state_both_[0];
     if (use_inverse_relations) {
-        inverse_relations_ = init();
-        inverse_relations_grad_ = torch::zeros_like(relations_);
-        inverse_relations_state_ = torch::zeros_like(relations_);
+        inverse_relations_ = rel_both_[1];
+        inverse_relations_state_ = state_both_[1];
     }
+    point_at_half(0);
     status_ = torch::zeros({1}, opts.dtype(torch::kInt32));
 }
 
+void Model::point_at_half(int half) {
+    const int64_t S = rel_both_.size(0), numel = rel_both_.numel();
+    auto g = grad_buf_.narrow(0, half * numel, numel).view({S, rel_both_.size(1), rel_both_.size(2)});
+    relations_grad_ = g[0];
+    if (S == 2) inverse_relations_grad_ = g[1];
+}
+
+void Model::broadcast(std::vector<torch::Device> devices) {
+    if (devices.empty() || devices[0] != relations_.device()) throw GegeRuntimeException("broadcast: the first device must be this model's");
+    if (!device_models_.empty()) throw GegeRuntimeException("broadcast: already replicated");
+    const int G = (int)devices.size();
+    if (G > 16) throw GegeRuntimeException("broadcast: at most 16 devices");
+    const int64_t numel = rel_both_.numel();
+    if (numel % 2) throw GegeRuntimeException("broadcast: the relation tables must hold an even number of floats");
+    device_models_.push_back(shared_from_this());
+    for (int i = 1; i < G; i++) {
+        auto m = std::make_shared<Model>(type_, relations_.size(0), relations_.size(1), use_inverse_relations_, dense_lr_, sparse_lr_, devices[i],
+                                         precision_ == GE2_PRECISION_F16 ? "f16" : "fp32");
+        m->rel_both_.copy_(rel_both_);
+        m->state_both_.copy_(state_both_);
+        device_models_.push_back(m);
+    }
+    for (int i = 0; i < G; i++) {
+        c10::cuda::CUDAGuard guard(devices[i]);
+        for (int j = 0; j < G; j++)
+            if (j != i) check(ge2_enable_peer_access(devices[j].index()), "ge2_enable_peer_access");
+        auto& m = *device_models_[i];
+        auto opts = torch::TensorOptions().dtype(torch::kFloat32).device(devices[i]);
+        m.grad_buf_ = torch::zeros({2 * numel + 2 * G + 8}, opts);  // two halves, G flags, verdict, wait counter (8-byte words)
+        m.step_dev_ = torch::zeros({1}, opts.dtype(torch::kInt64));
+        m.replica_ = i;
+        m.round_ = 0;
+        m.point_at_half(0);
+    }
+    std::vector<float*> ptrs;
+    for (auto& m : device_models_) ptrs.push_back(m->grad_buf_.data_ptr<float>());
+    for (auto& m : device_models_) {
+        m->peer_ptrs_ = ptrs;
+        if (m.get() != this) m->device_models_ = device_models_;
+    }
+    for (auto& dv : devices) {
+        c10::cuda::CUDAGuard guard(dv);
+        check(cudaDeviceSynchronize() == cudaSuccess ? GE2_OK : GE2_ERR_CUDA, "cudaDeviceSynchronize");
+    }
+}
+
+void Model::all_reduce() {
+    if (device_models_.empty()) throw GegeRuntimeException("all_reduce: call broadcast first");
+    const int G = (int)device_models_.size();
+    const int64_t numel = rel_both_.numel();
+    for (int i = 0; i < G; i++) {
+        auto& m = *device_models_[i];
+        c10::cuda::CUDAGuard guard(m.relations_.device());
+        auto stream = current_stream(m.relations_);
+        // sum over the replicas' halves (read over peer memory), divide by G, Adagrad on both tables, clear the other half
+        check(ge2_dense_adagrad_peers(m.rel_both_.data_ptr<float>(), m.state_both_.data_ptr<float>(), m.peer_ptrs_.data(), G, i, numel,
+                                      reinterpret_cast<const uint64_t*>(m.step_dev_.data_ptr<int64_t>()), m.dense_lr_, 1e-10f, 1.0f / G, 0,
+                                      m.status_.data_ptr<int32_t>(), stream),
+              "ge2_dense_adagrad_peers");
+        check(ge2_advance_step(reinterpret_cast<uint64_t*>(m.step_dev_.data_ptr<int64_t>()), 1, stream), "ge2_advance_step");
+        m.round_ += 1;
+        m.point_at_half((int)(m.round_ & 1));
+    }
+}
+
+void Model::check_status() {
+    std::vector<std::shared_ptr<Model>> all = device_models_;
+    if (all.empty()) {
+        const int32_t word = status_.cpu().item<int32_t>();
+        if (word) throw GegeRuntimeException("device status " + std::to_string(word));
+        return;
+    }
+    for (auto& m : all) {
+        const int32_t word = m->status_.cpu().item<int32_t>();
+        if (word) throw GegeRuntimeException("device status " + std::to_string(word) + " on replica " + std::to_string(m->replica_));
+    }
+}
+
 void Model::clear_grad() {
+    if (!device_models_.empty()) return;  // replicated form: all_reduce clears the half the round after next accumulates into
     relations_grad_.zero_();
     if (inverse_relations_grad_.defined()) inverse_relations_grad_.zero_();
 }
@@ -144,14 +233,10 @@ void Model::step() { step_after_all_reduce(1.0f); }
 
 void Model::step_after_all_reduce(float grad_scale) {
     c10::cuda::CUDAGuard guard(relations_.device());
-    check(ge2_dense_adagrad(relations_.data_ptr<float>(), relations_state_.data_ptr<float>(), relations_grad_.data_ptr<float>(), relations_.numel(),
+    // relation and inverse-relation tables, states and gradients sit back to back: one launch
+    check(ge2_dense_adagrad(rel_both_.data_ptr<float>(), state_both_.data_ptr<float>(), relations_grad_.data_ptr<float>(), rel_both_.numel(),
                             dense_lr_, 1e-10f, grad_scale, 0, current_stream(relations_)),
           "ge2_dense_adagrad");
-    if (inverse_relations_.defined())
-        check(ge2_dense_adagrad(inverse_relations_.data_ptr<float>(), inverse_relations_state_.data_ptr<float>(),
-                                inverse_relations_grad_.data_ptr<float>(), inverse_relations_.numel(), dense_lr_, 1e-10f, grad_scale, 0,
-                                current_stream(relations_)),
-              "ge2_dense_adagrad");
 }
 
 void Model::train_batch(std::shared_ptr<Batch> batch, bool call_step) {
@@ -188,12 +273,17 @@ void Model::train_batch(std::shared_ptr<Batch> batch, bool call_step) {
         src_negs = batch->src_neg_indices_mapping_.contiguous();
         d.src_negs = src_negs.data_ptr<int64_t>();
     }
-    if (batch->dst_neg_filter_.defined() && batch->dst_neg_filter_.size(0) > 0) {
+    torch::Tensor deg_rows;
+    if (batch->deg_sample_rows_.defined() && batch->deg_sample_rows_.numel() > 0) {
+        deg_rows = batch->deg_sample_rows_.contiguous();
+        d.deg_sample_rows = deg_rows.data_ptr<int64_t>();
+        d.n_deg = (int32_t)deg_rows.size(1);
+    } else if (batch->dst_neg_filter_.defined() && batch->dst_neg_filter_.size(0) > 0) {
         dst_filter = batch->dst_neg_filter_.contiguous();
         d.dst_filter = dst_filter.data_ptr<int64_t>();
         d.dst_filter_n = dst_filter.size(0);
     }
-    if (d.use_inverse && batch->src_neg_filter_.defined() && batch->src_neg_filter_.size(0) > 0) {
+    if (!deg_rows.defined() && d.use_inverse && batch->src_neg_filter_.defined() && batch->src_neg_filter_.size(0) > 0) {
         src_filter = batch->src_neg_filter_.contiguous();
         d.src_filter = src_filter.data_ptr<int64_t>();
         d.src_filter_n = src_filter.size(0);
@@ -241,6 +331,261 @@ void InMemory::indexAdd(Indices indices, torch::Tensor values) {
     check(ge2_index_add(data_.data_ptr<float>(), data_.size(0), indices.data_ptr<int64_t>(), indices.size(0), nullptr, (int32_t)data_.size(1),
                         values.data_ptr<float>(), nullptr, current_stream(data_)),
           "ge2_index_add");
+}
+
+// ---------------------------------------------------------------------------------------------------------------------
+// MemPartitionBufferStorage
+// ---------------------------------------------------------------------------------------------------------------------
+namespace {
+constexpr int kCapacity = 4;  // buffer_capacity of the reference's relay (buffer.cpp:950,1106)
+}
+
+MemPartitionBufferStorage::MemPartitionBufferStorage(int64_t dim0_size, int64_t dim1_size, int32_t num_partitions, std::vector<torch::Device> devices)
+    : dim0_(dim0_size), dim1_(dim1_size), num_partitions_(num_partitions), devices_(std::move(devices)) {
+    if (devices_.empty() || devices_.size() > 16) throw GegeRuntimeException("MemPartitionBufferStorage needs 1 to 16 CUDA devices");
+    if (num_partitions <= 0 || dim0_size <= 0 || dim1_size <= 0) throw GegeRuntimeException("MemPartitionBufferStorage: bad sizes");
+    partition_size_ = (dim0_ + num_partitions_ - 1) / num_partitions_;  // ceil, storage.cpp:368
+    if ((partition_size_ * dim1_ * 4) % 16) throw GegeRuntimeException("MemPartitionBufferStorage: a slab must be a multiple of 16 bytes");
+    const int G = (int)devices_.size();
+    for (int g = 0; g < G; g++) {
+        if (!devices_[g].is_cuda()) throw GegeRuntimeException("MemPartitionBufferStorage: CUDA devices only");
+        c10::cuda::CUDAGuard guard(devices_[g]);
+        for (int j = 0; j < G; j++)
+            if (j != g) check(ge2_enable_peer_access(devices_[j].index()), "ge2_enable_peer_access");
+        auto opts = torch::TensorOptions().dtype(torch::kFloat32).device(devices_[g]);
+        const int64_t n_home = (num_partitions_ - g + G - 1) / G;  // partitions p with p % G == g
+        home_.push_back(torch::zeros({std::max<int64_t>(n_home, 1) * partition_size_, dim1_}, opts));
+        bufs_.push_back({torch::zeros({kCapacity * partition_size_, dim1_}, opts), torch::zeros({kCapacity * partition_size_, dim1_}, opts)});
+        flags_.push_back(torch::zeros({G + 1}, opts.dtype(torch::kInt64)));
+        status_.push_back(torch::zeros({1}, opts.dtype(torch::kInt32)));
+    }
+    epoch_.assign(G, 0);
+    next_.assign(G, 0);
+    resident_.assign(G, std::vector<int64_t>(kCapacity, -1));
+}
+
+void MemPartitionBufferStorage::load(torch::Tensor values) {
+    if (values.dim() != 2 || values.size(0) != dim0_ || values.size(1) != dim1_) throw GegeRuntimeException("load: expected the whole [dim0, dim1] table");
+    const int G = (int)devices_.size();
+    for (int p = 0; p < num_partitions_; p++) {
+        const int64_t begin = p * partition_size_, rows = std::min(partition_size_, dim0_ - begin);
+        if (rows <= 0) continue;
+        home_[p % G].narrow(0, (p / G) * partition_size_, rows).copy_(values.narrow(0, begin, rows));
+    }
+}
+
+MemPartitionBufferStorage::Plan MemPartitionBufferStorage::make_plan(const std::vector<std::vector<int64_t>>& current,
+                                                                     const std::vector<std::vector<int64_t>>& next_states) {
+    // every device's next buffer is filled slot by slot (the state's partitions in ascending order) from wherever each
+    // partition is now -- a slot of some device's current buffer (the relay copy of storage.cpp:626-652) or its home slab --
+    // and a resident partition that nobody keeps is pulled by its home device
+    const int G = (int)devices_.size();
+    std::map<int64_t, std::pair<int, int>> in_buffer;
+    for (int g = 0; g < G; g++)
+        for (int k = 0; k < kCapacity; k++)
+            if (current[g][k] >= 0) in_buffer[current[g][k]] = {g, k};
+    Plan plan;
+    plan.slots.assign(G, std::vector<int64_t>(kCapacity, -1));
+    plan.pulls.assign(G, {});
+    std::map<int64_t, int> claimed;
+    for (int g = 0; g < G; g++) {
+        std::vector<int64_t> st = next_states[g];
+        std::sort(st.begin(), st.end());
+        if ((int)st.size() > kCapacity || std::adjacent_find(st.begin(), st.end()) != st.end())
+            throw GegeRuntimeException("a state holds at most 4 distinct partitions");
+        for (size_t k = 0; k < st.size(); k++) {
+            const int64_t p = st[k];
+            if (p < 0 || p >= num_partitions_) throw GegeRuntimeException("partition id out of range");
+            if (claimed.count(p)) throw GegeRuntimeException("the states of a superstep must be disjoint");
+            claimed[p] = g;
+            plan.slots[g][k] = p;
+            auto it = in_buffer.find(p);
+            if (it != in_buffer.end()) plan.pulls[g].push_back({false, false, it->second.first, it->second.second, (int64_t)k});
+            else plan.pulls[g].push_back({true, false, (int)(p % G), p / G, (int64_t)k});
+        }
+    }
+    for (auto& kv : in_buffer)
+        if (!claimed.count(kv.first)) plan.pulls[kv.first % G].push_back({false, true, kv.second.first, kv.second.second, kv.first / G});
+    return plan;
+}
+
+void MemPartitionBufferStorage::setBufferOrdering(std::vector<torch::Tensor> buffer_states) {
+    const int G = (int)devices_.size();
+    if (buffer_states.size() % G) throw GegeRuntimeException("setBufferOrdering: the number of states must be a multiple of the device count");
+    plans_.clear();
+    auto cur = resident_;
+    for (auto& n : next_)
+        if (n != 0) throw GegeRuntimeException("setBufferOrdering: swaps already in progress");
+    for (size_t k = 0; k < buffer_states.size() / G; k++) {
+        std::vector<std::vector<int64_t>> st(G);
+        for (int g = 0; g < G; g++) {
+            auto t = buffer_states[k * G + g].to(torch::kCPU).to(torch::kInt64).contiguous();
+            st[g].assign(t.data_ptr<int64_t>(), t.data_ptr<int64_t>() + t.numel());
+        }
+        plans_.push_back(make_plan(cur, st));
+        cur = plans_.back().slots;
+    }
+    plans_.push_back(make_plan(cur, std::vector<std::vector<int64_t>>(G)));  // the flush: everything goes home
+}
+
+bool MemPartitionBufferStorage::hasSwap(int32_t device_idx) { return next_.at(device_idx) + 1 < plans_.size(); }
+
+void MemPartitionBufferStorage::run_plan(const Plan& plan, int32_t g) {
+    const int G = (int)devices_.size();
+    c10::cuda::CUDAGuard guard(devices_[g]);
+    // after its n-th swap a device's active buffer is buffer n & 1, so the sources of swap n are the devices' buffers
+    // (n - 1) & 1 wherever their host threads are; the device-side barrier makes the data ready
+    const int old = (int)(next_[g] & 1), nw = old ^ 1;
+    const int64_t slab_bytes = partition_size_ * dim1_ * 4;
+    std::vector<const void*> src;
+    std::vector<void*> dst;
+    for (const auto& pl : plan.pulls[g]) {
+        const char* s = pl.src_home ? (const char*)home_[pl.src_dev].data_ptr<float>() : (const char*)bufs_[pl.src_dev][old].data_ptr<float>();
+        char* d = pl.dst_home ? (char*)home_[g].data_ptr<float>() : (char*)bufs_[g][nw].data_ptr<float>();
+        src.push_back(s + pl.src_index * slab_bytes);
+        dst.push_back(d + pl.dst_index * slab_bytes);
+    }
+    std::vector<void*> rows;
+    for (int j = 0; j < G; j++) rows.push_back(flags_[j].data_ptr<int64_t>());
+    ge2_swap_desc d{};
+    d.world = G;
+    d.rank = g;
+    d.flag_rows = rows.data();
+    d.epoch = ++epoch_[g];
+    d.wait_budget_us = 0;
+    d.num_pulls = (int32_t)src.size();
+    d.pull_src = src.data();
+    d.pull_dst = dst.data();
+    d.slab_bytes = slab_bytes;
+    d.status = status_[g].data_ptr<int32_t>();
+    check(ge2_swap_begin(&d, (ge2_stream_t)at::cuda::getCurrentCUDAStream(devices_[g].index()).stream()), "ge2_swap_begin");
+}
+
+void MemPartitionBufferStorage::performNextSwap(int32_t device_idx) {
+    if (!hasSwap(device_idx)) throw GegeRuntimeException("performNextSwap: no swap left");
+    run_plan(plans_[next_[device_idx]], device_idx);
+    next_[device_idx] += 1;
+}
+
+std::vector<int> MemPartitionBufferStorage::getNextAdmit(int32_t g) {
+    std::vector<int> out;
+    if (next_.at(g) >= plans_.size()) return out;
+    const auto& cur = next_[g] == 0 ? resident_[g] : plans_[next_[g] - 1].slots[g];
+    for (auto p : plans_[next_[g]].slots[g])
+        if (p >= 0 && std::find(cur.begin(), cur.end(), p) == cur.end()) out.push_back((int)p);
+    return out;
+}
+
+std::vector<int> MemPartitionBufferStorage::getNextEvict(int32_t g) {
+    std::vector<int> out;
+    if (next_.at(g) >= plans_.size()) return out;
+    const auto& cur = next_[g] == 0 ? resident_[g] : plans_[next_[g] - 1].slots[g];
+    const auto& nxt = plans_[next_[g]].slots[g];
+    for (auto p : cur)
+        if (p >= 0 && std::find(nxt.begin(), nxt.end(), p) == nxt.end()) out.push_back((int)p);
+    return out;
+}
+
+torch::Tensor MemPartitionBufferStorage::getPartitionToBufferSlotMap(int32_t g) {
+    auto map = torch::full({num_partitions_}, -1, torch::kInt64);
+    const auto& cur = next_.at(g) == 0 ? resident_[g] : plans_[next_[g] - 1].slots[g];
+    for (int k = 0; k < kCapacity; k++)
+        if (cur[k] >= 0) map[cur[k]] = k;
+    return map;
+}
+
+torch::Tensor MemPartitionBufferStorage::activeBuffer(int32_t g) {
+    return bufs_.at(g)[next_[g] & 1];
+}
+
+torch::Tensor MemPartitionBufferStorage::indexRead(Indices indices, int32_t device_idx) { return InMemory(activeBuffer(device_idx)).indexRead(indices); }
+
+void MemPartitionBufferStorage::indexAdd(Indices indices, torch::Tensor values, int32_t device_idx) {
+    InMemory(activeBuffer(device_idx)).indexAdd(indices, values);
+}
+
+torch::Tensor MemPartitionBufferStorage::unload() {
+    const int G = (int)devices_.size();
+    if (!plans_.empty()) {
+        for (int g = 0; g < G; g++) {
+            if (next_[g] + 1 != plans_.size()) throw GegeRuntimeException("unload: supersteps left");
+        }
+        const bool odd = next_[0] & 1;
+        for (int g = 0; g < G; g++) run_plan(plans_.back(), g);
+        if (odd)  // the next ordering starts from buffer 0 again: nothing is resident, only the numbering restarts
+            for (int g = 0; g < G; g++) std::swap(bufs_[g][0], bufs_[g][1]);
+        for (int g = 0; g < G; g++) next_[g] = 0;
+        plans_.clear();
+        resident_.assign(G, std::vector<int64_t>(kCapacity, -1));
+    }
+    checkStatus();
+    auto out = torch::empty({dim0_, dim1_}, torch::kFloat32);
+    for (int p = 0; p < num_partitions_; p++) {
+        const int64_t begin = p * partition_size_, rows = std::min(partition_size_, dim0_ - begin);
+        if (rows <= 0) continue;
+        out.narrow(0, begin, rows).copy_(home_[p % G].narrow(0, (p / G) * partition_size_, rows));
+    }
+    return out;
+}
+
+void MemPartitionBufferStorage::checkStatus() {
+    for (size_t g = 0; g < devices_.size(); g++) {
+        c10::cuda::CUDAGuard guard(devices_[g]);
+        const int32_t word = status_[g].cpu().item<int32_t>();  // synchronises the device's current stream
+        if (word) throw GegeRuntimeException("partition swap failed on device " + std::to_string(g) + " (status " + std::to_string(word) + ")");
+    }
+}
+
+// ---------------------------------------------------------------------------------------------------------------------
+// DataLoader
+// ---------------------------------------------------------------------------------------------------------------------
+DataLoader::DataLoader(torch::Tensor edges, std::shared_ptr<InMemory> node_embeddings, std::shared_ptr<InMemory> node_embeddings_state,
+                       int64_t batch_size, int32_t num_chunks, int32_t negatives_per_chunk, float degree_fraction, bool inverse_edges, uint64_t seed)
+    : edges_(edges.contiguous()), emb_(std::move(node_embeddings)), state_(std::move(node_embeddings_state)), B_(batch_size), C_(num_chunks),
+      N_(negatives_per_chunk), seed_(seed) {
+    require_cuda(edges_, "edges");
+    if (edges_.dim() != 2 || (edges_.size(1) != 2 && edges_.size(1) != 3) || edges_.scalar_type() != torch::kInt64)
+        throw GegeRuntimeException("edges must be an int64 [n, 2|3] tensor");
+    if (edges_.size(0) < B_) throw GegeRuntimeException("fewer edges than one batch");
+    n_deg_ = (int32_t)(N_ * degree_fraction);                       // negative.cpp:608
+    want_src_ = edges_.size(1) == 3 && inverse_edges;                // dataloader.cpp:1321
+    const int64_t n_ids = 2 * B_ + (want_src_ ? 2 : 1) * (int64_t)C_ * N_;
+    packed_ = torch::empty({n_ids}, edges_.options());
+    deg_rows_ = torch::empty({C_, std::max(n_deg_, 1)}, edges_.options());
+}
+
+std::shared_ptr<Batch> DataLoader::getBatch() {
+    c10::cuda::CUDAGuard guard(edges_.device());
+    const int64_t cols = edges_.size(1), nb = edges_.size(0) / B_, b = batch_id_ % nb;
+    const int64_t domain = emb_->data_.size(0);
+    auto slice = edges_.narrow(0, b * B_, B_);
+    const int64_t* e = slice.data_ptr<int64_t>();
+    check(ge2_sample_negatives(e, e + cols - 1, cols, (int32_t)B_, C_, N_, n_deg_, domain, want_src_ ? 1 : 0, seed_, (uint64_t)batch_id_,
+                               packed_.data_ptr<int64_t>(), n_deg_ > 0 ? deg_rows_.data_ptr<int64_t>() : nullptr, current_stream(edges_)),
+          "ge2_sample_negatives");
+    batch_id_ += 1;
+    auto tup = map_tensors_unique_inverse_cuda(packed_, true, domain);
+    auto batch = std::make_shared<Batch>();
+    batch->unique_node_indices_ = std::get<0>(tup);
+    const auto& inv = std::get<1>(tup);
+    const int64_t CN = (int64_t)C_ * N_;
+    auto src_l = inv.narrow(0, 0, B_), dst_l = inv.narrow(0, B_, B_);
+    batch->edges_ = cols == 3 ? torch::stack({src_l, slice.select(1, 1), dst_l}, 1) : torch::stack({src_l, dst_l}, 1);
+    int64_t off = 2 * B_;
+    if (want_src_) {
+        batch->src_neg_indices_mapping_ = inv.narrow(0, off, CN).view({C_, N_});
+        off += CN;
+    }
+    batch->dst_neg_indices_mapping_ = inv.narrow(0, off, CN).view({C_, N_});
+    if (n_deg_ > 0) batch->deg_sample_rows_ = deg_rows_.narrow(1, 0, n_deg_).clone();
+    batch->node_embeddings_ = emb_->indexRead(batch->unique_node_indices_);            // loadGPUParameters, dataloader.cpp:1354-1379
+    batch->node_embeddings_state_ = state_->indexRead(batch->unique_node_indices_);
+    return batch;
+}
+
+void DataLoader::updateEmbeddings(std::shared_ptr<Batch> batch) {
+    emb_->indexAdd(batch->unique_node_indices_, batch->node_gradients_);       // dataloader.cpp:1381-1395
+    state_->indexAdd(batch->unique_node_indices_, batch->node_state_update_);
 }
 
 }  // namespace ge2host

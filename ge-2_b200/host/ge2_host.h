@@ -8,9 +8,14 @@
 //   Batch, Batch::accumulateGradients   include/data/batch.h:13-79
 //   Model::train_batch / step / clear_grad / all_reduce hook   include/nn/model.h:37-59
 //   Storage::indexRead / indexAdd       include/storage/storage.h:49-51
+//   MemPartitionBufferStorage (performNextSwap, hasSwap, getNextAdmit/Evict, getPartitionToBufferSlotMap, indexRead/indexAdd
+//     with device_idx)                  include/storage/storage.h:113-187
+//   Model::broadcast / all_reduce       include/nn/model.h:59, src/nn/model.cpp:174-204,454-478
+//   DataLoader::getBatch / updateEmbeddings   src/data/dataloader.cpp:1069-1291,1354-1395
 #pragma once
 #include <torch/torch.h>
 
+#include <array>
 #include <memory>
 #include <stdexcept>
 #include <string>
@@ -43,6 +48,8 @@ class Batch {
     torch::Tensor edges_;                 // [B, 2|3] local ids (src[, rel], dst)
     torch::Tensor src_neg_filter_;        // [F, 2] (row, col)
     torch::Tensor dst_neg_filter_;
+    torch::Tensor deg_sample_rows_;       // [C, n_deg] batch row each degree-based negative was drawn from; when set, the
+                                          // local filter of both sides is derived from it on the device (no nonzero())
     torch::Tensor loss_;                  // scalar on the device, written by train_batch
 
     void accumulateGradients(float learning_rate);
@@ -53,7 +60,7 @@ enum class DecoderType { DISTMULT, COMPLEX };
 
 // The slice of the reference's Model that the training step touches: a DistMult / ComplEx edge decoder with its relation
 // tables, softmax cross-entropy with SUM reduction, a dense Adagrad optimizer for the relation tables.
-class Model {
+class Model : public std::enable_shared_from_this<Model> {
    public:
     Model(DecoderType type, int64_t num_relations, int64_t dim, bool use_inverse_relations, float dense_lr, float sparse_lr,
           torch::Device device, const std::string& precision = "fp32");
@@ -65,6 +72,17 @@ class Model {
     // with 1 / #replicas, which divides, steps and clears -- same arithmetic as model.cpp:174-204 of the reference.
     void step_after_all_reduce(float grad_scale);
 
+    // Replicas on several GPUs of this process (Model::broadcast, model.cpp:454-478): device_models_[i] lives on devices[i],
+    // device_models_[0] being this model.  Afterwards every replica accumulates its relation gradients into a buffer its
+    // peers can read, and all_reduce() -- called once per batch round after every replica's train_batch(batch, false) --
+    // averages the gradients over the replicas, steps every replica's relation tables and clears the gradients
+    // (Model::all_reduce + step_all, model.cpp:174-204) as ONE launch pair per device and no collective call:
+    // ge2_dense_adagrad_peers.  A replica that trained no batch in the round contributes zeros, as in the reference.
+    void broadcast(std::vector<torch::Device> devices);
+    void all_reduce();
+    void check_status();  // throws when a device-side status word is set (peer timeout, bad index, ...)
+    std::vector<std::shared_ptr<Model>> device_models_;
+
     torch::Tensor relations_, inverse_relations_;            // [R, D]
     torch::Tensor relations_grad_, inverse_relations_grad_;  // [R, D] accumulated like autograd's .grad
     torch::Tensor relations_state_, inverse_relations_state_;
@@ -74,7 +92,14 @@ class Model {
     int precision_;
 
    private:
+    void point_at_half(int half);
     torch::Tensor workspace_, status_;
+    torch::Tensor rel_both_, state_both_;  // [S, R, D]: the two tables (and their states) back to back
+    torch::Tensor grad_buf_;               // replicated form: two halves of S*R*D floats, arrival flags, verdict, wait counter
+    torch::Tensor step_dev_;               // replicated form: device-side round counter
+    std::vector<float*> peer_ptrs_;        // every replica's grad_buf_
+    int64_t round_ = 0;
+    int replica_ = 0;
 };
 
 // InMemory storage on the device (storage.cpp:1173-1259 of the reference)
@@ -84,6 +109,75 @@ class InMemory {
     torch::Tensor indexRead(Indices indices);
     void indexAdd(Indices indices, torch::Tensor values);
     torch::Tensor data_;
+};
+
+// Partition buffer over the GPUs of this process: every partition has a home slab on device p % G; a device's active set of
+// four partitions sits in one of its two buffers [4 * partition_size, dim1]; performNextSwap(device_idx) -- called by every
+// device thread (or by one thread for every device in turn: nothing blocks the host) -- pulls the next state's partitions
+// from wherever they are into the device's other buffer behind a device-side barrier (ge2_swap_begin).  The counterpart of
+// the reference's MemPartitionBufferStorage with its peer relay (storage.cpp:359-757); unlike it, nothing is staged through
+// the host when G * 4 < num_partitions.
+class MemPartitionBufferStorage {
+   public:
+    MemPartitionBufferStorage(int64_t dim0_size, int64_t dim1_size, int32_t num_partitions, std::vector<torch::Device> devices);
+
+    void load(torch::Tensor values);   // [dim0_size, dim1_size] on any device: the rows of partition p go to its home slab
+    torch::Tensor unload();            // every resident partition goes home; returns the whole table on the CPU
+    // buffer_states[k * G + g] = the partitions (up to four, int64) device g holds in superstep k (buffer.cpp:1134-1146)
+    void setBufferOrdering(std::vector<torch::Tensor> buffer_states);
+    bool hasSwap(int32_t device_idx = 0);
+    void performNextSwap(int32_t device_idx);
+    std::vector<int> getNextAdmit(int32_t device_idx = 0);
+    std::vector<int> getNextEvict(int32_t device_idx = 0);
+    torch::Tensor getPartitionToBufferSlotMap(int32_t device_idx = 0);  // [num_partitions] int64 on the CPU, -1 = not resident
+    torch::Tensor indexRead(Indices indices, int32_t device_idx);      // buffer-local row ids
+    void indexAdd(Indices indices, torch::Tensor values, int32_t device_idx);
+    torch::Tensor activeBuffer(int32_t device_idx);                    // [4 * partition_size, dim1] view of the current buffer
+    int64_t getPartitionSize(int32_t = 0) { return partition_size_; }
+    int64_t getNumInMemory(int32_t = 0) { return 4 * partition_size_; }
+    void checkStatus();
+
+   private:
+    struct Pull {
+        bool src_home, dst_home;
+        int src_dev;
+        int64_t src_index, dst_index;
+    };
+    struct Plan {
+        std::vector<std::vector<int64_t>> slots;  // per device: partition in each of the four slots, -1 = empty
+        std::vector<std::vector<Pull>> pulls;     // per device
+    };
+    Plan make_plan(const std::vector<std::vector<int64_t>>& current, const std::vector<std::vector<int64_t>>& next_states);
+    void run_plan(const Plan& plan, int32_t device_idx);
+
+    int64_t dim0_, dim1_, partition_size_;
+    int32_t num_partitions_;
+    std::vector<torch::Device> devices_;
+    std::vector<torch::Tensor> home_, flags_, status_;
+    std::vector<std::array<torch::Tensor, 2>> bufs_;
+    std::vector<uint64_t> epoch_;
+    std::vector<size_t> next_;   // per device: index of the next plan
+    std::vector<Plan> plans_;    // one per superstep, then the flush
+    std::vector<std::vector<int64_t>> resident_;  // slots before plans_[0]
+};
+
+// The reference's per-batch loader calls for a device-resident edge list (DataLoader::getBatch -> edgeSample + loadGPUParameters,
+// dataloader.cpp:1069-1291,1354-1379; DataLoader::updateEmbeddings, :1381-1395), unfused: sample, map_tensors, gather.
+class DataLoader {
+   public:
+    DataLoader(torch::Tensor edges, std::shared_ptr<InMemory> node_embeddings, std::shared_ptr<InMemory> node_embeddings_state, int64_t batch_size,
+               int32_t num_chunks, int32_t negatives_per_chunk, float degree_fraction, bool inverse_edges, uint64_t seed);
+    std::shared_ptr<Batch> getBatch();                  // batch number batch_id_++ of the edge list (wraps around)
+    void updateEmbeddings(std::shared_ptr<Batch> batch);  // indexAdd of the embedding and state updates
+    int64_t batch_id_ = 0;
+
+   private:
+    torch::Tensor edges_, packed_, deg_rows_, rel_ids_, step_dev_;
+    std::shared_ptr<InMemory> emb_, state_;
+    int64_t B_;
+    int32_t C_, N_, n_deg_;
+    bool want_src_;
+    uint64_t seed_;
 };
 
 }  // namespace ge2host
