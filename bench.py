@@ -324,6 +324,39 @@ def reference_gpu_ms(cfg, table, state, edges, steps, device):
     return a.elapsed_time(b) / steps
 
 
+def host_cpp_ms(cfg, table, state, edges, steps, device, precision):
+    """The same steps through the C++ host layer (ge-2_b200/host, the reference's own call sequence: DataLoader::getBatch ->
+    Model::train_batch -> DataLoader::updateEmbeddings, unfused, host-issued, one count read-back per batch inside map_tensors
+    as a drop-in for the reference's four).  Scratch copies of the tables; ms per step by CUDA events."""
+    import importlib.util
+
+    so = ROOT / "ge-2_b200" / "ge2_host.so"
+    spec = importlib.util.spec_from_file_location("ge2_host", so)
+    H = importlib.util.module_from_spec(spec)
+    spec.loader.exec_module(H)
+    kind = H.DecoderType.COMPLEX if cfg["decoder"] == "COMPLEX" else H.DecoderType.DISTMULT
+    model = H.Model(kind, cfg["relations"], cfg["D"], True, cfg["lr"], cfg["lr"], device, precision)
+    emb, st = H.InMemory(table.clone()), H.InMemory(state.clone())
+    loader = H.DataLoader(edges, emb, st, cfg["B"], cfg["C"], cfg["N"], cfg["degree_fraction"], True, 20262)
+
+    def one():
+        batch = loader.getBatch()
+        model.train_batch(batch, True)
+        loader.updateEmbeddings(batch)
+
+    for _ in range(3):
+        one()
+    a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    torch.cuda.synchronize()
+    a.record()
+    for _ in range(steps):
+        one()
+    b.record()
+    torch.cuda.synchronize()
+    model.check_status()
+    return a.elapsed_time(b) / steps
+
+
 def bucket_sizes_of(cfg, P, psize, seed, device):
     """sizes of all P * P buckets of the graph make_partitioned_edges generates (a counting pass over the same draws)"""
     return make_partitioned_edges(cfg, P, psize, [], seed, device, count_only=True)[1]
@@ -719,6 +752,7 @@ def main():
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-fp32-path", action="store_true", help="skip the side measurement of the fp32 CUDA-core path")
     ap.add_argument("--no-reference-gpu", action="store_true", help="skip timing the reference's own GPU code (oracle/_ref/gege_ref_cuda.so) on this GPU")
+    ap.add_argument("--no-host-cpp", action="store_true", help="N = 1: skip the side measurement through the C++ host layer")
     ap.add_argument("--no-epoch", action="store_true", help="N = 1: skip the one-epoch (triples / B steps) timed region")
     ap.add_argument("--no-kernel-rooflines", action="store_true", help="N = 1: skip the per-kernel timings behind roofline_kernels")
     ap.add_argument("--no-graph", action="store_true", help="N = 1: issue every launch from the host instead of replaying a CUDA graph")
@@ -923,6 +957,15 @@ def main():
             b32.record()
             torch.cuda.synchronize()
             line["fp32_path"] = dict(value=k32 * B / (a32.elapsed_time(b32) * 1e-3), unit="edges/s", ms_per_step=a32.elapsed_time(b32) / k32, steps=k32)
+        if world == 1 and not args.no_host_cpp:
+            try:
+                ms_cpp = host_cpp_ms(cfg, table, state, edges, min(K, 20), device, args.precision)
+                line["host_cpp"] = dict(value=B / (ms_cpp * 1e-3), unit="edges/s", ms_per_step=ms_cpp,
+                                        note="the reference's call sequence through the C++ host layer (getBatch -> train_batch -> updateEmbeddings), "
+                                             "unfused and host-issued with one count read-back per batch; the headline path is the fused, "
+                                             "graph-replayed launch sequence over the same C ABI")
+            except Exception as ex:
+                line["host_cpp"] = dict(unavailable=str(ex)[:160])
         if world == 1 and not args.no_reference_gpu:
             try:
                 ms_ref = reference_gpu_ms(cfg, table, state, edges, min(K, 20), device)

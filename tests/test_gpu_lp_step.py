@@ -84,6 +84,27 @@ def test_against_oracle(capi, cuda_device, precision, kind, B, C, N, D, R, U, n_
     assert rel_err(res2["node_grad"], res["node_grad"]) < 1e-5
 
 
+@pytest.mark.parametrize("emb_scale", [0.6, 0.75])
+def test_peaked_softmax_on_the_tensor_path(capi, cuda_device, emb_scale):
+    """Trained-looking inputs: |embedding| up to 3 and more, scores up to +-60...90, and rows whose softmax mass sits on a
+    dozen or fewer of the 1 000 negatives.  The fp16 probabilities of the gradient pass carry a power-of-two scale so that the small
+    ones stay out of the subnormal range; the stated 1e-2 bound must hold here as it does on the mild fixtures."""
+    case = workloads.make_case("COMPLEX", 1000, 2, 1000, 100, 200, 20000, 500, seed=5, relations=True, inverse=True, alpha=1.1, emb_scale=emb_scale)
+    o = O.lp_train_forward_backward(case.kind, case.edges, case.emb, case.rel, case.inv_rel, case.dst_negs, case.src_negs, case.filt, case.filt)
+    ns = o.neg_scores.astype(np.float64).copy()
+    ns[o.neg_scores == O.MASK_VALUE] = -np.inf
+    p = np.exp(ns - ns.max(1, keepdims=True))
+    p /= p.sum(1, keepdims=True)
+    k90 = ((np.sort(p, 1)[:, ::-1].cumsum(1) < 0.9).sum(1) + 1)
+    assert np.median(k90) <= 12 and np.abs(case.emb).max() > 2.8  # the case is what the docstring says
+    ref = dict(loss=o.loss, node_grad=o.node_grad, rel_grad=o.rel_grad, inv_rel_grad=o.inv_rel_grad, neg_scores=o.neg_scores,
+               pos_scores=o.pos_scores, inv_neg_scores=o.inv_neg_scores, inv_pos_scores=o.inv_pos_scores)
+    res = run_lp_step(capi, case, cuda_device, precision="f16", filter_mode="deg_rows")
+    check_against(res, ref, TOL["f16"], 2)
+    res = run_lp_step(capi, case, cuda_device, precision="fp32", filter_mode="deg_rows")
+    check_against(res, ref, TOL["fp32"], 2)
+
+
 def test_relation_grads_accumulate(capi, cuda_device):
     """rel_grad is accumulated into, like autograd's .grad across train_batch(call_step=false) calls."""
     import torch
