@@ -8,25 +8,30 @@
 // P = exp(S - lse), dQ = P K, dK = P^T Q.  The [rows x negatives] matrices never leave the SM.  Two launches:
 //
 //   lp_lse_kernel   S tile by tile, running (max, sum) per row in the exp2 domain                          -> lse, loss
-//   lp_grad_kernel  one code path for both gradients.  A "stationary" block X of 128 rows stays in shared memory and
-//                   tiles Y of 128 rows stream past it: Sx = X Y^T, W = exp2(Sx log2 e - lse) (lse of the QUERY row: the
-//                   accumulator's row when X = Q, its column when X = K), acc += W Y, accumulated in tensor memory over
-//                   the whole stream and written once:  X = Q, Y = K tiles -> dQ;   X = K tile, Y = Q blocks -> dK.
-//                   Nothing is reduced across CTAs except where a block's stream is cut at a CTA boundary (below).
+//   lp_grad_kernel  a block X of 128 query rows (Q) stays in shared memory and the tiles Y of 128 negatives (K) of its chunk
+//                   stream past it: S = X Y^T is recomputed (cheaper than storing it), W = exp2(S log2 e - lse) * 2^14 is
+//                   packed to fp16, dQ += W Y accumulates in tensor memory over the block's whole stream and is written
+//                   once; dK_tile = W^T X is produced per tile and added into global dK (the row blocks of a chunk meet
+//                   there) by TMA reduce-adds.
 //
 // Both launches are persistent: the (block, tile) units of the whole step are numbered consecutively and dealt to the
 // CTAs (one per SM) as contiguous ranges of equal length, so every SM is busy to the end whatever the number of blocks.
 // A block whose units straddle a CTA boundary is finished by two (rarely more) CTAs: in the logsumexp pass each leaves a
-// per-row partial (max, sum) and the last one to arrive combines them; in the gradient pass each adds its part of the
-// accumulator into the output rows with TMA reduce-adds (those rows are cleared by the first launch); whole blocks are
-// written with plain TMA stores.
+// per-row partial (max, sum) and the gradient pass combines them; in the gradient pass each adds its part of dQ into the
+// output rows with TMA reduce-adds (those rows are cleared by the first launch); whole blocks are written with plain TMA
+// stores.
 //
-// Shared memory holds X [128 x DP], a ring of three Y tiles [128 x DP] and (gradient pass) two W tiles [128 x 128], all
-// fp16 in the 128-byte-swizzled layout TMA writes (64-element column blocks of 128 rows at a 128-byte pitch).  That one
-// layout serves every contraction, because a block read along its rows is a K-major operand and read along its columns
-// an MN-major operand:
-//   Sx  [x, y] = X Y^T   A = X (K-major, k = d)   B = Y (K-major, k = d)     -> tensor-memory columns [0,128) / [128,256), alternating
-//   acc [x, d] += W Y    A = W (K-major, k = y)   B = Y (MN-major, k = y)    -> columns [256, ..) / [384, ..), alternating per block
+// Shared memory holds X [128 x DP], a ring of Y tiles [128 x DP] (five in the logsumexp pass, three in the gradient pass)
+// and, in the gradient pass, one W tile [128 x 128] and the drain warps' staging slabs; X, Y and W are fp16 in the
+// 128-byte-swizzled layout TMA writes (64-element column blocks of 128 rows at a 128-byte pitch).  That one layout serves
+// every contraction, because a block read along its rows is a K-major operand and read along its columns an MN-major
+// operand:
+//   S  [x, y] = X Y^T    A = X (K-major, k = d)    B = Y (K-major, k = d)
+//   dQ [x, d] += W Y     A = W (K-major, k = y)    B = Y (MN-major, k = y)
+//   dK [y, d] = W^T X    A = W (MN-major, k = x)   B = X (MN-major, k = x)
+// Tensor memory (512 columns), gradient pass: S at 0, dQ at 128, two dK accumulators at 256 and 384 that alternate from
+// tile to tile, so the contraction of one tile runs while the other's result is drained.  Logsumexp pass: two score
+// accumulators at 0 and 128.
 // (32-bit tf32 operands cannot do this: the hardware transposes them only from a different, 32-byte-atom swizzle.)
 // W is scaled by 2^14 before it is packed to fp16, so that probabilities down to 2^-38 keep their full significand instead
 // of falling into fp16's subnormal range; dQ and dK leave this kernel with that factor still on them and the scatter
@@ -34,13 +39,15 @@
 //
 // Warp roles, connected by mbarrier pipelines (no block-wide barrier inside the loops):
 //   warps 0-15  softmax: thread = accumulator row (tensor-memory lane).  lse pass: two groups of 8 warps take alternate
-//               tiles (64 columns per warp).  Gradient pass: all 16 warps on every tile (32 columns per warp), scores ->
+//               tiles (64 columns per warp).  Gradient pass: all 16 warps on every tile (32 columns per warp): scores ->
 //               registers (the accumulator is handed back at once) -> W in shared memory
-//   warps 16-19 lse pass: warp 16 combines the softmax warps' partials at the end of a block (and exchanges them with the
-//               other CTAs of a split block).  Gradient pass: drain, accumulator -> swizzled staging -> TMA store / reduce-add
-//   warp  20    lane 0: TMA producer (X at the start of a block, the Y ring, the lse slice that goes with a Y tile)
+//   warps 16-19 lse pass: warp 16 combines the softmax warps' partials at the end of a block; warps 17-19 clear dK and
+//               the dQ rows of split blocks.  Gradient pass: drain (with warps 23-26): accumulator -> swizzled staging
+//               slab -> TMA store / reduce-add, each warp its lane quarter and every second 32-column slab
+//   warp  20    lane 0: TMA producer (X at the start of a block, the Y ring)
 //   warp  21    lane 0: issues the score contractions; the warp also allocates and frees tensor memory
-//   warp  22    lane 0: issues the accumulator contractions of the gradient pass
+//   warp  22    lane 0: issues the dK and dQ contractions of the gradient pass
+//   warps 23-26 gradient pass only (864 threads): the second set of drain warps
 // Every mbarrier wait is bounded; a wait that runs out raises GE2_STATUS_PIPE_TIMEOUT and sets a block-wide abort flag
 // that every other wait polls, so all roles fall through to the common exit where tensor memory is released.
 #include <stdlib.h>
@@ -58,11 +65,13 @@ using namespace tc;
 constexpr int BM = 128;                 // rows of the stationary block (MMA M)
 constexpr int BN = 128;                 // rows of a streamed tile (MMA N of the score contraction)
 constexpr int kSoftmaxWarps = 16;       // 4 row quarters (tensor-memory lane groups) x 4 groups of 32 columns
-constexpr int kThreads = 736;           // 16 softmax warps + 4 drain warps + TMA warp + two MMA warps
+constexpr int kThreads = 736;           // lse pass: 16 softmax warps + 4 combine / clearing warps + TMA warp + two MMA warps
+constexpr int kThreadsB = 864;          // gradient pass: 16 softmax warps + 8 drain warps (16-19 and 23-26) + TMA warp + two MMA warps
+constexpr int kDrainWarps = 8;
 constexpr int kDrainWarp0 = kSoftmaxWarps, kTmaWarp = kDrainWarp0 + 4, kMmaWarp = kTmaWarp + 1, kGradWarp = kMmaWarp + 1;
 constexpr int kBlockBytes = 128 * 128;  // one 64-half column block of 128 rows
 constexpr int kMmaK = 16;               // k extent of one kind::f16 MMA (32 bytes)
-constexpr int kStages = 3;              // Y ring depth of the gradient pass (shared memory is full there)
+constexpr int kStages = 3;              // Y ring depth of the gradient pass (shared memory is full there: X, 3 Y, W, 16 staging slabs)
 constexpr int kStagesA = 5;             // Y ring depth of the lse pass (no W tiles: room for a deeper ring, which the load latency wants)
 constexpr int kMaxStages = kStagesA;
 constexpr int kMaxParts = 8;            // most CTAs that can share one row block in the lse pass; size of a row's partial list
@@ -75,7 +84,8 @@ constexpr float kDeadRow = 1e30f;       // "lse" of a row past the end of its ch
 // mbarrier slots (a superset; the lse pass uses the first group and the exchange barriers)
 enum Bar { kBarXFull = 0, kBarXEmpty, kBarYFull, kBarYEmpty = kBarYFull + kMaxStages, kBarSFull = kBarYEmpty + kMaxStages, kBarSEmpty = kBarSFull + 2,
            kBarWFull = kBarSEmpty + 2, kBarWEmpty = kBarWFull + 2, kBarAccFull = kBarWEmpty + 2, kBarAccEmpty = kBarAccFull + 2,
-           kBarXch = kBarAccEmpty + 2, kBarXchFree = kBarXch + 2, kNumBars = kBarXchFree + 2 };
+           kBarXch = kBarAccEmpty + 2, kBarXchFree = kBarXch + 2, kBarDkFull = kBarXchFree + 2, kBarDkEmpty = kBarDkFull + 2,
+           kNumBars = kBarDkEmpty + 2 };
 
 // How the units of a launch are dealt to its CTAs: CTA k takes units [k * units / grid, (k + 1) * units / grid).
 struct Sched {
@@ -96,10 +106,10 @@ struct Layout {
     static constexpr int kY = kX + kTileBytes;
     static constexpr int kW = kY + kStages * kTileBytes;
     // --- gradient pass ---
-    static constexpr int kMiscB = kW + 2 * kWBytes;               // barriers, tensor-memory address, abort flag, then the lse ring
+    static constexpr int kMiscB = kW + kWBytes;                   // barriers, tensor-memory address, abort flag
     static constexpr int kLseRing = kMiscB + 512;                 // kStages x 128 floats: lse of the rows of the Y tile in the same stage
-    static constexpr int kDrain = kMiscB + 2048;                  // 4 drain warps x 2 buffers x (32 rows x 128 bytes), 128-byte swizzled
-    static constexpr int kEndB = kDrain + 4 * 2 * 4096;
+    static constexpr int kDrain = kMiscB + 2048;                  // 8 drain warps x 2 slabs (32 rows x 128 bytes), 128-byte swizzled
+    static constexpr int kEndB = kDrain + kDrainWarps * 2 * 4096;
     static constexpr int kDynamicB = kEndB + 1024;                // 1024 bytes of slack to align the base
     // --- lse pass (no W tiles) ---
     static constexpr int kMiscA = kY + kStagesA * kTileBytes;
@@ -579,7 +589,7 @@ __global__ void __launch_bounds__(kThreads, 1)
 // launch 2: both gradients
 // =====================================================================================================================
 template <int DP>
-__global__ void __launch_bounds__(kThreads, 1)
+__global__ void __launch_bounds__(kThreadsB, 1)
     lp_grad_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK, const __grid_constant__ CUtensorMap tmDK,
                    const __grid_constant__ CUtensorMap tmDKt, const __grid_constant__ CUtensorMap tmDQ,
                    const __grid_constant__ CUtensorMap tmDQt, LpKernelArgs a, Sched sc) {
@@ -608,6 +618,15 @@ __global__ void __launch_bounds__(kThreads, 1)
         if (ok) ok = mbar_try_wait(&bars[bar], parity) ? 1 : 0;
         return __all_sync(0xffffffffu, ok) != 0;
     };
+    constexpr int kBarDqFull = kBarAccFull, kBarDqEmpty = kBarAccEmpty;
+    // Only real columns of dQ / dK leave the SM: D / 32 full slabs of 32 columns, then one narrow slab (its own tensor map,
+    // dense rows of `tail` floats) for the remainder rounded up to 4.  Worker warp w drains slab w / 4 of its lane quarter.
+    int full_slabs = d.D / 32, tail = ((d.D % 32) + 3) & ~3;
+    if (tail == 32) {
+        full_slabs++;
+        tail = 0;
+    }
+    const int drain_slabs = full_slabs + (tail > 0 ? 1 : 0);
     int tma_it = 0, tma_sg = -1;
     IterA tma_un(ub, sc);  // unit of iteration tma_it
     auto produce = [&](int it) -> bool {
@@ -634,16 +653,16 @@ __global__ void __launch_bounds__(kThreads, 1)
             mbar_init(&bars[kBarYFull + k], 1);
             mbar_init(&bars[kBarYEmpty + k], 1);
         }
+        mbar_init(&bars[kBarSFull], 1);
+        mbar_init(&bars[kBarSEmpty], kSoftmaxWarps);  // one arrival per worker warp: the score tile is in registers
+        mbar_init(&bars[kBarWFull], kSoftmaxWarps);
+        mbar_init(&bars[kBarWEmpty], 1);
         for (int k = 0; k < 2; k++) {
-            mbar_init(&bars[kBarSFull + k], 1);
-            mbar_init(&bars[kBarSEmpty + k], kSoftmaxWarps / 2);  // one arrival per warp of the group that owns the tile
-            mbar_init(&bars[kBarWFull + k], kSoftmaxWarps / 2);
-            mbar_init(&bars[kBarWEmpty + k], 1);
+            mbar_init(&bars[kBarDkFull + k], 1);                 // dK of a tile complete
+            mbar_init(&bars[kBarDkEmpty + k], kDrainWarps);      // ... and read by the drain warps
         }
-        mbar_init(&bars[kBarAccFull], 1);       // dQ of a block complete
-        mbar_init(&bars[kBarAccEmpty], 4);      // ... and read by the four drain warps
-        mbar_init(&bars[kBarAccFull + 1], 1);   // dK of a tile complete
-        mbar_init(&bars[kBarAccEmpty + 1], 4);  // ... and read by the four drain warps
+        mbar_init(&bars[kBarDqFull], 1);                         // dQ of a block complete
+        mbar_init(&bars[kBarDqEmpty], kDrainWarps);
         *s_abort = 0;
         mbar_init_fence();
         prefetch_tensormap(&tmQ);
@@ -664,11 +683,10 @@ __global__ void __launch_bounds__(kThreads, 1)
     tc_fence_after();
     griddep_wait();  // set-up done; from here on global memory written by the preceding kernel is read and its buffers rewritten
     const uint32_t tmem = *s_tmem;
-    // tensor memory: two score accumulators at 0 and 128 (one per softmax group), dQ at 256 (accumulated over the block's
-    // whole stream), dK of the current tile at 384
-    const uint32_t tS = tmem, tdQ = tmem + 256, tdK = tmem + 384;
+    // tensor memory: the score accumulator at 0, dQ at 128 (accumulated over the block's whole stream), two dK accumulators at
+    // 256 and 384 that alternate from tile to tile, so the contraction of one tile runs while the other's result is drained
+    const uint32_t tS = tmem, tdQ = tmem + 128, tdK0 = tmem + 256;
     const uint32_t lane_sel = (uint32_t)((warp & 3) * 32) << 16;
-    constexpr int kBarDqFull = kBarAccFull, kBarDqEmpty = kBarAccEmpty, kBarDkFull = kBarAccFull + 1, kBarDkEmpty = kBarAccEmpty + 1;
 
     if (warp == kTmaWarp) {
         if (lane == 0) {
@@ -688,14 +706,14 @@ __global__ void __launch_bounds__(kThreads, 1)
                     sg++;
                     if (!wait(kBarXFull, sg & 1)) break;
                 }
-                const int st = it % kStages, use = it / kStages, sb = it & 1, su = it >> 1;
+                const int st = it % kStages, use = it / kStages;
                 if (!wait(kBarYFull + st, use & 1)) break;
-                if (!wait(kBarSEmpty + sb, (su & 1) ^ 1)) break;
+                if (!wait(kBarSEmpty, (it & 1) ^ 1)) break;  // every worker warp holds the previous tile's scores in registers
                 tc_fence_after();
                 const uint64_t dYk = desc_kmajor_base(aY0 + st * LY::kTileBytes);
 #pragma unroll
-                for (int ks = 0; ks < DP / kMmaK; ks++) mma_f16_ss(tS + sb * 128, dXk + koff_kmajor(ks), dYk + koff_kmajor(ks), kIdescS, ks > 0);
-                mma_commit(&bars[kBarSFull + sb]);
+                for (int ks = 0; ks < DP / kMmaK; ks++) mma_f16_ss(tS, dXk + koff_kmajor(ks), dYk + koff_kmajor(ks), kIdescS, ks > 0);
+                mma_commit(&bars[kBarSFull]);
             }
         }
     } else if (warp == kGradWarp) {
@@ -720,21 +738,22 @@ __global__ void __launch_bounds__(kThreads, 1)
                 }
                 const int st = it % kStages, pb = it & 1;
                 // (no wait on X or the Y stage: W was made from scores that were made from them)
-                if (!wait(kBarWFull + pb, (it >> 1) & 1)) break;
-                if (!wait(kBarDkEmpty, (it & 1) ^ 1)) break;  // the drain of the previous tile has read dK
+                if (!wait(kBarWFull, it & 1)) break;
+                if (!wait(kBarDkEmpty + pb, ((it >> 1) & 1) ^ 1)) break;  // the tile before last has been drained out of this accumulator
                 tc_fence_after();
-                const uint32_t aW = aW0 + pb * LY::kWBytes;
+                const uint32_t tdK = tdK0 + pb * 128;
+                const uint32_t aW = aW0;
                 const uint64_t dWk = desc_kmajor_base(aW), dWm = desc_mnmajor_base(aW), dYm = desc_mnmajor_base(aY0 + st * LY::kTileBytes);
 #pragma unroll
                 for (int ks = 0; ks < BM / kMmaK; ks++)  // dK = W^T Q, k runs over the block's rows; first, so that its drain starts early
                     mma_f16_ss(tdK, dWm + koff_mnmajor(ks), dXm + koff_mnmajor(ks), kIdescDK, ks > 0);
-                mma_commit(&bars[kBarDkFull]);
+                mma_commit(&bars[kBarDkFull + pb]);
 #pragma unroll
                 for (int ks = 0; ks < BN / kMmaK; ks++)  // dQ += W K, k runs over the tile's negatives
                     mma_f16_ss(tdQ, dWk + koff_kmajor(ks), dYm + koff_mnmajor(ks), kIdescDQ, (!fresh || ks > 0) ? 1u : 0u);
                 fresh = false;
                 mma_commit(&bars[kBarYEmpty + st]);
-                mma_commit(&bars[kBarWEmpty + pb]);
+                mma_commit(&bars[kBarWEmpty]);
                 if (it == n_iter - 1 || un.tile == sc.T - 1) {
                     mma_commit(&bars[kBarDqFull]);
                     mma_commit(&bars[kBarXEmpty]);  // Q is an operand of the score and the dK contractions; those of this block are all behind this point
@@ -742,32 +761,23 @@ __global__ void __launch_bounds__(kThreads, 1)
             }
         }
     } else if (warp < kSoftmaxWarps) {
-        // ================================ softmax warps (0-15): W = exp2(S log2 e - lse) ================================
-        // Two groups of 8 warps take alternate tiles (group g = warp / 8 owns the iterations with (it & 1) == g, and with them
-        // score accumulator g and W buffer g), so the waits, tensor-memory loads and stores of one group overlap the
-        // arithmetic of the other.  Within a group, warp w takes rows 32*(w & 3) ... + 31 and columns 64*((w >> 2) & 1) ... + 63
-        // of the tile, as two passes of 32 columns; the score accumulator is handed back as soon as both are in registers.
-        const int grp = warp >> 3;
-        const int ch = (warp >> 2) & 1;
+        // ================================ softmax warps (0-15): W = exp2(S log2 e - lse) * 2^14 ================================
+        // All sixteen work on the same tile: warp w takes rows 32*(w & 3) ... + 31 (its quarter of the tensor-memory lanes) and
+        // columns 32*(w >> 2) ... + 31: one tensor-memory load, after which the score accumulator is handed back at once.
+        const int cg = warp >> 2;      // column group of the score tile
+        const int wq = warp & 3;       // lane quarter
         const int my_row = tid & 127;
         float lrow = kDeadRow;  // (shifted, base-2) lse of my row of the current block
-        auto load_mask_q = [&](int it, const IterA& un, int32_t (&m)[2]) {  // filter words of columns ch*64 + {0, 32} + lane of the K tile
-            m[0] = m[1] = -1;
+        auto load_mask_q = [&](int it, const IterA& un) -> int32_t {  // filter word of column cg*32 + lane of the K tile
             if (it < n_iter) {
                 const int n0 = un.tile * BN;
-                const int vn = min(BN, d.N - n0);
-#pragma unroll
-                for (int k = 0; k < 2; k++) {
-                    const int idx = ch * 64 + k * 32 + lane;
-                    if (idx < vn) m[k] = __ldg(&L.mask[(int64_t)un.zc * d.N + n0 + idx]);
-                }
+                const int idx = cg * 32 + lane;
+                if (idx < min(BN, d.N - n0)) return __ldg(&L.mask[(int64_t)un.zc * d.N + n0 + idx]);
             }
+            return -1;
         };
-        int32_t mnext[2];
-        IterA un(ub, sc), pre(ub, sc);  // `pre`: the unit whose filter words are fetched next (this group's tile after the current one)
-        if (grp == 1) pre.next(sc);
-        load_mask_q(grp, pre, mnext);
-        pre.next(sc);
+        IterA un(ub, sc), pre(ub, sc);  // `pre`: the unit whose filter word is fetched next
+        int32_t mnext = load_mask_q(0, pre);
         pre.next(sc);
         int row_base = 0;  // batch row (padded numbering, as the filter uses it) of row 0 of the current block
         for (int it = 0; it < n_iter; it++, un.next(sc)) {
@@ -815,109 +825,98 @@ __global__ void __launch_bounds__(kThreads, 1)
                     }
                 }
             }
-            if ((it & 1) != grp) continue;
-            const int su = it >> 1;
-            uint32_t mb[2], wor[2];  // bit j of mb[k] = column ch*64 + 32k + j of this tile is masked for my row
+            uint32_t mb = 0u;  // bit j = column cg*32 + j of this tile is masked for my row
             {
-                const int32_t mcur[2] = {mnext[0], mnext[1]};
-                load_mask_q(it + 2, pre, mnext);
+                const int32_t mcur = mnext;
+                mnext = load_mask_q(it + 1, pre);
                 pre.next(sc);
-                pre.next(sc);
-                const int brow = row_base + my_row, wrow0 = row_base + (warp & 3) * 32;
-#pragma unroll
-                for (int k = 0; k < 2; k++) {
-                    mb[k] = 0u;
-                    unsigned ballot = __ballot_sync(0xffffffffu, (unsigned)(mcur[k] - wrow0) < 32u);
-                    while (ballot != 0) {
-                        const int src = __ffs(ballot) - 1;
-                        ballot &= ballot - 1;
-                        if (__shfl_sync(0xffffffffu, mcur[k], src) == brow) mb[k] |= 1u << src;
-                    }
-                    wor[k] = __reduce_or_sync(0xffffffffu, mb[k]);
+                const int brow = row_base + my_row, wrow0 = row_base + wq * 32;
+                unsigned ballot = __ballot_sync(0xffffffffu, (unsigned)(mcur - wrow0) < 32u);
+                while (ballot != 0) {
+                    const int src = __ffs(ballot) - 1;
+                    ballot &= ballot - 1;
+                    if (__shfl_sync(0xffffffffu, mcur, src) == brow) mb |= 1u << src;
                 }
             }
-            if (!warp_wait(kBarSFull + grp, su & 1)) break;
-            // the contractions that read this group's W buffer two tiles ago must be done
-            if (!warp_wait(kBarWEmpty + grp, (su & 1) ^ 1)) break;
+            const uint32_t wor = __reduce_or_sync(0xffffffffu, mb);  // which 8-column groups hold a masked entry for any row of this warp
+            if (!warp_wait(kBarSFull, it & 1)) break;
             tc_fence_after();
-            unsigned char* sWb = sW + grp * LY::kWBytes;
-            const int nv_tile = min(BN, d.N - un.tile * BN) - ch * 64;
+            float v[32];
+            tmem_ld_32x32(tS + cg * 32 + lane_sel, v);
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(&bars[kBarSEmpty]);  // the piece is in registers: the score accumulator is free for the next tile
 #pragma unroll
-            for (int k = 0; k < 2; k++) {
-                float v[32];
-                tmem_ld_32x32(tS + grp * 128 + ch * 64 + k * 32 + lane_sel, v);
-                if (k == 1) {
-                    tc_fence_before();
-                    __syncwarp();
-                    if (lane == 0) mbar_arrive(&bars[kBarSEmpty + grp]);  // the tile is in registers: the score accumulator is free again
+            for (int j = 0; j < 32; j++) v[j] = exp2f_fast(fmaf(v[j], kLog2e, -lrow));
+            // Columns past the chunk's last negative: their zero scores are in no row's lse, so exp2 could overflow fp16
+            // and meet the zero row of K as inf * 0 in dQ (their dK rows are clipped by the tensor map).
+            const int nv = min(BN, d.N - un.tile * BN) - cg * 32;
+            if (nv < 32) {
+#pragma unroll
+                for (int j = 0; j < 32; j++) v[j] = j < nv ? v[j] : 0.f;
+            }
+            // Masked entries were overwritten in place by the reference: no gradient reaches them.  Nothing else needs
+            // zeroing: rows of Q past the chunk's end carry the dead-row lse (W = 0).
+#pragma unroll
+            for (int q = 0; q < 4; q++) {
+                if ((wor >> (q * 8)) & 0xffu) {  // warp-uniform
+#pragma unroll
+                    for (int j = 8 * q; j < 8 * q + 8; j++) v[j] = ((mb >> j) & 1u) ? 0.f : v[j];
                 }
+            }
+            // One W buffer: the contractions of the previous tile must have read it.  They were issued when that tile's W was
+            // complete and ran while this tile's scores were loaded and exponentiated, so the wait is short.
+            if (!warp_wait(kBarWEmpty, (it & 1) ^ 1)) break;
 #pragma unroll
-                for (int j = 0; j < 32; j++) v[j] = exp2f_fast(fmaf(v[j], kLog2e, -lrow));
-                // Columns past the chunk's last negative: their zero scores are in no row's lse, so exp2 could overflow fp16
-                // and meet the zero row of K as inf * 0 in dQ (their dK rows are clipped by the tensor map).
-                const int nv = nv_tile - k * 32;
-                if (nv < 32) {
-#pragma unroll
-                    for (int j = 0; j < 32; j++) v[j] = j < nv ? v[j] : 0.f;
-                }
-                // Masked entries were overwritten in place by the reference: no gradient reaches them.  Nothing else needs
-                // zeroing: rows of Q past the chunk's end carry the dead-row lse (W = 0).
-#pragma unroll
-                for (int q = 0; q < 4; q++) {
-                    if ((wor[k] >> (q * 8)) & 0xffu) {  // warp-uniform
-#pragma unroll
-                        for (int j = 8 * q; j < 8 * q + 8; j++) v[j] = ((mb[k] >> j) & 1u) ? 0.f : v[j];
-                    }
-                }
-#pragma unroll
-                for (int q = 0; q < 4; q++) {  // 8 halves = one 16-byte chunk
-                    uint4 pk;
-                    pk.x = pack_half2(v[8 * q + 0], v[8 * q + 1]);
-                    pk.y = pack_half2(v[8 * q + 2], v[8 * q + 3]);
-                    pk.z = pack_half2(v[8 * q + 4], v[8 * q + 5]);
-                    pk.w = pack_half2(v[8 * q + 6], v[8 * q + 7]);
-                    *reinterpret_cast<uint4*>(sWb + swz_chunk_offset(my_row, ch * 64 + k * 32 + q * 8)) = pk;
-                }
+            for (int q = 0; q < 4; q++) {  // 8 halves = one 16-byte chunk
+                uint4 pk;
+                pk.x = pack_half2(v[8 * q + 0], v[8 * q + 1]);
+                pk.y = pack_half2(v[8 * q + 2], v[8 * q + 3]);
+                pk.z = pack_half2(v[8 * q + 4], v[8 * q + 5]);
+                pk.w = pack_half2(v[8 * q + 6], v[8 * q + 7]);
+                *reinterpret_cast<uint4*>(sW + swz_chunk_offset(my_row, cg * 32 + q * 8)) = pk;
             }
             fence_proxy_async_smem();  // W was written with ordinary stores; the MMA reads it through the async proxy
             __syncwarp();
-            if (lane == 0) mbar_arrive(&bars[kBarWFull + grp]);
+            if (lane == 0) mbar_arrive(&bars[kBarWFull]);
         }
     } else {
-        // ================================ drain warps (16-19) ================================
-        // Every tile: the dK accumulator [128 negatives x D] goes through a per-warp staging buffer in shared memory (128-byte
-        // rows, 16-byte chunks XOR-swizzled by row: conflict-free stores, and the layout a SWIZZLE_128B tensor map expects)
-        // and from there into global dK as one TMA reduce-add per 32 x 32 slab: the row blocks of a chunk add up there (dK is
-        // cleared by the first launch).  At the end of a block dQ leaves the same way: a plain store when this CTA ran the
-        // block's whole stream, a reduce-add when the stream was cut at a CTA boundary.  Rows past the chunk's end are
-        // clipped by the tensor maps.  Only real columns travel: D / 32 full slabs, then one narrow slab (its own tensor
-        // map, dense rows of `tail` floats) for the remainder rounded up to 4.  Two staging buffers alternate, so a slab
-        // is written while the TMA engine still reads the previous one.
-        int full_slabs = d.D / 32, tail = ((d.D % 32) + 3) & ~3;
-        if (tail == 32) {
-            full_slabs++;
-            tail = 0;
-        }
-        const int n_slabs = full_slabs + (tail > 0 ? 1 : 0);
-        const int wq = warp - kDrainWarp0;
-        unsigned char* scr0 = smem + LY::kDrain + wq * 8192;
-        int slab = 0;  // counts this warp's TMA operations: consecutive ones alternate between the two staging buffers
-        // one accumulator -> global memory; `release` is arrived on as soon as the accumulator's last slab is in registers
+        // ================================ drain warps (16-19 and 23-26) ================================
+        // Every tile: the dK accumulator [128 negatives x D] (two alternate, so the contraction of the next tile runs
+        // meanwhile) goes through per-warp staging slabs in shared memory (128-byte rows, 16-byte chunks XOR-swizzled by
+        // row: conflict-free stores, and the layout a SWIZZLE_128B tensor map expects) and from there into global dK as one
+        // TMA reduce-add per 32 x 32 slab: the row blocks of a chunk add up there (dK is cleared by the first launch).  At
+        // the end of a block dQ leaves the same way: a plain store when this CTA ran the block's whole stream, a reduce-add
+        // when the stream was cut at a CTA boundary.  Rows past the chunk's end are clipped by the tensor maps.  Drain warp
+        // dw takes lane quarter dw & 3 and the slabs of parity dw >> 2; two staging slabs alternate, so a slab is written
+        // while the TMA engine still reads the previous one.
+        // a warp reaches only the tensor-memory lanes 32 * (warp % 4) ... + 31: each set of four consecutive warps covers all quarters
+        const int wq = warp & 3, half = warp < kTmaWarp ? 0 : 1;
+        const int dw = half * 4 + wq;
+        unsigned char* scr0 = smem + LY::kDrain + dw * 8192;
+        int slab = 0;  // counts this warp's TMA operations: consecutive ones alternate between the two staging slabs
+        int my_last = -1;  // the last slab this warp drains (-1: none)
+        for (int cb = half; cb < drain_slabs; cb += 2) my_last = cb;
+        // one accumulator -> global memory; `release` is arrived on as soon as this warp's last slab is in registers
         auto drain = [&](uint32_t tacc, const CUtensorMap* map_full, const CUtensorMap* map_tail, int y, int z, bool reduce, int release) {
             // The coordinates are pinned in ordinary registers here, where the whole warp is active: taken straight from the
             // index arithmetic into the one-lane section below, the third coordinate was seen to reach the store as 0.
             asm volatile("" : "+r"(y), "+r"(z));
+            if (my_last < 0) {
+                if (lane == 0) mbar_arrive(&bars[release]);
+                return;
+            }
 #pragma unroll 1
-            for (int cb = 0; cb < n_slabs; cb++) {
+            for (int cb = half; cb < drain_slabs; cb += 2) {
                 float v[32];
                 tmem_ld_32x32(tacc + lane_sel + cb * 32, v);  // warp-collective
-                if (cb == n_slabs - 1) {
+                if (cb == my_last) {
                     tc_fence_before();
                     __syncwarp();
                     if (lane == 0) mbar_arrive(&bars[release]);
                 }
                 unsigned char* scr = scr0 + (slab++ & 1) * 4096;
-                if (lane == 0) bulk_wait_group_read<1>();  // the operation that last used this buffer (two slabs ago) has read it
+                if (lane == 0) bulk_wait_group_read<1>();  // the operation that last used this slab (two operations ago) has read it
                 __syncwarp();
                 const bool narrow = cb == full_slabs;
                 if (!narrow) {
@@ -949,9 +948,9 @@ __global__ void __launch_bounds__(kThreads, 1)
                 // this CTA runs the whole stream of the block iff it starts at tile 0 and the block's last tile is in its range
                 whole = un.tile == 0 && (ub + it + sc.T <= ue);
             }
-            if (!warp_wait(kBarDkFull, it & 1)) { ok = false; break; }
+            if (!warp_wait(kBarDkFull + (it & 1), (it >> 1) & 1)) { ok = false; break; }
             tc_fence_after();
-            drain(tdK, &tmDK, &tmDKt, un.tile * BN + wq * 32, un.zc, true, kBarDkEmpty);
+            drain(tdK0 + (it & 1) * 128, &tmDK, &tmDKt, un.tile * BN + wq * 32, un.zc, true, kBarDkEmpty + (it & 1));
             if (it == n_iter - 1 || un.tile == sc.T - 1) {
                 if (!warp_wait(kBarDqFull, sg & 1)) { ok = false; break; }
                 tc_fence_after();
@@ -967,7 +966,8 @@ __global__ void __launch_bounds__(kThreads, 1)
     if (warp == kMmaWarp) {
         if (*s_abort && lane == 0) {
             for (int k = 0; k < kStages; k++) mbar_wait(&bars[kBarYFull + k], 0, 1u << 14);
-            for (int k = 0; k < 2; k++) mbar_wait(&bars[kBarAccFull + k], 0, 1u << 14);
+            for (int k = 0; k < 2; k++) mbar_wait(&bars[kBarDkFull + k], 0, 1u << 14);
+            mbar_wait(&bars[kBarDqFull], 0, 1u << 14);
         }
         __syncwarp();
         tc_fence_after();
@@ -1079,7 +1079,7 @@ int launch(const LpKernelArgs& a, cudaStream_t stream) {
         GE2_CUDA_TRY(launch_after(lp_lse_kernel<DP>, dim3((unsigned)sc.gridA), dim3(kThreads), Layout<DP>::kDynamicA, stream, tmQ, tmK, a, sc));
     }
     if (only != 1) {
-        GE2_CUDA_TRY(launch_after(lp_grad_kernel<DP>, dim3((unsigned)sc.gridB), dim3(kThreads), Layout<DP>::kDynamicB, stream, tmQ, tmK, tmDK, tmDKt, tmDQ,
+        GE2_CUDA_TRY(launch_after(lp_grad_kernel<DP>, dim3((unsigned)sc.gridB), dim3(kThreadsB), Layout<DP>::kDynamicB, stream, tmQ, tmK, tmDK, tmDKt, tmDQ,
                                   tmDQt, a, sc));
     }
     return GE2_OK;
