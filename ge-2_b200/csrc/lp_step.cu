@@ -34,25 +34,6 @@ __global__ void __launch_bounds__(256) mask_from_pairs_kernel(const int64_t* __r
     }
 }
 
-// deg_negative_local_filter on the device (negative.cpp:215-263): entry (c, j) masks row deg_rows[c][j] when that
-// row belongs to chunk c.  Same mask for both sides (the reference shares one filter tensor, negative.cpp:1049-1056).
-__global__ void __launch_bounds__(256) mask_from_deg_rows_kernel(const int64_t* __restrict__ deg_rows, int C, int n_deg, int npc, int B,
-                                                                 int N, int S, int64_t CN, int32_t* __restrict__ mask, int32_t* status) {
-    const int64_t total = (int64_t)C * n_deg;
-    const int64_t stride = (int64_t)gridDim.x * blockDim.x;
-    for (int64_t e = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; e < total; e += stride) {
-        const int c = (int)(e / n_deg), j = (int)(e % n_deg);
-        const int64_t row = deg_rows[e];
-        if (row < 0 || row >= B) {
-            or_status(status, GE2_STATUS_BAD_INDEX);
-            continue;
-        }
-        if ((int)(row / npc) == c) {
-            for (int s = 0; s < S; s++) mask[s * CN + (int64_t)c * N + j] = (int32_t)row;
-        }
-    }
-}
-
 // four consecutive columns [k, k+4) of a row of length D; columns past D read as zero.  `vec` = the row start is
 // 16-byte aligned and D % 4 == 0, so one vector load serves; otherwise 8-byte pairs (k even) or scalars.
 __device__ __forceinline__ float4 load4(const float* __restrict__ row, int k, int D, bool vec) {
@@ -166,6 +147,19 @@ __global__ void __launch_bounds__(256) lp_prep_kernel(LpKernelArgs a) {
             const int64_t id = (s == 0 ? d.dst_negs : d.src_negs)[j];
             const bool bad = id < 0 || id >= d.U;
             if (bad && gl == 0) or_status(d.status, GE2_STATUS_BAD_INDEX);
+            if (gl == 0 && d.deg_sample_rows != nullptr) {
+                // the filter word of this (side, chunk, column): deg_negative_local_filter on the device (negative.cpp:215-263 of
+                // the reference): entry (c, col) masks row deg_rows[c][col] when that row belongs to chunk c; the same for both
+                // sides (the reference shares one filter tensor, negative.cpp:1049-1056)
+                const int c = (int)(j / d.N), col = (int)(j - (int64_t)c * d.N);
+                int32_t m = -1;
+                if (col < d.n_deg) {
+                    const int64_t r = d.deg_sample_rows[(int64_t)c * d.n_deg + col];
+                    if (r < 0 || r >= d.B) or_status(d.status, GE2_STATUS_BAD_INDEX);
+                    else if ((int)(r / L.npc) == c) m = (int32_t)r;
+                }
+                L.mask[e] = m;
+            }
             const float* src = bad ? nullptr : emb_row(d, id);
             for (int k = gl * 4; k < ld; k += 32) {
                 const float4 v = bad ? make_float4(0.f, 0.f, 0.f, 0.f) : load4(src, k, D, vec_e);
@@ -500,12 +494,8 @@ extern "C" int ge2_lp_step(const ge2_lp_desc* desc, ge2_stream_t stream_) {
     if ((phases & 4) && !(desc->flags & GE2_LP_NODE_GRAD_IS_ZERO))
         GE2_CUDA_TRY(cudaMemsetAsync(desc->node_grad, 0, (size_t)desc->U * desc->D * 4, stream));
     if (phases & 1) {
-    GE2_CUDA_TRY(cudaMemsetAsync(L.mask, 0xFF, (size_t)L.S * L.CN * 4, stream));
-    if (desc->deg_sample_rows != nullptr) {
-        mask_from_deg_rows_kernel<<<stream_grid((int64_t)desc->C * desc->n_deg, 256), 256, 0, stream>>>(
-            desc->deg_sample_rows, desc->C, desc->n_deg, L.npc, desc->B, desc->N, L.S, L.CN, L.mask, desc->status);
-        GE2_LAUNCH_CHECK();
-    } else {
+    if (desc->deg_sample_rows == nullptr) {  // (with the degree-sample plan the prepare kernel writes every filter word itself)
+        GE2_CUDA_TRY(cudaMemsetAsync(L.mask, 0xFF, (size_t)L.S * L.CN * 4, stream));
         if (desc->dst_filter_n > 0) {
             mask_from_pairs_kernel<<<stream_grid(desc->dst_filter_n, 256), 256, 0, stream>>>(desc->dst_filter, desc->dst_filter_n, L.npc, L.Bp,
                                                                                            desc->N, L.mask, desc->status);

@@ -487,8 +487,7 @@ class BatchPipeline:
         """Kernels of libge2_b200.so launched per step (memsets not counted)."""
         cfg = self.cfg
         n = 1 + 3                              # sampler; unique-map: mark, scan, inverse
-        n += 1 if cfg.n_deg > 0 else 0         # filter mask from the degree-sampled rows
-        n += 1                                 # prepare (gather + relation operator + positive scores)
+        n += 1                                 # prepare (gather + relation operator + positive scores + filter words)
         n += 2 if cfg.precision == "f16" else 1  # scores: logsumexp pass + gradient pass (persistent launches), or the fp32 kernel
         n += 1                                 # finish (operator backward + scatter)
         n += 1                                 # sparse Adagrad scatter
