@@ -239,6 +239,8 @@ __global__ void __launch_bounds__(kFinWarps * 32) lp_finish_kernel(LpKernelArgs 
 
     // the negatives of this CTA: one row of dK each, added to the gradient row of the node it was drawn as
     auto scatter_negatives = [&]() {
+        // A row whose node holds a shared-memory row (claimed by the edges of this CTA: a hub) is summed there: with
+        // negatives drawn by degree a hub node owns thousands of these rows, and their atomics would serialise in L2.
         for (int64_t w = n_begin + warp; w < n_end; w += kFinWarps) {
             const int64_t e = w - e_rows;
             const int s = (int)(e / L.CN);
@@ -246,6 +248,14 @@ __global__ void __launch_bounds__(kFinWarps * 32) lp_finish_kernel(LpKernelArgs 
             const int64_t id = (s == 0 ? d.dst_negs : d.src_negs)[j];
             if (id < 0 || id >= d.U) continue;
             const float* dk = L.dK + e * ld;
+            const int sidx = (int)(((unsigned long long)id * 0x9E3779B97F4A7C15ull) >> 61);
+            if (sm.hot_tag[sidx] == id) {
+                for (int k = lane; k < D; k += 32) {
+                    const float v = dk[k] * gs;
+                    if (v != 0.f) atomicAdd(&sm.hot[sidx][k], v);
+                }
+                continue;
+            }
             float* grow = d.node_grad + id * D;
             if (vec_g) {
                 for (int k = lane * 4; k < D; k += 128) {
@@ -293,10 +303,6 @@ __global__ void __launch_bounds__(kFinWarps * 32) lp_finish_kernel(LpKernelArgs 
                     sm.slot[s][tid] = slot;
                 }
             }
-        }
-        if (!negs_done) {  // while the scalars of the first batch are on their way, the other warps start on the negatives
-            scatter_negatives();
-            negs_done = true;
         }
         __syncthreads();
         if (tid < 2 * kFinEdgeBatch) {  // thread (side, k): does the row of this endpoint occur again in the batch, or hold a slot already?
@@ -404,6 +410,10 @@ __global__ void __launch_bounds__(kFinWarps * 32) lp_finish_kernel(LpKernelArgs 
                     atomicAdd(gdst + c2, gd1);
                 }
             }
+        }
+        if (!negs_done) {  // after the first batch of edges, whose endpoints have claimed the shared-memory rows of the hubs
+            scatter_negatives();
+            negs_done = true;
         }
         __syncthreads();  // the batch's scalars are overwritten by the next batch
     }
