@@ -91,8 +91,7 @@ enum Bar { kBarXFull = 0, kBarXEmpty, kBarYFull, kBarYEmpty = kBarYFull + kMaxSt
 struct Sched {
     int RB, T, ZC;       // row blocks per chunk, negative tiles per chunk, sides * chunks
     int unitsA, gridA;   // lse pass: unit = (zc, row block, tile), numbered (zc * RB + rb) * T + tile
-    int unitsB, gridB;   // gradient pass: units [0, unitsA) as above (X = Q block, stream over the K tiles), then units
-                         // unitsA + (zc * T + tile) * RB + rb (X = K tile, stream over the Q blocks)
+    int unitsB, gridB;   // gradient pass: the same units (X = Q block, stream over the K tiles)
 };
 __host__ __device__ __forceinline__ int range_begin(int k, int units, int grid) { return (int)(((long long)k * units) / grid); }
 __host__ __device__ __forceinline__ int cta_of_unit(int u, int units, int grid) { return (int)((((long long)u + 1) * grid - 1) / units); }
@@ -107,7 +106,6 @@ struct Layout {
     static constexpr int kW = kY + kStages * kTileBytes;
     // --- gradient pass ---
     static constexpr int kMiscB = kW + kWBytes;                   // barriers, tensor-memory address, abort flag
-    static constexpr int kLseRing = kMiscB + 512;                 // kStages x 128 floats: lse of the rows of the Y tile in the same stage
     static constexpr int kDrain = kMiscB + 2048;                  // 8 drain warps x 2 slabs (32 rows x 128 bytes), 128-byte swizzled
     static constexpr int kEndB = kDrain + kDrainWarps * 2 * 4096;
     static constexpr int kDynamicB = kEndB + 1024;                // 1024 bytes of slack to align the base
@@ -175,32 +173,6 @@ __device__ __forceinline__ UnitA decode_a(int u, const Sched& sc) {
     r.rb = r.item - r.zc * sc.RB;
     return r;
 }
-// ... and of the gradient pass: `x_blk` / `y_blk` are 128-row block indices into the chunk's stationary / streamed matrix
-struct UnitB {
-    int kind;     // 0: X = Q block, Y = K tiles (dQ);  1: X = K tile, Y = Q blocks (dK)
-    int zc, x_blk, y_blk, n_stream;
-};
-__device__ __forceinline__ UnitB decode_b(int u, const Sched& sc) {
-    UnitB r;
-    if (u < sc.unitsA) {
-        const int item = u / sc.T;
-        r.kind = 0;
-        r.n_stream = sc.T;
-        r.y_blk = u - item * sc.T;
-        r.zc = item / sc.RB;
-        r.x_blk = item - r.zc * sc.RB;
-    } else {
-        const int v = u - sc.unitsA;
-        const int item = v / sc.RB;
-        r.kind = 1;
-        r.n_stream = sc.RB;
-        r.y_blk = v - item * sc.RB;
-        r.zc = item / sc.T;
-        r.x_blk = item - r.zc * sc.T;
-    }
-    return r;
-}
-
 // The loops walk their units with these instead of decoding every index (no divisions inside the pipelines).
 struct IterA {
     int item, tile, rb, zc;
@@ -216,23 +188,6 @@ struct IterA {
         }
     }
 };
-struct IterB {
-    int kind, zc, x_blk, y_blk, n_stream;
-    __device__ __forceinline__ IterB(int u, const Sched& sc) {
-        const UnitB un = decode_b(u, sc);
-        kind = un.kind, zc = un.zc, x_blk = un.x_blk, y_blk = un.y_blk, n_stream = un.n_stream;
-    }
-    __device__ __forceinline__ void next(const Sched& sc) {
-        if (++y_blk == n_stream) {
-            y_blk = 0;
-            if (++x_blk == (kind == 0 ? sc.RB : sc.T)) {
-                x_blk = 0;
-                if (++zc == sc.ZC && kind == 0) zc = 0, kind = 1, n_stream = sc.RB;  // the K-stationary units follow the Q-stationary ones
-            }
-        }
-    }
-};
-
 // =====================================================================================================================
 // launch 1: row logsumexp
 // =====================================================================================================================
