@@ -274,7 +274,8 @@ def reference_arm(args):
         "reference C++/libtorch decoder+loss+autograd+accumulateGradients, torch.unique for its broken CPU map_tensors" if cpu.kind == "reference" else "numpy restatement") + ")"
     line = dict(metric="train edges/sec/box", value=value, unit="edges/s", n_gpus=args.gpus, steps=args.steps, warmup=args.warmup,
                 ms_per_step=1e3 * dt / steps_run, higher_is_better=True, scaling="weak", vs_baseline=None, dtype="f32", data="synthetic",
-                impl="reference", config=dict(workload=cfg["name"], steps_run=steps_run),
+                impl="reference", config=dict(workload=cfg["name"] + (f", weak-scaled: {args.gpus} x nodes and triples, {4 * args.gpus} partitions" if args.gpus > 1 else ""),
+                                              steps_run=steps_run, note="the per-batch step of this workload (same batch, negatives and resident-domain sizes) on the host cores"),
                 cpu_baseline=dict(value=value, unit="edges/s", cores=cpu.cores, kind=cpu.kind, sample=sample),
                 e2e=dict(value=value, unit="edges/s", h2d_bytes_per_step=0, d2h_bytes_per_step=0))
     print(json.dumps(line), flush=True)
