@@ -104,6 +104,12 @@ __global__ void __launch_bounds__(256) index_rows_kernel(float* __restrict__ tab
         const int64_t row = __ldg(&ids[l]);
         if (row < 0 || row >= table_rows) {
             or_status(status, GE2_STATUS_BAD_INDEX);
+            if (!kAdd) {  // a row outside the table reads as zeros
+                float z[V];
+#pragma unroll
+                for (int k = 0; k < V; k++) z[k] = 0.f;
+                reinterpret_cast<VT*>(dense)[i] = from_arr<V>(z);
+            }
             continue;
         }
         VT* trow = reinterpret_cast<VT*>(table) + row * vec_per_row + c;

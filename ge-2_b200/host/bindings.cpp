@@ -76,5 +76,6 @@ PYBIND11_MODULE(ge2_host, m) {
         .def(py::init<torch::Tensor>())
         .def("indexRead", &InMemory::indexRead)
         .def("indexAdd", &InMemory::indexAdd)
+        .def("checkStatus", &InMemory::checkStatus)
         .def_readwrite("data", &InMemory::data_);
 }

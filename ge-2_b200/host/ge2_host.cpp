@@ -315,10 +315,20 @@ torch::Tensor InMemory::indexRead(Indices indices) {
     c10::cuda::CUDAGuard guard(data_.device());
     indices = indices.to(data_.device()).contiguous();
     auto out = torch::empty({indices.size(0), data_.size(1)}, data_.options());
+    if (!status_.defined()) status_ = torch::zeros({1}, data_.options().dtype(torch::kInt32));
     check(ge2_index_read(data_.data_ptr<float>(), data_.size(0), indices.data_ptr<int64_t>(), indices.size(0), nullptr, (int32_t)data_.size(1),
-                         out.data_ptr<float>(), nullptr, current_stream(data_)),
+                         out.data_ptr<float>(), status_.data_ptr<int32_t>(), current_stream(data_)),
           "ge2_index_read");
     return out;
+}
+
+void InMemory::checkStatus() {
+    if (!status_.defined()) return;
+    const int32_t word = status_.cpu().item<int32_t>();
+    if (word) {
+        status_.zero_();
+        throw GegeRuntimeException("storage index out of range (device status " + std::to_string(word) + ")");
+    }
 }
 
 void InMemory::indexAdd(Indices indices, torch::Tensor values) {
@@ -328,8 +338,9 @@ void InMemory::indexAdd(Indices indices, torch::Tensor values) {
     c10::cuda::CUDAGuard guard(data_.device());
     indices = indices.contiguous();
     values = values.contiguous();
+    if (!status_.defined()) status_ = torch::zeros({1}, data_.options().dtype(torch::kInt32));
     check(ge2_index_add(data_.data_ptr<float>(), data_.size(0), indices.data_ptr<int64_t>(), indices.size(0), nullptr, (int32_t)data_.size(1),
-                        values.data_ptr<float>(), nullptr, current_stream(data_)),
+                        values.data_ptr<float>(), status_.data_ptr<int32_t>(), current_stream(data_)),
           "ge2_index_add");
 }
 

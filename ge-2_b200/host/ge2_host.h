@@ -108,7 +108,13 @@ class InMemory {
     explicit InMemory(torch::Tensor data) : data_(std::move(data)) {}
     torch::Tensor indexRead(Indices indices);
     void indexAdd(Indices indices, torch::Tensor values);
+    // An index outside the table is skipped on the device (rows read as zero) and recorded in a status word; the reference's
+    // index ops throw at once, here the word is read where the caller synchronises anyway: throws GegeRuntimeException.
+    void checkStatus();
     torch::Tensor data_;
+
+   private:
+    torch::Tensor status_;
 };
 
 // Partition buffer over the GPUs of this process: every partition has a home slab on device p % G; a device's active set of

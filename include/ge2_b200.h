@@ -183,7 +183,8 @@ GE2_API int ge2_sparse_adagrad(const float *grad, float *state_local, float *out
 
 /* Storage::indexRead / indexAdd for device tables (cpp/include/storage/storage.h:49-51;
  * InMemory: cpp/src/storage/storage.cpp:1173-1259; MemPartitionBuffer: cpp/src/storage/buffer.cpp:973-1045,1221-1228).
- * ids must be distinct for index_add (the reference relies on that too, buffer.cpp:619). */
+ * ids must be distinct for index_add (the reference relies on that too, buffer.cpp:619).  An id outside [0, table_rows) sets
+ * GE2_STATUS_BAD_INDEX in *status (may be NULL); index_read writes a zero row for it, index_add skips it. */
 GE2_API int ge2_index_read(const float *table, int64_t table_rows, const int64_t *ids, int64_t n, const int32_t *n_dev, int32_t D,
                    float *out, int32_t *status, ge2_stream_t stream);
 GE2_API int ge2_index_add(float *table, int64_t table_rows, const int64_t *ids, int64_t n, const int32_t *n_dev, int32_t D,

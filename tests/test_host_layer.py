@@ -110,6 +110,13 @@ def test_map_tensors_and_storage(host, cuda_device):
     assert np.array_equal(st.data.cpu().numpy(), table)
     with pytest.raises(RuntimeError):
         st.indexAdd(torch.from_numpy(ids).to(cuda_device), torch.from_numpy(vals[:2]).to(cuda_device))
+    # an index outside the table: skipped on the device, reported at the next status check (the reference's index ops throw)
+    st.checkStatus()
+    got = st.indexRead(torch.tensor([3, 100, 7], device=cuda_device))
+    assert np.array_equal(got.cpu().numpy()[[0, 2]], table[[3, 7]]) and float(got[1].abs().max()) == 0.0
+    with pytest.raises(host.GegeRuntimeException, match="out of range"):
+        st.checkStatus()
+    st.checkStatus()  # the word was cleared
 
 
 def _n_devices():
