@@ -358,6 +358,54 @@ def host_cpp_ms(cfg, table, state, edges, steps, device, precision):
     return a.elapsed_time(b) / steps
 
 
+def unique_sweep(device):
+    """`--unique-sweep`: ge2_unique_bitmap (graph replay and host-issued) against the reference's own CUDA unique-map (bitmap
+    backend, oracle/_ref/gege_ref_cuda.so: test infrastructure) on the (n_ids, domain) pairs of the five configurations,
+    uniform random ids, CUDA events over 50 calls.  Prints one JSON line."""
+    pkg = importlib.import_module("ge-2_b200")
+    pkg.load_library()
+    capi = pkg.capi
+    os.environ.setdefault("GEGE_UNIQUE_BACKEND", "bitmap")
+    for k in ("GEGE_CSR_GATHER", "GEGE_CSR_DEBUG", "GEGE_STAGE_DEBUG"):
+        os.environ.setdefault(k, "0")
+    try:
+        import gege_ref_cuda as G
+    except Exception:
+        G = None
+
+    def ev(fn, reps=50):
+        for _ in range(5):
+            fn()
+        torch.cuda.synchronize()
+        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        a.record()
+        for _ in range(reps):
+            fn()
+        b.record()
+        torch.cuda.synchronize()
+        return a.elapsed_time(b) / reps * 1e3
+
+    rows = []
+    for n, dom in ((22_000, 14_951), (40_000, 1_000_000), (150_000, 1_211_896), (150_000, 10_413_060), (600_000, 12_500_000)):
+        g = torch.Generator(device=device).manual_seed(n)
+        ids = torch.randint(0, dom, (n,), device=device, generator=g)
+        ws = capi.unique_workspace(dom, device)
+        uq = torch.empty(min(n, dom), dtype=torch.int64, device=device)
+        inv = torch.empty(n, dtype=torch.int64, device=device)
+        cnt = torch.zeros(2, dtype=torch.int32, device=device)
+        call = lambda: capi.unique_bitmap(ids, dom, workspace=ws, out_unique=uq, out_inverse=inv, out_count=cnt)
+        host_us = ev(call)
+        gr = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(gr):
+            call()
+        graph_us = ev(gr.replay)
+        ref_us = ev(lambda: G.unique_inverse_cuda(ids, False, dom), reps=20) if G is not None else None
+        rows.append(dict(n_ids=n, domain=dom, distinct=int(cnt[0]), graph_us=round(graph_us, 1), host_issued_us=round(host_us, 1),
+                         reference_kernel_us=None if ref_us is None else round(ref_us, 1),
+                         algorithmic_bytes=16 * n + 8 * int(cnt[0])))
+    print(json.dumps(dict(unique_sweep=rows)), flush=True)
+
+
 def bucket_sizes_of(cfg, P, psize, seed, device):
     """sizes of all P * P buckets of the graph make_partitioned_edges generates (a counting pass over the same draws)"""
     return make_partitioned_edges(cfg, P, psize, [], seed, device, count_only=True)[1]
@@ -759,6 +807,7 @@ def main():
     ap.add_argument("--no-graph", action="store_true", help="N = 1: issue every launch from the host instead of replaying a CUDA graph")
     ap.add_argument("--no-pipeline", action="store_true", help="N = 1: do not draw batch t+1 on a side stream while batch t trains")
     ap.add_argument("--cpu-budget", type=float, default=15.0)
+    ap.add_argument("--unique-sweep", action="store_true", help="time the unique-map on the five (n_ids, domain) pairs against the reference's kernel and exit")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3)
 
@@ -773,6 +822,10 @@ def main():
         raise SystemExit("bench.py needs a CUDA device: the hot path has no CPU fallback")
     torch.cuda.set_device(local_rank)
     device = torch.device("cuda", local_rank)
+    if args.unique_sweep:
+        if rank == 0:
+            unique_sweep(device)
+        return
     if world > 1:
         import torch.distributed as dist
 
