@@ -3,11 +3,12 @@
 // Stands in for the bitmap backend of the reference's map_tensors_unique_inverse_cuda
 // (cuda/src/common/unique_map_cuda.cu:771-882 of the reference project: memset, mark, popcount, CUB scan,
 // extract, inverse, two stream syncs and four scalar read-backs).  Here:
-//   memset(bitset)                                       cudaMemsetAsync
+//   memset(control words + bitset)                       one cudaMemsetAsync (they are adjacent in the workspace)
 //   mark_kernel        ids -> bits                       n threads, 64-bit atomicOr (red) into an L2-resident bitset
 //   scan_extract_kernel popcount + exclusive scan + emit  one pass over the words; tiles chained by a
 //                                                        decoupled look-back (ticketed, bounded spin)
-//   inverse_kernel     rank of every input id            n threads
+//   inverse_kernel     rank of every input id            n threads; also hands the status word to the caller
+// The scan and the inverse kernel are launched with programmatic dependent launch behind their predecessors.
 // The bitset (domain/8 bytes) and the per-word offsets (domain/16 bytes) stay in the 126 MB L2 for every
 // configuration of interest (12.5 M-node domain: 1.6 MB + 0.8 MB), so HBM traffic is the ids in and the two
 // outputs: 16 n + 8 U bytes.
@@ -25,11 +26,20 @@ constexpr uint32_t kValueMask = (1u << 30) - 1;
 constexpr int kSpinLimit = 1 << 20;                          // look-back poll budget before giving up
 
 struct UniqueWorkspace {
+    uint32_t* tile_state;       // [num_tiles]   } control words: cleared together with the bitset by one memset
+    uint32_t* ticket;           // [1]           }
+    int32_t* status;            // [1]           } GE2_STATUS_* bits of this call
     unsigned long long* words;  // [num_words]
     int32_t* word_offsets;      // [num_words]
-    uint32_t* tile_state;       // [num_tiles]
-    uint32_t* ticket;           // [1]
 };
+
+constexpr size_t align256c(size_t x) { return (x + 255) & ~(size_t)255; }
+// control words (tile states, ticket, status, one spare), bitset, per-word offsets
+constexpr size_t unique_ws_bytes(int64_t domain) {
+    const int64_t nw = (domain + 63) >> 6;
+    const int64_t tiles = (nw + 1023) / 1024;
+    return align256c((size_t)(tiles + 4) * 4) + align256c((size_t)nw * 8) + align256c((size_t)nw * 4);
+}
 
 __host__ __device__ inline int64_t num_words_of(int64_t domain) { return (domain + 63) >> 6; }
 
@@ -53,11 +63,13 @@ __global__ void __launch_bounds__(256) mark_kernel(const int64_t* __restrict__ i
 __global__ void __launch_bounds__(kScanThreads) scan_extract_kernel(const unsigned long long* __restrict__ words, int64_t num_words,
                                                                     int32_t* __restrict__ word_offsets, uint32_t* tile_state,
                                                                     uint32_t* ticket, int num_tiles, int64_t* __restrict__ out_unique,
-                                                                    int64_t out_capacity, int32_t* __restrict__ out_count) {
+                                                                    int64_t out_capacity, int32_t* __restrict__ out_count,
+                                                                    int32_t* __restrict__ status) {
     __shared__ uint32_t s_warp_sums[kScanThreads / 32];
     __shared__ uint32_t s_tile;
     __shared__ uint32_t s_prefix;
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    griddep_wait();  // the bitset comes from the marking kernel
 
     for (;;) {
         if (tid == 0) s_tile = atomicAdd(ticket, 1u);
@@ -119,7 +131,7 @@ __global__ void __launch_bounds__(kScanThreads) scan_extract_kernel(const unsign
                         break;
                     }
                 }
-                if (failed) atomicOr(&out_count[1], GE2_STATUS_SCAN_TIMEOUT);
+                if (failed) atomicOr(status, GE2_STATUS_SCAN_TIMEOUT);
                 __threadfence();
                 atomicExch(&tile_state[tile], kFlagPrefix | ((prefix + tile_total) & kValueMask));
             }
@@ -150,7 +162,10 @@ __global__ void __launch_bounds__(kScanThreads) scan_extract_kernel(const unsign
 
 __global__ void __launch_bounds__(256) inverse_kernel(const int64_t* __restrict__ ids, int64_t n, int64_t domain,
                                                       const unsigned long long* __restrict__ words,
-                                                      const int32_t* __restrict__ word_offsets, int64_t* __restrict__ inverse) {
+                                                      const int32_t* __restrict__ word_offsets, int64_t* __restrict__ inverse,
+                                                      const int32_t* __restrict__ status, int32_t* __restrict__ out_status) {
+    griddep_wait();  // offsets and the count come from the scan kernel
+    if (blockIdx.x == 0 && threadIdx.x == 0) *out_status = *status;  // the marking and scan kernels are over: the word is final
     int64_t stride = (int64_t)gridDim.x * blockDim.x;
     for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += stride) {
         int64_t key = ids[i];
@@ -180,8 +195,6 @@ __global__ void pack_ids_kernel(const int64_t* p0, const int64_t* p1, const int6
     }
 }
 
-inline size_t align256(size_t x) { return (x + 255) & ~(size_t)255; }
-
 }  // namespace
 }  // namespace ge2
 
@@ -189,9 +202,7 @@ using namespace ge2;
 
 extern "C" size_t ge2_unique_workspace_bytes(int64_t domain) {
     if (domain <= 0) return 0;
-    const int64_t nw = num_words_of(domain);
-    const int64_t tiles = ceil_div<int64_t>(nw, kTileWords);
-    return align256((size_t)nw * 8) + align256((size_t)nw * 4) + align256((size_t)(tiles + 1) * 4);
+    return unique_ws_bytes(domain);
 }
 
 extern "C" int ge2_unique_bitmap(const int64_t* ids, int64_t n, int64_t domain, void* workspace, size_t workspace_bytes,
@@ -200,8 +211,10 @@ extern "C" int ge2_unique_bitmap(const int64_t* ids, int64_t n, int64_t domain, 
     if (n > 0 && (ids == nullptr || out_unique == nullptr || out_inverse == nullptr)) return GE2_ERR_INVALID_ARGUMENT;
     if (n > (int64_t)kValueMask) return GE2_ERR_UNSUPPORTED;  // the reference stops at INT32_MAX ids (unique_map_cuda.cu:784); the packed tile state here holds 30 bits
     cudaStream_t stream = as_stream(stream_);
-    GE2_CUDA_TRY(cudaMemsetAsync(out_count, 0, 2 * sizeof(int32_t), stream));
-    if (n == 0) return GE2_OK;
+    if (n == 0) {
+        GE2_CUDA_TRY(cudaMemsetAsync(out_count, 0, 2 * sizeof(int32_t), stream));
+        return GE2_OK;
+    }
     const int64_t nw = num_words_of(domain);
     if (nw > (int64_t)kValueMask) return GE2_ERR_UNSUPPORTED;
     const int64_t tiles = ceil_div<int64_t>(nw, kTileWords);
@@ -210,26 +223,28 @@ extern "C" int ge2_unique_bitmap(const int64_t* ids, int64_t n, int64_t domain, 
 
     char* p = (char*)workspace;
     UniqueWorkspace ws;
-    ws.words = (unsigned long long*)p;
-    p += align256((size_t)nw * 8);
-    ws.word_offsets = (int32_t*)p;
-    p += align256((size_t)nw * 4);
     ws.tile_state = (uint32_t*)p;
     ws.ticket = ws.tile_state + tiles;
+    ws.status = (int32_t*)(ws.tile_state + tiles + 1);
+    const size_t ctl_bytes = align256c((size_t)(tiles + 4) * 4);
+    p += ctl_bytes;
+    ws.words = (unsigned long long*)p;
+    p += align256c((size_t)nw * 8);
+    ws.word_offsets = (int32_t*)p;
 
-    // bitset and tile states/ticket are contiguous apart from word_offsets: two memsets
-    GE2_CUDA_TRY(cudaMemsetAsync(ws.words, 0, (size_t)nw * 8, stream));
-    GE2_CUDA_TRY(cudaMemsetAsync(ws.tile_state, 0, (size_t)(tiles + 1) * 4, stream));
+    // control words and bitset are adjacent: one memset; out_count needs none (the scan's last tile writes the count, the
+    // inverse kernel the status)
+    GE2_CUDA_TRY(cudaMemsetAsync(ws.tile_state, 0, ctl_bytes + (size_t)nw * 8, stream));
 
-    mark_kernel<<<stream_grid(n, 256), 256, 0, stream>>>(ids, n, domain, ws.words, out_count + 1);
+    mark_kernel<<<stream_grid(n, 256), 256, 0, stream>>>(ids, n, domain, ws.words, ws.status);
     GE2_LAUNCH_CHECK();
     const int64_t cap = n < domain ? n : domain;
     const int scan_grid = (int)(tiles < (int64_t)kNumSMs * 4 ? tiles : (int64_t)kNumSMs * 4);
-    scan_extract_kernel<<<scan_grid, kScanThreads, 0, stream>>>(ws.words, nw, ws.word_offsets, ws.tile_state, ws.ticket, (int)tiles,
-                                                               out_unique, cap, out_count);
-    GE2_LAUNCH_CHECK();
-    inverse_kernel<<<stream_grid(n, 256), 256, 0, stream>>>(ids, n, domain, ws.words, ws.word_offsets, out_inverse);
-    GE2_LAUNCH_CHECK();
+    GE2_CUDA_TRY(launch_after(scan_extract_kernel, dim3((unsigned)scan_grid), dim3(kScanThreads), 0, stream, (const unsigned long long*)ws.words, nw,
+                              ws.word_offsets, ws.tile_state, ws.ticket, (int)tiles, out_unique, cap, out_count, ws.status));
+    GE2_CUDA_TRY(launch_after(inverse_kernel, dim3((unsigned)stream_grid(n, 256)), dim3(256), 0, stream, ids, n, domain,
+                              (const unsigned long long*)ws.words, (const int32_t*)ws.word_offsets, out_inverse, (const int32_t*)ws.status,
+                              out_count + 1));
     return GE2_OK;
 }
 
@@ -263,12 +278,7 @@ namespace ge2 {
 namespace {
 
 constexpr int64_t kStaticMaxDomain = GE2_UNIQUE_STATIC_MAX_DOMAIN;
-constexpr size_t static_ws_bytes(int64_t domain) {
-    const int64_t nw = (domain + 63) >> 6;
-    const int64_t tiles = (nw + kTileWords - 1) / kTileWords;
-    return (((size_t)nw * 8 + 255) & ~(size_t)255) + (((size_t)nw * 4 + 255) & ~(size_t)255) + (((size_t)(tiles + 1) * 4 + 255) & ~(size_t)255);
-}
-constexpr size_t kStaticBytes = static_ws_bytes(kStaticMaxDomain);
+constexpr size_t kStaticBytes = unique_ws_bytes(kStaticMaxDomain);
 
 static __device__ __align__(256) unsigned char g_unique_static_scratch[kStaticBytes];
 
