@@ -1,5 +1,7 @@
-"""Partition buffer across GPUs: schedule of partition-disjoint supersteps, bucket assignment, and partition swaps as
-NCCL send/recv (one process per GPU, torch.distributed for the plumbing).
+"""Partition buffer across GPUs (one process per GPU, torch.distributed for the plumbing): schedule of partition-disjoint
+supersteps, bucket assignment, and partition swaps -- RelayBuffer: device-side pulls over NVLink peer memory behind a
+device-side barrier (ge2_swap_begin), with the state's edge list rebuilt on the device and a trainer loop around both
+(PartitionedTrainer); PartitionBuffer: the same moves as NCCL send/recv, for processes that cannot map each other's memory.
 
 Mirrors, in the reference project (paths relative to gege/src/cpp/src): the partition buffer of
 storage/buffer.cpp and storage/storage.cpp:359-757 (MemPartitionBufferStorage, capacity 4, performNextSwap :576-689),
@@ -8,7 +10,8 @@ exchange of nn/model.cpp:174-204.  Differences, on purpose:
   * every partition has a home slab on one GPU (p % world), so a swap never touches host memory, also when
     world * capacity < num_partitions (the reference's peer relay requires equality and otherwise stages through the host);
   * an admitted partition is fetched from wherever it currently is -- another rank's active buffer (the reference's relay
-    copy) or its home -- and evicted partitions go home; all of it is one batch of NCCL point-to-point operations;
+    copy) or its home -- and evicted partitions go home; one copy kernel per table (RelayBuffer) or one batch of NCCL
+    point-to-point operations (PartitionBuffer);
   * the schedule is a round-robin design over pairs of partitions (every two partitions share a state at least once per
     epoch, states of one superstep are disjoint); the reference's own ordering code can be plugged in instead, the buffer
     only needs the list of states.

@@ -316,8 +316,8 @@ GE2_API int ge2_swap_wait(ge2_stream_t swap_stream, ge2_stream_t compute_stream)
 
 /* Slab copies of MemPartitionBufferStorage::performNextSwap's relay branch that stay on one device
  * (cpp/src/storage/storage.cpp:626-652, src_dev == device_idx): moves[k] = {src_slot, dst_slot}; copies whole
- * partition slabs src[src_slot] -> dst[dst_slot] in one launch.  Slabs that cross devices travel by NCCL send/recv
- * issued by the host layer. */
+ * partition slabs src[src_slot] -> dst[dst_slot] in one launch.  Slabs that cross devices are pulled by ge2_swap_begin
+ * (or travel by NCCL send/recv issued by the host layer when the processes cannot map each other's memory). */
 GE2_API int ge2_copy_slabs(const float *src, float *dst, const int32_t *moves_host, int32_t num_moves, int64_t slab_floats,
                    ge2_stream_t stream);
 
