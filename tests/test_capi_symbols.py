@@ -56,3 +56,24 @@ def test_desc_struct_matches_header_size(ge2):
         size, off_ws, off_rel = map(int, subprocess.run([str(exe)], capture_output=True, text=True).stdout.split())
     D = ge2.capi.LpDesc
     assert ctypes.sizeof(D) == size and D.workspace.offset == off_ws and D.rel.offset == off_rel
+
+
+def test_swap_and_eval_structs_match_header(ge2):
+    """the ctypes mirrors of ge2_swap_desc and ge2_eval_desc agree with the C structs in size and in the offsets of a few members"""
+    import subprocess
+    import tempfile
+
+    src = ('#include "ge2_b200.h"\n#include <stdio.h>\n#include <stddef.h>\nint main(){printf("%zu %zu %zu %zu %zu %zu", sizeof(ge2_swap_desc), '
+           'offsetof(ge2_swap_desc, slab_bytes), offsetof(ge2_swap_desc, status), sizeof(ge2_eval_desc), offsetof(ge2_eval_desc, neg_ids), '
+           'offsetof(ge2_eval_desc, workspace));return 0;}')
+    with tempfile.TemporaryDirectory() as td:
+        c = Path(td) / "p.c"
+        c.write_text(src)
+        exe = Path(td) / "p"
+        r = subprocess.run(["gcc", "-std=c99", "-I", str(ROOT / "include"), str(c), "-o", str(exe)], capture_output=True, text=True)
+        if r.returncode != 0:
+            pytest.skip("no C compiler: " + r.stderr[:80])
+        s_size, s_slab, s_status, e_size, e_neg, e_ws = map(int, subprocess.run([str(exe)], capture_output=True, text=True).stdout.split())
+    S, E = ge2.capi.SwapDesc, ge2.capi.EvalDesc
+    assert ctypes.sizeof(S) == s_size and S.slab_bytes.offset == s_slab and S.status.offset == s_status
+    assert ctypes.sizeof(E) == e_size and E.neg_ids.offset == e_neg and E.workspace.offset == e_ws
