@@ -184,3 +184,26 @@ def test_state_shuffle_is_a_permutation_and_edge_list_restatement():
         back[:, col] = np.array([inv[s] for s in out[:, col] // psize]) * psize + out[:, col] % psize
     exp = np.concatenate([es[begin[b]:begin[b] + sizes[b]] for b in bk])
     assert sorted(map(tuple, back.tolist())) == sorted(map(tuple, exp.tolist()))
+
+
+@pytest.mark.parametrize("P,world", [(8, 2), (16, 2), (16, 4), (32, 8)])
+def test_size_aware_bucket_assignment_covers_once_and_is_no_longer_than_greedy(P, world):
+    """With bucket sizes every ordered bucket is still trained exactly once, by a state that holds both of its partitions, and
+    the epoch (sum over supersteps of the longest lane) is not longer than with the first-fit assignment."""
+    import numpy as np
+
+    rng = np.random.default_rng(P * 31 + world)
+    w = rng.dirichlet(np.full(P, 0.3))                      # skewed partition weights, like a hub-heavy graph
+    sizes = (np.outer(w, w) * 50_000_000).astype(np.int64).reshape(-1)
+    steps = partition.make_supersteps(P, world)
+    greedy = partition.state_buckets(steps, P)
+    balanced = partition.state_buckets(steps, P, sizes)
+    seen = sorted(b for lanes in balanced for lane in lanes for b in lane)
+    assert seen == list(range(P * P))
+    for k, lanes in enumerate(balanced):
+        for r, lane in enumerate(lanes):
+            st = steps[k][r]
+            for b in lane:
+                assert st is not None and b // P in st and b % P in st
+    length = lambda assign: sum(max(sum(int(sizes[b]) for b in lane) for lane in lanes) for lanes in assign)
+    assert length(balanced) <= length(greedy)
