@@ -465,6 +465,26 @@ def eval_ranks(kind, table, rel, inv_rel, edges, dst_filter=None, src_filter=Non
     return out[0], out[1]
 
 
+def tournament_selected_scores(chunked: np.ndarray, negatives: np.ndarray, selected: int):
+    """The reference's tournament selection of negatives, selector = scorer
+    (cpp/src/nn/decoders/edge/distmult_selected_neg_cuda.cpp:46-121): chunked [C, rows, D] query rows, negatives [C, N, D];
+    the N negatives of a chunk form `selected` groups of N / selected consecutive ones, and every row keeps, per group, the
+    negative that scores highest against it (first one on a tie).  Returns (scores [C * rows, selected] float32,
+    indices [C, rows * selected] int64, the column of the kept negative in its chunk).  The training step then runs its
+    softmax over these `selected` scores instead of all N, and gradients reach only the kept negatives."""
+    C, R, D = chunked.shape
+    N = negatives.shape[1]
+    if N % selected:
+        raise ValueError("negatives_num must be divisible by selected_negatives_num")
+    T = N // selected
+    scores = np.einsum("crd,cnd->crn", chunked.astype(np.float64), negatives.astype(np.float64)).astype(np.float32)
+    view = scores.reshape(C, R, selected, T)
+    local = view.argmax(axis=3)
+    kept = np.take_along_axis(view, local[..., None], axis=3)[..., 0]
+    idx = local + np.arange(selected, dtype=np.int64)[None, None, :] * T
+    return kept.reshape(C * R, selected), idx.reshape(C, R * selected).astype(np.int64)
+
+
 def global_filter(all_edges: np.ndarray, edges: np.ndarray, inverse: bool) -> np.ndarray:
     """compute_filter_corruption with global = true (cpp/src/data/samplers/negative.cpp:421-568): for evaluation edge i all
     (i, n) such that replacing its destination (inverse: its source) by n gives an edge of `all_edges` (same relation when the

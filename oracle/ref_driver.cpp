@@ -19,6 +19,7 @@
 #include "common/util.h"
 #ifdef GEGE_CUDA
 #include "common/unique_map_cuda.h"
+#include "nn/decoders/edge/distmult_selected_neg_cuda.h"
 #endif
 #include "data/batch.h"
 #include "data/samplers/negative.h"
@@ -167,6 +168,13 @@ std::tuple<torch::Tensor, torch::Tensor, std::string> ref_unique_inverse_cuda(to
     auto tup = map_tensors_unique_inverse_cuda(ids, sorted, &info, domain);
     return {std::get<0>(tup).clone(), std::get<1>(tup).clone(), info.executed_backend};
 }
+
+// The reference's tournament selection of negatives (distmult_selected_neg_cuda.cpp:46-121): per row and per group of
+// consecutive negatives the best-scoring one; same embeddings as selector and as scorer.
+std::tuple<torch::Tensor, torch::Tensor> ref_tournament_selected_scores(torch::Tensor chunked, torch::Tensor negatives, int64_t selected,
+                                                                        int64_t groups_per_tile) {
+    return distmult_tiled_tournament_selected_scores(chunked, negatives, chunked, negatives, selected, groups_per_tile);
+}
 #endif
 
 }  // namespace
@@ -184,5 +192,6 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
     m.def("index_add", &ref_index_add);
 #ifdef GEGE_CUDA
     m.def("unique_inverse_cuda", &ref_unique_inverse_cuda, py::call_guard<py::gil_scoped_release>());
+    m.def("tournament_selected_scores", &ref_tournament_selected_scores, py::call_guard<py::gil_scoped_release>());
 #endif
 }

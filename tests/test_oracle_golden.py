@@ -118,3 +118,22 @@ def test_ranks_and_mrr():
     r = O.ranks_from_scores(pos, neg)
     assert r.tolist() == [3, 1]
     assert abs(O.mrr(r) - (1 / 3 + 1) / 2) < 1e-6
+
+
+def test_tournament_selection_restatement():
+    """Tournament selection of negatives (distmult_selected_neg_cuda.cpp:46-121) against the same steps in torch on CPU:
+    batched products, a view into groups of consecutive negatives, the maximum of each group and its column."""
+    import torch
+
+    rng = np.random.default_rng(5)
+    C, R, N, D, sel = 2, 17, 48, 16, 6
+    q = rng.standard_normal((C, R, D)).astype(np.float32)
+    k = rng.standard_normal((C, N, D)).astype(np.float32)
+    scores, idx = O.tournament_selected_scores(q, k, sel)
+    T = N // sel
+    view = torch.from_numpy(q).bmm(torch.from_numpy(k).transpose(1, 2)).view(C, R, sel, T)
+    best, local = view.max(3)
+    assert np.allclose(scores, best.reshape(C * R, sel).numpy(), atol=1e-5)
+    assert np.array_equal(idx, (local + torch.arange(sel) * T).reshape(C, R * sel).numpy())
+    with pytest.raises(ValueError):
+        O.tournament_selected_scores(q, k, 5)

@@ -177,3 +177,29 @@ def test_adagrad_scatter_against_reference_gpu(capi, cuda_device, ref_cuda):
     # rounding of table + (-lr*g/(sqrt+eps)) computed fused here and as a separate delta there (same value, same add)
     assert torch.equal(state, exp_state)
     assert rel_err(table.cpu().numpy(), exp_table.cpu().numpy()) < 1e-6
+
+
+def test_tournament_selection_restatement_matches_reference(cuda_device, ref_cuda):
+    """The oracle's restatement of the reference's tournament selection of negatives against the reference's own function on
+    the GPU (no fused operator exists for it here: this pins the restatement such an operator would be checked against)."""
+    import torch
+    import ge2_oracle as O
+
+    rng = np.random.default_rng(12)
+    C, R, N, D, sel = 3, 50, 120, 32, 12
+    q = rng.standard_normal((C, R, D)).astype(np.float32)
+    k = rng.standard_normal((C, N, D)).astype(np.float32)
+    exp_scores, exp_idx = O.tournament_selected_scores(q, k, sel)
+    all_scores = np.einsum("crd,cnd->crn", q.astype(np.float64), k.astype(np.float64))
+    for groups_per_tile in (1, 5, 12):
+        scores, idx = ref_cuda.tournament_selected_scores(torch.from_numpy(q).to(cuda_device), torch.from_numpy(k).to(cuda_device), sel,
+                                                          groups_per_tile)
+        assert tuple(scores.shape) == (C * R, sel) and tuple(idx.shape) == (C, R * sel)
+        scores, idx = scores.cpu().numpy(), idx.cpu().numpy()
+        assert np.abs(scores - exp_scores).max() <= 1e-4 * np.abs(exp_scores).max()
+        # a different winner is allowed only on a float tie: its score must equal the expected winner's within rounding
+        got = np.take_along_axis(all_scores, idx.reshape(C, R, sel), axis=2)
+        want = np.take_along_axis(all_scores, exp_idx.reshape(C, R, sel), axis=2)
+        assert np.abs(got - want).max() <= 1e-5
+        assert (idx != exp_idx).mean() <= 0.01
+        assert np.array_equal(idx.reshape(C, R, sel) // (N // sel), np.broadcast_to(np.arange(sel), (C, R, sel)))
