@@ -406,6 +406,56 @@ def unique_sweep(device):
     print(json.dumps(dict(unique_sweep=rows)), flush=True)
 
 
+def selected_sweep(device):
+    """`--selected-sweep`: the selected-negative operators (tournament selection; scores of the chosen pairs forward and
+    backward) against the reference's own GPU code for them (oracle/_ref/gege_ref_cuda.so: test infrastructure) on batches
+    shaped like the benchmarked step (50 000 query rows, 1 000 negatives a chunk, D = 100), CUDA events over 20 calls.
+    Algorithmic bytes of the pair kernels: every chosen negative row read once (and, backward, added to once).
+    Prints one JSON line."""
+    pkg = importlib.import_module("ge-2_b200")
+    pkg.load_library()
+    capi = pkg.capi
+    try:
+        import gege_ref_cuda as G
+    except Exception:
+        G = None
+
+    def ev(fn, reps=20):
+        for _ in range(3):
+            fn()
+        torch.cuda.synchronize()
+        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        a.record()
+        for _ in range(reps):
+            fn()
+        b.record()
+        torch.cuda.synchronize()
+        return a.elapsed_time(b) / reps * 1e3
+
+    rows = []
+    D = 100
+    for chunks, R, N, K in ((10, 5000, 1000, 100), (10, 5000, 1000, 10), (50, 1000, 1000, 500)):
+        g = torch.Generator(device=device).manual_seed(K)
+        q = torch.randn((chunks, R, D), device=device, generator=g) * 0.3
+        neg = torch.randn((chunks, N, D), device=device, generator=g) * 0.3
+        sel_us = ev(lambda: capi.tournament_select(q, neg, K))
+        _, idx = capi.tournament_select(q, neg, K)
+        grad = torch.randn((chunks * R, K), device=device, generator=g)
+        row = dict(chunks=chunks, rows_per_chunk=R, negatives=N, selected=K, D=D, tournament_us=round(sel_us, 1),
+                   tournament_gflop=round(2e-9 * chunks * R * N * D, 2))
+        for kind, code in (("DOT", 1), ("L2", 2)):
+            row[f"scores_{kind}_us"] = round(ev(lambda: capi.selected_neg_scores(kind, q, neg, idx)), 1)
+            row[f"backward_{kind}_us"] = round(ev(lambda: capi.selected_neg_scores_backward(kind, grad, q, neg, idx)), 1)
+            if G is not None:
+                row[f"reference_scores_{kind}_us"] = round(ev(lambda: G.selected_neg_scores_forward(q, neg, idx, code), reps=5), 1)
+                row[f"reference_backward_{kind}_us"] = round(ev(lambda: G.selected_neg_scores_backward(grad, q, neg, idx, code), reps=5), 1)
+        row["pair_row_bytes"] = 4 * D * chunks * R * K
+        if G is not None:
+            row["reference_tournament_us"] = round(ev(lambda: G.tournament_selected_scores(q, neg, K, 64), reps=5), 1)
+        rows.append(row)
+    print(json.dumps(dict(selected_sweep=rows)), flush=True)
+
+
 def bucket_sizes_of(cfg, P, psize, seed, device):
     """sizes of all P * P buckets of the graph make_partitioned_edges generates (a counting pass over the same draws)"""
     return make_partitioned_edges(cfg, P, psize, [], seed, device, count_only=True)[1]
@@ -808,6 +858,7 @@ def main():
     ap.add_argument("--no-pipeline", action="store_true", help="N = 1: do not draw batch t+1 on a side stream while batch t trains")
     ap.add_argument("--cpu-budget", type=float, default=15.0)
     ap.add_argument("--unique-sweep", action="store_true", help="time the unique-map on the five (n_ids, domain) pairs against the reference's kernel and exit")
+    ap.add_argument("--selected-sweep", action="store_true", help="time the selected-negative operators against the reference's GPU code and exit")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3)
 
@@ -825,6 +876,10 @@ def main():
     if args.unique_sweep:
         if rank == 0:
             unique_sweep(device)
+        return
+    if args.selected_sweep:
+        if rank == 0:
+            selected_sweep(device)
         return
     if world > 1:
         import torch.distributed as dist

@@ -23,7 +23,8 @@ EXPORTS = [
     "ge2_index_add", "ge2_adagrad_scatter", "ge2_dense_adagrad", "ge2_sample_negatives", "ge2_remap_edges_to_slots",
     "ge2_copy_slabs", "ge2_unique_bitmap_static", "ge2_sample_batch", "ge2_advance_step", "ge2_dense_adagrad_peers",
     "ge2_enable_peer_access", "ge2_build_state_edges", "ge2_swap_begin", "ge2_swap_wait", "ge2_sample_batch_dev",
-    "ge2_eval_workspace_bytes", "ge2_eval_ranks",
+    "ge2_eval_workspace_bytes", "ge2_eval_ranks", "ge2_selected_neg_scores", "ge2_selected_neg_scores_backward",
+    "ge2_tournament_select",
 ]
 
 
@@ -116,6 +117,12 @@ def load_library():
     lib.ge2_remap_edges_to_slots.argtypes = [C.c_void_p, C.c_int64, C.c_int32, C.c_void_p, C.c_int32, C.c_int64, C.c_void_p, C.c_void_p, C.c_void_p]
     lib.ge2_copy_slabs.argtypes = [C.c_void_p, C.c_void_p, C.POINTER(C.c_int32), C.c_int32, C.c_int64, C.c_void_p]
     lib.ge2_check_device.argtypes = [C.c_int]
+    lib.ge2_selected_neg_scores.argtypes = [C.c_int, C.c_void_p, C.c_void_p, C.c_void_p, C.c_int64, C.c_int64, C.c_int64, C.c_int64, C.c_int,
+                                            C.c_void_p, C.c_void_p, C.c_void_p]
+    lib.ge2_selected_neg_scores_backward.argtypes = [C.c_int, C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_int64, C.c_int64, C.c_int64,
+                                                     C.c_int64, C.c_int, C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p]
+    lib.ge2_tournament_select.argtypes = [C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_int64, C.c_int64, C.c_int64, C.c_int64, C.c_int,
+                                          C.c_void_p, C.c_void_p, C.c_void_p]
     _lib = lib
     return lib
 
@@ -356,6 +363,59 @@ def eval_ranks(decoder, node_emb, edges, rel=None, inv_rel=None, dst_filter=None
     d.workspace, d.workspace_bytes = ws.data_ptr(), ws.numel()
     check(lib.ge2_eval_ranks(C.byref(d), cur_stream()), "ge2_eval_ranks")
     return dst_ranks, src_ranks
+
+
+SELECTED_KINDS = {"DOT": 1, "L2": 2}
+
+
+def _selected_shapes(chunked, negatives, selected):
+    chunks, rows, D = chunked.shape
+    assert negatives.shape[0] == chunks and negatives.shape[2] == D and selected.shape[0] == chunks
+    assert chunked.is_contiguous() and negatives.is_contiguous() and selected.is_contiguous()
+    K = selected.shape[1] // max(rows, 1)
+    assert selected.shape[1] == rows * K, "selected must be [chunks, rows_per_chunk * num_selected]"
+    return chunks, rows, negatives.shape[1], K, D
+
+
+def selected_neg_scores(kind, chunked, negatives, selected, status=None):
+    """Scores [chunks * rows, K] of chunked [chunks, rows, D] against negatives[chunk, selected[chunk, row * K + k]]."""
+    import torch
+
+    chunks, rows, N, K, D = _selected_shapes(chunked, negatives, selected)
+    out = torch.empty((chunks * rows, K), dtype=torch.float32, device=chunked.device)
+    check(load_library().ge2_selected_neg_scores(SELECTED_KINDS[kind], ptr(chunked), ptr(negatives), ptr(selected), chunks, rows, N, K, D,
+                                                 ptr(out), ptr(status), cur_stream()), "ge2_selected_neg_scores")
+    return out
+
+
+def selected_neg_scores_backward(kind, grad_out, chunked, negatives, selected, status=None):
+    """(grad_chunked, grad_negatives) of selected_neg_scores for grad_out [chunks * rows, K]."""
+    import torch
+
+    chunks, rows, N, K, D = _selected_shapes(chunked, negatives, selected)
+    assert tuple(grad_out.shape) == (chunks * rows, K) and grad_out.is_contiguous()
+    grad_chunked, grad_negatives = torch.empty_like(chunked), torch.empty_like(negatives)
+    check(load_library().ge2_selected_neg_scores_backward(SELECTED_KINDS[kind], ptr(grad_out), ptr(chunked), ptr(negatives), ptr(selected),
+                                                          chunks, rows, N, K, D, ptr(grad_chunked), ptr(grad_negatives), ptr(status),
+                                                          cur_stream()), "ge2_selected_neg_scores_backward")
+    return grad_chunked, grad_negatives
+
+
+def tournament_select(chunked, negatives, num_selected, score_chunked=None, score_negatives=None):
+    """Per row and group of num_negs / num_selected consecutive negatives the best-scoring one: (scores [chunks * rows,
+    num_selected], columns [chunks, rows * num_selected]).  score_* default to the selector's tensors."""
+    import torch
+
+    chunks, rows, D = chunked.shape
+    N = negatives.shape[1]
+    assert negatives.shape[0] == chunks and negatives.shape[2] == D and chunked.is_contiguous() and negatives.is_contiguous()
+    for t, like in ((score_chunked, chunked), (score_negatives, negatives)):
+        assert t is None or (t.shape == like.shape and t.is_contiguous())
+    scores = torch.empty((chunks * rows, num_selected), dtype=torch.float32, device=chunked.device)
+    idx = torch.empty((chunks, rows * num_selected), dtype=torch.int64, device=chunked.device)
+    check(load_library().ge2_tournament_select(ptr(chunked), ptr(negatives), ptr(score_chunked), ptr(score_negatives), chunks, rows, N,
+                                               num_selected, D, ptr(scores), ptr(idx), cur_stream()), "ge2_tournament_select")
+    return scores, idx
 
 
 def swap_wait(swap_stream: int, compute_stream: int):

@@ -1,0 +1,366 @@
+// Selected-negative scoring for the DNS / GAN / tournament samplers: a query row is scored against the few negatives chosen
+// for it instead of against its whole chunk.
+//
+// Follows, in the reference project:
+//   scores of chosen pairs, forward     gege/src/cuda/src/nn/decoders/edge/distmult_selected_neg_cuda.cu:15-85
+//                                       (one thread per (row, chosen negative) walking D; dot product, or
+//                                       sqrt(max(|q - n|^2, 1e-8)) for the L2 comparator)
+//   ... backward                        same file :88-202 (query gradient: a thread per (row, d) looping the chosen negatives;
+//                                       negative gradient: an atomic add per (row, chosen, d); L2: one thread per pair)
+//   tournament selection                gege/src/cpp/src/nn/decoders/edge/distmult_selected_neg_cuda.cpp:46-121 (per tile of
+//                                       groups: bmm -> view [.., groups, T] -> max(3) -> gather; the negatives of a chunk form
+//                                       `selected` groups of T = N / selected consecutive ones, a row keeps the best of each)
+//
+// Here a warp owns a query row: the row sits in registers (D <= 128, four values a lane), every chosen negative row is read
+// once with coalesced loads and serves the score, the query gradient and the negative gradient of its pair in one pass
+// (the reference's backward reads every pair twice, in two launches).  The tournament never stores the [rows x N] scores:
+// a CTA holds 64 query rows in shared memory, streams 64-column tiles whose edges fall on group boundaries, and scans each
+// tile for the group winners.  fp32 on the CUDA cores: the winner of a group is decided by comparing nearly equal scores.
+#include <math_constants.h>
+
+#include "common.cuh"
+
+namespace ge2 {
+namespace {
+
+constexpr int kMaxD = 128;
+constexpr int kPairThreads = 256, kPairWarps = kPairThreads / 32;
+constexpr float kL2Floor = 1e-8f;  // the reference's kSelectedNegL2Tol, compared in float
+
+struct PairArgs {
+    const float* chunked;     // [chunks * R, D]
+    const float* negatives;   // [chunks, N, D]
+    const int64_t* selected;  // [chunks * R, K] columns of the row's chunk
+    int64_t rows, R, N, K;
+    int D, kind;
+    int32_t* status;
+};
+
+__device__ __forceinline__ float warp_sum(float v) {
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+    return v;
+}
+
+// out[row, k] = score(chunked[row], negatives[chunk(row), selected[row, k]]); an index outside [0, N) scores 0 and sets BAD_INDEX
+__global__ void __launch_bounds__(kPairThreads) selected_scores_kernel(PairArgs a, float* __restrict__ out) {
+    const int lane = threadIdx.x & 31;
+    const int64_t warps = (int64_t)gridDim.x * kPairWarps;
+    for (int64_t row = (int64_t)blockIdx.x * kPairWarps + (threadIdx.x >> 5); row < a.rows; row += warps) {
+        const int64_t c = row / a.R;
+        const float* q = a.chunked + row * a.D;
+        float qv[4];
+#pragma unroll
+        for (int j = 0; j < 4; j++) qv[j] = lane + 32 * j < a.D ? __ldg(q + lane + 32 * j) : 0.f;
+        const int64_t* sel = a.selected + row * a.K;
+        const float* negs = a.negatives + c * a.N * a.D;
+        for (int64_t k = 0; k < a.K; k++) {
+            const int64_t idx = __ldg(sel + k);  // one address for the warp: idx and everything decided by it is warp-uniform
+            const bool ok = idx >= 0 && idx < a.N;
+            float part = 0.f;
+            if (ok) {
+                const float* n = negs + idx * a.D;
+#pragma unroll
+                for (int j = 0; j < 4; j++) {
+                    const float nv = lane + 32 * j < a.D ? __ldg(n + lane + 32 * j) : 0.f;
+                    if (a.kind == GE2_SELECTED_DOT) {
+                        part = __fmaf_rn(qv[j], nv, part);
+                    } else {
+                        const float diff = qv[j] - nv;  // lanes past D hold 0 - 0
+                        part = __fmaf_rn(diff, diff, part);
+                    }
+                }
+            }
+            part = warp_sum(part);
+            if (lane == 0) {
+                if (!ok) or_status(a.status, GE2_STATUS_BAD_INDEX);
+                out[row * a.K + k] = !ok ? 0.f : (a.kind == GE2_SELECTED_DOT ? part : sqrtf(fmaxf(part, kL2Floor)));
+            }
+        }
+    }
+}
+
+// grad_chunked[row] = sum_k d score / d q; grad_negatives (zeroed by the caller of the kernel) += d score / d n per pair.
+// dot: dq = g n, dn = g q.  L2: dq = g (q - n) / |q - n|, dn = -dq, nothing when |q - n|^2 <= 1e-8.
+__global__ void __launch_bounds__(kPairThreads) selected_scores_backward_kernel(PairArgs a, const float* __restrict__ grad_out,
+                                                                                float* __restrict__ grad_chunked,
+                                                                                float* __restrict__ grad_negatives) {
+    const int lane = threadIdx.x & 31;
+    const int64_t warps = (int64_t)gridDim.x * kPairWarps;
+    for (int64_t row = (int64_t)blockIdx.x * kPairWarps + (threadIdx.x >> 5); row < a.rows; row += warps) {
+        const int64_t c = row / a.R;
+        const float* q = a.chunked + row * a.D;
+        float qv[4], acc[4];
+#pragma unroll
+        for (int j = 0; j < 4; j++) {
+            qv[j] = lane + 32 * j < a.D ? __ldg(q + lane + 32 * j) : 0.f;
+            acc[j] = 0.f;
+        }
+        const int64_t* sel = a.selected + row * a.K;
+        const float* g_row = grad_out + row * a.K;
+        for (int64_t k = 0; k < a.K; k++) {
+            const int64_t idx = __ldg(sel + k);
+            if (idx < 0 || idx >= a.N) {  // warp-uniform
+                if (lane == 0) or_status(a.status, GE2_STATUS_BAD_INDEX);
+                continue;
+            }
+            const float g = __ldg(g_row + k);
+            const int64_t n_off = (c * a.N + idx) * a.D;
+            float nv[4];
+#pragma unroll
+            for (int j = 0; j < 4; j++) nv[j] = lane + 32 * j < a.D ? __ldg(a.negatives + n_off + lane + 32 * j) : 0.f;
+            if (a.kind == GE2_SELECTED_DOT) {
+#pragma unroll
+                for (int j = 0; j < 4; j++) {
+                    acc[j] = __fmaf_rn(g, nv[j], acc[j]);
+                    if (lane + 32 * j < a.D) atomicAdd(grad_negatives + n_off + lane + 32 * j, g * qv[j]);
+                }
+            } else {
+                float sq = 0.f;
+#pragma unroll
+                for (int j = 0; j < 4; j++) {
+                    nv[j] = qv[j] - nv[j];
+                    sq = __fmaf_rn(nv[j], nv[j], sq);
+                }
+                sq = warp_sum(sq);
+                if (sq <= kL2Floor) continue;  // warp-uniform: every lane holds the same sum
+                const float coeff = g / sqrtf(sq);
+#pragma unroll
+                for (int j = 0; j < 4; j++) {
+                    const float v = coeff * nv[j];
+                    acc[j] += v;
+                    if (lane + 32 * j < a.D) atomicAdd(grad_negatives + n_off + lane + 32 * j, -v);
+                }
+            }
+        }
+#pragma unroll
+        for (int j = 0; j < 4; j++)
+            if (lane + 32 * j < a.D) grad_chunked[row * a.D + lane + 32 * j] = acc[j];
+    }
+}
+
+// ---------------------------------------------------------------------------------------------------------------------------
+// tournament selection
+// ---------------------------------------------------------------------------------------------------------------------------
+constexpr int kTile = 64, kChunkD = 32, kTourThreads = 256;
+constexpr int kEtStride = kTile + 4, kStStride = kTile + 1;
+
+struct TourArgs {
+    const float* chunked;    // [chunks, R, D]
+    const float* negatives;  // [chunks, N, D]
+    int64_t R, N, K, T;      // T = N / K negatives in a group
+    int64_t units;           // work items of a (chunk, row tile): T <= 64: tiles of groups_per_unit whole groups; else one group
+    int groups_per_unit;
+    int D;
+    float* out_scores;       // [chunks * R, K]
+    int64_t* out_idx;        // [chunks * R, K] column of the winner in its chunk
+};
+
+inline size_t tour_smem_bytes(int D) { return (size_t)(D * kTile + kChunkD * kEtStride + kTile * kStStride) * sizeof(float); }
+
+// grid: x = tiles of 64 query rows, y = shares of the units, z = chunk.  256 threads as 16 x 16, each 4 rows x 4 columns.
+__global__ void __launch_bounds__(kTourThreads) tournament_kernel(TourArgs a) {
+    extern __shared__ __align__(16) float tour_smem[];
+    float* Qt = tour_smem;                  // [D][64]: the CTA's query rows, transposed
+    float* Et = Qt + a.D * kTile;           // [32][68]: a slice of the negative tile, transposed
+    float* St = Et + kChunkD * kEtStride;   // [64][65]: the tile's scores
+    const int tid = threadIdx.x, tx = tid & 15, ty = tid >> 4;
+    const int D = a.D;
+    const int64_t c = blockIdx.z, r0 = (int64_t)blockIdx.x * kTile;
+    const int rows_here = (int)(a.R - r0 < kTile ? a.R - r0 : kTile);
+    const float* Q = a.chunked + (c * a.R + r0) * D;
+    for (int k = tid; k < kTile * D; k += kTourThreads) {
+        const int row = k / D, cc = k - row * D;
+        Qt[cc * kTile + row] = row < rows_here ? __ldg(Q + k) : 0.f;
+    }
+    __syncthreads();
+    const float* Nc = a.negatives + c * a.N * D;
+    const bool whole_groups = a.T <= kTile;  // every group of a unit lies inside its one tile
+    for (int64_t u = blockIdx.y; u < a.units; u += gridDim.y) {
+        const int64_t g_begin = u * a.groups_per_unit;
+        const int g_count = (int)(a.K - g_begin < a.groups_per_unit ? a.K - g_begin : a.groups_per_unit);
+        const int64_t col_begin = g_begin * a.T, col_end = col_begin + (int64_t)g_count * a.T;
+        // a group wider than a tile: thread `row` keeps the running winner of its row over the group's tiles
+        float best_v = -CUDART_INF_F;
+        int64_t best_i = col_begin;
+        for (int64_t n0 = col_begin; n0 < col_end; n0 += kTile) {
+            float acc[4][4];
+#pragma unroll
+            for (int i = 0; i < 4; i++)
+#pragma unroll
+                for (int j = 0; j < 4; j++) acc[i][j] = 0.f;
+            for (int c0 = 0; c0 < D; c0 += kChunkD) {
+                {
+                    // 64 negatives x 32 columns: a thread loads 8 consecutive columns of one negative row
+                    const int node = tid >> 2, cc = (tid & 3) * 8;
+                    const int64_t col = n0 + node;
+                    const float* row = col < col_end ? Nc + col * D : nullptr;
+#pragma unroll
+                    for (int k = 0; k < 8; k++) {
+                        const int d = c0 + cc + k;
+                        Et[(cc + k) * kEtStride + node] = (row != nullptr && d < D) ? __ldg(row + d) : 0.f;
+                    }
+                }
+                __syncthreads();
+                const int kmax = D - c0 < kChunkD ? D - c0 : kChunkD;
+                for (int k = 0; k < kmax; k++) {
+                    const float4 qa = *reinterpret_cast<const float4*>(&Qt[(c0 + k) * kTile + ty * 4]);
+                    const float4 eb = *reinterpret_cast<const float4*>(&Et[k * kEtStride + tx * 4]);
+                    const float qv[4] = {qa.x, qa.y, qa.z, qa.w}, ev[4] = {eb.x, eb.y, eb.z, eb.w};
+#pragma unroll
+                    for (int i = 0; i < 4; i++)
+#pragma unroll
+                        for (int j = 0; j < 4; j++) acc[i][j] = __fmaf_rn(qv[i], ev[j], acc[i][j]);
+                }
+                __syncthreads();
+            }
+#pragma unroll
+            for (int i = 0; i < 4; i++)
+#pragma unroll
+                for (int j = 0; j < 4; j++) St[(ty * 4 + i) * kStStride + tx * 4 + j] = acc[i][j];
+            __syncthreads();
+            if (whole_groups) {
+                // one (row, group) per thread and turn; rows vary fastest, so a warp reads 32 different banks
+                const int T = (int)a.T;
+                for (int it = tid; it < kTile * g_count; it += kTourThreads) {
+                    const int row = it & (kTile - 1), g = it >> 6;
+                    const float* s = St + row * kStStride + g * T;
+                    float bv = s[0];
+                    int bi = 0;
+                    for (int j = 1; j < T; j++)
+                        if (s[j] > bv) {  // the first of equal scores wins
+                            bv = s[j];
+                            bi = j;
+                        }
+                    if (row < rows_here) {
+                        const int64_t o = (c * a.R + r0 + row) * a.K + g_begin + g;
+                        a.out_scores[o] = bv;
+                        a.out_idx[o] = n0 + (int64_t)g * T + bi;
+                    }
+                }
+            } else if (tid < kTile) {
+                const int len = (int)(col_end - n0 < kTile ? col_end - n0 : kTile);
+                const float* s = St + tid * kStStride;
+                for (int j = 0; j < len; j++)
+                    if (s[j] > best_v) {
+                        best_v = s[j];
+                        best_i = n0 + j;
+                    }
+            }
+            __syncthreads();  // the next tile overwrites St
+        }
+        if (!whole_groups && tid < rows_here) {
+            const int64_t o = (c * a.R + r0 + tid) * a.K + g_begin;
+            a.out_scores[o] = best_v;
+            a.out_idx[o] = best_i;
+        }
+    }
+}
+
+int check_pairs(int kind, const void* chunked, const void* negatives, const void* selected, int64_t chunks, int64_t rows_per_chunk,
+                int64_t num_negs, int64_t num_selected, int D) {
+    if (kind != GE2_SELECTED_DOT && kind != GE2_SELECTED_L2) return GE2_ERR_INVALID_ARGUMENT;
+    if (chunks < 0 || rows_per_chunk < 0 || num_negs <= 0 || num_selected < 0 || D <= 0) return GE2_ERR_INVALID_ARGUMENT;
+    if (D > kMaxD) return GE2_ERR_UNSUPPORTED;
+    if (chunks * rows_per_chunk * num_selected > 0 && (chunked == nullptr || negatives == nullptr || selected == nullptr)) return GE2_ERR_INVALID_ARGUMENT;
+    return GE2_OK;
+}
+
+PairArgs pair_args(int kind, const float* chunked, const float* negatives, const int64_t* selected, int64_t chunks, int64_t rows_per_chunk,
+                   int64_t num_negs, int64_t num_selected, int D, int32_t* status) {
+    PairArgs a;
+    a.chunked = chunked;
+    a.negatives = negatives;
+    a.selected = selected;
+    a.rows = chunks * rows_per_chunk;
+    a.R = rows_per_chunk;
+    a.N = num_negs;
+    a.K = num_selected;
+    a.D = D;
+    a.kind = kind;
+    a.status = status;
+    return a;
+}
+
+}  // namespace
+}  // namespace ge2
+
+using namespace ge2;
+
+extern "C" int ge2_selected_neg_scores(int kind, const float* chunked, const float* negatives, const int64_t* selected, int64_t chunks,
+                                       int64_t rows_per_chunk, int64_t num_negs, int64_t num_selected, int D, float* out_scores,
+                                       int32_t* status, ge2_stream_t stream_) {
+    const int rc = check_pairs(kind, chunked, negatives, selected, chunks, rows_per_chunk, num_negs, num_selected, D);
+    if (rc != GE2_OK) return rc;
+    const int64_t rows = chunks * rows_per_chunk;
+    if (rows * num_selected == 0) return GE2_OK;
+    if (out_scores == nullptr) return GE2_ERR_INVALID_ARGUMENT;
+    const PairArgs a = pair_args(kind, chunked, negatives, selected, chunks, rows_per_chunk, num_negs, num_selected, D, status);
+    selected_scores_kernel<<<stream_grid(rows, kPairWarps), kPairThreads, 0, as_stream(stream_)>>>(a, out_scores);
+    GE2_LAUNCH_CHECK();
+    return GE2_OK;
+}
+
+extern "C" int ge2_selected_neg_scores_backward(int kind, const float* grad_out, const float* chunked, const float* negatives,
+                                                const int64_t* selected, int64_t chunks, int64_t rows_per_chunk, int64_t num_negs,
+                                                int64_t num_selected, int D, float* grad_chunked, float* grad_negatives, int32_t* status,
+                                                ge2_stream_t stream_) {
+    const int rc = check_pairs(kind, chunked, negatives, selected, chunks, rows_per_chunk, num_negs, num_selected, D);
+    if (rc != GE2_OK) return rc;
+    const int64_t rows = chunks * rows_per_chunk;
+    cudaStream_t stream = as_stream(stream_);
+    if (chunks > 0) {
+        if (grad_negatives == nullptr) return GE2_ERR_INVALID_ARGUMENT;
+        GE2_CUDA_TRY(cudaMemsetAsync(grad_negatives, 0, (size_t)(chunks * num_negs * D) * sizeof(float), stream));
+    }
+    if (rows == 0) return GE2_OK;
+    if (grad_chunked == nullptr || (num_selected > 0 && grad_out == nullptr)) return GE2_ERR_INVALID_ARGUMENT;
+    // with nothing selected the kernel still writes the zero query gradient
+    const PairArgs a = pair_args(kind, chunked, negatives, selected, chunks, rows_per_chunk, num_negs, num_selected, D, status);
+    selected_scores_backward_kernel<<<stream_grid(rows, kPairWarps), kPairThreads, 0, stream>>>(a, grad_out, grad_chunked, grad_negatives);
+    GE2_LAUNCH_CHECK();
+    return GE2_OK;
+}
+
+extern "C" int ge2_tournament_select(const float* selector_chunked, const float* selector_negatives, const float* score_chunked,
+                                     const float* score_negatives, int64_t chunks, int64_t rows_per_chunk, int64_t num_negs,
+                                     int64_t num_selected, int D, float* out_scores, int64_t* out_idx, ge2_stream_t stream_) {
+    if (chunks < 0 || rows_per_chunk < 0 || num_negs <= 0 || num_selected <= 0 || D <= 0) return GE2_ERR_INVALID_ARGUMENT;
+    if (num_negs % num_selected != 0) return GE2_ERR_INVALID_ARGUMENT;  // the reference's TORCH_CHECK
+    if (D > kMaxD || chunks > 65535) return GE2_ERR_UNSUPPORTED;
+    if (chunks * rows_per_chunk == 0) return GE2_OK;
+    if (selector_chunked == nullptr || selector_negatives == nullptr || out_scores == nullptr || out_idx == nullptr) return GE2_ERR_INVALID_ARGUMENT;
+    if (score_chunked == nullptr) score_chunked = selector_chunked;
+    if (score_negatives == nullptr) score_negatives = selector_negatives;
+    cudaStream_t stream = as_stream(stream_);
+
+    TourArgs a;
+    a.chunked = selector_chunked;
+    a.negatives = selector_negatives;
+    a.R = rows_per_chunk;
+    a.N = num_negs;
+    a.K = num_selected;
+    a.T = num_negs / num_selected;
+    a.D = D;
+    a.groups_per_unit = a.T <= kTile ? (int)(kTile / a.T) : 1;
+    a.units = ceil_div<int64_t>(num_selected, a.groups_per_unit);
+    a.out_scores = out_scores;
+    a.out_idx = out_idx;
+    const int64_t row_tiles = ceil_div<int64_t>(rows_per_chunk, kTile);
+    if (row_tiles > 0x7fffffffLL) return GE2_ERR_UNSUPPORTED;
+    int64_t shares = ceil_div<int64_t>((int64_t)kNumSMs * 4, row_tiles * chunks);  // about four CTAs per SM over the whole grid
+    if (shares > a.units) shares = a.units;
+    if (shares > 65535) shares = 65535;
+    const size_t smem = tour_smem_bytes(D);
+    // per-device function attribute; setting it on every call keeps multi-device processes correct and is not a stream operation
+    GE2_CUDA_TRY(cudaFuncSetAttribute(tournament_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+    dim3 grid((unsigned)row_tiles, (unsigned)shares, (unsigned)chunks);
+    tournament_kernel<<<grid, kTourThreads, smem, stream>>>(a);
+    GE2_LAUNCH_CHECK();
+    if (score_chunked != selector_chunked || score_negatives != selector_negatives) {
+        // a selector separate from the scorer: the winners are scored again with the scorer's rows
+        return ge2_selected_neg_scores(GE2_SELECTED_DOT, score_chunked, score_negatives, out_idx, chunks, rows_per_chunk, num_negs, num_selected,
+                                       D, out_scores, nullptr, stream_);
+    }
+    return GE2_OK;
+}

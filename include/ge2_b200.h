@@ -363,6 +363,40 @@ typedef struct ge2_eval_desc {
 GE2_API size_t ge2_eval_workspace_bytes(const ge2_eval_desc *desc);
 GE2_API int ge2_eval_ranks(const ge2_eval_desc *desc, ge2_stream_t stream);
 
+/* =====================================================================================================
+ * Selected-negative scoring (the DNS / GAN / tournament samplers of the reference): a query row is scored against the few
+ * negatives chosen for it.  chunked [chunks, rows_per_chunk, D] (relation-adjusted, padded query rows), negatives
+ * [chunks, num_negs, D], selected [chunks, rows_per_chunk * num_selected] int64 columns of the row's own chunk, all dense
+ * fp32 / int64 device arrays; D <= 128.
+ *
+ * ge2_selected_neg_scores replaces selected_neg_scores_cuda_forward (cuda/src/nn/decoders/edge/distmult_selected_neg_cuda.cu:
+ * 204-268): out_scores [chunks * rows_per_chunk, num_selected]; kind DOT is the dot product, L2 is sqrt(max(|q - n|^2, 1e-8)).
+ * ge2_selected_neg_scores_backward replaces selected_neg_scores_cuda_backward (same file :270-362): grad_out as out_scores;
+ * grad_chunked [chunks, rows_per_chunk, D] is written, grad_negatives [chunks, num_negs, D] is zeroed and accumulated.
+ * A selected column outside [0, num_negs) scores 0, contributes no gradient and sets GE2_STATUS_BAD_INDEX in *status (may be
+ * NULL); the reference reads out of bounds there.
+ *
+ * ge2_tournament_select replaces distmult_tiled_tournament_selected_scores (cpp/src/nn/decoders/edge/
+ * distmult_selected_neg_cuda.cpp:46-121): the num_negs negatives of a chunk form num_selected groups of num_negs / num_selected
+ * consecutive ones (num_negs must divide evenly, else GE2_ERR_INVALID_ARGUMENT); per row and group the negative with the highest
+ * selector score is kept (the first of equal ones; a NaN score never wins).  out_idx [chunks, rows_per_chunk * num_selected] is its
+ * column in the chunk, out_scores [chunks * rows_per_chunk, num_selected] its score by the score_* tensors (NULL: the
+ * selector's, which is also what equal pointers mean).  The reference's groups_per_tile only sizes its temporary score
+ * matrix; no score matrix is stored here.  chunks <= 65535.
+ * ===================================================================================================== */
+#define GE2_SELECTED_DOT 1 /* the values of the reference's SelectedNegScoreKind */
+#define GE2_SELECTED_L2 2
+GE2_API int ge2_selected_neg_scores(int kind, const float *chunked, const float *negatives, const int64_t *selected, int64_t chunks,
+                                    int64_t rows_per_chunk, int64_t num_negs, int64_t num_selected, int D, float *out_scores,
+                                    int32_t *status, ge2_stream_t stream);
+GE2_API int ge2_selected_neg_scores_backward(int kind, const float *grad_out, const float *chunked, const float *negatives,
+                                             const int64_t *selected, int64_t chunks, int64_t rows_per_chunk, int64_t num_negs,
+                                             int64_t num_selected, int D, float *grad_chunked, float *grad_negatives, int32_t *status,
+                                             ge2_stream_t stream);
+GE2_API int ge2_tournament_select(const float *selector_chunked, const float *selector_negatives, const float *score_chunked,
+                                  const float *score_negatives, int64_t chunks, int64_t rows_per_chunk, int64_t num_negs,
+                                  int64_t num_selected, int D, float *out_scores, int64_t *out_idx, ge2_stream_t stream);
+
 #ifdef __cplusplus
 }
 #endif

@@ -485,6 +485,50 @@ def tournament_selected_scores(chunked: np.ndarray, negatives: np.ndarray, selec
     return kept.reshape(C * R, selected), idx.reshape(C, R * selected).astype(np.int64)
 
 
+SELECTED_DOT, SELECTED_L2 = 1, 2  # the reference's SelectedNegScoreKind (distmult_selected_neg_cuda.h:5)
+_SELECTED_L2_TOL = 1e-8
+
+
+def _selected_rows(chunked, negatives, selected):
+    C, R, D = chunked.shape
+    K = selected.shape[1] // max(R, 1)
+    idx = selected.reshape(C, R, K)
+    picked = negatives[np.arange(C)[:, None, None], idx]  # [C, R, K, D]
+    return C, R, D, K, idx, picked.astype(np.float64)
+
+
+def selected_neg_scores(chunked: np.ndarray, negatives: np.ndarray, selected: np.ndarray, kind: int) -> np.ndarray:
+    """Scores of every query row against the negatives chosen for it
+    (cuda/src/nn/decoders/edge/distmult_selected_neg_cuda.cu:15-85): chunked [C, R, D], negatives [C, N, D], selected
+    [C, R * K] columns of the row's chunk; DOT: q . n, L2: sqrt(max(|q - n|^2, 1e-8)).  Returns [C * R, K] float32."""
+    C, R, D, K, _, picked = _selected_rows(chunked, negatives, selected)
+    q = chunked.astype(np.float64)[:, :, None, :]
+    if kind == SELECTED_DOT:
+        out = (q * picked).sum(-1)
+    else:
+        out = np.sqrt(np.maximum(((q - picked) ** 2).sum(-1), _SELECTED_L2_TOL))
+    return out.reshape(C * R, K).astype(np.float32)
+
+
+def selected_neg_scores_backward(grad_out: np.ndarray, chunked: np.ndarray, negatives: np.ndarray, selected: np.ndarray, kind: int):
+    """Gradients of selected_neg_scores (distmult_selected_neg_cuda.cu:88-202): (grad_chunked [C, R, D], grad_negatives
+    [C, N, D]).  DOT: dq += g n, dn += g q.  L2: dq += g (q - n) / |q - n|, dn -= the same, nothing when |q - n|^2 <= 1e-8."""
+    C, R, D, K, idx, picked = _selected_rows(chunked, negatives, selected)
+    q = chunked.astype(np.float64)[:, :, None, :]
+    g = grad_out.astype(np.float64).reshape(C, R, K, 1)
+    if kind == SELECTED_DOT:
+        dq_pair, dn_pair = g * picked, g * np.broadcast_to(q, picked.shape)
+    else:
+        diff = q - picked
+        sq = (diff ** 2).sum(-1, keepdims=True)
+        coeff = np.where(sq > _SELECTED_L2_TOL, g / np.sqrt(np.maximum(sq, 1e-300)), 0.0)
+        dq_pair, dn_pair = coeff * diff, -coeff * diff
+    grad_neg = np.zeros(negatives.shape, np.float64)
+    for c in range(C):
+        np.add.at(grad_neg[c], idx[c].reshape(-1), dn_pair[c].reshape(-1, D))
+    return dq_pair.sum(2).astype(np.float32), grad_neg.astype(np.float32)
+
+
 def global_filter(all_edges: np.ndarray, edges: np.ndarray, inverse: bool) -> np.ndarray:
     """compute_filter_corruption with global = true (cpp/src/data/samplers/negative.cpp:421-568): for evaluation edge i all
     (i, n) such that replacing its destination (inverse: its source) by n gives an edge of `all_edges` (same relation when the

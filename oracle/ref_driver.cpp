@@ -175,6 +175,15 @@ std::tuple<torch::Tensor, torch::Tensor> ref_tournament_selected_scores(torch::T
                                                                         int64_t groups_per_tile) {
     return distmult_tiled_tournament_selected_scores(chunked, negatives, chunked, negatives, selected, groups_per_tile);
 }
+
+// The reference's scoring of chosen negatives and its gradients (distmult_selected_neg_cuda.cu:204-362).
+torch::Tensor ref_selected_neg_scores_forward(torch::Tensor chunked, torch::Tensor negatives, torch::Tensor selected, int64_t kind) {
+    return selected_neg_scores_cuda_forward(chunked, negatives, selected, kind);
+}
+std::tuple<torch::Tensor, torch::Tensor> ref_selected_neg_scores_backward(torch::Tensor grad_out, torch::Tensor chunked, torch::Tensor negatives,
+                                                                          torch::Tensor selected, int64_t kind) {
+    return selected_neg_scores_cuda_backward(grad_out, chunked, negatives, selected, kind);
+}
 #endif
 
 }  // namespace
@@ -193,5 +202,7 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
 #ifdef GEGE_CUDA
     m.def("unique_inverse_cuda", &ref_unique_inverse_cuda, py::call_guard<py::gil_scoped_release>());
     m.def("tournament_selected_scores", &ref_tournament_selected_scores, py::call_guard<py::gil_scoped_release>());
+    m.def("selected_neg_scores_forward", &ref_selected_neg_scores_forward, py::call_guard<py::gil_scoped_release>());
+    m.def("selected_neg_scores_backward", &ref_selected_neg_scores_backward, py::call_guard<py::gil_scoped_release>());
 #endif
 }

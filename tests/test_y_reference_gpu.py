@@ -203,3 +203,33 @@ def test_tournament_selection_restatement_matches_reference(cuda_device, ref_cud
         assert np.abs(got - want).max() <= 1e-5
         assert (idx != exp_idx).mean() <= 0.01
         assert np.array_equal(idx.reshape(C, R, sel) // (N // sel), np.broadcast_to(np.arange(sel), (C, R, sel)))
+
+
+@pytest.mark.parametrize("kind,code", [("DOT", 1), ("L2", 2)])
+def test_selected_negative_operators_against_reference_gpu(capi, cuda_device, ref_cuda, kind, code):
+    """ge2_tournament_select and ge2_selected_neg_scores(_backward) against the reference's own functions on the same device
+    tensors; the oracle's restatements of the pair kernels are pinned by the same outputs."""
+    import torch
+    import ge2_oracle as O
+
+    rng = np.random.default_rng(40 + code)
+    C, R, N, D, K = 3, 70, 200, 100, 20
+    q = rng.standard_normal((C, R, D)).astype(np.float32)
+    n = rng.standard_normal((C, N, D)).astype(np.float32)
+    grad = rng.standard_normal((C * R, K)).astype(np.float32)
+    tq, tn, tg = (torch.from_numpy(a).to(cuda_device) for a in (q, n, grad))
+    ref_scores, ref_idx = ref_cuda.tournament_selected_scores(tq, tn, K, 64)
+    scores, idx = capi.tournament_select(tq, tn, K)
+    assert (idx != ref_idx).float().mean().item() <= 0.01
+    assert (scores - ref_scores).abs().max().item() <= 1e-4 * ref_scores.abs().max().item()
+    sel = ref_idx.contiguous()
+    ref_out = ref_cuda.selected_neg_scores_forward(tq, tn, sel, code)
+    ref_dq, ref_dn = ref_cuda.selected_neg_scores_backward(tg, tq, tn, sel, code)
+    out = capi.selected_neg_scores(kind, tq, tn, sel)
+    dq, dn = capi.selected_neg_scores_backward(kind, tg, tq, tn, sel)
+    exp_out = O.selected_neg_scores(q, n, sel.cpu().numpy(), code)
+    exp_dq, exp_dn = O.selected_neg_scores_backward(grad, q, n, sel.cpu().numpy(), code)
+    for got, ref, exp in ((out, ref_out, exp_out), (dq, ref_dq, exp_dq), (dn, ref_dn, exp_dn)):
+        scale = ref.abs().max().item()
+        assert (got - ref).abs().max().item() <= 1e-4 * scale
+        assert np.abs(ref.cpu().numpy() - exp).max() <= 1e-4 * scale
