@@ -18,6 +18,8 @@
 // tile for the group winners.  fp32 on the CUDA cores: the winner of a group is decided by comparing nearly equal scores.
 #include <math_constants.h>
 
+#include <algorithm>
+
 #include "common.cuh"
 
 namespace ge2 {
@@ -143,26 +145,38 @@ __global__ void __launch_bounds__(kPairThreads) selected_scores_backward_kernel(
 // tournament selection
 // ---------------------------------------------------------------------------------------------------------------------------
 constexpr int kTile = 64, kChunkD = 32, kTourThreads = 256;
-constexpr int kEtStride = kTile + 4, kStStride = kTile + 1;
+constexpr int kQtStride = kTile + 4, kEtStride = kTile + 4, kStStride = kTile + 1;
 
 struct TourArgs {
     const float* chunked;    // [chunks, R, D]
     const float* negatives;  // [chunks, N, D]
     int64_t R, N, K, T;      // T = N / K negatives in a group
     int64_t units;           // work items of a (chunk, row tile): T <= 64: tiles of groups_per_unit whole groups; else one group
+    int64_t units_per_cta;   // a CTA takes this many consecutive units
     int groups_per_unit;
     int D;
     float* out_scores;       // [chunks * R, K]
     int64_t* out_idx;        // [chunks * R, K] column of the winner in its chunk
 };
 
-inline size_t tour_smem_bytes(int D) { return (size_t)(D * kTile + kChunkD * kEtStride + kTile * kStStride) * sizeof(float); }
+inline size_t tour_smem_bytes(int D) { return (size_t)(D * kQtStride + kChunkD * kEtStride + kTile * kStStride) * sizeof(float); }
+
+// the slice [c0, c0 + 32) of 64 negative rows starting at column n0: a thread holds 8 consecutive values of one row
+__device__ __forceinline__ void tour_fetch(float (&r)[8], const float* __restrict__ Nc, int64_t n0, int64_t col_end, int c0, int D, int tid) {
+    const int64_t col = n0 + (tid >> 2);
+    const int d0 = c0 + (tid & 3) * 8;
+    const float* row = Nc + col * D;
+#pragma unroll
+    for (int k = 0; k < 8; k++) r[k] = (col < col_end && d0 + k < D) ? __ldg(row + d0 + k) : 0.f;
+}
 
 // grid: x = tiles of 64 query rows, y = shares of the units, z = chunk.  256 threads as 16 x 16, each 4 rows x 4 columns.
-__global__ void __launch_bounds__(kTourThreads) tournament_kernel(TourArgs a) {
+// The slices of the negative tiles go global -> registers -> shared memory, the next slice (of this tile or of the CTA's next
+// tile) in flight while the current one is multiplied.
+__global__ void __launch_bounds__(kTourThreads, 3) tournament_kernel(TourArgs a) {
     extern __shared__ __align__(16) float tour_smem[];
-    float* Qt = tour_smem;                  // [D][64]: the CTA's query rows, transposed
-    float* Et = Qt + a.D * kTile;           // [32][68]: a slice of the negative tile, transposed
+    float* Qt = tour_smem;                  // [D][68]: the CTA's query rows, transposed
+    float* Et = Qt + a.D * kQtStride;       // [32][68]: a slice of the negative tile, transposed
     float* St = Et + kChunkD * kEtStride;   // [64][65]: the tile's scores
     const int tid = threadIdx.x, tx = tid & 15, ty = tid >> 4;
     const int D = a.D;
@@ -171,14 +185,19 @@ __global__ void __launch_bounds__(kTourThreads) tournament_kernel(TourArgs a) {
     const float* Q = a.chunked + (c * a.R + r0) * D;
     for (int k = tid; k < kTile * D; k += kTourThreads) {
         const int row = k / D, cc = k - row * D;
-        Qt[cc * kTile + row] = row < rows_here ? __ldg(Q + k) : 0.f;
+        Qt[cc * kQtStride + row] = row < rows_here ? __ldg(Q + k) : 0.f;
     }
-    __syncthreads();
     const float* Nc = a.negatives + c * a.N * D;
     const bool whole_groups = a.T <= kTile;  // every group of a unit lies inside its one tile
-    for (int64_t u = blockIdx.y; u < a.units; u += gridDim.y) {
+    const int64_t u_first = (int64_t)blockIdx.y * a.units_per_cta;
+    const int64_t u_last = u_first + a.units_per_cta < a.units ? u_first + a.units_per_cta : a.units;
+    // columns of unit u: [unit_begin(u), unit_end(u))
+    auto unit_groups = [&](int64_t u) { return (int)(a.K - u * a.groups_per_unit < a.groups_per_unit ? a.K - u * a.groups_per_unit : a.groups_per_unit); };
+    float pre[8];
+    if (u_first < u_last) tour_fetch(pre, Nc, u_first * a.groups_per_unit * a.T, (u_first * a.groups_per_unit + unit_groups(u_first)) * a.T, 0, D, tid);
+    for (int64_t u = u_first; u < u_last; u++) {
         const int64_t g_begin = u * a.groups_per_unit;
-        const int g_count = (int)(a.K - g_begin < a.groups_per_unit ? a.K - g_begin : a.groups_per_unit);
+        const int g_count = unit_groups(u);
         const int64_t col_begin = g_begin * a.T, col_end = col_begin + (int64_t)g_count * a.T;
         // a group wider than a tile: thread `row` keeps the running winner of its row over the group's tiles
         float best_v = -CUDART_INF_F;
@@ -191,20 +210,23 @@ __global__ void __launch_bounds__(kTourThreads) tournament_kernel(TourArgs a) {
                 for (int j = 0; j < 4; j++) acc[i][j] = 0.f;
             for (int c0 = 0; c0 < D; c0 += kChunkD) {
                 {
-                    // 64 negatives x 32 columns: a thread loads 8 consecutive columns of one negative row
                     const int node = tid >> 2, cc = (tid & 3) * 8;
-                    const int64_t col = n0 + node;
-                    const float* row = col < col_end ? Nc + col * D : nullptr;
 #pragma unroll
-                    for (int k = 0; k < 8; k++) {
-                        const int d = c0 + cc + k;
-                        Et[(cc + k) * kEtStride + node] = (row != nullptr && d < D) ? __ldg(row + d) : 0.f;
-                    }
+                    for (int k = 0; k < 8; k++) Et[(cc + k) * kEtStride + node] = pre[k];
                 }
-                __syncthreads();
+                __syncthreads();  // also orders the writes of Qt before its first use
+                // what comes after this slice: the tile's next slice, the unit's next tile, or the CTA's next unit
+                if (c0 + kChunkD < D) {
+                    tour_fetch(pre, Nc, n0, col_end, c0 + kChunkD, D, tid);
+                } else if (n0 + kTile < col_end) {
+                    tour_fetch(pre, Nc, n0 + kTile, col_end, 0, D, tid);
+                } else if (u + 1 < u_last) {
+                    const int64_t nb = (u + 1) * a.groups_per_unit * a.T;
+                    tour_fetch(pre, Nc, nb, nb + (int64_t)unit_groups(u + 1) * a.T, 0, D, tid);
+                }
                 const int kmax = D - c0 < kChunkD ? D - c0 : kChunkD;
                 for (int k = 0; k < kmax; k++) {
-                    const float4 qa = *reinterpret_cast<const float4*>(&Qt[(c0 + k) * kTile + ty * 4]);
+                    const float4 qa = *reinterpret_cast<const float4*>(&Qt[(c0 + k) * kQtStride + ty * 4]);
                     const float4 eb = *reinterpret_cast<const float4*>(&Et[k * kEtStride + tx * 4]);
                     const float qv[4] = {qa.x, qa.y, qa.z, qa.w}, ev[4] = {eb.x, eb.y, eb.z, eb.w};
 #pragma unroll
@@ -348,10 +370,23 @@ extern "C" int ge2_tournament_select(const float* selector_chunked, const float*
     a.out_idx = out_idx;
     const int64_t row_tiles = ceil_div<int64_t>(rows_per_chunk, kTile);
     if (row_tiles > 0x7fffffffLL) return GE2_ERR_UNSUPPORTED;
-    int64_t shares = ceil_div<int64_t>((int64_t)kNumSMs * 4, row_tiles * chunks);  // about four CTAs per SM over the whole grid
-    if (shares > a.units) shares = a.units;
-    if (shares > 65535) shares = 65535;
     const size_t smem = tour_smem_bytes(D);
+    // How many CTAs share the units of a (row tile, chunk): the split with the shortest bound on the makespan of CTAs handed
+    // out greedily to `slots` resident places -- all work / slots + the work of one CTA, its query-tile load counted as a third
+    // of a unit.  Three CTAs an SM by registers.
+    const int64_t per_sm = std::max<int64_t>(1, std::min<int64_t>(3, (int64_t)(227 * 1024) / (int64_t)(smem + 1024)));
+    const int64_t slots = (int64_t)kNumSMs * per_sm, base = row_tiles * chunks;
+    int64_t shares = 1;
+    double best_cost = 0.0;
+    for (int64_t s = 1; s <= std::min<int64_t>(a.units, 64); s++) {
+        const int64_t per = ceil_div<int64_t>(a.units, s), used = ceil_div<int64_t>(a.units, per);  // `used` CTAs get work
+        const double cost = ((double)(base * used) / (double)slots + 1.0) * ((double)per + 0.33);
+        if (s == 1 || cost < best_cost - 1e-9) {
+            best_cost = cost;
+            shares = used;
+            a.units_per_cta = per;
+        }
+    }
     // per-device function attribute; setting it on every call keeps multi-device processes correct and is not a stream operation
     GE2_CUDA_TRY(cudaFuncSetAttribute(tournament_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
     dim3 grid((unsigned)row_tiles, (unsigned)shares, (unsigned)chunks);
