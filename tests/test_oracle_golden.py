@@ -137,3 +137,30 @@ def test_tournament_selection_restatement():
     assert np.array_equal(idx, (local + torch.arange(sel) * T).reshape(C, R * sel).numpy())
     with pytest.raises(ValueError):
         O.tournament_selected_scores(q, k, 5)
+
+
+@pytest.mark.parametrize("kind", [O.SELECTED_DOT, O.SELECTED_L2])
+def test_selected_neg_scores_restatement_against_autograd(kind):
+    """Scores of chosen pairs and their gradients (distmult_selected_neg_cuda.cu:15-202) against torch autograd in float64
+    on the same gather: dot product, or sqrt(max(|q - n|^2, 1e-8)) whose floor passes no gradient."""
+    import torch
+
+    rng = np.random.default_rng(kind)
+    C, R, N, D, K = 2, 7, 11, 10, 3
+    q = rng.standard_normal((C, R, D)).astype(np.float32)
+    n = rng.standard_normal((C, N, D)).astype(np.float32)
+    sel = rng.integers(0, N, (C, R * K))
+    sel[0, :2] = 4               # a negative chosen twice by one row
+    n[1, 5], sel[1, 2 * K] = q[1, 2], 5   # a pair at distance 0
+    tq = torch.tensor(q, dtype=torch.float64, requires_grad=True)
+    tn = torch.tensor(n, dtype=torch.float64, requires_grad=True)
+    picked = tn[torch.arange(C)[:, None, None], torch.tensor(sel).view(C, R, K)]
+    if kind == O.SELECTED_DOT:
+        out = (tq[:, :, None, :] * picked).sum(-1)
+    else:
+        out = torch.sqrt(torch.clamp(((tq[:, :, None, :] - picked) ** 2).sum(-1), min=1e-8))
+    grad = rng.standard_normal((C * R, K)).astype(np.float32)
+    out.backward(torch.tensor(grad, dtype=torch.float64).view(C, R, K))
+    assert np.abs(O.selected_neg_scores(q, n, sel, kind) - out.detach().numpy().reshape(C * R, K)).max() < 1e-5
+    dq, dn = O.selected_neg_scores_backward(grad, q, n, sel, kind)
+    assert np.abs(dq - tq.grad.numpy()).max() < 1e-5 and np.abs(dn - tn.grad.numpy()).max() < 1e-5
