@@ -11,6 +11,15 @@ PYBIND11_MODULE(ge2_host, m) {
     m.def("map_tensors", &map_tensors, py::arg("unmapped_tensors"), py::arg("sorted") = true, py::arg("value_domain_size") = -1);
     m.def("map_tensors_unique_inverse_cuda", &map_tensors_unique_inverse_cuda, py::arg("all_ids"), py::arg("sorted") = true,
           py::arg("value_domain_size") = -1);
+    py::enum_<SelectedNegScoreKind>(m, "SelectedNegScoreKind")
+        .value("NONE", SelectedNegScoreKind::NONE)
+        .value("DOT", SelectedNegScoreKind::DOT)
+        .value("L2", SelectedNegScoreKind::L2);
+    m.def("selected_neg_scores", &selected_neg_scores);
+    m.def("selected_neg_scores_cuda_forward", &selected_neg_scores_cuda_forward);
+    m.def("selected_neg_scores_cuda_backward", &selected_neg_scores_cuda_backward);
+    m.def("distmult_tiled_tournament_selected_scores", &distmult_tiled_tournament_selected_scores);
+    m.def("selected_neg_status", &selected_neg_status);
     py::class_<Batch, std::shared_ptr<Batch>>(m, "Batch")
         .def(py::init<>())
         .def_readwrite("unique_node_indices", &Batch::unique_node_indices_)

@@ -98,6 +98,156 @@ std::tuple<torch::Tensor, std::vector<torch::Tensor>> map_tensors(std::vector<to
     return {std::get<0>(tup), mapped};
 }
 
+// ---------------------------------------------------------------------------------------------------------------------------
+// selected-negative operators
+// ---------------------------------------------------------------------------------------------------------------------------
+namespace {
+
+torch::Tensor& selected_status_word(const torch::Device& device) {
+    thread_local std::map<int, torch::Tensor> words;
+    auto& w = words[device.index()];
+    if (!w.defined()) w = torch::zeros({1}, torch::dtype(torch::kInt32).device(device));
+    return w;
+}
+
+struct SelectedShapes {
+    int64_t chunks, rows, negs, selected;
+    int D;
+};
+
+SelectedShapes selected_shapes(const torch::Tensor& chunked, const torch::Tensor& negatives, const torch::Tensor& selected, int64_t score_kind) {
+    require_cuda(chunked, "chunked_adjusted_embeddings");
+    require_cuda(negatives, "negative_embeddings");
+    require_cuda(selected, "selected_neg_indices");
+    TORCH_CHECK(chunked.dim() == 3, "chunked_adjusted_embeddings must be rank 3");
+    TORCH_CHECK(negatives.dim() == 3, "negative_embeddings must be rank 3");
+    TORCH_CHECK(selected.dim() == 2, "selected_neg_indices must be rank 2");
+    TORCH_CHECK(chunked.size(0) == negatives.size(0), "chunk and negative chunk counts must match");
+    TORCH_CHECK(chunked.size(0) == selected.size(0), "chunk and selected index chunk counts must match");
+    TORCH_CHECK(chunked.size(2) == negatives.size(2), "embedding dimensions must match");
+    TORCH_CHECK(selected.scalar_type() == torch::kInt64, "selected_neg_indices must be int64");
+    TORCH_CHECK(chunked.scalar_type() == torch::kFloat32 && negatives.scalar_type() == torch::kFloat32, "embeddings must be float32");
+    TORCH_CHECK(score_kind == GE2_SELECTED_DOT || score_kind == GE2_SELECTED_L2, "score_kind must be DOT or L2");
+    SelectedShapes s;
+    s.chunks = chunked.size(0);
+    s.rows = chunked.size(1);
+    s.negs = negatives.size(1);
+    s.D = (int)chunked.size(2);
+    s.selected = selected.size(1) / std::max<int64_t>(s.rows, 1);
+    TORCH_CHECK(selected.size(1) == s.rows * s.selected, "selected_neg_indices width must be num_per_chunk * selected_negatives_num");
+    return s;
+}
+
+class SelectedNegScores : public torch::autograd::Function<SelectedNegScores> {
+   public:
+    static torch::autograd::variable_list forward(torch::autograd::AutogradContext* ctx, torch::Tensor chunked, torch::Tensor negatives,
+                                                  torch::Tensor selected, int64_t score_kind) {
+        auto out = selected_neg_scores_cuda_forward(chunked, negatives, selected, score_kind);
+        ctx->save_for_backward({chunked, negatives, selected});
+        ctx->saved_data["score_kind"] = score_kind;
+        return {out};
+    }
+    static torch::autograd::variable_list backward(torch::autograd::AutogradContext* ctx, torch::autograd::variable_list grad_outs) {
+        auto saved = ctx->get_saved_variables();
+        auto grads = selected_neg_scores_cuda_backward(grad_outs[0], saved[0], saved[1], saved[2], ctx->saved_data["score_kind"].toInt());
+        return {std::get<0>(grads), std::get<1>(grads), torch::Tensor(), torch::Tensor()};
+    }
+};
+
+// the tournament's scores as a function of the scorer's tensors: forward is the selection kernel's output, backward the chosen
+// pairs' dot-product gradient (what autograd derives for the reference's bmm -> gather)
+class TournamentScores : public torch::autograd::Function<TournamentScores> {
+   public:
+    static torch::autograd::variable_list forward(torch::autograd::AutogradContext* ctx, torch::Tensor score_chunked, torch::Tensor score_negatives,
+                                                  torch::Tensor selector_chunked, torch::Tensor selector_negatives, int64_t selected_num) {
+        const int64_t chunks = score_chunked.size(0), rows = score_chunked.size(1), negs = score_negatives.size(1);
+        auto scores = torch::empty({chunks * rows, selected_num}, score_chunked.options());
+        auto columns = torch::empty({chunks, rows * selected_num}, score_chunked.options().dtype(torch::kInt64));
+        check(ge2_tournament_select(selector_chunked.data_ptr<float>(), selector_negatives.data_ptr<float>(), score_chunked.data_ptr<float>(),
+                                    score_negatives.data_ptr<float>(), chunks, rows, negs, selected_num, (int)score_chunked.size(2),
+                                    scores.data_ptr<float>(), columns.data_ptr<int64_t>(), current_stream(score_chunked)),
+              "ge2_tournament_select");
+        ctx->save_for_backward({score_chunked, score_negatives, columns});
+        ctx->mark_non_differentiable({columns});
+        return {scores, columns};
+    }
+    static torch::autograd::variable_list backward(torch::autograd::AutogradContext* ctx, torch::autograd::variable_list grad_outs) {
+        auto saved = ctx->get_saved_variables();
+        auto grads = selected_neg_scores_cuda_backward(grad_outs[0], saved[0], saved[1], saved[2], GE2_SELECTED_DOT);
+        return {std::get<0>(grads), std::get<1>(grads), torch::Tensor(), torch::Tensor(), torch::Tensor()};
+    }
+};
+
+}  // namespace
+
+torch::Tensor selected_neg_scores_cuda_forward(torch::Tensor chunked_adjusted_embeddings, torch::Tensor negative_embeddings,
+                                               torch::Tensor selected_neg_indices, int64_t score_kind) {
+    const SelectedShapes s = selected_shapes(chunked_adjusted_embeddings, negative_embeddings, selected_neg_indices, score_kind);
+    c10::cuda::CUDAGuard guard(chunked_adjusted_embeddings.device());
+    auto chunked = chunked_adjusted_embeddings.contiguous(), negatives = negative_embeddings.contiguous(), selected = selected_neg_indices.contiguous();
+    auto out = torch::empty({s.chunks * s.rows, s.selected}, chunked.options());
+    check(ge2_selected_neg_scores((int)score_kind, chunked.data_ptr<float>(), negatives.data_ptr<float>(), selected.data_ptr<int64_t>(), s.chunks,
+                                  s.rows, s.negs, s.selected, s.D, out.data_ptr<float>(), selected_status_word(chunked.device()).data_ptr<int32_t>(),
+                                  current_stream(chunked)),
+          "ge2_selected_neg_scores");
+    return out;
+}
+
+std::tuple<torch::Tensor, torch::Tensor> selected_neg_scores_cuda_backward(torch::Tensor grad_out, torch::Tensor chunked_adjusted_embeddings,
+                                                                           torch::Tensor negative_embeddings, torch::Tensor selected_neg_indices,
+                                                                           int64_t score_kind) {
+    const SelectedShapes s = selected_shapes(chunked_adjusted_embeddings, negative_embeddings, selected_neg_indices, score_kind);
+    require_cuda(grad_out, "grad_out");
+    TORCH_CHECK(grad_out.dim() == 2, "grad_out must be rank 2");
+    TORCH_CHECK(grad_out.size(0) == s.chunks * s.rows, "grad_out leading dimension must equal chunk_num * num_per_chunk");
+    TORCH_CHECK(grad_out.size(1) == s.selected, "selected_neg_indices width must be num_per_chunk * selected_negatives_num");
+    c10::cuda::CUDAGuard guard(chunked_adjusted_embeddings.device());
+    auto grad = grad_out.contiguous().to(torch::kFloat32);
+    auto chunked = chunked_adjusted_embeddings.contiguous(), negatives = negative_embeddings.contiguous(), selected = selected_neg_indices.contiguous();
+    auto grad_chunked = torch::empty_like(chunked), grad_negatives = torch::empty_like(negatives);  // the call zeroes grad_negatives
+    check(ge2_selected_neg_scores_backward((int)score_kind, grad.data_ptr<float>(), chunked.data_ptr<float>(), negatives.data_ptr<float>(),
+                                           selected.data_ptr<int64_t>(), s.chunks, s.rows, s.negs, s.selected, s.D, grad_chunked.data_ptr<float>(),
+                                           grad_negatives.data_ptr<float>(), selected_status_word(chunked.device()).data_ptr<int32_t>(),
+                                           current_stream(chunked)),
+          "ge2_selected_neg_scores_backward");
+    return {grad_chunked, grad_negatives};
+}
+
+torch::Tensor selected_neg_scores(torch::Tensor chunked_adjusted_embeddings, torch::Tensor negative_embeddings, torch::Tensor selected_neg_indices,
+                                  SelectedNegScoreKind score_kind) {
+    return SelectedNegScores::apply(chunked_adjusted_embeddings, negative_embeddings, selected_neg_indices, static_cast<int64_t>(score_kind))[0];
+}
+
+std::tuple<torch::Tensor, torch::Tensor> distmult_tiled_tournament_selected_scores(torch::Tensor selector_chunked_embeddings,
+                                                                                    torch::Tensor selector_negative_embeddings,
+                                                                                    torch::Tensor score_chunked_embeddings,
+                                                                                    torch::Tensor score_negative_embeddings,
+                                                                                    int64_t selected_negatives_num, int64_t /*groups_per_tile*/) {
+    for (const auto* t : {&selector_chunked_embeddings, &selector_negative_embeddings, &score_chunked_embeddings, &score_negative_embeddings}) {
+        require_cuda(*t, "tournament embeddings");
+        TORCH_CHECK(t->dim() == 3, "tournament embeddings must be rank 3");
+        TORCH_CHECK(t->scalar_type() == torch::kFloat32, "embeddings must be float32");
+    }
+    TORCH_CHECK(selector_chunked_embeddings.sizes() == score_chunked_embeddings.sizes(), "selector and score chunked embeddings must match");
+    TORCH_CHECK(selector_negative_embeddings.sizes() == score_negative_embeddings.sizes(), "selector and score negative embeddings must match");
+    TORCH_CHECK(selector_chunked_embeddings.size(0) == selector_negative_embeddings.size(0), "chunk counts must match");
+    TORCH_CHECK(selector_chunked_embeddings.size(2) == selector_negative_embeddings.size(2), "embedding dimensions must match");
+    TORCH_CHECK(selected_negatives_num > 0, "selected_negatives_num must be positive");
+    TORCH_CHECK(score_negative_embeddings.size(1) % selected_negatives_num == 0, "negatives_num must be divisible by selected_negatives_num");
+    c10::cuda::CUDAGuard guard(score_chunked_embeddings.device());
+    auto out = TournamentScores::apply(score_chunked_embeddings.contiguous(), score_negative_embeddings.contiguous(),
+                                       selector_chunked_embeddings.detach().contiguous(), selector_negative_embeddings.detach().contiguous(),
+                                       selected_negatives_num);
+    return {out[0], out[1]};
+}
+
+int32_t selected_neg_status(torch::Device device) {
+    auto& w = selected_status_word(device);
+    const int32_t v = w.cpu().item<int32_t>();
+    w.zero_();
+    return v;
+}
+
 void Batch::accumulateGradients(float learning_rate) {
     if (!node_gradients_.defined()) return;
     require_cuda(node_gradients_, "node_gradients_");

@@ -12,6 +12,8 @@
 //     with device_idx)                  include/storage/storage.h:113-187
 //   Model::broadcast / all_reduce       include/nn/model.h:59, src/nn/model.cpp:174-204,454-478
 //   DataLoader::getBatch / updateEmbeddings   src/data/dataloader.cpp:1069-1291,1354-1395
+//   selected_neg_scores (autograd), selected_neg_scores_cuda_forward / _backward, distmult_tiled_tournament_selected_scores
+//                                       include/nn/decoders/edge/distmult_selected_neg_cuda.h:5-29
 #pragma once
 #include <torch/torch.h>
 
@@ -35,6 +37,28 @@ std::tuple<torch::Tensor, torch::Tensor> map_tensors_unique_inverse_cuda(torch::
 
 std::tuple<torch::Tensor, std::vector<torch::Tensor>> map_tensors(std::vector<torch::Tensor> unmapped_tensors, bool sorted = true,
                                                                   int64_t value_domain_size = -1);
+
+// The reference's selected-negative operators (include/nn/decoders/edge/distmult_selected_neg_cuda.h:5-29): same names,
+// arguments and shapes.  fp32 CUDA tensors, D <= 128.  A selected column outside its chunk scores 0, gets no gradient and is
+// recorded in a per-device status word that selected_neg_status() returns and clears (the reference reads out of bounds).
+enum class SelectedNegScoreKind : int64_t { NONE = 0, DOT = 1, L2 = 2 };
+
+torch::Tensor selected_neg_scores_cuda_forward(torch::Tensor chunked_adjusted_embeddings, torch::Tensor negative_embeddings,
+                                               torch::Tensor selected_neg_indices, int64_t score_kind);
+std::tuple<torch::Tensor, torch::Tensor> selected_neg_scores_cuda_backward(torch::Tensor grad_out, torch::Tensor chunked_adjusted_embeddings,
+                                                                           torch::Tensor negative_embeddings, torch::Tensor selected_neg_indices,
+                                                                           int64_t score_kind);
+// differentiable in the first two arguments
+torch::Tensor selected_neg_scores(torch::Tensor chunked_adjusted_embeddings, torch::Tensor negative_embeddings, torch::Tensor selected_neg_indices,
+                                  SelectedNegScoreKind score_kind);
+// (scores [chunks * rows, selected], columns [chunks, rows * selected]); the scores are differentiable in the score_* tensors,
+// the selector's only choose.  groups_per_tile is accepted and ignored: no score tile is stored.
+std::tuple<torch::Tensor, torch::Tensor> distmult_tiled_tournament_selected_scores(torch::Tensor selector_chunked_embeddings,
+                                                                                    torch::Tensor selector_negative_embeddings,
+                                                                                    torch::Tensor score_chunked_embeddings,
+                                                                                    torch::Tensor score_negative_embeddings,
+                                                                                    int64_t selected_negatives_num, int64_t groups_per_tile);
+int32_t selected_neg_status(torch::Device device);
 
 class Batch {
    public:

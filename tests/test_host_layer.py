@@ -37,6 +37,10 @@ def test_interface_names(host):
     for member in ("train_batch", "all_reduce", "broadcast", "step", "clear_grad"):
         assert hasattr(host.Model, member)
     assert hasattr(host.DataLoader, "getBatch") and hasattr(host.DataLoader, "updateEmbeddings")
+    for name in ("selected_neg_scores", "selected_neg_scores_cuda_forward", "selected_neg_scores_cuda_backward",
+                 "distmult_tiled_tournament_selected_scores", "SelectedNegScoreKind"):
+        assert hasattr(host, name)
+    assert int(host.SelectedNegScoreKind.DOT) == 1 and int(host.SelectedNegScoreKind.L2) == 2  # distmult_selected_neg_cuda.h:5
     b = host.Batch()
     for member in ("edges", "unique_node_indices", "node_embeddings", "node_embeddings_state", "node_gradients", "node_state_update",
                    "src_neg_indices_mapping", "dst_neg_indices_mapping", "src_neg_filter", "dst_neg_filter", "accumulateGradients"):
@@ -51,6 +55,74 @@ def test_cpu_tensors_are_rejected(host):
         host.map_tensors([torch.zeros((2, 2), dtype=torch.int64)], True, 10)
     with pytest.raises(host.GegeRuntimeException, match="CUDA device"):
         host.Model(host.DecoderType.DISTMULT, 3, 8, True, 0.1, 0.1, torch.device("cpu"))
+
+
+def test_selected_negative_functions_reject_cpu_tensors(host):
+    q, n, sel = torch.zeros(1, 2, 4), torch.zeros(1, 3, 4), torch.zeros(1, 2, dtype=torch.int64)
+    with pytest.raises(host.GegeRuntimeException, match="no CPU path"):
+        host.selected_neg_scores(q, n, sel, host.SelectedNegScoreKind.DOT)
+    with pytest.raises(host.GegeRuntimeException, match="no CPU path"):
+        host.distmult_tiled_tournament_selected_scores(q, n, q, n, 3, 64)
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("kind", ["DOT", "L2"])
+def test_selected_neg_scores_autograd_through_the_host_layer(host, cuda_device, kind):
+    """selected_neg_scores as the reference's decoder calls it (decoder_methods.cpp:996-998): forward and both gradients against
+    the same gather written with torch operators, whose autograd is the comparator."""
+    g = torch.Generator(device=cuda_device).manual_seed(5)
+    C, R, N, D, K = 3, 40, 60, 100, 6
+    q = torch.randn((C, R, D), device=cuda_device, generator=g, requires_grad=True)
+    n = torch.randn((C, N, D), device=cuda_device, generator=g, requires_grad=True)
+    sel = torch.randint(0, N, (C, R * K), device=cuda_device, generator=g)
+    w = torch.randn((C * R, K), device=cuda_device, generator=g)
+    out = host.selected_neg_scores(q, n, sel, getattr(host.SelectedNegScoreKind, kind))
+    (out * w).sum().backward()
+    got = (out.detach(), q.grad.clone(), n.grad.clone())
+    q.grad, n.grad = None, None
+    picked = n[torch.arange(C, device=cuda_device)[:, None, None], sel.view(C, R, K)]
+    if kind == "DOT":
+        ref = (q[:, :, None, :] * picked).sum(-1)
+    else:
+        ref = torch.sqrt(torch.clamp(((q[:, :, None, :] - picked) ** 2).sum(-1), min=1e-8))
+    ref = ref.reshape(C * R, K)
+    (ref * w).sum().backward()
+    for a, b in zip(got, (ref.detach(), q.grad, n.grad)):
+        assert (a - b).abs().max().item() <= 1e-4 * max(1.0, b.abs().max().item())
+    assert host.selected_neg_status(cuda_device) == 0
+    bad = sel.clone()
+    bad[1, 3] = N
+    host.selected_neg_scores_cuda_forward(q.detach(), n.detach(), bad, 1)
+    assert host.selected_neg_status(cuda_device) == 8 and host.selected_neg_status(cuda_device) == 0  # reported once, then cleared
+
+
+@pytest.mark.gpu
+def test_tournament_scores_autograd_through_the_host_layer(host, cuda_device):
+    """distmult_tiled_tournament_selected_scores with a selector separate from the scorer: columns chosen by the selector,
+    scores and gradients by the scorer (the reference's bmm -> max -> gather, distmult_selected_neg_cuda.cpp:92-106)."""
+    g = torch.Generator(device=cuda_device).manual_seed(6)
+    C, R, N, D, K = 2, 70, 120, 64, 12
+    sq = torch.randn((C, R, D), device=cuda_device, generator=g)
+    sn = torch.randn((C, N, D), device=cuda_device, generator=g)
+    q = torch.randn((C, R, D), device=cuda_device, generator=g, requires_grad=True)
+    n = torch.randn((C, N, D), device=cuda_device, generator=g, requires_grad=True)
+    w = torch.randn((C * R, K), device=cuda_device, generator=g)
+    scores, cols = host.distmult_tiled_tournament_selected_scores(sq, sn, q, n, K, 64)
+    (scores * w).sum().backward()
+    got = (scores.detach(), q.grad.clone(), n.grad.clone())
+    q.grad, n.grad = None, None
+    T = N // K
+    sel_scores = sq.bmm(sn.transpose(1, 2)).view(C, R, K, T)
+    local = sel_scores.argmax(3)
+    ref_cols = local + torch.arange(K, device=cuda_device) * T
+    agree = cols.view(C, R, K) == ref_cols
+    assert agree.float().mean().item() >= 0.99  # another winner only on a float tie
+    ref = q.bmm(n.transpose(1, 2)).gather(2, cols.view(C, R, K)).reshape(C * R, K)  # scored on the columns the kernel kept
+    (ref * w).sum().backward()
+    for a, b in zip(got, (ref.detach(), q.grad, n.grad)):
+        assert (a - b).abs().max().item() <= 1e-4 * max(1.0, b.abs().max().item())
+    with pytest.raises(Exception, match="divisible"):
+        host.distmult_tiled_tournament_selected_scores(sq, sn, q, n, 7, 64)
 
 
 @pytest.mark.gpu
