@@ -40,6 +40,26 @@ def test_host_only_entry_points(ge2):
     assert lib.ge2_lp_workspace_bytes(ctypes.byref(d), ctypes.byref(out)) == 1
 
 
+def test_selected_negative_entry_points_validate_before_any_cuda_call(ge2):
+    """Shapes the reference rejects with TORCH_CHECK (distmult_selected_neg_cuda.cpp:63-76, .cu:215-217) come back as
+    GE2_ERR_INVALID_ARGUMENT; D above the kernels' 128 as GE2_ERR_UNSUPPORTED; empty inputs are accepted without a launch."""
+    lib = ge2.load_library()
+    p = 4096  # never dereferenced: every call below returns before it touches the device
+    tour = lambda chunks, rows, negs, sel, D: lib.ge2_tournament_select(p, p, None, None, chunks, rows, negs, sel, D, p, p, None)  # noqa: E731
+    assert tour(2, 5, 10, 3, 8) == 1       # negatives not divisible into groups
+    assert tour(2, 5, 10, 0, 8) == 1
+    assert tour(2, 5, 10, 5, 129) == 4     # D > 128
+    assert tour(70000, 5, 10, 5, 8) == 4   # more chunks than a grid dimension holds
+    assert tour(0, 5, 10, 5, 8) == 0 and tour(2, 0, 10, 5, 8) == 0
+    fwd = lambda kind, chunks, rows, negs, sel, D: lib.ge2_selected_neg_scores(kind, p, p, p, chunks, rows, negs, sel, D, p, None, None)  # noqa: E731
+    assert fwd(0, 1, 1, 1, 1, 8) == 1      # SelectedNegScoreKind::NONE
+    assert fwd(3, 1, 1, 1, 1, 8) == 1
+    assert fwd(1, 1, 1, 0, 1, 8) == 1      # no negatives to index
+    assert fwd(2, 1, 1, 1, 1, 200) == 4
+    assert fwd(1, 3, 0, 5, 2, 8) == 0 and fwd(2, 3, 4, 5, 0, 8) == 0
+    assert lib.ge2_selected_neg_scores_backward(7, p, p, p, p, 1, 1, 1, 1, 8, p, p, None, None) == 1
+
+
 def test_desc_struct_matches_header_size(ge2):
     """ctypes mirror and C struct agree in size (a C probe compiled against the header prints sizeof)."""
     import subprocess
